@@ -1,0 +1,139 @@
+/*
+ * jla_b200.h - C ABI of the B200 (sm_100a) kernels for the chunkwise gated delta rule family
+ * (simple GLA / Mamba-2 SSD core, DeltaNet, Gated DeltaNet, KDA), forward and backward.
+ *
+ * The reference (jla-org/jax-linear-attention) is pure Python: its kernels are Pallas programs that JAX
+ * lowers to XLA custom calls, so it has no foreign-function layer of its own. These entry points are what an
+ * XLA typed-FFI handler (one per entry point) or a ctypes host binds instead of:
+ *
+ *   src/jla/ops/mosaic_gpu/scalar_gate.py:309-348   _forward      (kkt_fwd + fused_fwd_wy / fused_fwd)
+ *   src/jla/ops/mosaic_gpu/scalar_gate.py:357-452   _backward     (state_fwd, state_bwd, chunk_grads / dqkwg)
+ *   src/jla/ops/mosaic_gpu/vector_gate_ops.py:98-164 KDA forward / backward kernel chains
+ *   src/jla/ops/reference.py:105-205                _recurrence   (fp32 token scan, cu_seqlens semantics)
+ *
+ * Rules of the ABI:
+ *   - plain C types only; all pointers are DEVICE pointers owned by the caller (except the args struct itself,
+ *     which is host memory and is read before the call returns);
+ *   - every call only enqueues work on `stream` and returns; nothing here allocates, frees or synchronises;
+ *   - scratch and residual memory is provided by the caller, sized by the *_bytes() queries (XLA custom calls
+ *     must not allocate: declare them as extra result buffers);
+ *   - return value 0 = enqueued, negative = rejected (jla_status); jla_last_error() gives the reason text.
+ *
+ * Tensor layouts (row-major, innermost last), following src/jla/ops/reference.py:8-35:
+ *   q, k    [B, T, Hk, K]   dtype            v, o, do, dv [B, T, H, V]   dtype      (H % Hk == 0)
+ *   g       [B, T, H] f32 (scalar gates) or [B, T, H, K] f32 (KDA), natural-log decay, <= 0
+ *   beta    [B, T, H] f32
+ *   h0/final/dht/dh0 [R, H, K, V] f32 with R = B, or R = num_seqs when cu_seqlens is given (then B must be 1)
+ *   segment_ids [B, T] int32 (state restarts where the id changes along T)
+ *   cu_seqlens  [num_seqs + 1] int32, cu[0] == 0, cu[num_seqs] == T
+ *   dq, dk  [B, T, Hk, K]   dtype (summed over each group's heads in fp32, rounded once)
+ *   dg      like g, f32;   dbeta [B, T, H] f32
+ */
+#ifndef JLA_B200_H_
+#define JLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* jla_stream_t; /* a cudaStream_t */
+
+enum jla_kind {              /* src/jla/ops/__init__.py:47-60 (KINDS) */
+  JLA_KIND_SIMPLE_GLA = 0,   /* S = exp(g) S + k^T v                      (Mamba-2 SSD core)          */
+  JLA_KIND_DELTANET = 1,     /* S = S + beta k^T (v - k S)                                            */
+  JLA_KIND_GATED_DELTANET = 2, /* S' = exp(g) S; S = S' + beta k^T (v - k S')                         */
+  JLA_KIND_KDA = 3           /* S' = diag(exp(g)) S; S = S' + beta k^T (v - k S')   (g per key channel) */
+};
+
+enum jla_dtype { JLA_DTYPE_BF16 = 0, JLA_DTYPE_F16 = 1, JLA_DTYPE_F32 = 2 };
+
+enum jla_path {
+  JLA_PATH_AUTO = 0,      /* f32 tensors: RECURRENT; bf16/f16: CHUNKED                                          */
+  JLA_PATH_RECURRENT = 1, /* fp32 token scan in the order of reference.py:140-157 (any K, V <= 256)            */
+  JLA_PATH_CHUNKED = 2    /* chunk-64 tensor-core kernels (bf16/f16, K and V in {64, 128})                      */
+};
+
+enum jla_flags {
+  JLA_FLAG_QK_L2NORM = 1,     /* normalise q and k over the head dim in fp32, eps 1e-6 (reference.py:65-69)   */
+  JLA_FLAG_SAVE_RESIDUALS = 2 /* forward: fill `residuals` for a later jla_linear_attention_bwd             */
+};
+
+enum jla_status {
+  JLA_OK = 0,
+  JLA_ERR_BAD_ARGUMENT = -1,  /* null pointer, inconsistent sizes, unknown enum                                 */
+  JLA_ERR_UNSUPPORTED = -2,   /* valid call that no kernel here covers (reason in jla_last_error)              */
+  JLA_ERR_WORKSPACE = -3,     /* scratch or residual buffer smaller than the *_bytes() query                    */
+  JLA_ERR_CUDA = -4           /* a CUDA runtime call failed at enqueue time                                    */
+};
+
+typedef struct jla_problem {
+  int32_t kind;       /* enum jla_kind */
+  int32_t dtype;      /* enum jla_dtype of q, k, v, o and their gradients */
+  int32_t path;       /* enum jla_path */
+  int32_t flags;      /* enum jla_flags, or-ed */
+  int32_t B, T, H, Hk, K, V;
+  int32_t num_seqs;   /* sequences in cu_seqlens, 0 without */
+  float scale;        /* applied to q (reference.py:130-132); the caller resolves None to K^-0.5 */
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* g;            /* NULL for DELTANET */
+  const float* beta;         /* NULL for SIMPLE_GLA */
+  const float* h0;           /* optional initial state */
+  const int32_t* segment_ids; /* optional */
+  const int32_t* cu_seqlens;  /* optional; excludes segment_ids */
+} jla_problem;
+
+typedef struct jla_fwd_io {
+  void* o;              /* [B, T, H, V] dtype */
+  float* final_state;   /* optional [R, H, K, V] */
+  void* residuals;      /* jla_residual_bytes() bytes when JLA_FLAG_SAVE_RESIDUALS, else may be NULL */
+  size_t residual_bytes;
+  void* scratch;        /* jla_fwd_scratch_bytes() bytes */
+  size_t scratch_bytes;
+} jla_fwd_io;
+
+typedef struct jla_bwd_io {
+  const void* d_o;          /* [B, T, H, V] dtype: cotangent of o */
+  const float* d_final;     /* optional [R, H, K, V]: cotangent of the final state */
+  void* dq;                 /* [B, T, Hk, K] dtype */
+  void* dk;                 /* [B, T, Hk, K] dtype */
+  void* dv;                 /* [B, T, H, V] dtype */
+  float* dg;                /* like g; NULL for DELTANET */
+  float* dbeta;             /* [B, T, H]; NULL for SIMPLE_GLA */
+  float* dh0;               /* optional [R, H, K, V] */
+  const void* residuals;    /* what the forward wrote (same problem, JLA_FLAG_SAVE_RESIDUALS) */
+  size_t residual_bytes;
+  void* scratch;            /* jla_bwd_scratch_bytes() bytes */
+  size_t scratch_bytes;
+} jla_bwd_io;
+
+/* Library/ABI version: major * 1000 + minor. */
+int jla_abi_version(void);
+
+/* Text of the last rejected call on this host thread ("" if none). */
+const char* jla_last_error(void);
+
+/* NULL if the library has a kernel for `p` (pointers in `p` are ignored), else the reason as text.
+ * Mirrors unsupported_reason() of src/jla/ops/mosaic_gpu/scalar_gate.py:476-515 and
+ * src/jla/ops/mosaic_gpu/vector_gate_ops.py:262-304. */
+const char* jla_unsupported_reason(const jla_problem* p);
+
+/* Buffer sizes in bytes for problem `p` (0 is a valid answer; pointers in `p` are ignored). */
+size_t jla_residual_bytes(const jla_problem* p);
+size_t jla_fwd_scratch_bytes(const jla_problem* p);
+size_t jla_bwd_scratch_bytes(const jla_problem* p);
+
+/* Forward: o and (optionally) the final state; replaces scalar_gate._forward / the KDA forward chain. */
+int jla_linear_attention_fwd(const jla_problem* p, const jla_fwd_io* io, jla_stream_t stream);
+
+/* Backward for cotangents (d_o, d_final); replaces scalar_gate._backward / the KDA backward chain. */
+int jla_linear_attention_bwd(const jla_problem* p, const jla_bwd_io* io, jla_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JLA_B200_H_ */

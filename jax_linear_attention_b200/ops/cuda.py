@@ -1,0 +1,244 @@
+"""The ``"cuda"`` implementation of the linear-attention kinds: host side of ``libjla_b200.so``.
+
+One function per kind with the signatures of the reference's kernel entry points
+(``src/jla/ops/mosaic_gpu/gated_delta_rule.py:24-37``, ``mosaic_gpu/kda.py:23-37``,
+``mosaic_gpu/scalar_gate.py:591-603``) and the semantics of ``src/jla/ops/reference.py``:
+``(o, final_state | None)``, ``o`` in ``q``'s dtype, the state float32. Differences from the
+reference's kernels, all widening: ``cu_seqlens`` is supported (per-sequence initial and final
+states, ``reference.py:170-203``), any ``T`` runs without padding copies, and ``precision="highest"``
+selects the fp32 token-scan kernels for any dtype.
+
+Gradients flow through a ``torch.autograd.Function`` (the role ``jax.custom_vjp`` has in
+``mosaic_gpu/scalar_gate.py:455-469``): the forward saves the residuals the C ABI asks for and the
+backward is one ``jla_linear_attention_bwd`` call. There is no fallback path.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any
+
+import torch
+
+from .. import _lib
+
+CHUNK = 64
+SUPPORTED_HEAD_DIMS = (64, 128)
+_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+_COMMON_OPTIONS = frozenset({"scale", "initial_state", "output_final_state", "cu_seqlens", "segment_ids",
+                             "chunk_size", "precision"})
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _shape(x) -> tuple:
+    return tuple(x.shape)
+
+
+def _path(precision) -> str:
+    if precision in (None, "default", "auto"):
+        return "auto"
+    if precision in ("highest", "recurrent", "float32"):
+        return "recurrent"
+    if precision == "chunked":
+        return "chunked"
+    raise ValueError(f"unknown precision {precision!r}; expected None, 'highest' or 'chunked'")
+
+
+def _problem(kind: str, dtype, B, T, H, Hk, K, V, num_seqs, scale, flags, precision) -> _lib.Problem:
+    p = _lib.Problem()
+    p.kind, p.dtype, p.path, p.flags = _lib.KIND[kind], _DTYPES[dtype], _lib.PATH[_path(precision)], flags
+    p.B, p.T, p.H, p.Hk, p.K, p.V, p.num_seqs, p.scale = B, T, H, Hk, K, V, num_seqs, float(scale)
+    return p
+
+
+def unsupported_reason(kind: str, q, k, v, gates: tuple, options: dict) -> str | None:
+    """Why the CUDA kernels cannot run this call (``None`` if they can).
+
+    Works on anything with ``.shape`` and ``.dtype`` (tensors or shape structs), so it can be evaluated
+    on per-shard shapes; mirrors ``unsupported_reason`` of ``mosaic_gpu/scalar_gate.py:476-515``.
+    """
+    delta = kind != "simple_gla"
+    allowed = _COMMON_OPTIONS | ({"use_qk_l2norm"} if delta else set()) | ({"sub_chunk"} if kind == "kda" else set())
+    extra = sorted(set(options) - allowed)
+    if extra:
+        return f"unsupported options {extra}"
+    if options.get("chunk_size", CHUNK) not in (None, CHUNK):
+        return f"chunk_size must be {CHUNK}"
+    if len(_shape(q)) != 4 or _shape(k) != _shape(q) or len(_shape(v)) != 4 or _shape(v)[:2] != _shape(q)[:2]:
+        return f"expected q, k [B, T, Hk, K] and v [B, T, H, V]; got {_shape(q)}, {_shape(k)}, {_shape(v)}"
+    batch, seq_len, kv_heads, key_dim = _shape(q)
+    heads, value_dim = _shape(v)[2:]
+    if kv_heads == 0 or heads % kv_heads:
+        return f"value heads {heads} must be a multiple of key heads {kv_heads}"
+    dtypes = {q.dtype, k.dtype, v.dtype}
+    if len(dtypes) != 1 or q.dtype not in _DTYPES:
+        return f"q, k, v must share a dtype in {tuple(_DTYPES)}; got {q.dtype}, {k.dtype}, {v.dtype}"
+    gate_shape = (batch, seq_len, heads)
+    names = {"simple_gla": ("g",), "deltanet": ("beta",), "gated_deltanet": ("g", "beta"), "kda": ("g", "beta")}[kind]
+    for name, gate in zip(names, gates):
+        want = (*gate_shape, key_dim) if (kind == "kda" and name == "g") else gate_shape
+        if _shape(gate) != want:
+            return f"{name} must be {want}; got {_shape(gate)}"
+    cu, seg = options.get("cu_seqlens"), options.get("segment_ids")
+    if cu is not None and seg is not None:
+        return "pass cu_seqlens or segment_ids, not both"
+    if cu is not None and batch != 1:
+        return "cu_seqlens packs sequences along T and requires batch size 1"
+    rows = batch if cu is None else _shape(cu)[0] - 1
+    state = options.get("initial_state")
+    if state is not None and _shape(state) != (rows, heads, key_dim, value_dim):
+        return (f"initial_state must be [{'N' if cu is not None else 'B'}, H, K, V] = "
+                f"{(rows, heads, key_dim, value_dim)}; got {_shape(state)}")
+    if seg is not None and (_shape(seg) != (batch, seq_len) or seg.dtype in (torch.float16, torch.bfloat16,
+                                                                                torch.float32, torch.float64)):
+        return f"segment_ids must be integer [B, T] = {(batch, seq_len)}; got {seg.dtype}{_shape(seg)}"
+    try:
+        precision = _path(options.get("precision"))
+    except ValueError as err:
+        return str(err)
+    p = _problem(kind, q.dtype, batch, seq_len, heads, kv_heads, key_dim, value_dim,
+                 0 if cu is None else max(rows, 0), 1.0, 0, precision)
+    return _lib.unsupported_reason(p)
+
+
+def _supports(kind: str):
+    def supports(q, k, v, *gates, **options) -> bool:
+        return unsupported_reason(kind, q, k, v, gates, options) is None
+    return supports
+
+
+class _LinearAttention(torch.autograd.Function):
+    """``(o, final) = op(q, k, v, g, beta, h0)``; the config rides in ``cfg``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, h0, cfg: dict):
+        lib = _lib.load()
+        B, T, Hk, K = q.shape
+        H, V = v.shape[2:]
+        needs_grad = any(x is not None and x.requires_grad for x in (q, k, v, g, beta, h0))
+        flags = (_lib.FLAG_QK_L2NORM if cfg["l2norm"] else 0) | (_lib.FLAG_SAVE_RESIDUALS if needs_grad else 0)
+        cu, seg = cfg["cu_seqlens"], cfg["segment_ids"]
+        rows = B if cu is None else cu.numel() - 1
+        p = _problem(cfg["kind"], q.dtype, B, T, H, Hk, K, V, 0 if cu is None else rows, cfg["scale"], flags,
+                     cfg["precision"])
+        p.q, p.k, p.v, p.g, p.beta, p.h0 = (_ptr(x) for x in (q, k, v, g, beta, h0))
+        p.segment_ids, p.cu_seqlens = _ptr(seg), _ptr(cu)
+        dev = q.device
+        o = torch.empty_like(v)
+        final = torch.empty(rows, H, K, V, dtype=torch.float32, device=dev) if cfg["output_final_state"] else None
+        res_bytes = lib.jla_residual_bytes(C.byref(p)) if needs_grad else 0
+        residuals = torch.empty(res_bytes, dtype=torch.uint8, device=dev) if res_bytes else None
+        scr_bytes = lib.jla_fwd_scratch_bytes(C.byref(p))
+        scratch = torch.empty(scr_bytes, dtype=torch.uint8, device=dev) if scr_bytes else None
+        io = _lib.FwdIO(_ptr(o), _ptr(final), _ptr(residuals), res_bytes, _ptr(scratch), scr_bytes)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        with torch.cuda.device(dev):
+            _lib.check(lib.jla_linear_attention_fwd(C.byref(p), C.byref(io), C.c_void_p(stream)),
+                       f"{cfg['kind']} forward")
+        ctx.cfg, ctx.flags, ctx.rows = cfg, flags, rows
+        ctx.save_for_backward(q, k, v, g, beta, h0, residuals)
+        return o, final
+
+    @staticmethod
+    def backward(ctx, d_o, d_final):
+        lib = _lib.load()
+        q, k, v, g, beta, h0, residuals = ctx.saved_tensors
+        cfg = ctx.cfg
+        B, T, Hk, K = q.shape
+        H, V = v.shape[2:]
+        cu, seg = cfg["cu_seqlens"], cfg["segment_ids"]
+        p = _problem(cfg["kind"], q.dtype, B, T, H, Hk, K, V, 0 if cu is None else ctx.rows, cfg["scale"], ctx.flags,
+                     cfg["precision"])
+        p.q, p.k, p.v, p.g, p.beta, p.h0 = (_ptr(x) for x in (q, k, v, g, beta, h0))
+        p.segment_ids, p.cu_seqlens = _ptr(seg), _ptr(cu)
+        dev = q.device
+        d_o = d_o.contiguous() if d_o is not None else torch.zeros_like(v)
+        d_final = None if d_final is None else d_final.contiguous().float()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dg = None if g is None else torch.empty_like(g)
+        dbeta = None if beta is None else torch.empty_like(beta)
+        dh0 = None if h0 is None else torch.empty_like(h0)
+        scr_bytes = lib.jla_bwd_scratch_bytes(C.byref(p))
+        scratch = torch.empty(scr_bytes, dtype=torch.uint8, device=dev) if scr_bytes else None
+        io = _lib.BwdIO(_ptr(d_o), _ptr(d_final), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dg), _ptr(dbeta), _ptr(dh0),
+                        _ptr(residuals), 0 if residuals is None else residuals.numel(), _ptr(scratch), scr_bytes)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        with torch.cuda.device(dev):
+            _lib.check(lib.jla_linear_attention_bwd(C.byref(p), C.byref(io), C.c_void_p(stream)),
+                       f"{cfg['kind']} backward")
+        return dq, dk, dv, dg, dbeta, dh0, None
+
+
+def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_state, cu_seqlens, segment_ids,
+         use_qk_l2norm=False, chunk_size=CHUNK, precision=None, sub_chunk=None):
+    del sub_chunk  # the kernels choose their own sub-blocking
+    for name, x in (("q", q), ("k", k), ("v", v)):
+        if not isinstance(x, torch.Tensor) or not x.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor: the 'cuda' implementation has no CPU fallback")
+    options: dict[str, Any] = dict(scale=scale, initial_state=initial_state, output_final_state=output_final_state,
+                                   cu_seqlens=cu_seqlens, segment_ids=segment_ids, chunk_size=chunk_size,
+                                   precision=precision)
+    gates = tuple(x for x in (g, beta) if x is not None)
+    why = unsupported_reason(kind, q, k, v, gates, options)
+    if why is not None:
+        raise ValueError(f"the CUDA kernels cannot run this {kind} call: {why}")
+    dev = q.device
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+
+    def f32(x):
+        return None if x is None else x.to(device=dev, dtype=torch.float32).contiguous()
+
+    def i32(x):
+        return None if x is None else torch.as_tensor(x).to(device=dev, dtype=torch.int32).contiguous()
+
+    cfg = dict(kind=kind, scale=float(scale), l2norm=bool(use_qk_l2norm), precision=precision,
+               output_final_state=bool(output_final_state), cu_seqlens=i32(cu_seqlens), segment_ids=i32(segment_ids))
+    o, final = _LinearAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), f32(g), f32(beta),
+                                      f32(initial_state), cfg)
+    return o, (final if output_final_state else None)
+
+
+def simple_gla(q, k, v, g, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+               segment_ids=None, chunk_size=CHUNK, precision=None):
+    """Linear attention with one log-decay per head (Mamba-2 SSD core: ``scale=1``); ``q``/``k`` may have
+    fewer heads than ``v`` (value head ``h`` reads key head ``h // (H / Hk)``)."""
+    return _run("simple_gla", q, k, v, g, None, scale=scale, initial_state=initial_state,
+                output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
+                chunk_size=chunk_size, precision=precision)
+
+
+def delta_rule(q, k, v, beta, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+               segment_ids=None, use_qk_l2norm=False, chunk_size=CHUNK, precision=None):
+    """DeltaNet: the delta-rule write with no decay."""
+    return _run("deltanet", q, k, v, None, beta, scale=scale, initial_state=initial_state,
+                output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
+                use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision)
+
+
+def gated_delta_rule(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=False,
+                     cu_seqlens=None, segment_ids=None, use_qk_l2norm=False, chunk_size=CHUNK, precision=None):
+    """Gated DeltaNet: delta rule with one log-decay per head."""
+    return _run("gated_deltanet", q, k, v, g, beta, scale=scale, initial_state=initial_state,
+                output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
+                use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision)
+
+
+def kda(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+        segment_ids=None, use_qk_l2norm=False, chunk_size=CHUNK, sub_chunk=16, precision=None):
+    """Kimi Delta Attention: delta rule with a log-decay per key channel (``g [B, T, H, K]``)."""
+    return _run("kda", q, k, v, g, beta, scale=scale, initial_state=initial_state,
+                output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
+                use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision, sub_chunk=sub_chunk)
+
+
+FUNCTIONS = {
+    "simple_gla": simple_gla,
+    "deltanet": delta_rule,
+    "gated_deltanet": gated_delta_rule,
+    "kda": kda,
+}
+SUPPORTS = {kind: _supports(kind) for kind in FUNCTIONS}
