@@ -1,0 +1,120 @@
+// Shared definitions of the chunk-64 tensor-core kernels (JLA_PATH_CHUNKED): the chunk table, the layout of
+// the residual and scratch buffers, and the per-token decay / document scalars every kernel derives.
+//
+// Chunk math (per head and chunk, S = state entering the chunk), gate-free formulation as in the reference's
+// kernels (src/jla/ops/mosaic_gpu/gated_delta_rule_kernels.py:351-370, scalar_gate_fused.py:427-504):
+//   A0 = strict_lower(beta_i k_i.k_j) * same      T0 = (I + A0)^-1        Ag = T0 * D * beta_j
+//   D_ij = exp(G_i - G_j) * same (i >= j)         W = V - (cin Gamma) * (K S)        Vn = Ag W
+//   O = scale [(cin Gamma) * (Q S) + ((Q K^T) * D) Vn]      S+ = keep gamma S + ((tail Gamma_r) * K)^T Vn
+// Chunks never straddle rows: every row (batch element or cu_seqlens sequence) is cut into its own chunks, the
+// last one possibly partial (missing tokens behave as zero padding: k = 0, g = 0, beta = 0).
+#pragma once
+
+#include "common.cuh"
+
+namespace jla {
+
+struct ChunkMeta {
+  int tok0;   // first token (flat index over B*T)
+  int len;    // valid tokens, 1..64; 0 = unused slot
+  int row;
+  int flags;  // bit 0: the chunk's first token starts a new document (the entering state is not seen)
+};
+
+// Byte offsets inside the residual buffer (forward -> backward) and the backward scratch.
+struct Plan {
+  int rows, nc;       // rows; chunk slots (upper bound on the number of chunks)
+  bool delta, l2norm, save;
+  size_t meta, row_chunks, gates, runs, t0, qn, kn, h, vn, residual_bytes;  // residual buffer
+  size_t fwd_scratch_bytes;                                                 // same layout without h, vn
+  size_t dh, dvn, dq_acc, dk_acc, bwd_scratch_bytes;                        // backward scratch
+};
+
+inline int elem_size(int dtype) { return dtype == JLA_DTYPE_F32 ? 4 : 2; }
+
+inline Plan make_plan(const jla_problem& p) {
+  Plan pl{};
+  const bool varlen = p.num_seqs > 0;
+  pl.rows = varlen ? p.num_seqs : p.B;
+  const int per_row = (p.T + kChunk - 1) / kChunk;
+  pl.nc = varlen ? per_row + p.num_seqs : p.B * per_row;
+  pl.delta = p.kind != JLA_KIND_SIMPLE_GLA;
+  pl.l2norm = (p.flags & JLA_FLAG_QK_L2NORM) != 0;
+  pl.save = (p.flags & JLA_FLAG_SAVE_RESIDUALS) != 0;
+  const size_t es = elem_size(p.dtype);
+  const size_t tokens = (size_t)p.B * p.T;
+  Carver c(nullptr);
+  auto off = [&](size_t bytes) {
+    c.off = align_up(c.off);
+    const size_t o = c.off;
+    c.off += bytes;
+    return o;
+  };
+  pl.meta = off((size_t)pl.nc * sizeof(ChunkMeta));
+  pl.row_chunks = off((size_t)(pl.rows + 1) * 2 * sizeof(int));
+  pl.gates = off((size_t)pl.nc * p.H * 128 * sizeof(float));  // per (chunk, head): G[64] then beta[64]
+  pl.runs = off((size_t)pl.nc * 64);
+  pl.t0 = off(pl.delta ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
+  pl.qn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
+  pl.kn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
+  pl.fwd_scratch_bytes = align_up(c.off);
+  pl.h = off((size_t)pl.nc * p.H * p.K * p.V * es);
+  pl.vn = off(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
+  pl.residual_bytes = align_up(c.off);
+  Carver b(nullptr);
+  auto boff = [&](size_t bytes) {
+    b.off = align_up(b.off);
+    const size_t o = b.off;
+    b.off += bytes;
+    return o;
+  };
+  const bool direct = p.H == p.Hk && !pl.l2norm;  // dq, dk written straight in the tensor dtype
+  pl.dh = boff((size_t)pl.nc * p.H * p.K * p.V * es);
+  pl.dvn = boff(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
+  pl.dq_acc = boff(direct ? 0 : tokens * p.H * p.K * sizeof(float));
+  pl.dk_acc = boff(direct ? 0 : tokens * p.H * p.K * sizeof(float));
+  pl.bwd_scratch_bytes = align_up(b.off);
+  return pl;
+}
+
+// Per-token scalars of one chunk, derived from the staged G[64] (chunk-local cumulative log decay) and run ids.
+struct RowScalars {
+  float G, gam, gamr;  // exp(G) if the token sees the entering state else 0; exp(G_last - G) if it reaches S+ else 0
+  int run;
+};
+
+__device__ __forceinline__ RowScalars row_scalars(const float* Gs, const unsigned char* runs, int flags, int i) {
+  RowScalars r;
+  r.G = Gs[i];
+  r.run = runs[i];
+  const bool cin = r.run == 0 && !(flags & 1);
+  const bool tail = r.run == runs[63];
+  r.gam = cin ? __expf(r.G) : 0.f;
+  r.gamr = tail ? __expf(Gs[63] - r.G) : 0.f;
+  return r;
+}
+
+__device__ __forceinline__ float keep_gamma(const float* Gs, const unsigned char* runs, int flags) {
+  return (runs[63] == 0 && !(flags & 1)) ? __expf(Gs[63]) : 0.f;
+}
+
+// D_ij for i >= j in the same run, else 0.
+__device__ __forceinline__ float decay_ij(const float* Gs, const unsigned char* runs, int i, int j, float Gi, int runi) {
+  return (j <= i && runs[j] == runi) ? __expf(Gi - Gs[j]) : 0.f;
+}
+
+// ---- launchers (chunked_*.cu) -----------------------------------------------------------------------------
+struct ChunkedCtx {
+  jla_problem p;
+  Plan plan;
+  char* res;            // residual-layout buffer (residuals when saving, else the forward scratch)
+  const void* q_eff;    // q, k after the optional L2 norm
+  const void* k_eff;
+};
+
+int launch_prep(const ChunkedCtx& c, cudaStream_t s);                           // tables, G/beta/runs, T0, l2norm
+int launch_sg_fwd(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s);
+int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s);
+int l2norm_fwd(const void* x, void* y, int dtype, long rows, int K, cudaStream_t stream);
+
+}  // namespace jla

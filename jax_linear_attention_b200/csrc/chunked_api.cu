@@ -1,0 +1,90 @@
+// Orchestration of the chunked path: support predicate, buffer sizes, and the kernel sequences of the forward
+// (tables -> gates -> [L2 norm] -> T0 -> fused forward) and the backward (reverse state pass -> chunk gradients
+// -> key-gradient epilogue).
+#include "chunked.cuh"
+
+namespace jla {
+
+const char* chunked_unsupported(const jla_problem& p) {
+  if (p.dtype == JLA_DTYPE_F32) return "the chunked tensor-core kernels take bf16 or f16 tensors (f32 runs the recurrent path)";
+  if (p.kind == JLA_KIND_KDA) return "KDA has no chunked kernel yet: pass precision='highest' (recurrent path)";
+  if ((p.K != 64 && p.K != 128) || (p.V != 64 && p.V != 128)) return "head dims K, V must be in (64, 128)";
+  return nullptr;
+}
+
+size_t chunked_residual_bytes(const jla_problem& p) { return make_plan(p).residual_bytes; }
+
+size_t chunked_fwd_scratch_bytes(const jla_problem& p) {
+  const Plan pl = make_plan(p);
+  return pl.save ? 0 : pl.fwd_scratch_bytes;
+}
+
+size_t chunked_bwd_scratch_bytes(const jla_problem& p) { return make_plan(p).bwd_scratch_bytes; }
+
+static ChunkedCtx make_ctx(const jla_problem& p, char* res) {
+  ChunkedCtx c;
+  c.p = p;
+  c.plan = make_plan(p);
+  c.res = res;
+  c.q_eff = c.plan.l2norm ? static_cast<const void*>(res + c.plan.qn) : p.q;
+  c.k_eff = c.plan.l2norm ? static_cast<const void*>(res + c.plan.kn) : p.k;
+  return c;
+}
+
+int chunked_fwd(const jla_problem& p, const jla_fwd_io& io, cudaStream_t stream) {
+  const Plan pl = make_plan(p);
+  char* res;
+  if (pl.save) {
+    if (!io.residuals || io.residual_bytes < pl.residual_bytes) {
+      set_error("residual buffer too small: %zu < %zu bytes", io.residuals ? io.residual_bytes : (size_t)0,
+                pl.residual_bytes);
+      return JLA_ERR_WORKSPACE;
+    }
+    res = static_cast<char*>(io.residuals);
+  } else {
+    if (!io.scratch || io.scratch_bytes < pl.fwd_scratch_bytes) {
+      set_error("forward scratch too small: %zu < %zu bytes", io.scratch ? io.scratch_bytes : (size_t)0,
+                pl.fwd_scratch_bytes);
+      return JLA_ERR_WORKSPACE;
+    }
+    res = static_cast<char*>(io.scratch);
+  }
+  const ChunkedCtx c = make_ctx(p, res);
+  int rc = launch_prep(c, stream);
+  if (rc != JLA_OK) return rc;
+  return launch_sg_fwd(c, io, stream);
+}
+
+int chunked_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t stream) {
+  jla_problem ps = p;
+  ps.flags |= JLA_FLAG_SAVE_RESIDUALS;
+  const Plan pl = make_plan(ps);
+  if (!io.residuals || io.residual_bytes < pl.residual_bytes) {
+    set_error("residual buffer too small: %zu < %zu bytes", io.residuals ? io.residual_bytes : (size_t)0,
+              pl.residual_bytes);
+    return JLA_ERR_WORKSPACE;
+  }
+  if (pl.bwd_scratch_bytes && (!io.scratch || io.scratch_bytes < pl.bwd_scratch_bytes)) {
+    set_error("backward scratch too small: %zu < %zu bytes", io.scratch ? io.scratch_bytes : (size_t)0,
+              pl.bwd_scratch_bytes);
+    return JLA_ERR_WORKSPACE;
+  }
+  const ChunkedCtx c = make_ctx(ps, static_cast<char*>(const_cast<void*>(io.residuals)));
+  return launch_sg_bwd(c, io, static_cast<char*>(io.scratch), stream);
+}
+
+}  // namespace jla
+
+extern "C" int jla_chunked_get_layout(const jla_problem* p, jla_chunked_layout* out) {
+  if (!p || !out) return JLA_ERR_BAD_ARGUMENT;
+  jla_problem ps = *p;
+  ps.flags |= JLA_FLAG_SAVE_RESIDUALS;
+  const jla::Plan pl = jla::make_plan(ps);
+  out->num_chunk_slots = pl.nc;
+  out->meta = pl.meta; out->row_chunks = pl.row_chunks; out->gates = pl.gates; out->runs = pl.runs;
+  out->t0 = pl.t0; out->qn = pl.qn; out->kn = pl.kn; out->h = pl.h; out->vn = pl.vn;
+  out->residual_bytes = pl.residual_bytes;
+  out->dh = pl.dh; out->dvn = pl.dvn; out->dq_acc = pl.dq_acc; out->dk_acc = pl.dk_acc;
+  out->bwd_scratch_bytes = pl.bwd_scratch_bytes;
+  return JLA_OK;
+}

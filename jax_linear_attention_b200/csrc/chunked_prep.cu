@@ -1,0 +1,251 @@
+// Prologue kernels of the chunked path: the chunk table, the per-chunk gate cumsum / document runs, and the
+// gate-free triangular inverse T0 = (I + strict_lower(beta_i k_i.k_j))^-1 (K K^T on tensor cores, the inverse by
+// blocked fp32 elimination).
+#include "chunked.cuh"
+#include "mma.cuh"
+
+namespace jla {
+namespace {
+
+// One block. Dense rows: chunk id = row * per_row + i. Packed sequences: every sequence gets ceil(len / 64)
+// consecutive slots; unused slots get len = 0.
+__global__ void build_tables_kernel(Rows rows, int nc, ChunkMeta* meta, int2* row_chunks) {
+  const int nrows = rows.count();
+  const int tid = threadIdx.x, nt = blockDim.x;
+  if (rows.cu == nullptr) {
+    const int per = (rows.T + kChunk - 1) / kChunk;
+    for (int r = tid; r <= nrows; r += nt) row_chunks[r] = make_int2(r * per, r < nrows ? per : 0);
+    for (int c = tid; c < nc; c += nt) {
+      const int r = c / max(per, 1), i = c - r * per;
+      ChunkMeta m;
+      m.tok0 = r * rows.T + i * kChunk;
+      m.len = min(kChunk, rows.T - i * kChunk);
+      m.row = r;
+      m.flags = 0;
+      meta[c] = m;
+    }
+    return;
+  }
+  __shared__ int total;
+  if (tid == 0) {
+    int acc = 0;
+    for (int r = 0; r < nrows; ++r) {
+      const int len = rows.cu[r + 1] - rows.cu[r];
+      const int cnt = (len + kChunk - 1) / kChunk;
+      row_chunks[r] = make_int2(acc, cnt);
+      acc += cnt;
+    }
+    row_chunks[nrows] = make_int2(acc, 0);
+    total = acc;
+  }
+  __syncthreads();
+  for (int r = tid; r < nrows; r += nt) {
+    const int2 rc = row_chunks[r];
+    const int tok0 = rows.cu[r], len = rows.cu[r + 1] - tok0;
+    for (int i = 0; i < rc.y; ++i) {
+      ChunkMeta m;
+      m.tok0 = tok0 + i * kChunk;
+      m.len = min(kChunk, len - i * kChunk);
+      m.row = r;
+      m.flags = 0;
+      meta[rc.x + i] = m;
+    }
+  }
+  for (int c = total + tid; c < nc; c += nt) meta[c] = ChunkMeta{0, 0, 0, 0};
+}
+
+// One block per chunk slot: G = chunk-local cumsum of g and beta, head-major; run ids of the tokens; flag bit 0.
+__global__ void prep_gates_kernel(Rows rows, int H, const float* __restrict__ g, const float* __restrict__ beta,
+                                  ChunkMeta* meta, float* __restrict__ gates, unsigned char* __restrict__ runs) {
+  const int c = blockIdx.x;
+  const ChunkMeta m = meta[c];
+  if (m.len == 0) return;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float* out = gates + ((long)c * H + h) * 128;
+    float acc = 0.f;
+    for (int i = 0; i < kChunk; ++i) {
+      const bool ok = i < m.len;
+      if (ok && g) acc += g[(long)(m.tok0 + i) * H + h];
+      out[i] = acc;
+      out[64 + i] = (ok && beta) ? beta[(long)(m.tok0 + i) * H + h] : 0.f;
+    }
+  }
+  if (threadIdx.x == 0) {
+    int row_tok0, row_len;
+    rows.range(m.row, row_tok0, row_len);
+    int run = 0;
+    for (int i = 0; i < kChunk; ++i) {
+      if (i > 0 && i < m.len && rows.resets(m.tok0 + i, row_tok0)) ++run;
+      runs[(long)c * 64 + i] = (unsigned char)run;
+    }
+    if (rows.resets(m.tok0, row_tok0)) meta[c].flags = 1;
+  }
+}
+
+struct KktParams {
+  const ChunkMeta* meta;
+  const void* k;
+  const float* gates;
+  const unsigned char* runs;
+  void* t0;
+  int H, Hk;
+};
+
+// T0 for one (chunk, head). 4 warps: K K^T with mma.sync (each warp 16 rows x 64 columns), then the inverse of
+// the unit lower-triangular 64 x 64 matrix in fp32: the four 16 x 16 diagonal blocks by forward substitution
+// (one column per thread), then X21 = -X22 L21 X11 at block sizes 16 and 32.
+template <typename T, int K>
+__global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
+  constexpr int LDK = K + 8, LDA = 65, LDM = 33;
+  const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
+  const ChunkMeta m = p.meta[c];
+  if (m.len == 0) return;
+  const int hk = h / (p.H / p.Hk);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* ks = reinterpret_cast<T*>(smem_raw);
+  float* A = reinterpret_cast<float*>(ks + 64 * LDK);
+  float* X = A + 64 * LDA;
+  float* M = X + 64 * LDA;        // [32][33]
+  float* betas = M + 32 * LDM;    // [64]
+  int* run = reinterpret_cast<int*>(betas + 64);
+
+  load_tile_async<T, 64, K>(ks, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * K, (long)p.Hk * K,
+                            m.len, tid, 128);
+  cp_async_commit();
+  if (tid < 64) {
+    betas[tid] = p.gates[((long)c * p.H + h) * 128 + 64 + tid];
+    run[tid] = p.runs[(long)c * 64 + tid];
+  }
+  for (int idx = tid; idx < 64 * LDA; idx += 128) X[idx] = 0.f;
+  cp_async_wait<0>();
+  __syncthreads();
+
+  {
+    float acc[8][4];
+    zero_acc(acc);
+    warp_gemm<T, 8, K / 16, A_ROW, B_NK>(acc, ks + warp * 16 * LDK, LDK, ks, LDK, lane);
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = warp * 16 + g + ((e >> 1) << 3), j = nt * 8 + 2 * t + (e & 1);
+        A[i * LDA + j] = (j < i && run[i] == run[j]) ? betas[i] * acc[nt][e] : 0.f;
+      }
+    }
+  }
+  __syncthreads();
+
+  if (tid < 64) {  // diagonal 16 x 16 blocks: column `col` of the inverse of block `b`
+    const int b = tid >> 4, col = tid & 15;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float s = (i == col) ? 1.f : 0.f;
+#pragma unroll
+      for (int mm = 0; mm < i; ++mm) s -= A[(16 * b + i) * LDA + 16 * b + mm] * x[mm];
+      x[i] = s;
+      X[(16 * b + i) * LDA + 16 * b + col] = s;
+    }
+  }
+  __syncthreads();
+
+  // level 1: two problems (blocks 0-1 and 2-3), 16 x 16 each
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int o = tid * 4 + e, pr = o >> 8, i = (o >> 4) & 15, j = o & 15;
+    const int r0 = 32 * pr + 16, c0 = 32 * pr;
+    float s = 0.f;
+    for (int mm = 0; mm < 16; ++mm) s += A[(r0 + i) * LDA + c0 + mm] * X[(c0 + mm) * LDA + c0 + j];
+    M[(pr * 16 + i) * LDM + j] = s;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int o = tid * 4 + e, pr = o >> 8, i = (o >> 4) & 15, j = o & 15;
+    const int r0 = 32 * pr + 16, c0 = 32 * pr;
+    float s = 0.f;
+    for (int mm = 0; mm < 16; ++mm) s += X[(r0 + i) * LDA + r0 + mm] * M[(pr * 16 + mm) * LDM + j];
+    X[(r0 + i) * LDA + c0 + j] = -s;
+  }
+  __syncthreads();
+  // level 2: rows 32-63, columns 0-31
+  float m2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int o = tid * 8 + e, i = o >> 5, j = o & 31;
+    float s = 0.f;
+    for (int mm = 0; mm < 32; ++mm) s += A[(32 + i) * LDA + mm] * X[mm * LDA + j];
+    m2[e] = s;
+  }
+  __syncthreads();  // level-1 M fully consumed before it is overwritten
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int o = tid * 8 + e, i = o >> 5, j = o & 31;
+    M[i * LDM + j] = m2[e];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int o = tid * 8 + e, i = o >> 5, j = o & 31;
+    float s = 0.f;
+    for (int mm = 0; mm < 32; ++mm) s += X[(32 + i) * LDA + 32 + mm] * M[mm * LDM + j];
+    X[(32 + i) * LDA + j] = -s;
+  }
+  __syncthreads();
+
+  T* out = static_cast<T*>(p.t0) + ((long)c * p.H + h) * 64 * 64;
+  for (int idx = tid; idx < 64 * 8; idx += 128) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    uint4 v;
+    v.x = pack2<T>(X[r * LDA + c8 + 0], X[r * LDA + c8 + 1]);
+    v.y = pack2<T>(X[r * LDA + c8 + 2], X[r * LDA + c8 + 3]);
+    v.z = pack2<T>(X[r * LDA + c8 + 4], X[r * LDA + c8 + 5]);
+    v.w = pack2<T>(X[r * LDA + c8 + 6], X[r * LDA + c8 + 7]);
+    *reinterpret_cast<uint4*>(out + r * 64 + c8) = v;
+  }
+}
+
+template <typename T, int K>
+int launch_kkt(const KktParams& kp, int blocks, cudaStream_t s) {
+  const size_t smem = 64 * (K + 8) * sizeof(T) + (2 * 64 * 65 + 32 * 33 + 64) * sizeof(float) + 64 * sizeof(int);
+  auto* kern = kkt_inv_kernel<T, K>;
+  if (smem > 48 * 1024) JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<blocks, 128, smem, s>>>(kp);
+  JLA_LAUNCH_OK();
+  return JLA_OK;
+}
+
+}  // namespace
+
+int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
+  const jla_problem& p = c.p;
+  const Plan& pl = c.plan;
+  if (pl.nc == 0 || pl.rows == 0) return JLA_OK;
+  const Rows rows = make_rows(p);
+  ChunkMeta* meta = reinterpret_cast<ChunkMeta*>(c.res + pl.meta);
+  int2* row_chunks = reinterpret_cast<int2*>(c.res + pl.row_chunks);
+  float* gates = reinterpret_cast<float*>(c.res + pl.gates);
+  unsigned char* runs = reinterpret_cast<unsigned char*>(c.res + pl.runs);
+  build_tables_kernel<<<1, 256, 0, s>>>(rows, pl.nc, meta, row_chunks);
+  JLA_LAUNCH_OK();
+  prep_gates_kernel<<<pl.nc, 64, 0, s>>>(rows, p.H, p.g, p.beta, meta, gates, runs);
+  JLA_LAUNCH_OK();
+  if (pl.l2norm) {
+    const long nrows = (long)p.B * p.T * p.Hk;
+    int rc = l2norm_fwd(p.q, c.res + pl.qn, p.dtype, nrows, p.K, s);
+    if (rc != JLA_OK) return rc;
+    rc = l2norm_fwd(p.k, c.res + pl.kn, p.dtype, nrows, p.K, s);
+    if (rc != JLA_OK) return rc;
+  }
+  if (!pl.delta) return JLA_OK;
+  KktParams kp{meta, c.k_eff, gates, runs, c.res + pl.t0, p.H, p.Hk};
+  const int blocks = pl.nc * p.H;
+  if (p.dtype == JLA_DTYPE_BF16) {
+    return p.K == 64 ? launch_kkt<__nv_bfloat16, 64>(kp, blocks, s) : launch_kkt<__nv_bfloat16, 128>(kp, blocks, s);
+  }
+  return p.K == 64 ? launch_kkt<__half, 64>(kp, blocks, s) : launch_kkt<__half, 128>(kp, blocks, s);
+}
+
+}  // namespace jla
