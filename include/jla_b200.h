@@ -147,6 +147,15 @@ typedef struct jla_chunked_layout {
 } jla_chunked_layout;
 int jla_chunked_get_layout(const jla_problem* p, jla_chunked_layout* out);
 
+/* Diagnostics: per-kernel device time. While enabled, every kernel launch of the library is bracketed by CUDA
+ * events on its stream (no synchronisation at launch). jla_profile_read() waits for the recorded events and returns
+ * the summed duration and launch count of one kernel since the last jla_profile_reset(); kernel ids run from 0 until
+ * jla_profile_kernel_name() returns NULL. (The reference times its kernels with CUPTI: benchmarks/harness.py:55-80.) */
+int jla_profile_enable(int on);
+int jla_profile_reset(void);
+const char* jla_profile_kernel_name(int kernel_id);
+int jla_profile_read(int kernel_id, double* total_ms, int* launches);
+
 #ifdef __cplusplus
 }
 #endif

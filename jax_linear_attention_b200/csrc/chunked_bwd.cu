@@ -10,6 +10,7 @@
 // src/jla/ops/mosaic_gpu/gated_delta_rule_bwd.py:303-853; here column sums are shuffle reductions instead of
 // second, transposed products).
 #include "chunked.cuh"
+#include "profile.cuh"
 #include "mma.cuh"
 
 namespace jla {
@@ -581,14 +582,20 @@ int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, cudaStrea
     auto* kern = sg_bwd_state_kernel<T, K, V, DELTA>;
     constexpr int smem = BwdStateSmem<T, K, V, DELTA>::kBytes;
     JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<rows_blocks, 256, smem, s>>>(bp);
+    {
+      ProfScope ps(kProfSgBwdState, s);
+      kern<<<rows_blocks, 256, smem, s>>>(bp);
+    }
     JLA_LAUNCH_OK();
   }
   {
     auto* kern = sg_chunk_grads_kernel<T, K, V, DELTA>;
     constexpr int smem = GradSmem<T, K, V, DELTA>::kBytes;
     JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<chunk_blocks, 256, smem, s>>>(bp);
+    {
+      ProfScope ps(kProfSgChunkGrads, s);
+      kern<<<chunk_blocks, 256, smem, s>>>(bp);
+    }
     JLA_LAUNCH_OK();
   }
   return JLA_OK;

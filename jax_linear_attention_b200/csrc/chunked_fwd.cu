@@ -8,6 +8,7 @@
 // (src/jla/ops/mosaic_gpu/scalar_gate_fused.py:436-458). q/k/v/T0 tiles of the next chunk are prefetched with
 // cp.async while the current chunk computes.
 #include "chunked.cuh"
+#include "profile.cuh"
 #include "mma.cuh"
 
 namespace jla {
@@ -226,7 +227,10 @@ int launch_one(const FwdParams& fp, int blocks, cudaStream_t s) {
   auto* kern = sg_fwd_kernel<T, K, V, DELTA>;
   constexpr int smem = FwdSmem<T, K, V, DELTA>::kBytes;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<blocks, 256, smem, s>>>(fp);
+  {
+    ProfScope ps(kProfSgFwd, s);
+    kern<<<blocks, 256, smem, s>>>(fp);
+  }
   JLA_LAUNCH_OK();
   return JLA_OK;
 }

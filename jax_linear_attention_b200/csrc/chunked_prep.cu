@@ -2,6 +2,7 @@
 // gate-free triangular inverse T0 = (I + strict_lower(beta_i k_i.k_j))^-1 (K K^T on tensor cores, the inverse by
 // blocked fp32 elimination).
 #include "chunked.cuh"
+#include "profile.cuh"
 #include "mma.cuh"
 
 namespace jla {
@@ -212,7 +213,10 @@ int launch_kkt(const KktParams& kp, int blocks, cudaStream_t s) {
   const size_t smem = 64 * (K + 8) * sizeof(T) + (2 * 64 * 65 + 32 * 33 + 64) * sizeof(float) + 64 * sizeof(int);
   auto* kern = kkt_inv_kernel<T, K>;
   if (smem > 48 * 1024) JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<blocks, 128, smem, s>>>(kp);
+  {
+    ProfScope ps(kProfKktInv, s);
+    kern<<<blocks, 128, smem, s>>>(kp);
+  }
   JLA_LAUNCH_OK();
   return JLA_OK;
 }
@@ -228,9 +232,15 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
   int2* row_chunks = reinterpret_cast<int2*>(c.res + pl.row_chunks);
   float* gates = reinterpret_cast<float*>(c.res + pl.gates);
   unsigned char* runs = reinterpret_cast<unsigned char*>(c.res + pl.runs);
-  build_tables_kernel<<<1, 256, 0, s>>>(rows, pl.nc, meta, row_chunks);
+  {
+    ProfScope ps(kProfTables, s);
+    build_tables_kernel<<<1, 256, 0, s>>>(rows, pl.nc, meta, row_chunks);
+  }
   JLA_LAUNCH_OK();
-  prep_gates_kernel<<<pl.nc, 64, 0, s>>>(rows, p.H, p.g, p.beta, meta, gates, runs);
+  {
+    ProfScope ps(kProfGates, s);
+    prep_gates_kernel<<<pl.nc, 64, 0, s>>>(rows, p.H, p.g, p.beta, meta, gates, runs);
+  }
   JLA_LAUNCH_OK();
   if (pl.l2norm) {
     const long nrows = (long)p.B * p.T * p.Hk;

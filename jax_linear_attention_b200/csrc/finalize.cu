@@ -1,6 +1,7 @@
 // HBM-bound epilogue / prologue kernels shared by both paths: key-gradient group sums with the L2-norm
 // backward, and the forward L2 norm of q and k.
 #include "common.cuh"
+#include "profile.cuh"
 
 namespace jla {
 namespace {
@@ -79,8 +80,11 @@ int finalize_t(const float* acc, const void* raw, void* out, long rows, int H, i
   if (rows == 0) return JLA_OK;
   const int warps = 8;
   const long blocks = (rows + warps - 1) / warps;
-  finalize_key_grad_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(
-      acc, static_cast<const T*>(raw), static_cast<T*>(out), rows, H, Hk, K, l2norm ? 1 : 0);
+  {
+    ProfScope ps(kProfFinalize, stream);
+    finalize_key_grad_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(
+        acc, static_cast<const T*>(raw), static_cast<T*>(out), rows, H, Hk, K, l2norm ? 1 : 0);
+  }
   JLA_LAUNCH_OK();
   return JLA_OK;
 }
@@ -90,8 +94,11 @@ int l2norm_t(const void* x, void* y, long rows, int K, cudaStream_t stream) {
   if (rows == 0) return JLA_OK;
   const int warps = 8;
   const long blocks = (rows + warps - 1) / warps;
-  l2norm_fwd_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(y),
-                                                                     rows, K);
+  {
+    ProfScope ps(kProfL2Norm, stream);
+    l2norm_fwd_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(y),
+                                                                       rows, K);
+  }
   JLA_LAUNCH_OK();
   return JLA_OK;
 }

@@ -13,6 +13,7 @@
 #include <stdio.h>
 
 #include "common.cuh"
+#include "profile.cuh"
 
 namespace jla {
 namespace {
@@ -390,7 +391,10 @@ int launch(const RecParams& rp, bool bwd, int rows, cudaStream_t stream) {
   auto* kern = bwd ? rec_bwd_kernel<T, KPT> : rec_fwd_kernel<T, KPT>;
   if (smem > 48 * 1024) JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(rp.H, rows), block(rp.V * KS);
-  kern<<<grid, block, smem, stream>>>(rp);
+  {
+    ProfScope ps(bwd ? kProfRecBwd : kProfRecFwd, stream);
+    kern<<<grid, block, smem, stream>>>(rp);
+  }
   JLA_LAUNCH_OK();
   return JLA_OK;
 }

@@ -1,0 +1,150 @@
+"""GPU parity of the chunk-64 tensor-core kernels (bf16 / f16 operands, fp32 state and accumulation).
+
+Tolerance of the path: relative L2 error <= 1e-2 for outputs and gradients against the float64 oracle on the
+same (bf16-representable) inputs. Stage-level checks use the reference's own metric max|x - want| / max|want|
+and thresholds (T0 4e-3, stages 1e-2: tests/test_mosaic_gpu_gated_delta_rule.py:104-146).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import staged
+from oracle.cases import baseline_config, make_case, max_rel, rel_l2, seg_to_cu
+from tests._util import ChunkedLayout, cabi_fwd_bwd, compare, run_cuda, run_oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.mark.parametrize("kind,K,V,Hk", [("gated_deltanet", 128, 128, 2), ("gated_deltanet", 64, 64, 1),
+                                         ("deltanet", 64, 128, 2), ("simple_gla", 128, 64, 1)])
+def test_stages_match_the_cpu_model(kind, K, V, Hk):
+    case = make_case(kind, B=2, T=200, H=2, Hk=Hk, K=K, V=V, seed=5, docs="mixed", h0=True)
+    scale = case["meta"]["scale"]
+    delta = kind != "simple_gla"
+    out = cabi_fwd_bwd(kind, case, scale=scale)
+    f64 = torch.float64
+    d = {n: torch.tensor(case[n], dtype=f64) for n in ("q", "k", "v", "g", "beta", "h0") if n in case}
+    st = staged.forward(d["q"], d["k"], d["v"], d.get("g"), d.get("beta"), delta=delta, scale=scale, h0=d["h0"],
+                        segment_ids=torch.tensor(case["seg"]))
+    bw = staged.backward(st, torch.tensor(case["do"], dtype=f64), torch.tensor(case["dht"], dtype=f64))
+    lay = ChunkedLayout(out["problem"], out["residuals"], out["bwd_scratch"])
+    G, beta = lay.gates()
+    assert max_rel(G, st["G"]) < 1e-5
+    if delta:
+        assert max_rel(beta, st["beta"]) == 0.0
+        assert max_rel(lay.t0(), st["T0"]) < 4e-3
+        assert max_rel(lay.vn(), st["Vn"]) < 1e-2
+        assert max_rel(lay.dvn(), bw["dVn"]) < 1e-2
+    assert max_rel(lay.h(), st["h"]) < 1e-2
+    assert max_rel(lay.dh(), bw["dh"]) < 1e-2
+
+
+CASES = [
+    # kind, kwargs
+    ("gated_deltanet", dict(B=2, T=1000, H=4, K=128, V=128, docs=None, h0=True)),          # dense, odd T
+    ("gated_deltanet", dict(B=2, T=1536, H=4, K=128, V=128, docs="mixed", h0=True)),       # random documents
+    ("gated_deltanet", dict(B=2, T=777, H=4, K=64, V=64, docs="mixed", h0=True)),          # K = V = 64
+    ("gated_deltanet", dict(B=1, T=1100, H=8, Hk=2, K=128, V=128, docs="mixed", h0=True)),  # grouped key heads
+    ("gated_deltanet", dict(B=1, T=1024, H=4, K=128, V=128, docs="mixed", h0=True, gates="extreme")),
+    ("gated_deltanet", dict(B=1, T=1000, H=4, K=128, V=128, docs="mixed", h0=True, beta_scale=2.0)),
+    ("gated_deltanet", dict(B=2, T=1000, H=4, Hk=2, K=128, V=128, docs="mixed", h0=True, l2norm=True)),
+    ("gated_deltanet", dict(B=4, T=700, H=8, K=128, V=128, docs="mixed", h0=True)),
+    ("gated_deltanet", dict(B=1, T=17, H=2, K=128, V=64, docs=None, h0=False)),            # shorter than a chunk
+    ("deltanet", dict(B=2, T=1000, H=4, K=128, V=128, docs=None, h0=True)),
+    ("deltanet", dict(B=2, T=777, H=4, K=64, V=64, docs="mixed", h0=True)),
+    ("deltanet", dict(B=2, T=1000, H=4, K=128, V=128, docs="mixed", h0=True, l2norm=True)),
+    ("simple_gla", dict(B=2, T=1000, H=4, K=128, V=128, docs=None, h0=True)),
+    ("simple_gla", dict(B=1, T=1100, H=8, Hk=2, K=128, V=64, docs="mixed", h0=True)),
+    ("simple_gla", dict(B=2, T=1000, H=8, Hk=1, K=128, V=64, docs="mixed", h0=True)),      # Mamba-2 shared B/C
+    ("simple_gla", dict(B=1, T=1024, H=4, K=128, V=128, docs="mixed", h0=True, gates="extreme")),
+]
+
+
+@pytest.mark.parametrize("kind,spec", CASES, ids=[f"{k}-{i}" for i, (k, _) in enumerate(CASES)])
+def test_outputs_and_gradients_bf16(kind, spec):
+    case = make_case(kind, seed=100 + len(str(spec)), **spec)
+    scale, l2 = case["meta"]["scale"], bool(spec.get("l2norm"))
+    want = run_oracle(kind, case, scale=scale, l2norm=l2, chunked=True)
+    got = run_cuda(kind, case, scale=scale, dtype="bfloat16", l2norm=l2)
+    table = compare(got, want, TOL, f"{kind} {spec}")
+    assert all(np.isfinite(v).all() for v in got.values()), table
+
+
+def test_float16():
+    case = make_case("gated_deltanet", B=1, T=300, H=2, K=128, V=128, seed=3, dtype="float16", docs="mixed", h0=True)
+    want = run_oracle("gated_deltanet", case, scale=case["meta"]["scale"], chunked=True)
+    got = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="float16")
+    compare(got, want, 3e-3, "float16")  # 11-bit mantissa: tighter than bf16
+
+
+@pytest.mark.parametrize("kind", ["simple_gla", "gated_deltanet"])
+def test_cu_seqlens_per_sequence_states_and_empty_sequence(kind):
+    case = make_case(kind, B=1, T=700, H=2, K=128, V=64, seed=12)
+    cu = [0, 13, 13, 77, 141, 500, 700]
+    rng = np.random.default_rng(0)
+    case["h0"] = (0.5 * rng.standard_normal((6, 2, 128, 64))).astype(np.float32)
+    case["dht"] = (0.1 * rng.standard_normal((6, 2, 128, 64))).astype(np.float32)
+    want = run_oracle(kind, case, scale=case["meta"]["scale"], cu_seqlens=cu)
+    got = run_cuda(kind, case, scale=case["meta"]["scale"], dtype="bfloat16", cu_seqlens=cu)
+    compare(got, want, TOL, kind)
+    assert np.array_equal(got["ht"][1], case["h0"][1])
+    assert np.array_equal(got["dh0"][1], case["dht"][1])
+
+
+def test_cu_seqlens_equals_segment_ids():
+    """Packing with cu_seqlens or with segment ids gives the same outputs (zero initial states)."""
+    case = make_case("gated_deltanet", B=1, T=900, H=2, K=128, V=128, seed=14, docs="mixed")
+    cu = seg_to_cu(case["seg"][0])
+    a = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="bfloat16", grads=False)
+    del case["seg"]
+    b = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="bfloat16", grads=False, cu_seqlens=cu)
+    assert rel_l2(b["o"], a["o"]) < 4e-3  # chunk boundaries differ, so rounding differs
+    assert rel_l2(b["ht"][-1], a["ht"][0]) < 4e-3
+
+
+def test_final_state_chains_across_two_calls():
+    from jax_linear_attention_b200 import ops
+
+    case = make_case("gated_deltanet", B=2, T=1024, H=2, K=128, V=128, seed=15, h0=True)
+    t = {n: torch.tensor(case[n], device="cuda", dtype=torch.bfloat16 if n in "qkv" else torch.float32)
+         for n in ("q", "k", "v", "g", "beta", "h0")}
+    o, s = ops.linear_attention("gated_deltanet", t["q"], t["k"], t["v"], g=t["g"], beta=t["beta"],
+                                initial_state=t["h0"], output_final_state=True)
+    h = 512  # chunk aligned: the two halves walk exactly the same chunks, so the results are identical
+    o1, s1 = ops.linear_attention("gated_deltanet", t["q"][:, :h], t["k"][:, :h], t["v"][:, :h], g=t["g"][:, :h],
+                                  beta=t["beta"][:, :h], initial_state=t["h0"], output_final_state=True)
+    o2, s2 = ops.linear_attention("gated_deltanet", t["q"][:, h:], t["k"][:, h:], t["v"][:, h:], g=t["g"][:, h:],
+                                  beta=t["beta"][:, h:], initial_state=s1, output_final_state=True)
+    assert torch.equal(torch.cat([o1, o2], 1), o) and torch.equal(s2, s)
+
+
+def test_baseline_config1_full_size_slices_and_properties():
+    """BASELINE config 1 at full size (B8 T2048 H16 d128, bf16, packed documents): two (b, h) slices against the
+    oracle, plus the size-independent property that every head of every batch row is independent (running a
+    slice alone gives the same bits)."""
+    from jax_linear_attention_b200 import ops
+
+    case = baseline_config(1)
+    dev = "cuda"
+    t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16 if n in ("q", "k", "v", "do") else torch.float32,
+                         requires_grad=n in ("q", "k", "v", "g", "beta"))
+         for n in ("q", "k", "v", "g", "beta", "do")}
+    seg = torch.tensor(case["seg"], device=dev)
+    o, s = ops.linear_attention("gated_deltanet", t["q"], t["k"], t["v"], g=t["g"], beta=t["beta"], segment_ids=seg,
+                                output_final_state=True)
+    grads = torch.autograd.grad(o, [t[n] for n in ("q", "k", "v", "g", "beta")], t["do"])
+    assert all(bool(torch.isfinite(x).all()) for x in (o, s, *grads))
+    for b, h in ((0, 0), (7, 15)):
+        sl = {n: case[n][b:b + 1, :, h:h + 1] for n in ("q", "k", "v", "g", "beta", "do")}
+        sl["seg"] = case["seg"][b:b + 1]
+        sl["dht"] = np.zeros((1, 1, 128, 128), np.float32)
+        want = run_oracle("gated_deltanet", sl, scale=128 ** -0.5, chunked=True)
+        got = dict(o=o.detach()[b:b + 1, :, h:h + 1].float().cpu().numpy(),
+                   ht=s.detach()[b:b + 1, h:h + 1].cpu().numpy())
+        for n, gr in zip(("q", "k", "v", "g", "beta"), grads):
+            got["d" + n] = gr[b:b + 1, :, h:h + 1].float().cpu().numpy()
+        compare(got, want, TOL, f"config1 slice {b},{h}")
+        alone = run_cuda("gated_deltanet", sl, scale=128 ** -0.5, dtype="bfloat16")
+        assert np.array_equal(alone["o"], got["o"]) and np.array_equal(alone["dk"], got["dk"])
