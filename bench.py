@@ -242,6 +242,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -313,10 +314,10 @@ def main() -> None:
         for dst, src in zip(out_host, outs):
             dst.copy_(src, non_blocking=True)
 
-    for _ in range(2):
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
+    for _ in range(2 if e2e_steps else 0):
         e2e_step()
     barrier()
-    e2e_steps = max(3, min(args.steps, 10))
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
@@ -327,7 +328,7 @@ def main() -> None:
         tms = torch.tensor([e2e_ms], device=device)
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         e2e_ms = float(tms.item())
-    d2h = sum(t.numel() * t.element_size() for t in out_host)
+    d2h = sum(t.numel() * t.element_size() for t in out_host) if out_host else 0
 
     if rank == 0:
         pk = peaks()
@@ -364,8 +365,9 @@ def main() -> None:
             dtype="bf16", data="synthetic",
             config=dict(workload=WORKLOADS[args.workload]["name"], per_gpu_batch=list(shape[:2]),
                         l2="inputs larger than L2 (q,k,v,dO 268 MB + residuals per step)", parallelism=f"batch x heads, {world} GPU(s), no communication"),
-            e2e=dict(value=world * tokens / (e2e_ms / e2e_steps * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
-                     d2h_bytes_per_step=d2h, steps=e2e_steps, ms_per_step=e2e_ms / e2e_steps),
+            e2e=None if not e2e_steps else dict(
+                value=world * tokens / (e2e_ms / e2e_steps * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
+                d2h_bytes_per_step=d2h, steps=e2e_steps, ms_per_step=e2e_ms / e2e_steps),
             gpu_launches=launches,
             clocks=clocks.summary(),
             roofline=roof,
