@@ -156,6 +156,13 @@ int jla_profile_reset(void);
 const char* jla_profile_kernel_name(int kernel_id);
 int jla_profile_read(int kernel_id, double* total_ms, int* launches);
 
+/* Diagnostics: one-CTA check of the tcgen05 primitive layer. Computes C[m][n] (f32) = A * B with bf16 operands
+ * staged in 128-byte-swizzled shared memory: a = A[m][kd] (K-major view) or A^T[kd][m] (MN-major view, a_mn_major),
+ * b = B^T[n][kd] or B[kd][n] (b_mn_major). *status is set to 1 if the MMA completion never arrived (bounded wait).
+ * Shapes: (64,128,128), (64,64,64), (64,64,128), (128,128,64). No counterpart in the reference. */
+int jla_selftest_umma(int m, int n, int kd, int a_mn_major, int b_mn_major, const void* a, const void* b, float* c,
+                      int* status, jla_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
