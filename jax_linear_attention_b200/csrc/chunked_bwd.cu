@@ -9,6 +9,8 @@
 // and the gate / beta gradients as row and column sums of the same tiles (the reference's split backward:
 // src/jla/ops/mosaic_gpu/gated_delta_rule_bwd.py:303-853; here column sums are shuffle reductions instead of
 // second, transposed products).
+#include <stdlib.h>
+
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
@@ -577,7 +579,7 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
 }
 
 template <typename T, int K, int V, bool DELTA>
-int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, cudaStream_t s) {
+int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, bool legacy_grads, cudaStream_t s) {
   {
     auto* kern = sg_bwd_state_kernel<T, K, V, DELTA>;
     constexpr int smem = BwdStateSmem<T, K, V, DELTA>::kBytes;
@@ -588,7 +590,7 @@ int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, cudaStrea
     }
     JLA_LAUNCH_OK();
   }
-  {
+  if (legacy_grads) {
     auto* kern = sg_chunk_grads_kernel<T, K, V, DELTA>;
     constexpr int smem = GradSmem<T, K, V, DELTA>::kBytes;
     JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -602,11 +604,11 @@ int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, cudaStrea
 }
 
 template <typename T, bool DELTA>
-int launch_kv(const BwdParams& bp, int K, int V, int rb, int cb, cudaStream_t s) {
-  if (K == 128 && V == 128) return launch_one<T, 128, 128, DELTA>(bp, rb, cb, s);
-  if (K == 128 && V == 64) return launch_one<T, 128, 64, DELTA>(bp, rb, cb, s);
-  if (K == 64 && V == 128) return launch_one<T, 64, 128, DELTA>(bp, rb, cb, s);
-  return launch_one<T, 64, 64, DELTA>(bp, rb, cb, s);
+int launch_kv(const BwdParams& bp, int K, int V, int rb, int cb, bool legacy, cudaStream_t s) {
+  if (K == 128 && V == 128) return launch_one<T, 128, 128, DELTA>(bp, rb, cb, legacy, s);
+  if (K == 128 && V == 64) return launch_one<T, 128, 64, DELTA>(bp, rb, cb, legacy, s);
+  if (K == 64 && V == 128) return launch_one<T, 64, 128, DELTA>(bp, rb, cb, legacy, s);
+  return launch_one<T, 64, 64, DELTA>(bp, rb, cb, legacy, s);
 }
 
 }  // namespace
@@ -644,13 +646,20 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
   bp.Hk = p.Hk;
   bp.scale = p.scale;
   const int rb = pl.rows * p.H, cb = pl.nc * p.H;
+  // JLA_B200_LEGACY_GRADS=1 keeps the mma.sync chunk-gradient kernel (for A/B comparison); default: tcgen05.
+  static const bool legacy = [] {
+    const char* e = getenv("JLA_B200_LEGACY_GRADS");
+    return e && e[0] == '1';
+  }();
   int rc;
   if (p.dtype == JLA_DTYPE_BF16) {
-    rc = pl.delta ? launch_kv<__nv_bfloat16, true>(bp, p.K, p.V, rb, cb, s)
-                  : launch_kv<__nv_bfloat16, false>(bp, p.K, p.V, rb, cb, s);
+    rc = pl.delta ? launch_kv<__nv_bfloat16, true>(bp, p.K, p.V, rb, cb, legacy, s)
+                  : launch_kv<__nv_bfloat16, false>(bp, p.K, p.V, rb, cb, legacy, s);
   } else {
-    rc = pl.delta ? launch_kv<__half, true>(bp, p.K, p.V, rb, cb, s) : launch_kv<__half, false>(bp, p.K, p.V, rb, cb, s);
+    rc = pl.delta ? launch_kv<__half, true>(bp, p.K, p.V, rb, cb, legacy, s)
+                  : launch_kv<__half, false>(bp, p.K, p.V, rb, cb, legacy, s);
   }
+  if (rc == JLA_OK && !legacy) rc = launch_chunk_grads_tc(c, io, scratch, direct, s);
   if (rc != JLA_OK || direct) return rc;
   rc = finalize_key_grad(bp.dq_acc, p.q, io.dq, p.dtype, tokens, p.H, p.Hk, p.K, pl.l2norm, s);
   if (rc != JLA_OK) return rc;
