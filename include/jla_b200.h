@@ -133,6 +133,20 @@ int jla_linear_attention_fwd(const jla_problem* p, const jla_fwd_io* io, jla_str
 /* Backward for cotangents (d_o, d_final); replaces scalar_gate._backward / the KDA backward chain. */
 int jla_linear_attention_bwd(const jla_problem* p, const jla_bwd_io* io, jla_stream_t stream);
 
+/* Forward for hosts that have no scratch buffer to pass and are not allowed to allocate one (a custom call inside
+ * another runtime's executor that reserved no workspace, a server whose memory pool is frozen after start-up).
+ * This entry point has no counterpart in the reference. Same computation and results as jla_linear_attention_fwd
+ * without JLA_FLAG_SAVE_RESIDUALS; the scratch is a fixed array of jla_noalloc_scratch_limit() bytes (32 MiB) of
+ * device memory that belongs to the library and is held on every GPU that loads it until the process exits.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - A call whose jla_fwd_scratch_bytes() exceeds the limit is rejected with JLA_ERR_WORKSPACE.
+ *   - The first call on a device looks up the array's device address (one cudaGetSymbolAddress, with that device
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on a device share the array: calls that may overlap on the GPU (different streams) race on it.
+ *     Keep them on one stream or order them with events. Nothing needs clearing between calls. */
+size_t jla_noalloc_scratch_limit(void);
+int jla_linear_attention_fwd_noalloc(const jla_problem* p, void* o, float* final_state, jla_stream_t stream);
+
 /* Diagnostics: where the chunked path keeps its intermediates, so that tests can compare them stage by stage
  * with the CPU model (the reference checks its kernels per stage too:
  * tests/test_mosaic_gpu_gated_delta_rule.py:104-146). Byte offsets into the residual buffer written by a forward
