@@ -28,7 +28,13 @@ int chunked_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t stream)
 namespace {
 
 int resolve_path(const jla_problem& p) {
-  if (p.path == JLA_PATH_AUTO) return p.dtype == JLA_DTYPE_F32 ? JLA_PATH_RECURRENT : JLA_PATH_CHUNKED;
+  if (p.path == JLA_PATH_AUTO) {
+    // f32 tensors run the exact token scan; so does KDA until its chunked kernels exist (chunked_unsupported()).
+    if (p.dtype == JLA_DTYPE_F32 || chunked_unsupported(p) != nullptr) {
+      return recurrent_unsupported(p) == nullptr || p.dtype == JLA_DTYPE_F32 ? JLA_PATH_RECURRENT : JLA_PATH_CHUNKED;
+    }
+    return JLA_PATH_CHUNKED;
+  }
   return p.path;
 }
 

@@ -1,0 +1,225 @@
+"""Sequence (context) parallel linear attention: one sequence split over the ranks of a group along T.
+
+Role of the reference's ``src/jla/distributed/context_parallel.py:113-182``, redesigned for one process per GPU
+with point-to-point hand-offs instead of all-gathered affine maps. Rank ``r`` holds tokens
+``[r * T/P, (r + 1) * T/P)`` of every batch row. The recurrent state is the only thing that crosses a shard edge:
+
+1. every rank runs the op on its whole shard from a zero state (rank 0: from ``initial_state``); this is already
+   exact for every token at or after the shard's first document start, because a document start discards the
+   carried state (the observation the reference's intra-GPU split uses: ``scalar_gate_docs.py:16-27``);
+2. the fp32 chunk-final state ``[B, H, K, V]`` goes to the next rank with ``send``/``recv`` (NCCL over NVLink on GPUs,
+   gloo in the CPU tests). A rank whose rows all contain a document start sends right after step 1, so no serial
+   chain forms across ranks; otherwise it first applies the correction of step 3 and then sends;
+3. the correction: the op is re-run on the prefix of each row up to its first document start, now from the received
+   state, and replaces those outputs (and the final state if the row has no document start at all).
+
+The backward mirrors this with ``dS`` flowing right to left: the prefix pass is differentiated first (its result,
+the gradient of the received state, goes to the previous rank at once unless the row's prefix reaches the shard
+end), then the gradient of the sent state is received and the full-shard pass is differentiated. This is exact for
+every kind, including the delta rule, where the entering state acts through a K x K transition and cannot be
+applied as a decayed additive term.
+
+Document boundaries are read on the host (one small device-to-host copy per call) to size the prefixes.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+
+_GATES = {"simple_gla": ("g",), "deltanet": ("beta",), "gated_deltanet": ("g", "beta"), "kda": ("g", "beta")}
+
+
+def _first_starts(seg_local, prev_last, t_local: int) -> list[int]:
+    """Per row, the index of the first token that starts a new document (``t_local`` if none)."""
+    if seg_local is None:
+        return None
+    seg = seg_local.cpu()
+    starts = []
+    for b in range(seg.shape[0]):
+        row = seg[b]
+        change = torch.zeros(t_local, dtype=torch.bool)
+        change[1:] = row[1:] != row[:-1]
+        if prev_last is not None:
+            change[0] = bool(row[0] != prev_last[b])
+        idx = torch.nonzero(change)
+        starts.append(int(idx[0]) if idx.numel() else t_local)
+    return starts
+
+
+class _ContextParallel(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, call, kind, group, seg, want_final, *tensors):
+        # tensors = (q, k, v, *gates, h0 or None)
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        ranks = dist.get_process_group_ranks(group)
+        prev_rank = ranks[rank - 1] if rank > 0 else None
+        next_rank = ranks[rank + 1] if rank < world - 1 else None
+        *xs, h0 = tensors
+        q = xs[0]
+        batch, t_local = q.shape[:2]
+        dev = q.device
+        sdt = torch.float64 if q.dtype == torch.float64 else torch.float32  # dtype of the carried state
+
+        prev_last = None
+        if seg is not None and world > 1:  # the previous rank's last segment id decides whether token 0 is a start
+            last = seg[:, -1].contiguous()
+            recv = torch.empty_like(last)
+            reqs = []
+            if next_rank is not None:
+                reqs.append(dist.isend(last, next_rank, group=group))
+            if prev_rank is not None:
+                reqs.append(dist.irecv(recv, prev_rank, group=group))
+            for r in reqs:
+                r.wait()
+            prev_last = recv.cpu() if prev_rank is not None else None
+
+        leaves = [x.detach().requires_grad_(True) for x in xs]
+        h0_leaf = None if (h0 is None or rank > 0) else h0.detach().requires_grad_(True)
+        if rank == 0:
+            starts = [0] * batch
+        elif seg is None:
+            starts = [t_local] * batch
+        else:
+            starts = _first_starts(seg, prev_last, t_local)
+        early = all(s < t_local for s in starts)
+        # a shard without any document start is covered entirely by the correction pass: skip the zero-state pass
+        skip_a = rank > 0 and all(s == t_local for s in starts)
+        o_a = f_a = None
+        if not skip_a:
+            with torch.enable_grad():
+                o_a, f_a = call(kind, leaves, h0_leaf, seg, slice(None), None)
+            o = o_a.detach().clone()
+            f = f_a.detach().clone()
+        else:
+            o = torch.empty(batch, t_local, xs[2].shape[2], xs[2].shape[3], dtype=xs[2].dtype, device=dev)
+            f = torch.empty(batch, xs[2].shape[2], q.shape[3], xs[2].shape[3], dtype=sdt, device=dev)
+        send_req = None
+        if next_rank is not None and early:
+            send_req = dist.isend(f.contiguous(), next_rank, group=group)
+        s_in_leaf, prefix = None, []
+        if rank > 0:
+            s_in = torch.empty_like(f)
+            dist.recv(s_in, prev_rank, group=group)
+            s_in_leaf = s_in.requires_grad_(True)
+            with torch.enable_grad():
+                for b, length in enumerate(starts):
+                    if length == 0:
+                        prefix.append(None)
+                        continue
+                    o_p, f_p = call(kind, leaves, s_in_leaf, seg, slice(0, length), b)
+                    prefix.append((o_p, f_p))
+                    o[b, :length] = o_p.detach()[0]
+                    if length == t_local:
+                        f[b] = f_p.detach()[0]
+        if send_req is not None:
+            send_req.wait()
+        if next_rank is not None and not early:
+            dist.send(f.contiguous(), next_rank, group=group)
+
+        ctx.state = dict(leaves=leaves, h0_leaf=h0_leaf, o_a=o_a, f_a=f_a, s_in_leaf=s_in_leaf, prefix=prefix,
+                         starts=starts, t_local=t_local, group=group, prev_rank=prev_rank, next_rank=next_rank,
+                         n_in=len(xs), has_h0=h0 is not None, dev=dev, f_shape=tuple(f.shape), sdt=sdt)
+        return o, f
+
+    @staticmethod
+    def backward(ctx, d_o, d_f):
+        st = ctx.state
+        leaves, starts, t_local, group = st["leaves"], st["starts"], st["t_local"], st["group"]
+        grads = [torch.zeros_like(x) for x in leaves]
+        d_o = d_o.contiguous()
+        # gradient of the state this rank sent on (last rank: the caller's cotangent of the final state)
+        g_f = None
+
+        def recv_gf():
+            nonlocal g_f
+            if st["next_rank"] is not None:
+                g_f = torch.empty(st["f_shape"], dtype=st["sdt"], device=st["dev"])
+                dist.recv(g_f, st["next_rank"], group=group)
+            else:
+                g_f = (d_f.contiguous() if d_f is not None
+                       else torch.zeros(st["f_shape"], dtype=st["sdt"], device=st["dev"]))
+
+        d_s_in = None
+        if st["s_in_leaf"] is not None:
+            needs_gf = any(s == t_local for s in starts)
+            if needs_gf:
+                recv_gf()
+            d_s_in = torch.zeros_like(st["s_in_leaf"])
+            for b, item in enumerate(st["prefix"]):
+                if item is None:
+                    continue
+                o_p, f_p = item
+                cot_f = g_f[b:b + 1] if starts[b] == t_local else torch.zeros_like(f_p)
+                got = torch.autograd.grad([o_p, f_p], [*leaves, st["s_in_leaf"]], [d_o[b:b + 1, :starts[b]], cot_f],
+                                          allow_unused=True)
+                for acc, x in zip(grads, got[:-1]):
+                    if x is not None:
+                        acc += x
+                if got[-1] is not None:
+                    d_s_in += got[-1]
+            dist.send(d_s_in.contiguous(), st["prev_rank"], group=group)
+        if g_f is None:
+            recv_gf()
+        if st["o_a"] is None:  # the whole shard was handled by the correction pass
+            return (None, None, None, None, None, *grads, None)
+        cot_o = d_o.clone()
+        cot_f = g_f.clone()
+        for b, s in enumerate(starts):
+            if st["s_in_leaf"] is not None:
+                cot_o[b, :s] = 0  # those outputs came from the prefix pass
+                if s == t_local:
+                    cot_f[b] = 0
+        wrt = leaves + ([st["h0_leaf"]] if st["h0_leaf"] is not None else [])
+        got = torch.autograd.grad([st["o_a"], st["f_a"]], wrt, [cot_o, cot_f], allow_unused=True)
+        for acc, x in zip(grads, got[:len(leaves)]):
+            if x is not None:
+                acc += x
+        d_h0 = None
+        if st["has_h0"]:
+            d_h0 = got[-1] if st["h0_leaf"] is not None else None
+        return (None, None, None, None, None, *grads, d_h0)
+
+
+def _default_call(impl, options):
+    def call(kind, leaves, state, seg, tslice, row):
+        q, k, v, *gates = leaves
+        rows = slice(None) if row is None else slice(row, row + 1)
+        names = _GATES[kind]
+        kw = dict(options)
+        kw.update({n: g[rows, tslice] for n, g in zip(names, gates)})
+        if seg is not None:
+            kw["segment_ids"] = seg[rows, tslice]
+        init = None if state is None else state[rows]
+        return ops.linear_attention(kind, q[rows, tslice], k[rows, tslice], v[rows, tslice], impl=impl,
+                                    initial_state=init, output_final_state=True, **kw)
+    return call
+
+
+def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: str = "auto", call=None, **inputs):
+    """``(o_local, final_state)`` for this rank's T-shard ``q, k, v [B, T/P, ...]`` (gates and ``segment_ids``
+    sharded the same way). ``initial_state`` is read on the first rank; the final state of the whole sequence is
+    returned on the last rank when ``output_final_state`` is set (``None`` elsewhere). ``cu_seqlens`` is not
+    supported: pass ``segment_ids``, as in the reference's sequence-parallel op.
+
+    ``call(kind, leaves, state, seg, tslice, row)`` may replace the op (tests inject the CPU oracle).
+    """
+    if kind not in _GATES:
+        raise ValueError(f"unknown linear-attention kind {kind!r}; expected one of {sorted(_GATES)}")
+    if inputs.get("cu_seqlens") is not None:
+        raise NotImplementedError("context parallelism does not support cu_seqlens; pass segment_ids")
+    group = group if group is not None else dist.group.WORLD
+    names = _GATES[kind]
+    missing = [n for n in names if inputs.get(n) is None]
+    if missing:
+        raise ValueError(f"{kind} takes gates {names}; missing {missing}")
+    gates = [inputs.pop(n) for n in names]
+    h0 = inputs.pop("initial_state", None)
+    want_final = bool(inputs.pop("output_final_state", False))
+    seg = inputs.pop("segment_ids", None)
+    call = call or _default_call(impl, inputs)
+    o, f = _ContextParallel.apply(call, kind, group, seg, want_final, q, k, v, *gates, h0)
+    last = dist.get_rank(group) == dist.get_world_size(group) - 1
+    return o, (f if (want_final and last) else None)
