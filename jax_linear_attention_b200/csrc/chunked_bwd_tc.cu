@@ -1,7 +1,8 @@
 // Chunk-parallel gradients (dq, dk, dbeta, dg) on the Blackwell tensor cores: every product is a tcgen05.mma
 // (M = 64 tokens) reading 128-byte-swizzled bf16/f16 tiles straight from shared memory, accumulating in TMEM;
-// eight warps read the accumulators back in the m16n8 fragment layout for the elementwise work (decay masks,
-// row/column sums, rounding of the next operand). Same math as sg_chunk_grads_kernel (chunked_bwd.cu):
+// the tiles arrive by TMA (cp.async.bulk.tensor, one thread issues them, mbarriers count the bytes); sixteen
+// warps read the accumulators back in the m16n8 fragment layout for the elementwise work (decay masks, row and
+// column sums, rounding of the next operand). Same math as sg_chunk_grads_kernel (chunked_bwd.cu):
 //
 //   dP  = scale (dO Vn^T) D      dQ = scale (cin Gamma)(dO S^T) + dP K
 //   dAg = tril(dVn W^T)   dT0 = dAg D beta_j   dA0 = -strict(T0^T dT0 T0^T) same
@@ -10,16 +11,20 @@
 // Transposed operands cost nothing: a tile stored [rows][64-element blocks] is read K-major (contraction along
 // the contiguous axis) or MN-major (contraction along the rows) by choosing the descriptor.
 //
-// One CTA per (chunk, head), 256 threads. TMEM columns: [0,128) dq part 1 then Vn dS+^T, [128,256) dk,
+// One CTA per (chunk, head), 512 threads: warp w owns rows 16 (w % 4) .. +15 (its TMEM lane quadrant) and the
+// (w / 4)-th quarter of the columns. TMEM columns: [0,128) dq part 1 then Vn dS+^T, [128,256) dk,
 // [256,384) K S / dP K / M1 / dW S^T, [384,448) and [448,512) the 64 x 64 tiles.
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
+#include "tma.cuh"
 #include "umma.cuh"
 
 namespace jla {
 
 __device__ int g_tc_status = 0;  // set to a non-zero code when a bounded wait gave up
+__device__ unsigned long long g_tc_trace[32];  // phase timestamps (ns) of one CTA, for tuning
+#define TC_TRACE(i) do { if (blockIdx.x == 2000 && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_tc_trace[i] = _t; } } while (0)
 
 namespace {
 
@@ -29,7 +34,6 @@ struct GradTcParams {
   const ChunkMeta* meta;
   const float* gates;
   const unsigned char* runs;
-  const void *q, *k, *v, *t0, *d_o, *h, *vn, *dh, *dvn, *dv;
   void *dq, *dk;
   float *dq_acc, *dk_acc;
   float *dg, *dbeta;
@@ -37,38 +41,39 @@ struct GradTcParams {
   float scale;
 };
 
+struct GradTcMaps {
+  CUtensorMap q, k, v, d_o, dv, h, dh, vn, dvn, t0;
+};
+
 template <int K, int V, bool DELTA>
 struct GradTcSmem {
   static constexpr int kK = 0;
   static constexpr int kQ = kK + 64 * K * 2;
-  static constexpr int kDo = kQ + 64 * K * 2;
-  static constexpr int kV = kDo + 64 * V * 2;
+  static constexpr int kDo = kQ + 64 * K * 2;          // dO, later dVn
+  static constexpr int kV = kDo + 64 * V * 2;          // V -> W in place, later dW
   static constexpr int kVn = DELTA ? kV + 64 * V * 2 : kV;
   static constexpr int kS = kVn + 64 * V * 2;
   static constexpr int kT0 = kS + K * V * 2;
-  static constexpr int kXa = kT0 + 8192;
-  static constexpr int kXb = kXa + 8192;
-  static constexpr int kXc = kXb + 8192;
-  static constexpr int kVec = kXc + 8192;             // G[64] beta[64] dG[64] dbeta[64] sdot[4] (f32), runs[64] (u8)
-  static constexpr int kBars = kVec + 260 * 4 + 64;   // 8 mbarriers + tmem slot
-  static constexpr int kBytes = kBars + 8 * 8 + 16 + 1024;  // + slack for the 1024-byte alignment of the base
+  static constexpr int kXa = kT0 + 8192;               // dP, later M1
+  static constexpr int kXb = kXa + 8192;               // dT0, later dA0 beta_i
+  static constexpr int kD = kXb + 8192;                // decay matrix D[64][68] f32
+  static constexpr int kVec = kD + 64 * 68 * 4;        // G beta gam gamr dG dbeta: [64] f32 each; sdot[4]; runs[64] u8
+  static constexpr int kBars = kVec + (6 * 64 + 4) * 4 + 64;
+  static constexpr int kBytes = kBars + 12 * 8 + 16 + 1024;  // 12 mbarriers, tmem slot, alignment slack
   static_assert(K * V * 2 <= 64 * K * 2 + 64 * V * 2, "dS+ must fit over q | dO");
+  static_assert(kBars % 8 == 0, "mbarrier alignment");
 };
 
-// cp.async a [rows_valid x COLS] row-major tile into the swizzled layout (missing rows are zero-filled).
-template <typename T, int ROWS, int COLS>
-__device__ __forceinline__ void load_tile_swz(unsigned char* tile, const T* src, long gstride, int rows_valid, int tid,
-                                              int nthreads) {
-  constexpr int VPR = COLS / 8;
+constexpr int LDD = 68;
+
+// zero rows [first, 64) of a [64 x COLS] swizzled tile (tokens past the end of a partial chunk)
+template <typename T, int COLS>
+__device__ __forceinline__ void zero_tail_rows(unsigned char* tile, int first, int tid, int nthreads) {
   T* dst = reinterpret_cast<T*>(tile);
-  for (int idx = tid; idx < ROWS * VPR; idx += nthreads) {
-    const int r = idx / VPR, c = (idx - r * VPR) * 8;
-    T* d = dst + swz_tile(ROWS, r, c);
-    if (r < rows_valid) {
-      cp_async16(d, src + r * gstride + c);
-    } else {
-      *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
-    }
+  constexpr int VPR = COLS / 8;
+  for (int idx = tid; idx < (64 - first) * VPR; idx += nthreads) {
+    const int r = first + idx / VPR, c = (idx % VPR) * 8;
+    *reinterpret_cast<uint4*>(dst + swz_tile(64, r, c)) = make_uint4(0, 0, 0, 0);
   }
 }
 
@@ -143,17 +148,18 @@ __device__ __forceinline__ void row_dots_swz(const float (&x)[NT][4], const unsi
 }
 
 template <typename T, int K, int V, bool DELTA>
-__global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams p) {
+__global__ void __launch_bounds__(512, 1)
+sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p) {
   using L = GradTcSmem<K, V, DELTA>;
   constexpr int FMT = umma::Fmt<T>::value;
-  constexpr int KNT = K / 16, VNT = V / 16;  // n-tiles of this warp's half of a K- or V-wide accumulator
+  constexpr int KNT = K / 32, VNT = V / 32;  // n-tiles of this warp's quarter of a K- or V-wide accumulator
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
   if (m.len == 0) return;
   const int hk = h / (p.H / p.Hk);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int r0 = 16 * (warp & 3), ch = warp >> 2;
-  const int kc0 = (K / 2) * ch, vc0 = (V / 2) * ch, cc0 = 32 * ch;
+  const int r0 = 16 * (warp & 3), cq = warp >> 2;
+  const int kc0 = (K / 4) * cq, vc0 = (V / 4) * cq, cc0 = 16 * cq;
 
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -166,51 +172,66 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
   unsigned char* t0S = base + L::kT0;
   unsigned char* Xa = base + L::kXa;
   unsigned char* Xb = base + L::kXb;
-  unsigned char* Xc = base + L::kXc;
   unsigned char* dSS = qS;  // dS+ overlays q | dO once both are dead
+  float* Dm = reinterpret_cast<float*>(base + L::kD);
   float* Gs = reinterpret_cast<float*>(base + L::kVec);
   float* betas = Gs + 64;
-  float* dGv = betas + 64;
+  float* gam = betas + 64;
+  float* gamr = gam + 64;
+  float* dGv = gamr + 64;
   float* dbv = dGv + 64;
   float* sdot = dbv + 64;
   unsigned char* runs = reinterpret_cast<unsigned char*>(sdot + 4);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::kBars);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::kBars);  // [0..7] MMA batches, [8..11] TMA loads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   const uint32_t aK = umma::smem_addr(kS), aQ = umma::smem_addr(qS), aDo = umma::smem_addr(doS), aV = umma::smem_addr(vS),
                  aVn = umma::smem_addr(vnS), aS = umma::smem_addr(SS), aT0 = umma::smem_addr(t0S),
-                 aXa = umma::smem_addr(Xa), aXb = umma::smem_addr(Xb), aXc = umma::smem_addr(Xc),
-                 adS = umma::smem_addr(dSS);
+                 aXa = umma::smem_addr(Xa), aXb = umma::smem_addr(Xb), adS = umma::smem_addr(dSS);
+  const int ch_off = c * p.H + h;
 
-  const long ch_off = (long)c * p.H + h;
-  const T* gk = static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * K;
-  const T* gq = static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * K;
-  const T* gv = static_cast<const T*>(p.v) + ((long)m.tok0 * p.H + h) * V;
-  const T* gdo = static_cast<const T*>(p.d_o) + ((long)m.tok0 * p.H + h) * V;
-  // group 0: k, S, v, T0, gates, runs
-  load_tile_swz<T, 64, K>(kS, gk, (long)p.Hk * K, m.len, tid, 256);
-  load_tile_swz<T, K, V>(SS, static_cast<const T*>(p.h) + ch_off * K * V, V, K, tid, 256);
-  load_tile_swz<T, 64, V>(vS, gv, (long)p.H * V, m.len, tid, 256);
-  if (DELTA) load_tile_swz<T, 64, 64>(t0S, static_cast<const T*>(p.t0) + ch_off * 4096, 64, 64, tid, 256);
-  if (tid < 32) cp_async16(Gs + tid * 4, p.gates + ch_off * 128 + tid * 4);
-  if (tid >= 32 && tid < 36) cp_async16(runs + (tid - 32) * 16, p.runs + (long)c * 64 + (tid - 32) * 16);
-  cp_async_commit();
-  // group 1: dO, Vn, q
-  load_tile_swz<T, 64, V>(doS, gdo, (long)p.H * V, m.len, tid, 256);
-  if (DELTA) load_tile_swz<T, 64, V>(vnS, static_cast<const T*>(p.vn) + ch_off * 64 * V, V, 64, tid, 256);
-  load_tile_swz<T, 64, K>(qS, gq, (long)p.Hk * K, m.len, tid, 256);
-  cp_async_commit();
-
+  TC_TRACE(0);
+  if (tid == 0) {
+    for (int i = 0; i < 12; ++i) umma::mbar_init(bars + i, 1);
+    umma::mbar_init_fence();
+    // load group 0: k, S, v, T0 ; group 1: dO, Vn, q
+    uint32_t bytes = 64 * K * 2 + K * V * 2 + 64 * V * 2 + (DELTA ? 8192 : 0);
+    tma::expect_tx(bars + 8, bytes);
+    tma::load_tile<64, K>(kS, &maps.k, 0, hk, m.tok0, bars + 8);
+    tma::load_tile<K, V>(SS, &maps.h, 0, 0, ch_off * K, bars + 8);
+    tma::load_tile<64, V>(vS, &maps.v, 0, h, m.tok0, bars + 8);
+    if (DELTA) tma::load_tile<64, 64>(t0S, &maps.t0, 0, 0, ch_off * 64, bars + 8);
+    bytes = 64 * V * 2 + 64 * K * 2 + (DELTA ? 64 * V * 2 : 0);
+    tma::expect_tx(bars + 9, bytes);
+    tma::load_tile<64, V>(doS, &maps.d_o, 0, h, m.tok0, bars + 9);
+    if (DELTA) tma::load_tile<64, V>(vnS, &maps.vn, 0, 0, ch_off * 64, bars + 9);
+    tma::load_tile<64, K>(qS, &maps.q, 0, hk, m.tok0, bars + 9);
+  }
+  if (warp == 1) umma::tmem_alloc(tmem_slot, 512);
   if (tid < 64) {
+    Gs[tid] = p.gates[(long)ch_off * 128 + tid];
+    betas[tid] = p.gates[(long)ch_off * 128 + 64 + tid];
+    runs[tid] = p.runs[(long)c * 64 + tid];
     dGv[tid] = 0.f;
     dbv[tid] = 0.f;
+    if (tid == 0) sdot[0] = 0.f;
   }
-  if (tid == 0) {
-    sdot[0] = 0.f;
-    for (int i = 0; i < 8; ++i) umma::mbar_init(bars + i, 1);
-    umma::mbar_init_fence();
+  __syncthreads();
+  if (tid < 64) {
+    const RowScalars rs = row_scalars(Gs, runs, m.flags, tid);
+    gam[tid] = rs.gam;
+    gamr[tid] = rs.gamr;
   }
-  if (warp == 0) umma::tmem_alloc(tmem_slot, 512);
-  cp_async_wait<1>();
+  for (int idx = tid; idx < 64 * 64; idx += 512) {  // D_ij = exp(G_i - G_j) for i >= j in the same run
+    const int i = idx >> 6, j = idx & 63;
+    Dm[i * LDD + j] = decay_ij(Gs, runs, i, j, Gs[i], runs[i]);
+  }
+  TC_TRACE(1);
+  bool ok = umma::mbar_wait(bars + 8, 0);
+  TC_TRACE(2);
+  if (m.len < 64) {
+    zero_tail_rows<T, K>(kS, m.len, tid, 512);
+    zero_tail_rows<T, V>(vS, m.len, tid, 512);
+  }
   umma::fence_async_smem();
   umma::fence_before_sync();
   __syncthreads();
@@ -218,31 +239,39 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
   const uint32_t tmem = *tmem_slot;
   const uint32_t tl = tmem + ((uint32_t)(32 * (warp & 3)) << 16);  // this warp's lane quadrant
   constexpr uint32_t cQ = 0, cK = 128, cT1 = 256, cP1 = 384, cP2 = 448;
-  bool ok = true;
 
   // ---- batch 1: T1 = K S (for W) -------------------------------------------------------------------------
-  if (DELTA && tid == 0) {
+  if (DELTA && tid == 0 && ok) {
     umma::gemm<64, V, K / 16, false, true, FMT>(tmem + cT1, aK, 64, aS, K, false);
     umma::commit(bars + 0);
   }
-  cp_async_wait<0>();
+  __syncwarp();
+  TC_TRACE(3);
+  ok = umma::mbar_wait(bars + 9, 0) && ok;
+  TC_TRACE(4);
+  if (m.len < 64) {
+    zero_tail_rows<T, V>(doS, m.len, tid, 512);
+    zero_tail_rows<T, K>(qS, m.len, tid, 512);
+  }
   umma::fence_async_smem();
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
   // ---- batch 2: P1 = dO Vn^T, P2 = Q K^T, accQ = dO S^T ------------------------------------------------------
-  if (tid == 0) {
+  if (tid == 0 && ok) {
     umma::gemm<64, 64, V / 16, false, false, FMT>(tmem + cP1, aDo, 64, aVn, 64, false);
     umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP2, aQ, 64, aK, 64, false);
     umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cQ, aDo, 64, aS, K, false);
     umma::commit(bars + 1);
   }
   __syncwarp();
-  const RowScalars rs0 = row_scalars(Gs, runs, m.flags, r0 + g);
-  const RowScalars rs1 = row_scalars(Gs, runs, m.flags, r0 + g + 8);
+  const int i0 = r0 + g, i1 = r0 + g + 8;
+  const float gam0 = gam[i0], gam1 = gam[i1], gamr0 = gamr[i0], gamr1 = gamr[i1];
 
   if (DELTA) {  // epilogue 1: W = V - (cin Gamma)(K S), in place over V
+    TC_TRACE(5);
     ok = umma::mbar_wait(bars + 0, 0) && ok;
+    TC_TRACE(6);
     umma::fence_after_sync();
     if (ok) {
       float acc[VNT][4];
@@ -252,41 +281,45 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
 #pragma unroll
       for (int nt = 0; nt < VNT; ++nt) {
         const int col = vc0 + nt * 8 + 2 * t;
-        uint32_t* w0 = reinterpret_cast<uint32_t*>(vt + swz_tile(64, r0 + g, col));
-        uint32_t* w1 = reinterpret_cast<uint32_t*>(vt + swz_tile(64, r0 + g + 8, col));
+        uint32_t* w0 = reinterpret_cast<uint32_t*>(vt + swz_tile(64, i0, col));
+        uint32_t* w1 = reinterpret_cast<uint32_t*>(vt + swz_tile(64, i1, col));
         const float2 v0 = unpack2<T>(*w0), v1 = unpack2<T>(*w1);
-        *w0 = pack2<T>(v0.x - rs0.gam * acc[nt][0], v0.y - rs0.gam * acc[nt][1]);
-        *w1 = pack2<T>(v1.x - rs1.gam * acc[nt][2], v1.y - rs1.gam * acc[nt][3]);
+        *w0 = pack2<T>(v0.x - gam0 * acc[nt][0], v0.y - gam0 * acc[nt][1]);
+        *w1 = pack2<T>(v1.x - gam1 * acc[nt][2], v1.y - gam1 * acc[nt][3]);
       }
     }
   }
   {  // epilogue 2: dP = scale (dO Vn^T) D ; E = dP (Q K^T)
+    TC_TRACE(7);
     ok = umma::mbar_wait(bars + 1, 0) && ok;
+    TC_TRACE(8);
     umma::fence_after_sync();
+    if (DELTA && tid == 0 && ok) {  // dO is dead: fetch dVn into its buffer
+      tma::expect_tx(bars + 10, 64 * V * 2);
+      tma::load_tile<64, V>(doS, &maps.dvn, 0, 0, ch_off * 64, bars + 10);
+    }
+    __syncwarp();
     if (ok) {
-      float accP[4][4], accE[4][4];
-      umma::ld_16x256b<4>(accP, tl + cP1 + cc0);
-      umma::ld_16x256b<4>(accE, tl + cP2 + cc0);
+      float accP[2][4], accE[2][4];
+      umma::ld_16x256b<2>(accP, tl + cP1 + cc0);
+      umma::ld_16x256b<2>(accE, tl + cP2 + cc0);
       umma::wait_ld();
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
+      for (int nt = 0; nt < 2; ++nt) {
         const int j = cc0 + nt * 8 + 2 * t;
-        accP[nt][0] *= p.scale * decay_ij(Gs, runs, r0 + g, j, rs0.G, rs0.run);
-        accP[nt][1] *= p.scale * decay_ij(Gs, runs, r0 + g, j + 1, rs0.G, rs0.run);
-        accP[nt][2] *= p.scale * decay_ij(Gs, runs, r0 + g + 8, j, rs1.G, rs1.run);
-        accP[nt][3] *= p.scale * decay_ij(Gs, runs, r0 + g + 8, j + 1, rs1.G, rs1.run);
+        const float2 d0 = *reinterpret_cast<const float2*>(Dm + i0 * LDD + j);
+        const float2 d1 = *reinterpret_cast<const float2*>(Dm + i1 * LDD + j);
+        accP[nt][0] *= p.scale * d0.x;
+        accP[nt][1] *= p.scale * d0.y;
+        accP[nt][2] *= p.scale * d1.x;
+        accP[nt][3] *= p.scale * d1.y;
 #pragma unroll
         for (int e = 0; e < 4; ++e) accE[nt][e] *= accP[nt][e];
       }
-      row_sums_add<4>(accE, dGv, r0, lane, 1.f);
-      col_sums_add<4>(accE, dGv, cc0, lane, -1.f);
-      store_acc_swz<T, 4>(Xa, 64, r0, cc0, accP, lane);
+      row_sums_add<2>(accE, dGv, r0, lane, 1.f);
+      col_sums_add<2>(accE, dGv, cc0, lane, -1.f);
+      store_acc_swz<T, 2>(Xa, 64, r0, cc0, accP, lane);
     }
-  }
-  // dO is dead (batch 2 complete): fetch dVn into its buffer
-  if (DELTA) {
-    load_tile_swz<T, 64, V>(doS, static_cast<const T*>(p.dvn) + ch_off * 64 * V, V, 64, tid, 256);
-    cp_async_commit();
   }
   umma::fence_async_smem();
   umma::fence_before_sync();
@@ -300,12 +333,10 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
   }
   __syncwarp();
   if (DELTA) {
-    cp_async_wait<0>();
-    umma::fence_async_smem();
-    umma::fence_before_sync();
-    __syncthreads();
-    umma::fence_after_sync();
-    // ---- batch 3b: P1 = dVn W^T, P2 = K K^T ------------------------------------------------------------------
+    TC_TRACE(9);
+    ok = umma::mbar_wait(bars + 10, 0) && ok;
+    TC_TRACE(10);  // dVn landed (whole 64-row tile from the scratch: no tail to clear)
+    // ---- batch 3b: P1 = dVn W^T, P2 = K K^T (W was written before the barrier above) ---------------------------
     if (tid == 0 && ok) {
       umma::gemm<64, 64, V / 16, false, false, FMT>(tmem + cP1, aDo, 64, aV, 64, false);
       umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP2, aK, 64, aK, 64, false);
@@ -314,14 +345,16 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
     __syncwarp();
   }
   {  // epilogue 3: dq = scale (cin Gamma)(dO S^T) + dP K
+    TC_TRACE(11);
     ok = umma::mbar_wait(bars + 2, 0) && ok;
+    TC_TRACE(12);
     umma::fence_after_sync();
     if (ok) {
       float accQ[KNT][4], accT[KNT][4];
       umma::ld_16x256b<KNT>(accQ, tl + cQ + kc0);
       umma::ld_16x256b<KNT>(accT, tl + cT1 + kc0);
       umma::wait_ld();
-      const float s0 = p.scale * rs0.gam, s1 = p.scale * rs1.gam;
+      const float s0 = p.scale * gam0, s1 = p.scale * gam1;
 #pragma unroll
       for (int nt = 0; nt < KNT; ++nt) {
         accQ[nt][0] *= s0;
@@ -332,16 +365,16 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
       float d0, d1;
       row_dots_swz<T, KNT>(accQ, qS, 64, r0, kc0, lane, d0, d1);
       if (t == 0) {
-        atomicAdd(dGv + r0 + g, d0);
-        atomicAdd(dGv + r0 + g + 8, d1);
+        atomicAdd(dGv + i0, d0);
+        atomicAdd(dGv + i1, d1);
       }
-      const long tok0 = (long)m.tok0 + r0 + g;
+      const long tok0 = (long)m.tok0 + i0;
 #pragma unroll
       for (int nt = 0; nt < KNT; ++nt) {
         const int col = kc0 + nt * 8 + 2 * t;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          if (r0 + g + 8 * hh >= m.len) continue;
+          if (i0 + 8 * hh >= m.len) continue;
           const long tok = tok0 + 8 * hh;
           const float x0 = accQ[nt][2 * hh] + accT[nt][2 * hh], x1 = accQ[nt][2 * hh + 1] + accT[nt][2 * hh + 1];
           if (p.dq_acc) {
@@ -355,55 +388,61 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
   }
   if (DELTA) {
     {  // epilogue 4: dAg = tril(dVn W^T); F = dAg Ag; dT0 = dAg D beta_j
+      TC_TRACE(13);
       ok = umma::mbar_wait(bars + 3, 0) && ok;
+      TC_TRACE(14);
       umma::fence_after_sync();
-      // q, dVn and W are dead now: fetch dW (over W) and dS+ (over q | dO)
-      load_tile_swz<T, 64, V>(vS, static_cast<const T*>(p.dv) + ((long)m.tok0 * p.H + h) * V, (long)p.H * V, m.len, tid,
-                              256);
-      load_tile_swz<T, K, V>(dSS, static_cast<const T*>(p.dh) + ch_off * K * V, V, K, tid, 256);
-      cp_async_commit();
       if (ok) {
-        float accA[4][4], accF[4][4], accB[4][4];
-        umma::ld_16x256b<4>(accA, tl + cP1 + cc0);
+        float accA[2][4], accF[2][4], accB[2][4];
+        umma::ld_16x256b<2>(accA, tl + cP1 + cc0);
         umma::wait_ld();
         const T* t0t = reinterpret_cast<const T*>(t0S);
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
+        for (int nt = 0; nt < 2; ++nt) {
+          const int j = cc0 + nt * 8 + 2 * t;
+          const float2 d0 = *reinterpret_cast<const float2*>(Dm + i0 * LDD + j);
+          const float2 d1 = *reinterpret_cast<const float2*>(Dm + i1 * LDD + j);
+          const float2 ta = unpack2<T>(*reinterpret_cast<const uint32_t*>(t0t + swz_tile(64, i0, j)));
+          const float2 tb = unpack2<T>(*reinterpret_cast<const uint32_t*>(t0t + swz_tile(64, i1, j)));
+          const float dd[4] = {d0.x, d0.y, d1.x, d1.y};
+          const float tt[4] = {ta.x, ta.y, tb.x, tb.y};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int i = r0 + g + ((e >> 1) << 3), j = cc0 + nt * 8 + 2 * t + (e & 1);
-            const RowScalars& rs = (e >> 1) ? rs1 : rs0;
-            const float d = decay_ij(Gs, runs, i, j, rs.G, rs.run);
-            const float t0v = to_f32(t0t[swz_tile(64, i, j)]);
+            const float bj = betas[j + (e & 1)];
             const float dag = accA[nt][e];
-            accB[nt][e] = dag * t0v * d;
-            accF[nt][e] = accB[nt][e] * betas[j];
-            accA[nt][e] = dag * d * betas[j];
+            accB[nt][e] = dag * tt[e] * dd[e];
+            accF[nt][e] = accB[nt][e] * bj;
+            accA[nt][e] = dag * dd[e] * bj;
           }
         }
-        row_sums_add<4>(accF, dGv, r0, lane, 1.f);
-        col_sums_add<4>(accF, dGv, cc0, lane, -1.f);
-        col_sums_add<4>(accB, dbv, cc0, lane, 1.f);
-        store_acc_swz<T, 4>(Xb, 64, r0, cc0, accA, lane);
+        row_sums_add<2>(accF, dGv, r0, lane, 1.f);
+        col_sums_add<2>(accF, dGv, cc0, lane, -1.f);
+        col_sums_add<2>(accB, dbv, cc0, lane, 1.f);
+        store_acc_swz<T, 2>(Xb, 64, r0, cc0, accA, lane);
       }
     }
     umma::fence_async_smem();
     umma::fence_before_sync();
-    __syncthreads();
+    __syncthreads();  // every warp is past its reads of q (epilogue 3); W and dVn were consumed by batch 3b
     umma::fence_after_sync();
-    // ---- batch 4: M1 = dT0 T0^T (into T1[0:64]) ----------------------------------------------------------------
+    // ---- batch 4: M1 = dT0 T0^T (into T1[0:64]); fetch dW over W and dS+ over q | dO -------------------------------
     if (tid == 0 && ok) {
       umma::gemm<64, 64, 4, false, false, FMT>(tmem + cT1, aXb, 64, aT0, 64, false);
       umma::commit(bars + 4);
+      tma::expect_tx(bars + 11, 64 * V * 2 + K * V * 2);
+      tma::load_tile<64, V>(vS, &maps.dv, 0, h, m.tok0, bars + 11);
+      tma::load_tile<K, V>(dSS, &maps.dh, 0, 0, ch_off * K, bars + 11);
     }
     __syncwarp();
+    TC_TRACE(15);
     ok = umma::mbar_wait(bars + 4, 0) && ok;
+    TC_TRACE(16);
     umma::fence_after_sync();
     if (ok) {
-      float accM[4][4];
-      umma::ld_16x256b<4>(accM, tl + cT1 + cc0);
+      float accM[2][4];
+      umma::ld_16x256b<2>(accM, tl + cT1 + cc0);
       umma::wait_ld();
-      store_acc_swz<T, 4>(Xc, 64, r0, cc0, accM, lane);
+      store_acc_swz<T, 2>(Xa, 64, r0, cc0, accM, lane);  // dP is dead: M1 takes its tile
     }
     umma::fence_async_smem();
     umma::fence_before_sync();
@@ -411,35 +450,47 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
     umma::fence_after_sync();
     // ---- batch 5: P1 = T0^T M1 -----------------------------------------------------------------------------------
     if (tid == 0 && ok) {
-      umma::gemm<64, 64, 4, true, true, FMT>(tmem + cP1, aT0, 64, aXc, 64, false);
+      umma::gemm<64, 64, 4, true, true, FMT>(tmem + cP1, aT0, 64, aXa, 64, false);
       umma::commit(bars + 5);
     }
     __syncwarp();
+    TC_TRACE(17);
     ok = umma::mbar_wait(bars + 5, 0) && ok;
+    TC_TRACE(18);
     umma::fence_after_sync();
     if (ok) {  // epilogue 6: dA0 = -strict(P1) same; dbeta_i += sum_j dA0_ij (k_i . k_j); Xb = dA0 beta_i
-      float accA0[4][4], accKK[4][4];
-      umma::ld_16x256b<4>(accA0, tl + cP1 + cc0);
-      umma::ld_16x256b<4>(accKK, tl + cP2 + cc0);
+      float accA0[2][4], accKK[2][4];
+      umma::ld_16x256b<2>(accA0, tl + cP1 + cc0);
+      umma::ld_16x256b<2>(accKK, tl + cP2 + cc0);
       umma::wait_ld();
+      const float b0 = betas[i0], b1 = betas[i1];
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
+      for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int i = r0 + g + ((e >> 1) << 3), j = cc0 + nt * 8 + 2 * t + (e & 1);
-          const float a = (j < i && runs[j] == runs[i]) ? -accA0[nt][e] : 0.f;
+          const int i = (e >> 1) ? i1 : i0, j = cc0 + nt * 8 + 2 * t + (e & 1);
+          const float a = (j < i && Dm[i * LDD + j] != 0.f) ? -accA0[nt][e] : 0.f;  // strictly lower, same run
           accKK[nt][e] *= a;
-          accA0[nt][e] = a * betas[i];
+          accA0[nt][e] = a * ((e >> 1) ? b1 : b0);
         }
       }
-      row_sums_add<4>(accKK, dbv, r0, lane, 1.f);
-      store_acc_swz<T, 4>(Xb, 64, r0, cc0, accA0, lane);
+      row_sums_add<2>(accKK, dbv, r0, lane, 1.f);
+      store_acc_swz<T, 2>(Xb, 64, r0, cc0, accA0, lane);
     }
   } else {
-    load_tile_swz<T, K, V>(dSS, static_cast<const T*>(p.dh) + ch_off * K * V, V, K, tid, 256);
-    cp_async_commit();
+    umma::fence_before_sync();
+    __syncthreads();  // every warp is past its reads of q
+    umma::fence_after_sync();
+    if (tid == 0 && ok) {
+      tma::expect_tx(bars + 11, K * V * 2);
+      tma::load_tile<K, V>(dSS, &maps.dh, 0, 0, ch_off * K, bars + 11);
+    }
+    __syncwarp();
   }
-  cp_async_wait<0>();
+  TC_TRACE(19);
+  ok = umma::mbar_wait(bars + 11, 0) && ok;
+  TC_TRACE(20);
+  if (DELTA && m.len < 64) zero_tail_rows<T, V>(vS, m.len, tid, 512);
   umma::fence_async_smem();
   umma::fence_before_sync();
   __syncthreads();
@@ -459,7 +510,7 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
     float part = 0.f;
     const uint32_t* a = reinterpret_cast<const uint32_t*>(SS);
     const uint32_t* b = reinterpret_cast<const uint32_t*>(dSS);
-    for (int idx = tid; idx < K * V / 2; idx += 256) {
+    for (int idx = tid; idx < K * V / 2; idx += 512) {
       const float2 x = unpack2<T>(a[idx]), y = unpack2<T>(b[idx]);
       part += x.x * y.x + x.y * y.y;
     }
@@ -467,7 +518,9 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
     for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
     if (lane == 0) atomicAdd(sdot, part);
   }
+  TC_TRACE(21);
   ok = umma::mbar_wait(bars + 6, 0) && ok;
+  TC_TRACE(22);
   umma::fence_after_sync();
   if (ok) {  // epilogue 7: dk and the state terms of dG
     float accK[KNT][4], accT[KNT][4];
@@ -478,43 +531,43 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
       umma::wait_ld();
 #pragma unroll
       for (int nt = 0; nt < KNT; ++nt) {
-        accT[nt][0] *= rs0.gam;
-        accT[nt][1] *= rs0.gam;
-        accT[nt][2] *= rs1.gam;
-        accT[nt][3] *= rs1.gam;
+        accT[nt][0] *= gam0;
+        accT[nt][1] *= gam0;
+        accT[nt][2] *= gam1;
+        accT[nt][3] *= gam1;
 #pragma unroll
         for (int e = 0; e < 4; ++e) accK[nt][e] -= accT[nt][e];
       }
       row_dots_swz<T, KNT>(accT, kS, 64, r0, kc0, lane, d0, d1);
       if (t == 0) {
-        atomicAdd(dGv + r0 + g, -d0);
-        atomicAdd(dGv + r0 + g + 8, -d1);
+        atomicAdd(dGv + i0, -d0);
+        atomicAdd(dGv + i1, -d1);
       }
     }
     umma::ld_16x256b<KNT>(accT, tl + cQ + kc0);
     umma::wait_ld();
 #pragma unroll
     for (int nt = 0; nt < KNT; ++nt) {
-      accT[nt][0] *= rs0.gamr;
-      accT[nt][1] *= rs0.gamr;
-      accT[nt][2] *= rs1.gamr;
-      accT[nt][3] *= rs1.gamr;
+      accT[nt][0] *= gamr0;
+      accT[nt][1] *= gamr0;
+      accT[nt][2] *= gamr1;
+      accT[nt][3] *= gamr1;
 #pragma unroll
       for (int e = 0; e < 4; ++e) accK[nt][e] += accT[nt][e];
     }
     row_dots_swz<T, KNT>(accT, kS, 64, r0, kc0, lane, d0, d1);
     if (t == 0) {
-      atomicAdd(dGv + r0 + g, -d0);
-      atomicAdd(dGv + r0 + g + 8, -d1);
+      atomicAdd(dGv + i0, -d0);
+      atomicAdd(dGv + i1, -d1);
       atomicAdd(dGv + 63, d0 + d1);
     }
-    const long tok0 = (long)m.tok0 + r0 + g;
+    const long tok0 = (long)m.tok0 + i0;
 #pragma unroll
     for (int nt = 0; nt < KNT; ++nt) {
       const int col = kc0 + nt * 8 + 2 * t;
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        if (r0 + g + 8 * hh >= m.len) continue;
+        if (i0 + 8 * hh >= m.len) continue;
         const long tok = tok0 + 8 * hh;
         if (p.dk_acc) {
           *reinterpret_cast<float2*>(p.dk_acc + (tok * p.H + h) * K + col) = make_float2(accK[nt][2 * hh], accK[nt][2 * hh + 1]);
@@ -527,7 +580,8 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
   }
   umma::fence_before_sync();
   __syncthreads();
-  if (warp == 0) umma::tmem_dealloc(tmem, 512);
+  TC_TRACE(23);
+  if (warp == 1) umma::tmem_dealloc(tmem, 512);
   if (!ok) {
     if (tid == 0) atomicExch(&g_tc_status, 1);
     return;
@@ -544,24 +598,24 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_tc_kernel(GradTcParams 
 }
 
 template <typename T, int K, int V, bool DELTA>
-int launch_one(const GradTcParams& gp, int blocks, cudaStream_t s) {
+int launch_one(const GradTcMaps& maps, const GradTcParams& gp, int blocks, cudaStream_t s) {
   auto* kern = sg_chunk_grads_tc_kernel<T, K, V, DELTA>;
   constexpr int smem = GradTcSmem<K, V, DELTA>::kBytes;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   {
     ProfScope ps(kProfSgChunkGrads, s);
-    kern<<<blocks, 256, smem, s>>>(gp);
+    kern<<<blocks, 512, smem, s>>>(maps, gp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
 }
 
 template <typename T, bool DELTA>
-int launch_kv(const GradTcParams& gp, int K, int V, int blocks, cudaStream_t s) {
-  if (K == 128 && V == 128) return launch_one<T, 128, 128, DELTA>(gp, blocks, s);
-  if (K == 128 && V == 64) return launch_one<T, 128, 64, DELTA>(gp, blocks, s);
-  if (K == 64 && V == 128) return launch_one<T, 64, 128, DELTA>(gp, blocks, s);
-  return launch_one<T, 64, 64, DELTA>(gp, blocks, s);
+int launch_kv(const GradTcMaps& maps, const GradTcParams& gp, int K, int V, int blocks, cudaStream_t s) {
+  if (K == 128 && V == 128) return launch_one<T, 128, 128, DELTA>(maps, gp, blocks, s);
+  if (K == 128 && V == 64) return launch_one<T, 128, 64, DELTA>(maps, gp, blocks, s);
+  if (K == 64 && V == 128) return launch_one<T, 64, 128, DELTA>(maps, gp, blocks, s);
+  return launch_one<T, 64, 64, DELTA>(maps, gp, blocks, s);
 }
 
 }  // namespace
@@ -570,20 +624,27 @@ int launch_kv(const GradTcParams& gp, int K, int V, int blocks, cudaStream_t s) 
 int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, bool direct, cudaStream_t s) {
   const jla_problem& p = c.p;
   const Plan& pl = c.plan;
+  const uint64_t tokens = (uint64_t)p.B * p.T, slots = (uint64_t)pl.nc * p.H;
+  GradTcMaps maps;
+  bool ok = tma::encode_3d(&maps.q, c.q_eff, p.K, p.Hk, tokens, 64) && tma::encode_3d(&maps.k, c.k_eff, p.K, p.Hk, tokens, 64) &&
+            tma::encode_3d(&maps.v, p.v, p.V, p.H, tokens, 64) && tma::encode_3d(&maps.d_o, io.d_o, p.V, p.H, tokens, 64) &&
+            tma::encode_3d(&maps.dv, io.dv, p.V, p.H, tokens, 64) &&
+            tma::encode_3d(&maps.h, c.res + pl.h, p.V, 1, slots * p.K, p.K) &&
+            tma::encode_3d(&maps.dh, scratch + pl.dh, p.V, 1, slots * p.K, p.K);
+  if (ok && pl.delta) {
+    ok = tma::encode_3d(&maps.vn, c.res + pl.vn, p.V, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.dvn, scratch + pl.dvn, p.V, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.t0, c.res + pl.t0, 64, 1, slots * 64, 64);
+  } else if (ok) {
+    maps.vn = maps.v;
+    maps.dvn = maps.v;
+    maps.t0 = maps.v;
+  }
+  if (!ok) return JLA_ERR_CUDA;
   GradTcParams gp{};
   gp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
   gp.gates = reinterpret_cast<const float*>(c.res + pl.gates);
   gp.runs = reinterpret_cast<const unsigned char*>(c.res + pl.runs);
-  gp.q = c.q_eff;
-  gp.k = c.k_eff;
-  gp.v = p.v;
-  gp.t0 = c.res + pl.t0;
-  gp.d_o = io.d_o;
-  gp.h = c.res + pl.h;
-  gp.vn = c.res + pl.vn;
-  gp.dh = scratch + pl.dh;
-  gp.dvn = scratch + pl.dvn;
-  gp.dv = io.dv;
   gp.dq = io.dq;
   gp.dk = io.dk;
   gp.dq_acc = direct ? nullptr : reinterpret_cast<float*>(scratch + pl.dq_acc);
@@ -595,10 +656,15 @@ int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scrat
   gp.scale = p.scale;
   const int blocks = pl.nc * p.H;
   if (p.dtype == JLA_DTYPE_BF16) {
-    return pl.delta ? launch_kv<__nv_bfloat16, true>(gp, p.K, p.V, blocks, s)
-                    : launch_kv<__nv_bfloat16, false>(gp, p.K, p.V, blocks, s);
+    return pl.delta ? launch_kv<__nv_bfloat16, true>(maps, gp, p.K, p.V, blocks, s)
+                    : launch_kv<__nv_bfloat16, false>(maps, gp, p.K, p.V, blocks, s);
   }
-  return pl.delta ? launch_kv<__half, true>(gp, p.K, p.V, blocks, s) : launch_kv<__half, false>(gp, p.K, p.V, blocks, s);
+  return pl.delta ? launch_kv<__half, true>(maps, gp, p.K, p.V, blocks, s)
+                  : launch_kv<__half, false>(maps, gp, p.K, p.V, blocks, s);
+}
+
+int read_tc_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 32) == cudaSuccess ? JLA_OK : JLA_ERR_CUDA;
 }
 
 int read_tc_status(int* out) {
@@ -610,3 +676,5 @@ int read_tc_status(int* out) {
 }
 
 }  // namespace jla
+
+extern "C" int jla_debug_tc_trace(unsigned long long* out) { return jla::read_tc_trace(out); }

@@ -103,6 +103,16 @@ __device__ __forceinline__ void mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
       : "memory");
 }
+// Same with the A operand in TMEM: rows = lanes, 16-bit elements packed two per 32-bit column (element k of a row in
+// column k / 2, even k in the low half), as tcgen05.st writes them. One k-step of 16 = 8 columns.
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
 // Arrive on `bar` once all MMAs issued so far by this thread have completed (implies fence::before_thread_sync).
 __device__ __forceinline__ void commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar))
@@ -113,17 +123,31 @@ __device__ __forceinline__ void commit(uint64_t* bar) {
 //   a_tile / b_tile : 1024-byte aligned tile bases (byte addresses in the shared window)
 //   *_MN            : operand view (see the file header); *_rows: rows of one column block of that tile
 // K-major operands may span several column blocks along the contraction (4 k-steps per block).
+// The two base descriptors are built once; every further k-step only adds a compile-time constant to the
+// address field (the single issuing thread is on the critical path, so its instruction count matters).
 template <int M, int N, int KSTEPS, bool A_MN, bool B_MN, int FMT>
 __device__ __forceinline__ void gemm(uint32_t d_tmem, uint32_t a_tile, int a_rows, uint32_t b_tile, int b_rows,
                                      bool accumulate) {
   constexpr uint32_t idesc = instr_desc(M, N, FMT, A_MN, B_MN);
+  const uint64_t a0 = smem_desc(a_tile, A_MN ? a_rows * 128 : 16, 1024);
+  const uint64_t b0 = smem_desc(b_tile, B_MN ? b_rows * 128 : 16, 1024);
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
-    const uint32_t a_addr = A_MN ? a_tile + ks * 2048 : a_tile + (ks >> 2) * a_rows * 128 + (ks & 3) * 32;
-    const uint32_t b_addr = B_MN ? b_tile + ks * 2048 : b_tile + (ks >> 2) * b_rows * 128 + (ks & 3) * 32;
-    const uint64_t ad = smem_desc(a_addr, A_MN ? a_rows * 128 : 16, 1024);
-    const uint64_t bd = smem_desc(b_addr, B_MN ? b_rows * 128 : 16, 1024);
-    mma(d_tmem, ad, bd, idesc, accumulate || ks > 0);
+    const uint32_t a_off = A_MN ? ks * 2048 : (ks >> 2) * a_rows * 128 + (ks & 3) * 32;
+    const uint32_t b_off = B_MN ? ks * 2048 : (ks >> 2) * b_rows * 128 + (ks & 3) * 32;
+    mma(d_tmem, a0 + (a_off >> 4), b0 + (b_off >> 4), idesc, accumulate || ks > 0);
+  }
+}
+
+// D[tmem] (+)= A[tmem, M x 16*KSTEPS packed 16-bit] * B[smem]. A is always "K-major" (its rows are the lanes).
+template <int M, int N, int KSTEPS, bool B_MN, int FMT>
+__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, int b_rows, bool accumulate) {
+  constexpr uint32_t idesc = instr_desc(M, N, FMT, 0, B_MN);
+  const uint64_t b0 = smem_desc(b_tile, B_MN ? b_rows * 128 : 16, 1024);
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const uint32_t b_off = B_MN ? ks * 2048 : (ks >> 2) * b_rows * 128 + (ks & 3) * 32;
+    mma_ts(d_tmem, a_tmem + ks * 8, b0 + (b_off >> 4), idesc, accumulate || ks > 0);
   }
 }
 
@@ -173,6 +197,14 @@ __device__ __forceinline__ void st_32x32b_x32(uint32_t taddr, const float (&v)[3
       "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
       "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
       "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+// 32 lanes x 16 columns (thread = lane): used for packed 16-bit operand rows (32 elements).
+__device__ __forceinline__ void st_32x32b_x16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
 __device__ __forceinline__ void wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
