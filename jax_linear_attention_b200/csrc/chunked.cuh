@@ -103,6 +103,10 @@ __device__ __forceinline__ float decay_ij(const float* Gs, const unsigned char* 
   return (j <= i && runs[j] == runi) ? __expf(Gi - Gs[j]) : 0.f;
 }
 
+// The tcgen05 kernels cover K = V = 128 and keep the residuals h and Vn transposed ([V][K], [V][64]); other head
+// sizes, or JLA_B200_LEGACY=1 (A/B comparison), use the mma.sync kernels with row-major residuals.
+bool use_tc_kernels(const jla_problem& p);  // chunked_api.cu
+
 // ---- launchers (chunked_*.cu) -----------------------------------------------------------------------------
 struct ChunkedCtx {
   jla_problem p;
@@ -116,6 +120,7 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s);                           
 int launch_sg_fwd(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s);
 int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s);
 int l2norm_fwd(const void* x, void* y, int dtype, long rows, int K, cudaStream_t stream);
+int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s);
 int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, bool direct, cudaStream_t s);
 int read_tc_status(int* out);  // non-zero once a bounded tensor-core wait has given up
 

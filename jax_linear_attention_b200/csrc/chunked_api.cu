@@ -1,6 +1,8 @@
 // Orchestration of the chunked path: support predicate, buffer sizes, and the kernel sequences of the forward
 // (tables -> gates -> [L2 norm] -> T0 -> fused forward) and the backward (reverse state pass -> chunk gradients
 // -> key-gradient epilogue).
+#include <stdlib.h>
+
 #include "chunked.cuh"
 
 namespace jla {
@@ -10,6 +12,14 @@ const char* chunked_unsupported(const jla_problem& p) {
   if (p.kind == JLA_KIND_KDA) return "KDA has no chunked kernel yet: pass precision='highest' (recurrent path)";
   if ((p.K != 64 && p.K != 128) || (p.V != 64 && p.V != 128)) return "head dims K, V must be in (64, 128)";
   return nullptr;
+}
+
+bool use_tc_kernels(const jla_problem& p) {
+  static const bool legacy = [] {
+    const char* e = getenv("JLA_B200_LEGACY");
+    return e && e[0] == '1';
+  }();
+  return !legacy && p.K == 128 && p.V == 128 && p.dtype != JLA_DTYPE_F32;
 }
 
 size_t chunked_residual_bytes(const jla_problem& p) { return make_plan(p).residual_bytes; }
@@ -52,7 +62,7 @@ int chunked_fwd(const jla_problem& p, const jla_fwd_io& io, cudaStream_t stream)
   const ChunkedCtx c = make_ctx(p, res);
   int rc = launch_prep(c, stream);
   if (rc != JLA_OK) return rc;
-  return launch_sg_fwd(c, io, stream);
+  return use_tc_kernels(p) ? launch_sg_fwd_tc(c, io, stream) : launch_sg_fwd(c, io, stream);
 }
 
 int chunked_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t stream) {

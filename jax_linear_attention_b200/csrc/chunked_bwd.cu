@@ -646,11 +646,7 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
   bp.Hk = p.Hk;
   bp.scale = p.scale;
   const int rb = pl.rows * p.H, cb = pl.nc * p.H;
-  // JLA_B200_LEGACY_GRADS=1 keeps the mma.sync chunk-gradient kernel (for A/B comparison); default: tcgen05.
-  static const bool legacy = [] {
-    const char* e = getenv("JLA_B200_LEGACY_GRADS");
-    return e && e[0] == '1';
-  }();
+  const bool legacy = !use_tc_kernels(p);  // mma.sync chunk gradients (row-major residuals)
   int rc;
   if (p.dtype == JLA_DTYPE_BF16) {
     rc = pl.delta ? launch_kv<__nv_bfloat16, true>(bp, p.K, p.V, rb, cb, legacy, s)

@@ -147,7 +147,7 @@ __device__ __forceinline__ void row_dots_swz(const float (&x)[NT][4], const unsi
   d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
 }
 
-template <typename T, int K, int V, bool DELTA>
+template <typename T, int K, int V, bool DELTA, bool TR>
 __global__ void __launch_bounds__(512, 1)
 sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p) {
   using L = GradTcSmem<K, V, DELTA>;
@@ -203,7 +203,8 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
     bytes = 64 * V * 2 + 64 * K * 2 + (DELTA ? 64 * V * 2 : 0);
     tma::expect_tx(bars + 9, bytes);
     tma::load_tile<64, V>(doS, &maps.d_o, 0, h, m.tok0, bars + 9);
-    if (DELTA) tma::load_tile<64, V>(vnS, &maps.vn, 0, 0, ch_off * 64, bars + 9);
+    if (DELTA && !TR) tma::load_tile<64, V>(vnS, &maps.vn, 0, 0, ch_off * 64, bars + 9);
+    if (DELTA && TR) tma::load_tile<V, 64>(vnS, &maps.vn, 0, 0, ch_off * V, bars + 9);
     tma::load_tile<64, K>(qS, &maps.q, 0, hk, m.tok0, bars + 9);
   }
   if (warp == 1) umma::tmem_alloc(tmem_slot, 512);
@@ -242,7 +243,8 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
 
   // ---- batch 1: T1 = K S (for W) -------------------------------------------------------------------------
   if (DELTA && tid == 0 && ok) {
-    umma::gemm<64, V, K / 16, false, true, FMT>(tmem + cT1, aK, 64, aS, K, false);
+    if (TR) umma::gemm<64, V, K / 16, false, false, FMT>(tmem + cT1, aK, 64, aS, V, false);
+    else umma::gemm<64, V, K / 16, false, true, FMT>(tmem + cT1, aK, 64, aS, K, false);
     umma::commit(bars + 0);
   }
   __syncwarp();
@@ -259,9 +261,11 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
   umma::fence_after_sync();
   // ---- batch 2: P1 = dO Vn^T, P2 = Q K^T, accQ = dO S^T ------------------------------------------------------
   if (tid == 0 && ok) {
-    umma::gemm<64, 64, V / 16, false, false, FMT>(tmem + cP1, aDo, 64, aVn, 64, false);
+    if (TR && DELTA) umma::gemm<64, 64, V / 16, false, true, FMT>(tmem + cP1, aDo, 64, aVn, V, false);
+    else umma::gemm<64, 64, V / 16, false, false, FMT>(tmem + cP1, aDo, 64, aVn, 64, false);
     umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP2, aQ, 64, aK, 64, false);
-    umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cQ, aDo, 64, aS, K, false);
+    if (TR) umma::gemm<64, K, V / 16, false, true, FMT>(tmem + cQ, aDo, 64, aS, V, false);
+    else umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cQ, aDo, 64, aS, K, false);
     umma::commit(bars + 1);
   }
   __syncwarp();
@@ -500,19 +504,30 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
     if (DELTA) {
       umma::gemm<64, K, 4, false, true, FMT>(tmem + cK, aXb, 64, aK, 64, true);
       umma::gemm<64, K, 4, true, true, FMT>(tmem + cK, aXb, 64, aK, 64, true);
-      umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cT1, aV, 64, aS, K, false);
+      if (TR) umma::gemm<64, K, V / 16, false, true, FMT>(tmem + cT1, aV, 64, aS, V, false);
+      else umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cT1, aV, 64, aS, K, false);
     }
-    umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cQ, aVn, 64, adS, K, false);
+    if (TR && DELTA) umma::gemm<64, K, V / 16, true, false, FMT>(tmem + cQ, aVn, V, adS, K, false);
+    else umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cQ, aVn, 64, adS, K, false);
     umma::commit(bars + 6);
   }
   __syncwarp();
   {  // keep gamma <S, dS+> while the products run (both tiles share one layout)
     float part = 0.f;
-    const uint32_t* a = reinterpret_cast<const uint32_t*>(SS);
-    const uint32_t* b = reinterpret_cast<const uint32_t*>(dSS);
-    for (int idx = tid; idx < K * V / 2; idx += 512) {
-      const float2 x = unpack2<T>(a[idx]), y = unpack2<T>(b[idx]);
-      part += x.x * y.x + x.y * y.y;
+    if (TR) {  // S is stored transposed ([V][K]), dS+ row-major ([K][V])
+      const T* a = reinterpret_cast<const T*>(SS);
+      const T* b = reinterpret_cast<const T*>(dSS);
+      for (int idx = tid; idx < K * V; idx += 512) {
+        const int kk = idx / V, vv = idx - kk * V;
+        part += to_f32(a[swz_tile(V, vv, kk)]) * to_f32(b[swz_tile(K, kk, vv)]);
+      }
+    } else {
+      const uint32_t* a = reinterpret_cast<const uint32_t*>(SS);
+      const uint32_t* b = reinterpret_cast<const uint32_t*>(dSS);
+      for (int idx = tid; idx < K * V / 2; idx += 512) {
+        const float2 x = unpack2<T>(a[idx]), y = unpack2<T>(b[idx]);
+        part += x.x * y.x + x.y * y.y;
+      }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
@@ -597,9 +612,9 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
   }
 }
 
-template <typename T, int K, int V, bool DELTA>
+template <typename T, int K, int V, bool DELTA, bool TR = false>
 int launch_one(const GradTcMaps& maps, const GradTcParams& gp, int blocks, cudaStream_t s) {
-  auto* kern = sg_chunk_grads_tc_kernel<T, K, V, DELTA>;
+  auto* kern = sg_chunk_grads_tc_kernel<T, K, V, DELTA, TR>;
   constexpr int smem = GradTcSmem<K, V, DELTA>::kBytes;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   {
@@ -611,8 +626,8 @@ int launch_one(const GradTcMaps& maps, const GradTcParams& gp, int blocks, cudaS
 }
 
 template <typename T, bool DELTA>
-int launch_kv(const GradTcMaps& maps, const GradTcParams& gp, int K, int V, int blocks, cudaStream_t s) {
-  if (K == 128 && V == 128) return launch_one<T, 128, 128, DELTA>(maps, gp, blocks, s);
+int launch_kv(const GradTcMaps& maps, const GradTcParams& gp, int K, int V, int blocks, bool tr, cudaStream_t s) {
+  if (K == 128 && V == 128) return tr ? launch_one<T, 128, 128, DELTA, true>(maps, gp, blocks, s) : launch_one<T, 128, 128, DELTA>(maps, gp, blocks, s);
   if (K == 128 && V == 64) return launch_one<T, 128, 64, DELTA>(maps, gp, blocks, s);
   if (K == 64 && V == 128) return launch_one<T, 64, 128, DELTA>(maps, gp, blocks, s);
   return launch_one<T, 64, 64, DELTA>(maps, gp, blocks, s);
@@ -632,7 +647,9 @@ int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scrat
             tma::encode_3d(&maps.h, c.res + pl.h, p.V, 1, slots * p.K, p.K) &&
             tma::encode_3d(&maps.dh, scratch + pl.dh, p.V, 1, slots * p.K, p.K);
   if (ok && pl.delta) {
-    ok = tma::encode_3d(&maps.vn, c.res + pl.vn, p.V, 1, slots * 64, 64) &&
+    const bool trv = use_tc_kernels(p);
+    ok = (trv ? tma::encode_3d(&maps.vn, c.res + pl.vn, 64, 1, slots * p.V, p.V)
+              : tma::encode_3d(&maps.vn, c.res + pl.vn, p.V, 1, slots * 64, 64)) &&
          tma::encode_3d(&maps.dvn, scratch + pl.dvn, p.V, 1, slots * 64, 64) &&
          tma::encode_3d(&maps.t0, c.res + pl.t0, 64, 1, slots * 64, 64);
   } else if (ok) {
@@ -655,12 +672,23 @@ int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scrat
   gp.Hk = p.Hk;
   gp.scale = p.scale;
   const int blocks = pl.nc * p.H;
+  const bool tr = use_tc_kernels(p);
   if (p.dtype == JLA_DTYPE_BF16) {
-    return pl.delta ? launch_kv<__nv_bfloat16, true>(maps, gp, p.K, p.V, blocks, s)
-                    : launch_kv<__nv_bfloat16, false>(maps, gp, p.K, p.V, blocks, s);
+    return pl.delta ? launch_kv<__nv_bfloat16, true>(maps, gp, p.K, p.V, blocks, tr, s)
+                    : launch_kv<__nv_bfloat16, false>(maps, gp, p.K, p.V, blocks, tr, s);
   }
-  return pl.delta ? launch_kv<__half, true>(maps, gp, p.K, p.V, blocks, s)
-                  : launch_kv<__half, false>(maps, gp, p.K, p.V, blocks, s);
+  return pl.delta ? launch_kv<__half, true>(maps, gp, p.K, p.V, blocks, tr, s)
+                  : launch_kv<__half, false>(maps, gp, p.K, p.V, blocks, tr, s);
+}
+
+int* tc_status_ptr() {
+  static int* ptr = nullptr;
+  if (!ptr) {
+    void* q = nullptr;
+    if (cudaGetSymbolAddress(&q, g_tc_status) != cudaSuccess) return nullptr;
+    ptr = static_cast<int*>(q);
+  }
+  return ptr;
 }
 
 int read_tc_trace(unsigned long long* out) {

@@ -189,10 +189,23 @@ class ChunkedLayout:
     def t0(self):
         return self.chunked(self._view(self.res, self.lay.t0, (self.nc, self.p.H, 64, 64), self.dtype))
 
+    @property
+    def transposed(self):
+        """K = V = 128 runs the tcgen05 kernels, which keep h and Vn transposed ([V][K], [V][64])."""
+        import os
+
+        return self.p.K == 128 and self.p.V == 128 and os.environ.get("JLA_B200_LEGACY", "0") != "1"
+
     def h(self):
+        if self.transposed:
+            x = self._view(self.res, self.lay.h, (self.nc, self.p.H, self.p.V, self.p.K), self.dtype)
+            return self.chunked(x.transpose(-1, -2))
         return self.chunked(self._view(self.res, self.lay.h, (self.nc, self.p.H, self.p.K, self.p.V), self.dtype))
 
     def vn(self):
+        if self.transposed:
+            x = self._view(self.res, self.lay.vn, (self.nc, self.p.H, self.p.V, 64), self.dtype)
+            return self.chunked(x.transpose(-1, -2))
         return self.chunked(self._view(self.res, self.lay.vn, (self.nc, self.p.H, 64, self.p.V), self.dtype))
 
     def dh(self):
