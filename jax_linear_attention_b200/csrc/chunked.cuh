@@ -25,7 +25,7 @@ struct ChunkMeta {
 struct Plan {
   int rows, nc;       // rows; chunk slots (upper bound on the number of chunks)
   bool delta, l2norm, save;
-  size_t meta, row_chunks, gates, runs, t0, qn, kn, h, vn, residual_bytes;  // residual buffer
+  size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, residual_bytes;  // residual buffer
   size_t fwd_scratch_bytes;                                                 // same layout without h, vn
   size_t dh, dvn, dq_acc, dk_acc, bwd_scratch_bytes;                        // backward scratch
 };
@@ -55,6 +55,7 @@ inline Plan make_plan(const jla_problem& p) {
   pl.gates = off((size_t)pl.nc * p.H * 128 * sizeof(float));  // per (chunk, head): G[64] then beta[64]
   pl.runs = off((size_t)pl.nc * 64);
   pl.t0 = off(pl.delta ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
+  pl.ag = off(pl.delta ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);  // Ag = T0 * D * beta_j (gated), for the forward
   pl.qn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
   pl.kn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
   pl.fwd_scratch_bytes = align_up(c.off);

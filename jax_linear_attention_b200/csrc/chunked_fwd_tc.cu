@@ -29,7 +29,7 @@ constexpr int K = 128, V = 128;
 constexpr int NS = 3;  // stages of the input ring
 
 struct FwdTcMaps {
-  CUtensorMap q, k, v, t0;
+  CUtensorMap q, k, v, ag;
 };
 
 struct FwdTcParams {
@@ -54,13 +54,13 @@ struct Smem {
   static constexpr int kGates = kAgb + 2 * 8192;         // per stage: G[64], beta[64] f32 (512 B) + runs (64 B) + meta (16 B)
   static constexpr int kGateStride = 640;
   static constexpr int kScal = kGates + NS * kGateStride;  // per stage and warp: gam[64], gamr[64] (state group); gam[64] (score group)
-  static constexpr int kBars = kScal + NS * 3072;
+  static constexpr int kBars = kScal + NS * 4096;
   static constexpr int kNumBars = 2 * NS + 16;
   static constexpr int kBytes = kBars + kNumBars * 8 + 64 + 1024;
 };
 
 enum {  // mbarrier indices after the 2 * NS full / empty barriers
-  B_PDONE = 2 * NS, B_PFREE, B_PA0, B_PA1, B_ST, B_M1, B_W, B_M2, B_VN, B_M3, B_ODONE, B_OFREE
+  B_PDONE = 2 * NS, B_PFREE, B_PA0, B_PA1, B_ST, B_M1, B_W, B_M2, B_VN, B_M3, B_ODONE, B_OFREE0, B_OFREE1
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -100,7 +100,7 @@ __device__ __forceinline__ void ld_row32(float (&v)[32], uint32_t taddr) {
 }
 
 template <typename T, bool DELTA>
-__global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant__ FwdTcMaps maps, FwdTcParams p) {
+__global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant__ FwdTcMaps maps, FwdTcParams p) {
   constexpr int FMT = umma::Fmt<T>::value;
   const int row = blockIdx.x / p.H, h = blockIdx.x - row * p.H;
   const int hk = h / (p.H / p.Hk);
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
   auto st_G = [&](int s) { return reinterpret_cast<float*>(base + Smem::kGates + s * Smem::kGateStride); };
   auto st_runs = [&](int s) { return reinterpret_cast<unsigned char*>(st_G(s) + 128); };
   auto st_meta = [&](int s) { return reinterpret_cast<volatile int*>(st_runs(s) + 64); };
-  auto st_gam = [&](int s) { return reinterpret_cast<float*>(base + Smem::kScal + s * 3072); };
+  auto st_gam = [&](int s) { return reinterpret_cast<float*>(base + Smem::kScal + s * 4096); };
   unsigned char* Pb = base + Smem::kPb;
   unsigned char* Agb = base + Smem::kAgb;
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + Smem::kBars);
@@ -127,20 +127,21 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       umma::mbar_init(bars + s, 1);                  // full: the producer's expect_tx arrival (+ bytes)
-      umma::mbar_init(bars + NS + s, 1 + 4 + 4);     // empty: MMA commit + the warps of both groups
+      umma::mbar_init(bars + NS + s, 1 + 8 + 8);     // empty: MMA commit + the warps of both groups
     }
     umma::mbar_init(bars + B_PDONE, 1);
-    umma::mbar_init(bars + B_PFREE, 4);
-    umma::mbar_init(bars + B_PA0, 4);
-    umma::mbar_init(bars + B_PA1, 4);
-    umma::mbar_init(bars + B_ST, 4);
+    umma::mbar_init(bars + B_PFREE, 8);
+    umma::mbar_init(bars + B_PA0, 8);
+    umma::mbar_init(bars + B_PA1, 8);
+    umma::mbar_init(bars + B_ST, 8);
     umma::mbar_init(bars + B_M1, 1);
-    umma::mbar_init(bars + B_W, 4);
+    umma::mbar_init(bars + B_W, 8);
     umma::mbar_init(bars + B_M2, 1);
-    umma::mbar_init(bars + B_VN, 4);
+    umma::mbar_init(bars + B_VN, 8);
     umma::mbar_init(bars + B_M3, 1);
     umma::mbar_init(bars + B_ODONE, 1);
-    umma::mbar_init(bars + B_OFREE, 4);
+    umma::mbar_init(bars + B_OFREE0, 8);
+    umma::mbar_init(bars + B_OFREE1, 8);
     umma::mbar_init_fence();
     *abort_flag = 0;
   }
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  constexpr uint32_t cS = 0, cSb = 128, cA1 = 192, cWb = 256, cVg = 288, cO1 = 320, cO2 = 384, cP = 448;
+  constexpr uint32_t cS = 0, cSb = 128, cA1 = 192, cWb = 256, cVg = 288, cO = 320 /* two 64-column buffers */, cP = 448;
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------ TMA producer
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
         tma::load_tile<64, K>(st_k(s), &maps.k, 0, hk, m.tok0, bars + s);
         tma::load_tile<64, K>(st_q(s), &maps.q, 0, hk, m.tok0, bars + s);
         tma::load_tile<64, V>(st_v(s), &maps.v, 0, h, m.tok0, bars + s);
-        if (DELTA) tma::load_tile<64, 64>(st_t0(s), &maps.t0, 0, 0, (c * p.H + h) * 64, bars + s);
+        if (DELTA) tma::load_tile<64, 64>(st_t0(s), &maps.ag, 0, 0, (c * p.H + h) * 64, bars + s);
         bulk_copy(st_G(s), p.gates + ((long)c * p.H + h) * 128, 512, bars + s);
         bulk_copy(st_runs(s), p.runs + (long)c * 64, 64, bars + s);
       }
@@ -175,42 +176,53 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
   } else if (warp == 1) {
     // -------------------------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      for (int it = 0; it < n; ++it) {
+      auto issue_p = [&](int it) {  // Q K^T of chunk `it` (its inputs are prefetched): runs one chunk ahead of the chain
+        const int s = it % NS;
+        if (!wait(bars + s, (it / NS) & 1, abort_flag)) return false;
+        if (!wait(bars + B_PFREE, (it & 1) ^ 1, abort_flag)) return false;
+        umma::fence_after_sync();
+        umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP, umma::smem_addr(st_q(s)), 64, umma::smem_addr(st_k(s)), 64,
+                                                      false);
+        umma::commit(bars + B_PDONE);
+        return true;
+      };
+      bool okm = n > 0 ? issue_p(0) : true;
+      for (int it = 0; it < n && okm; ++it) {
         const int s = it % NS;
         const uint32_t ph = it & 1;
         const uint32_t aq = umma::smem_addr(st_q(s)), ak = umma::smem_addr(st_k(s));
-        if (!wait(bars + s, (it / NS) & 1, abort_flag)) break;
-        if (!wait(bars + B_PFREE, ph ^ 1, abort_flag)) break;
-        umma::fence_after_sync();
-        umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP, aq, 64, ak, 64, false);  // Q K^T
-        umma::commit(bars + B_PDONE);
         if (!wait(bars + B_ST, ph, abort_flag)) break;
-        if (!wait(bars + B_OFREE, ph ^ 1, abort_flag)) break;
         umma::fence_after_sync();
-        if (DELTA) umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, ak, 64, false);  // S^T K^T
-        umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cO1, tmem + cSb, aq, 64, false);             // S^T Q^T
-        umma::commit(bars + B_M1);
+        if (DELTA) {
+          umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, ak, 64, false);  // S^T K^T
+          umma::commit(bars + B_M1);
+        }
+        if (it + 1 < n && !issue_p(it + 1)) break;
+        // q has been scaled by (cin Gamma)_i in place by the score group (part of "PA ready")
         if (!wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
+        if (!wait(bars + B_OFREE0 + (it & 1), ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        umma::fence_after_sync();
+        const uint32_t co = cO + (it & 1) * 64;
+        umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + co, tmem + cSb, aq, 64, false);  // S^T ((cin Gamma) Q)^T
         if (DELTA) {
           if (!wait(bars + B_W, ph, abort_flag)) break;
           umma::fence_after_sync();
-          umma::gemm_ts<128, 64, 4, false, FMT>(tmem + cA1, tmem + cWb, umma::smem_addr(Agb + (it & 1) * 8192), 64,
-                                                false);  // W^T Ag^T
+          umma::gemm_ts<128, 64, 4, false, FMT>(tmem + cA1, tmem + cWb, umma::smem_addr(st_t0(s)), 64, false);  // W^T Ag^T
           umma::commit(bars + B_M2);
         }
         if (!wait(bars + B_VN, ph, abort_flag)) break;
         umma::fence_after_sync();
         umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cVg, ak, 64, true);  // S^T += (Gamma_r Vn)^T K
         umma::commit(bars + B_M3);
-        umma::gemm_ts<128, 64, 4, false, FMT>(tmem + cO2, tmem + cWb, umma::smem_addr(Pb + (it & 1) * 8192), 64,
-                                              false);  // Vn^T P^T
+        umma::gemm_ts<128, 64, 4, false, FMT>(tmem + co, tmem + cWb, umma::smem_addr(Pb + (it & 1) * 8192), 64,
+                                              true);  // += Vn^T P^T
         umma::commit(bars + B_ODONE);
         umma::commit(bars + NS + s);
       }
     }
-  } else if (warp >= 4 && warp < 8) {
-    // ------------------------------------------------------------------------------- state group (thread = row v)
-    const int q4 = warp - 4, v = 32 * q4 + lane;
+  } else if (warp >= 4 && warp < 12) {
+    // ------------------------------------------------- state group: thread = value row v, warp pair = column halves
+    const int q4 = warp & 3, half = (warp - 4) >> 2, v = 32 * q4 + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     bool ok = true;
     for (int it = 0; it < n && ok; ++it) {
@@ -221,7 +233,7 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
       const float* Gs = st_G(s);
       const unsigned char* runs = st_runs(s);
       const int len = st_meta(s)[1], flags = st_meta(s)[2];
-      float* gam = st_gam(s) + q4 * 128;  // this warp's own copy: no cross-warp barrier on the serial chain
+      float* gam = st_gam(s) + (warp - 4) * 128;  // this warp's own copy: no cross-warp barrier on the serial chain
       float* gamr = gam + 64;
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) {
@@ -238,9 +250,10 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
         if (!ok) break;
         umma::fence_after_sync();
       }
-      T* hT = p.hT_out ? static_cast<T*>(p.hT_out) + (((long)c * p.H + h) * V + v) * K : nullptr;
+      uint32_t hpk[32];  // the 16-bit copy of this half row, stored as a residual once the chain is released
 #pragma unroll
-      for (int blk = 0; blk < 4; ++blk) {
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int blk = 2 * half + b2;
         float x[32];
         if (it == 0) {
           const float* h0 = p.h0 ? p.h0 + ((long)row * p.H + h) * K * V : nullptr;
@@ -251,14 +264,11 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
         }
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(x[2 * i], x[2 * i + 1]);
-        umma::st_32x32b_x16(tl + cSb + blk * 16, pk);
-        if (hT) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            *reinterpret_cast<uint4*>(hT + blk * 32 + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-          }
+        for (int i = 0; i < 16; ++i) {
+          pk[i] = pack2<T>(x[2 * i], x[2 * i + 1]);
+          hpk[b2 * 16 + i] = pk[i];
         }
+        umma::st_32x32b_x16(tl + cSb + blk * 16, pk);
 #pragma unroll
         for (int i = 0; i < 32; ++i) x[i] *= kg;
         umma::st_32x32b_x32(tl + cS + blk * 32, x);
@@ -267,26 +277,33 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
       umma::fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + B_ST);
+      if (p.hT_out) {
+        T* hT = static_cast<T*>(p.hT_out) + (((long)c * p.H + h) * V + v) * K + 64 * half;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          *reinterpret_cast<uint4*>(hT + i * 8) = make_uint4(hpk[4 * i], hpk[4 * i + 1], hpk[4 * i + 2], hpk[4 * i + 3]);
+        }
+      }
 
       const T* vs = reinterpret_cast<const T*>(st_v(s));
+      const int j0 = 32 * half;  // this warp's 32 tokens (columns of the [V x 64] accumulators)
       if (DELTA) {
         // ---- W^T = V^T - (cin Gamma)_j (S^T K^T)
         ok = wait(bars + B_M1, ph, abort_flag);
         if (!ok) break;
         umma::fence_after_sync();
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
+        {
           float x[32];
-          ld_row32<T>(x, tl + cA1 + blk * 32);
+          ld_row32<T>(x, tl + cA1 + j0);
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int j = blk * 32 + 2 * i;
+            const int j = j0 + 2 * i;
             const float w0 = to_f32(vs[swz_tile(64, j, v)]) - gam[j] * x[2 * i];
             const float w1 = to_f32(vs[swz_tile(64, j + 1, v)]) - gam[j + 1] * x[2 * i + 1];
             pk[i] = pack2<T>(w0, w1);
           }
-          umma::st_32x32b_x16(tl + cWb + blk * 16, pk);
+          umma::st_32x32b_x16(tl + cWb + 16 * half, pk);
         }
         umma::wait_st();
         umma::fence_before_sync();
@@ -296,24 +313,30 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
         ok = wait(bars + B_M2, ph, abort_flag);
         if (!ok) break;
         umma::fence_after_sync();
-        T* vnT = p.vnT_out ? static_cast<T*>(p.vnT_out) + (((long)c * p.H + h) * V + v) * 64 : nullptr;
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
+        {
           float x[32];
-          ld_row32<T>(x, tl + cA1 + blk * 32);
+          ld_row32<T>(x, tl + cA1 + j0);
           uint32_t pk[16], pg[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int j = blk * 32 + 2 * i;
+            const int j = j0 + 2 * i;
             pk[i] = pack2<T>(x[2 * i], x[2 * i + 1]);
             pg[i] = pack2<T>(x[2 * i] * gamr[j], x[2 * i + 1] * gamr[j + 1]);
           }
-          umma::st_32x32b_x16(tl + cWb + blk * 16, pk);
-          umma::st_32x32b_x16(tl + cVg + blk * 16, pg);
-          if (vnT) {
+          umma::st_32x32b_x16(tl + cWb + 16 * half, pk);
+          umma::st_32x32b_x16(tl + cVg + 16 * half, pg);
+          umma::wait_st();
+          umma::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(bars + B_VN);
+            mbar_arrive(bars + NS + s);  // done with this stage's v and gate vectors
+          }
+          if (p.vnT_out) {
+            T* vnT = static_cast<T*>(p.vnT_out) + (((long)c * p.H + h) * V + v) * 64 + j0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              *reinterpret_cast<uint4*>(vnT + blk * 32 + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+              *reinterpret_cast<uint4*>(vnT + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
             }
           }
         }
@@ -324,26 +347,23 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
           if (!ok) break;
           umma::fence_after_sync();
         }
+        uint32_t pk[16], pg[16];
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-          uint32_t pk[16], pg[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int j = blk * 32 + 2 * i;
-            const float a = to_f32(vs[swz_tile(64, j, v)]), b = to_f32(vs[swz_tile(64, j + 1, v)]);
-            pk[i] = pack2<T>(a, b);
-            pg[i] = pack2<T>(a * gamr[j], b * gamr[j + 1]);
-          }
-          umma::st_32x32b_x16(tl + cWb + blk * 16, pk);
-          umma::st_32x32b_x16(tl + cVg + blk * 16, pg);
+        for (int i = 0; i < 16; ++i) {
+          const int j = j0 + 2 * i;
+          const float a = to_f32(vs[swz_tile(64, j, v)]), b = to_f32(vs[swz_tile(64, j + 1, v)]);
+          pk[i] = pack2<T>(a, b);
+          pg[i] = pack2<T>(a * gamr[j], b * gamr[j + 1]);
         }
-      }
-      umma::wait_st();
-      umma::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bars + B_VN);
-        mbar_arrive(bars + NS + s);  // done with this stage's v and gate vectors
+        umma::st_32x32b_x16(tl + cWb + 16 * half, pk);
+        umma::st_32x32b_x16(tl + cVg + 16 * half, pg);
+        umma::wait_st();
+        umma::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bars + B_VN);
+          mbar_arrive(bars + NS + s);
+        }
       }
     }
     // ---- final state
@@ -352,7 +372,8 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
     if (ok && p.final_state) {
       float* f = p.final_state + ((long)row * p.H + h) * K * V;
 #pragma unroll
-      for (int blk = 0; blk < 4; ++blk) {
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int blk = 2 * half + b2;
         float x[32];
         if (n == 0) {
           const float* h0 = p.h0 ? p.h0 + ((long)row * p.H + h) * K * V : nullptr;
@@ -365,22 +386,22 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
         for (int i = 0; i < 32; ++i) f[(long)(blk * 32 + i) * V + v] = x[i];
       }
     }
-  } else if (warp >= 8) {
-    // ------------------------------------------------------------- score group: P, Ag one chunk ahead; outputs
-    const int q4 = warp - 8, g = lane >> 2, t = lane & 3;
+  } else if (warp >= 12) {
+    // ---------------------------------- score group: P and the scaled q one chunk ahead; outputs. Warp pairs split
+    // the 64 columns (tokens j for P, tokens i for the outputs) in halves.
+    const int q4 = warp & 3, half = (warp - 12) >> 2, g = lane >> 2, t = lane & 3;
     const int r0 = 16 * q4, v = 32 * q4 + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     bool ok = true;
-    auto build = [&](int it) {  // P = (Q K^T) D and Ag = T0 D beta_j of chunk `it`, rows r0 .. r0 + 15
+    auto build = [&](int it) {  // P = (Q K^T) D of chunk `it`: rows r0 .. r0 + 15, columns 32 half .. + 31
       const int s = it % NS, buf = it & 1;
       if (!wait(bars + s, (it / NS) & 1, abort_flag)) return false;
       const float* Gs = st_G(s);
-      const float* betas = Gs + 64;
       const unsigned char* runs = st_runs(s);
       if (!wait(bars + B_PDONE, it & 1, abort_flag)) return false;
       umma::fence_after_sync();
-      float acc[8][4];
-      umma::ld_16x256b<8>(acc, tl + cP);
+      float acc[4][4];
+      umma::ld_16x256b<4>(acc, tl + cP + 32 * half);
       umma::wait_ld();
       umma::fence_before_sync();
       __syncwarp();
@@ -389,21 +410,30 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
       const float G0 = Gs[i0], G1 = Gs[i1];
       const int run0 = runs[i0], run1 = runs[i1];
       T* pt = reinterpret_cast<T*>(Pb + buf * 8192);
-      T* at = reinterpret_cast<T*>(Agb + buf * 8192);
-      const T* t0t = reinterpret_cast<const T*>(st_t0(s));
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int j = nt * 8 + 2 * t;
+      for (int nt = 0; nt < 4; ++nt) {
+        const int j = 32 * half + nt * 8 + 2 * t;
         const float d00 = decay_ij(Gs, runs, i0, j, G0, run0), d01 = decay_ij(Gs, runs, i0, j + 1, G0, run0);
         const float d10 = decay_ij(Gs, runs, i1, j, G1, run1), d11 = decay_ij(Gs, runs, i1, j + 1, G1, run1);
         *reinterpret_cast<uint32_t*>(pt + swz_tile(64, i0, j)) = pack2<T>(acc[nt][0] * d00, acc[nt][1] * d01);
         *reinterpret_cast<uint32_t*>(pt + swz_tile(64, i1, j)) = pack2<T>(acc[nt][2] * d10, acc[nt][3] * d11);
-        if (DELTA) {
-          const float2 ta = unpack2<T>(*reinterpret_cast<const uint32_t*>(t0t + swz_tile(64, i0, j)));
-          const float2 tb = unpack2<T>(*reinterpret_cast<const uint32_t*>(t0t + swz_tile(64, i1, j)));
-          const float b0 = betas[j], b1 = betas[j + 1];
-          *reinterpret_cast<uint32_t*>(at + swz_tile(64, i0, j)) = pack2<T>(ta.x * d00 * b0, ta.y * d01 * b1);
-          *reinterpret_cast<uint32_t*>(at + swz_tile(64, i1, j)) = pack2<T>(tb.x * d10 * b0, tb.y * d11 * b1);
+      }
+      {  // q <- (cin Gamma)_i q in place (Q K^T has been read): the S^T Q^T product then needs no column scaling
+        const int flags = st_meta(s)[2];
+        const int tg = (warp - 12) * 32 + lane, i = tg >> 2, quarter = tg & 3;
+        const float cgi = row_scalars(Gs, runs, flags, i).gam;
+        T* qt = reinterpret_cast<T*>(st_q(s));
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4* ptr = reinterpret_cast<uint4*>(qt + swz_tile(64, i, quarter * 32 + ch * 8));
+          uint4 x = *ptr;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack2<T>(w[e]);
+            w[e] = pack2<T>(f.x * cgi, f.y * cgi);
+          }
+          *ptr = x;
         }
       }
       umma::fence_async_smem();
@@ -418,37 +448,35 @@ __global__ void __launch_bounds__(384, 1) sg_fwd_tc_kernel(const __grid_constant
         ok = build(it + 1);
         if (!ok) break;
       }
-      // ---- O^T = scale [(cin Gamma)_i (S^T Q^T) + Vn^T P^T], thread = value row v
+      // ---- O^T = scale [S^T ((cin Gamma) Q)^T + Vn^T P^T], thread = value row v, 32 tokens per warp
       ok = wait(bars + B_ODONE, it & 1, abort_flag);
       if (!ok) break;
       umma::fence_after_sync();
-      const float* Gs = st_G(s);
-      const unsigned char* runs = st_runs(s);
-      const int tok0 = st_meta(s)[0], len = st_meta(s)[1], flags = st_meta(s)[2];
-      T* o = static_cast<T*>(p.o) + ((long)tok0 * p.H + h) * V + v;
-      float* gamP = st_gam(s) + 512 + q4 * 64;
-      gamP[lane] = row_scalars(Gs, runs, flags, lane).gam;
-      gamP[lane + 32] = row_scalars(Gs, runs, flags, lane + 32).gam;
-      __syncwarp();
-#pragma unroll
-      for (int blk = 0; blk < 2; ++blk) {
-        float a[32], b[32];
-        umma::ld_32x32b_x32(a, tl + cO1 + blk * 32);
-        umma::ld_32x32b_x32(b, tl + cO2 + blk * 32);
+      const int tok0 = st_meta(s)[0], len = st_meta(s)[1];
+      // Free the accumulator, then transpose through this warp's slice of the (dead) q tile so that the global
+      // stores are 16-byte vectors along the value axis.
+      T* stg = reinterpret_cast<T*>(st_q(s)) + (warp - 12) * 32 * 32;  // [32 tokens][32 value columns]
+      {
+        float a[32];
+        umma::ld_32x32b_x32(a, tl + cO + (it & 1) * 64 + 32 * half);
         umma::wait_ld();
-        if (blk == 1) {
-          umma::fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bars + B_OFREE);
-        }
+        umma::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + B_OFREE0 + (it & 1));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int tok = blk * 32 + i;
-          if (tok < len) o[(long)tok * p.H * V] = from_f32<T>(p.scale * (gamP[tok] * a[i] + b[i]));
+        for (int i = 0; i < 32; ++i) stg[i * 32 + lane] = from_f32<T>(p.scale * a[i]);
+      }
+      __syncwarp();
+      T* o = static_cast<T*>(p.o) + ((long)(tok0 + 32 * half) * p.H + h) * V + 32 * q4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = lane + 32 * i, tok = idx >> 2, part = idx & 3;
+        if (32 * half + tok < len) {
+          *reinterpret_cast<uint4*>(o + (long)tok * p.H * V + part * 8) = *reinterpret_cast<const uint4*>(stg + tok * 32 + part * 8);
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + NS + s);  // done with this stage's T0 and gate vectors
+      if (lane == 0) mbar_arrive(bars + NS + s);  // done with this stage's gate vectors and the q tile
     }
   }
   umma::fence_before_sync();
@@ -463,7 +491,7 @@ int launch_one(const FwdTcMaps& maps, const FwdTcParams& fp, int blocks, cudaStr
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
   {
     ProfScope ps(kProfSgFwd, s);
-    kern<<<blocks, 384, Smem::kBytes, s>>>(maps, fp);
+    kern<<<blocks, 640, Smem::kBytes, s>>>(maps, fp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
@@ -482,8 +510,8 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
   FwdTcMaps maps;
   bool ok = tma::encode_3d(&maps.q, c.q_eff, p.K, p.Hk, tokens, 64) && tma::encode_3d(&maps.k, c.k_eff, p.K, p.Hk, tokens, 64) &&
             tma::encode_3d(&maps.v, p.v, p.V, p.H, tokens, 64);
-  if (ok && pl.delta) ok = tma::encode_3d(&maps.t0, c.res + pl.t0, 64, 1, slots * 64, 64);
-  if (ok && !pl.delta) maps.t0 = maps.v;
+  if (ok && pl.delta) ok = tma::encode_3d(&maps.ag, c.res + pl.ag, 64, 1, slots * 64, 64);
+  if (ok && !pl.delta) maps.ag = maps.v;
   if (!ok) return JLA_ERR_CUDA;
   FwdTcParams fp{};
   fp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);

@@ -89,6 +89,7 @@ struct KktParams {
   const float* gates;
   const unsigned char* runs;
   void* t0;
+  void* ag;
   int H, Hk;
 };
 
@@ -109,13 +110,15 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
   float* X = A + 64 * LDA;
   float* M = X + 64 * LDA;        // [32][33]
   float* betas = M + 32 * LDM;    // [64]
-  int* run = reinterpret_cast<int*>(betas + 64);
+  float* Gs = betas + 64;         // [64]
+  int* run = reinterpret_cast<int*>(Gs + 64);
 
   load_tile_async<T, 64, K>(ks, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * K, (long)p.Hk * K,
                             m.len, tid, 128);
   cp_async_commit();
   if (tid < 64) {
     betas[tid] = p.gates[((long)c * p.H + h) * 128 + 64 + tid];
+    Gs[tid] = p.gates[((long)c * p.H + h) * 128 + tid];
     run[tid] = p.runs[(long)c * 64 + tid];
   }
   for (int idx = tid; idx < 64 * LDA; idx += 128) X[idx] = 0.f;
@@ -206,11 +209,28 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
     v.w = pack2<T>(X[r * LDA + c8 + 6], X[r * LDA + c8 + 7]);
     *reinterpret_cast<uint4*>(out + r * 64 + c8) = v;
   }
+  // the gated form Ag_ij = T0_ij exp(G_i - G_j) beta_j (same run, j <= i) that the forward multiplies with
+  T* outg = static_cast<T*>(p.ag) + ((long)c * p.H + h) * 64 * 64;
+  for (int idx = tid; idx < 64 * 8; idx += 128) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    float a[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int j = c8 + e;
+      a[e] = (j <= r && run[j] == run[r]) ? X[r * LDA + j] * __expf(Gs[r] - Gs[j]) * betas[j] : 0.f;
+    }
+    uint4 v;
+    v.x = pack2<T>(a[0], a[1]);
+    v.y = pack2<T>(a[2], a[3]);
+    v.z = pack2<T>(a[4], a[5]);
+    v.w = pack2<T>(a[6], a[7]);
+    *reinterpret_cast<uint4*>(outg + r * 64 + c8) = v;
+  }
 }
 
 template <typename T, int K>
 int launch_kkt(const KktParams& kp, int blocks, cudaStream_t s) {
-  const size_t smem = 64 * (K + 8) * sizeof(T) + (2 * 64 * 65 + 32 * 33 + 64) * sizeof(float) + 64 * sizeof(int);
+  const size_t smem = 64 * (K + 8) * sizeof(T) + (2 * 64 * 65 + 32 * 33 + 128) * sizeof(float) + 64 * sizeof(int);
   auto* kern = kkt_inv_kernel<T, K>;
   if (smem > 48 * 1024) JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
@@ -250,7 +270,7 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
     if (rc != JLA_OK) return rc;
   }
   if (!pl.delta) return JLA_OK;
-  KktParams kp{meta, c.k_eff, gates, runs, c.res + pl.t0, p.H, p.Hk};
+  KktParams kp{meta, c.k_eff, gates, runs, c.res + pl.t0, c.res + pl.ag, p.H, p.Hk};
   const int blocks = pl.nc * p.H;
   if (p.dtype == JLA_DTYPE_BF16) {
     return p.K == 64 ? launch_kkt<__nv_bfloat16, 64>(kp, blocks, s) : launch_kkt<__nv_bfloat16, 128>(kp, blocks, s);

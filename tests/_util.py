@@ -161,7 +161,7 @@ class ChunkedLayout:
 
         class Layout(C.Structure):
             _fields_ = [("num_chunk_slots", C.c_int32)] + [(n, C.c_size_t) for n in (
-                "meta", "row_chunks", "gates", "runs", "t0", "qn", "kn", "h", "vn", "residual_bytes", "dh", "dvn",
+                "meta", "row_chunks", "gates", "runs", "t0", "ag", "qn", "kn", "h", "vn", "residual_bytes", "dh", "dvn",
                 "dq_acc", "dk_acc", "bwd_scratch_bytes")]
 
         lay = Layout()
