@@ -648,7 +648,9 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
   const int rb = pl.rows * p.H, cb = pl.nc * p.H;
   const bool legacy = !use_tc_kernels(p);  // mma.sync chunk gradients (row-major residuals)
   int rc;
-  if (p.dtype == JLA_DTYPE_BF16) {
+  if (!legacy) {
+    rc = launch_sg_bwd_state_tc(c, io, scratch, s);
+  } else if (p.dtype == JLA_DTYPE_BF16) {
     rc = pl.delta ? launch_kv<__nv_bfloat16, true>(bp, p.K, p.V, rb, cb, legacy, s)
                   : launch_kv<__nv_bfloat16, false>(bp, p.K, p.V, rb, cb, legacy, s);
   } else {

@@ -23,8 +23,6 @@
 namespace jla {
 
 __device__ int g_tc_status = 0;  // set to a non-zero code when a bounded wait gave up
-__device__ unsigned long long g_tc_trace[32];  // phase timestamps (ns) of one CTA, for tuning
-#define TC_TRACE(i) do { if (blockIdx.x == 2000 && tid == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_tc_trace[i] = _t; } } while (0)
 
 namespace {
 
@@ -188,8 +186,6 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
                  aVn = umma::smem_addr(vnS), aS = umma::smem_addr(SS), aT0 = umma::smem_addr(t0S),
                  aXa = umma::smem_addr(Xa), aXb = umma::smem_addr(Xb), adS = umma::smem_addr(dSS);
   const int ch_off = c * p.H + h;
-
-  TC_TRACE(0);
   if (tid == 0) {
     for (int i = 0; i < 12; ++i) umma::mbar_init(bars + i, 1);
     umma::mbar_init_fence();
@@ -226,9 +222,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
     const int i = idx >> 6, j = idx & 63;
     Dm[i * LDD + j] = decay_ij(Gs, runs, i, j, Gs[i], runs[i]);
   }
-  TC_TRACE(1);
   bool ok = umma::mbar_wait(bars + 8, 0);
-  TC_TRACE(2);
   if (m.len < 64) {
     zero_tail_rows<T, K>(kS, m.len, tid, 512);
     zero_tail_rows<T, V>(vS, m.len, tid, 512);
@@ -248,9 +242,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
     umma::commit(bars + 0);
   }
   __syncwarp();
-  TC_TRACE(3);
   ok = umma::mbar_wait(bars + 9, 0) && ok;
-  TC_TRACE(4);
   if (m.len < 64) {
     zero_tail_rows<T, V>(doS, m.len, tid, 512);
     zero_tail_rows<T, K>(qS, m.len, tid, 512);
@@ -273,9 +265,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
   const float gam0 = gam[i0], gam1 = gam[i1], gamr0 = gamr[i0], gamr1 = gamr[i1];
 
   if (DELTA) {  // epilogue 1: W = V - (cin Gamma)(K S), in place over V
-    TC_TRACE(5);
     ok = umma::mbar_wait(bars + 0, 0) && ok;
-    TC_TRACE(6);
     umma::fence_after_sync();
     if (ok) {
       float acc[VNT][4];
@@ -294,13 +284,12 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
     }
   }
   {  // epilogue 2: dP = scale (dO Vn^T) D ; E = dP (Q K^T)
-    TC_TRACE(7);
     ok = umma::mbar_wait(bars + 1, 0) && ok;
-    TC_TRACE(8);
     umma::fence_after_sync();
     if (DELTA && tid == 0 && ok) {  // dO is dead: fetch dVn into its buffer
       tma::expect_tx(bars + 10, 64 * V * 2);
-      tma::load_tile<64, V>(doS, &maps.dvn, 0, 0, ch_off * 64, bars + 10);
+      if (TR) tma::load_tile<V, 64>(doS, &maps.dvn, 0, 0, ch_off * V, bars + 10);
+      else tma::load_tile<64, V>(doS, &maps.dvn, 0, 0, ch_off * 64, bars + 10);
     }
     __syncwarp();
     if (ok) {
@@ -337,21 +326,18 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
   }
   __syncwarp();
   if (DELTA) {
-    TC_TRACE(9);
-    ok = umma::mbar_wait(bars + 10, 0) && ok;
-    TC_TRACE(10);  // dVn landed (whole 64-row tile from the scratch: no tail to clear)
+    ok = umma::mbar_wait(bars + 10, 0) && ok;  // dVn landed (whole 64-row tile from the scratch: no tail to clear)
     // ---- batch 3b: P1 = dVn W^T, P2 = K K^T (W was written before the barrier above) ---------------------------
     if (tid == 0 && ok) {
-      umma::gemm<64, 64, V / 16, false, false, FMT>(tmem + cP1, aDo, 64, aV, 64, false);
+      if (TR) umma::gemm<64, 64, V / 16, true, false, FMT>(tmem + cP1, aDo, V, aV, 64, false);
+      else umma::gemm<64, 64, V / 16, false, false, FMT>(tmem + cP1, aDo, 64, aV, 64, false);
       umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP2, aK, 64, aK, 64, false);
       umma::commit(bars + 3);
     }
     __syncwarp();
   }
   {  // epilogue 3: dq = scale (cin Gamma)(dO S^T) + dP K
-    TC_TRACE(11);
     ok = umma::mbar_wait(bars + 2, 0) && ok;
-    TC_TRACE(12);
     umma::fence_after_sync();
     if (ok) {
       float accQ[KNT][4], accT[KNT][4];
@@ -392,9 +378,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
   }
   if (DELTA) {
     {  // epilogue 4: dAg = tril(dVn W^T); F = dAg Ag; dT0 = dAg D beta_j
-      TC_TRACE(13);
       ok = umma::mbar_wait(bars + 3, 0) && ok;
-      TC_TRACE(14);
       umma::fence_after_sync();
       if (ok) {
         float accA[2][4], accF[2][4], accB[2][4];
@@ -438,9 +422,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
       tma::load_tile<K, V>(dSS, &maps.dh, 0, 0, ch_off * K, bars + 11);
     }
     __syncwarp();
-    TC_TRACE(15);
     ok = umma::mbar_wait(bars + 4, 0) && ok;
-    TC_TRACE(16);
     umma::fence_after_sync();
     if (ok) {
       float accM[2][4];
@@ -458,9 +440,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
       umma::commit(bars + 5);
     }
     __syncwarp();
-    TC_TRACE(17);
     ok = umma::mbar_wait(bars + 5, 0) && ok;
-    TC_TRACE(18);
     umma::fence_after_sync();
     if (ok) {  // epilogue 6: dA0 = -strict(P1) same; dbeta_i += sum_j dA0_ij (k_i . k_j); Xb = dA0 beta_i
       float accA0[2][4], accKK[2][4];
@@ -491,9 +471,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
     }
     __syncwarp();
   }
-  TC_TRACE(19);
   ok = umma::mbar_wait(bars + 11, 0) && ok;
-  TC_TRACE(20);
   if (DELTA && m.len < 64) zero_tail_rows<T, V>(vS, m.len, tid, 512);
   umma::fence_async_smem();
   umma::fence_before_sync();
@@ -507,21 +485,15 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
       if (TR) umma::gemm<64, K, V / 16, false, true, FMT>(tmem + cT1, aV, 64, aS, V, false);
       else umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cT1, aV, 64, aS, K, false);
     }
-    if (TR && DELTA) umma::gemm<64, K, V / 16, true, false, FMT>(tmem + cQ, aVn, V, adS, K, false);
+    if (TR && DELTA) umma::gemm<64, K, V / 16, true, true, FMT>(tmem + cQ, aVn, V, adS, V, false);
+    else if (TR) umma::gemm<64, K, V / 16, false, true, FMT>(tmem + cQ, aVn, 64, adS, V, false);
     else umma::gemm<64, K, V / 16, false, false, FMT>(tmem + cQ, aVn, 64, adS, K, false);
     umma::commit(bars + 6);
   }
   __syncwarp();
   {  // keep gamma <S, dS+> while the products run (both tiles share one layout)
     float part = 0.f;
-    if (TR) {  // S is stored transposed ([V][K]), dS+ row-major ([K][V])
-      const T* a = reinterpret_cast<const T*>(SS);
-      const T* b = reinterpret_cast<const T*>(dSS);
-      for (int idx = tid; idx < K * V; idx += 512) {
-        const int kk = idx / V, vv = idx - kk * V;
-        part += to_f32(a[swz_tile(V, vv, kk)]) * to_f32(b[swz_tile(K, kk, vv)]);
-      }
-    } else {
+    {
       const uint32_t* a = reinterpret_cast<const uint32_t*>(SS);
       const uint32_t* b = reinterpret_cast<const uint32_t*>(dSS);
       for (int idx = tid; idx < K * V / 2; idx += 512) {
@@ -533,9 +505,7 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
     for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
     if (lane == 0) atomicAdd(sdot, part);
   }
-  TC_TRACE(21);
   ok = umma::mbar_wait(bars + 6, 0) && ok;
-  TC_TRACE(22);
   umma::fence_after_sync();
   if (ok) {  // epilogue 7: dk and the state terms of dG
     float accK[KNT][4], accT[KNT][4];
@@ -595,7 +565,6 @@ sg_chunk_grads_tc_kernel(const __grid_constant__ GradTcMaps maps, GradTcParams p
   }
   umma::fence_before_sync();
   __syncthreads();
-  TC_TRACE(23);
   if (warp == 1) umma::tmem_dealloc(tmem, 512);
   if (!ok) {
     if (tid == 0) atomicExch(&g_tc_status, 1);
@@ -650,7 +619,8 @@ int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scrat
     const bool trv = use_tc_kernels(p);
     ok = (trv ? tma::encode_3d(&maps.vn, c.res + pl.vn, 64, 1, slots * p.V, p.V)
               : tma::encode_3d(&maps.vn, c.res + pl.vn, p.V, 1, slots * 64, 64)) &&
-         tma::encode_3d(&maps.dvn, scratch + pl.dvn, p.V, 1, slots * 64, 64) &&
+         (trv ? tma::encode_3d(&maps.dvn, scratch + pl.dvn, 64, 1, slots * p.V, p.V)
+              : tma::encode_3d(&maps.dvn, scratch + pl.dvn, p.V, 1, slots * 64, 64)) &&
          tma::encode_3d(&maps.t0, c.res + pl.t0, 64, 1, slots * 64, 64);
   } else if (ok) {
     maps.vn = maps.v;
@@ -691,10 +661,6 @@ int* tc_status_ptr() {
   return ptr;
 }
 
-int read_tc_trace(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 32) == cudaSuccess ? JLA_OK : JLA_ERR_CUDA;
-}
-
 int read_tc_status(int* out) {
   int v = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
@@ -704,5 +670,3 @@ int read_tc_status(int* out) {
 }
 
 }  // namespace jla
-
-extern "C" int jla_debug_tc_trace(unsigned long long* out) { return jla::read_tc_trace(out); }

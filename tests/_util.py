@@ -209,7 +209,13 @@ class ChunkedLayout:
         return self.chunked(self._view(self.res, self.lay.vn, (self.nc, self.p.H, 64, self.p.V), self.dtype))
 
     def dh(self):
+        if self.transposed:
+            x = self._view(self.scr, self.lay.dh, (self.nc, self.p.H, self.p.V, self.p.K), self.dtype)
+            return self.chunked(x.transpose(-1, -2))
         return self.chunked(self._view(self.scr, self.lay.dh, (self.nc, self.p.H, self.p.K, self.p.V), self.dtype))
 
     def dvn(self):
+        if self.transposed:
+            x = self._view(self.scr, self.lay.dvn, (self.nc, self.p.H, self.p.V, 64), self.dtype)
+            return self.chunked(x.transpose(-1, -2))
         return self.chunked(self._view(self.scr, self.lay.dvn, (self.nc, self.p.H, 64, self.p.V), self.dtype))
