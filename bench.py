@@ -42,7 +42,16 @@ WORKLOADS = {
     "gdn": dict(name="config1: gated_deltanet B8 T2048 H16 K128 V128 chunk64 bf16, packed docs U[64,2048]", index=1),
     "ssd": dict(name="config2: mamba2 SSD B8 T2048 H64 P64 N128 G1 bf16", index=2),
     "kda": dict(name="config3: kda B4 T4096 H16 K128 V128 bf16, packed docs U[128,4096]", index=3),
+    "longctx": dict(name="config4: gated_deltanet B1 T1064960 H16 K128 V128 bf16, packed docs U[4096,131072], "
+                         "sequence-parallel over the ranks", index=4),
 }
+METRICS = {
+    "gdn": None,  # the headline metric
+    "ssd": "Mamba-2 SSD chunk fwd+bwd tokens/s (B8·T2048·H64·P64·N128 bf16)",
+    "kda": "KDA fwd+bwd tokens/s (B4·T4096·H16·d128 bf16)",
+    "longctx": "GDN fwd+bwd tokens/s on one 1,064,960-token sequence (H16·d128 bf16), sequence-parallel",
+}
+LONG_T = 1_064_960
 
 
 def peaks() -> dict:
@@ -124,6 +133,33 @@ def host_case(workload: str, seed: int) -> dict:
     return baseline_config(WORKLOADS[workload]["index"], seed=seed)
 
 
+def longctx_device_inputs(device, rank: int, world: int, seed: int = 0) -> dict:
+    """Config 4 shard of this rank, drawn on the device (17 GB of fp32 NumPy per tensor would not fit a host
+    round trip): q, k ~ N(0,1) L2-normalised, v, dO ~ N(0,1), beta = sigmoid(N(0,1)), g = logsigmoid(N(0,1)+3);
+    document lengths U[4096, 131072] drawn once on the host for the whole sequence."""
+    from oracle.cases import uniform_docs
+
+    tl = LONG_T // world
+    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+
+    def randn(*shape):
+        return torch.randn(*shape, generator=gen, device=device, dtype=torch.float32)
+
+    def unit(x):
+        return (x * torch.rsqrt((x * x).sum(-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+
+    seg = torch.from_numpy(uniform_docs(np.random.default_rng(seed), 1, LONG_T, 4096, 131072))
+    out = dict(q=unit(randn(1, tl, 16, 128)), k=unit(randn(1, tl, 16, 128)), v=randn(1, tl, 16, 128).to(torch.bfloat16),
+               do=randn(1, tl, 16, 128).to(torch.bfloat16), beta=torch.sigmoid(randn(1, tl, 16)),
+               g=torch.nn.functional.logsigmoid(randn(1, tl, 16) + 3.0))
+    out["seg"] = seg[:, rank * tl:(rank + 1) * tl].to(device=device, dtype=torch.int32)
+    if world == 1:
+        ids = out["seg"][0]
+        starts = torch.nonzero(ids[1:] != ids[:-1]).flatten() + 1
+        out["cu"] = torch.cat([starts.new_zeros(1), starts, starts.new_full((1,), ids.numel())]).to(torch.int32)
+    return out
+
+
 def to_torch_host(case: dict, workload: str) -> dict:
     """Pinned host tensors in the dtypes of the op call."""
     out = {}
@@ -143,7 +179,7 @@ def to_torch_host(case: dict, workload: str) -> dict:
 
 
 GRAD_NAMES = {"gdn": ("q", "k", "v", "g", "beta"), "kda": ("q", "k", "v", "g", "beta"),
-              "ssd": ("x", "dt", "A", "B", "C")}
+              "ssd": ("x", "dt", "A", "B", "C"), "longctx": ("q", "k", "v", "g", "beta")}
 
 
 def run_step(workload: str, dev: dict):
@@ -156,6 +192,15 @@ def run_step(workload: str, dev: dict):
         from jax_linear_attention_b200.layers.ssm import mamba2_ssd
 
         o, _ = mamba2_ssd(dev["x"], dev["dt"], dev["A"], dev["B"], dev["C"], d=dev["D"], segment_ids=dev.get("seg"))
+    elif workload == "longctx":
+        if "cu" in dev:  # one GPU: the documents are the rows
+            o, _ = ops.linear_attention("gated_deltanet", dev["q"], dev["k"], dev["v"], g=dev["g"], beta=dev["beta"],
+                                        cu_seqlens=dev["cu"])
+        else:
+            from jax_linear_attention_b200.distributed import context_parallel_linear_attention
+
+            o, _ = context_parallel_linear_attention("gated_deltanet", dev["q"], dev["k"], dev["v"], g=dev["g"],
+                                                     beta=dev["beta"], segment_ids=dev["seg"])
     else:
         kind = "gated_deltanet" if workload == "gdn" else "kda"
         o, _ = ops.linear_attention(kind, dev["q"], dev["k"], dev["v"], g=dev["g"], beta=dev["beta"],
@@ -266,12 +311,21 @@ def main() -> None:
     from jax_linear_attention_b200 import _lib
 
     lib = _lib.load()
-    case = host_case(args.workload, seed=rank)
-    host = to_torch_host(case, args.workload)
-    dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+    longctx = args.workload == "longctx"
+    if longctx:
+        dev = longctx_device_inputs(device, rank, world)
+        host = {n: t.cpu().pin_memory() for n, t in dev.items() if n != "cu"}
+        case = {"q": dev["q"], "v": dev["v"]}
+        shape = (1, LONG_T // world)
+        tokens = LONG_T // world  # per rank; the job processes LONG_T tokens per step (strong scaling)
+        args.steps = min(args.steps, 5)
+    else:
+        case = host_case(args.workload, seed=rank)
+        host = to_torch_host(case, args.workload)
+        dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+        shape = case["q"].shape if "q" in case else case["x"].shape
+        tokens = shape[0] * shape[1]
     torch.cuda.synchronize()
-    shape = case["q"].shape if "q" in case else case["x"].shape
-    tokens = shape[0] * shape[1]
 
     def barrier():
         if dist is not None:
@@ -307,6 +361,8 @@ def main() -> None:
     def e2e_step():
         nonlocal out_host
         d = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+        if "cu" in dev:
+            d["cu"] = dev["cu"]
         o, grads = run_step(args.workload, d)
         outs = [o.detach(), *grads]
         if out_host is None:
@@ -333,7 +389,7 @@ def main() -> None:
     if rank == 0:
         pk = peaks()
         launches = sum(v["launches"] for v in prof.values())
-        K, V = (shape[3], case["v"].shape[3]) if "q" in case else (case["B"].shape[3], case["x"].shape[3])
+        K, V = (case["q"].shape[3], case["v"].shape[3]) if "q" in case else (case["B"].shape[3], case["x"].shape[3])
         H = case["v"].shape[2] if "v" in case else case["x"].shape[2]
         units = (tokens // CHUNK) * H  # (chunk, head) pairs per launch
         model = kernel_model(K, V, delta=args.workload != "ssd", save=True)
@@ -360,11 +416,14 @@ def main() -> None:
         step_bytes = 2816.0 * tokens * H
         sec = ms_per_step * 1e-3
         line = dict(
-            metric=METRIC, value=world * tokens / sec, unit="tokens/s", n_gpus=world, steps=args.steps,
-            warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None,
+            metric=METRICS[args.workload] or METRIC, value=world * tokens / sec, unit="tokens/s", n_gpus=world,
+            steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True,
+            scaling="strong" if longctx else "weak", vs_baseline=None,
             dtype="bf16", data="synthetic",
             config=dict(workload=WORKLOADS[args.workload]["name"], per_gpu_batch=list(shape[:2]),
-                        l2="inputs larger than L2 (q,k,v,dO 268 MB + residuals per step)", parallelism=f"batch x heads, {world} GPU(s), no communication"),
+                        l2="inputs larger than L2 (hundreds of MB of q,k,v,dO + residuals per step)",
+                        parallelism=(f"sequence-parallel over {world} GPU(s), NCCL send/recv of the fp32 state" if longctx
+                                     else f"batch x heads, {world} GPU(s), no communication")),
             e2e=None if not e2e_steps else dict(
                 value=world * tokens / (e2e_ms / e2e_steps * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
                 d2h_bytes_per_step=d2h, steps=e2e_steps, ms_per_step=e2e_ms / e2e_steps),
@@ -376,7 +435,7 @@ def main() -> None:
             kernels={n: dict(launches=v["launches"], ms_per_launch=v["total_ms"] / v["launches"]) for n, v in prof.items()},
         )
         if not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(case, rows=4) if args.workload != "ssd" else None
+            line["cpu_baseline"] = cpu_baseline(case, rows=4) if args.workload in ("gdn", "kda") else None
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()

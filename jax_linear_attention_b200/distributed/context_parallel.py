@@ -184,17 +184,32 @@ class _ContextParallel(torch.autograd.Function):
 
 
 def _default_call(impl, options):
+    """The op on (a slice of) the local shard. A single packed row is handed over as ``cu_seqlens`` (the document
+    boundaries are on the host anyway), so that every document is an independent row for the kernels instead of
+    one long serial chain; the carried state goes to the first document, the state after the last one comes back."""
     def call(kind, leaves, state, seg, tslice, row):
         q, k, v, *gates = leaves
         rows = slice(None) if row is None else slice(row, row + 1)
         names = _GATES[kind]
         kw = dict(options)
         kw.update({n: g[rows, tslice] for n, g in zip(names, gates)})
+        ql, kl, vl = q[rows, tslice], k[rows, tslice], v[rows, tslice]
+        init = None if state is None else state[rows]
+        if seg is not None and ql.shape[0] == 1 and ql.shape[1] > 0:
+            ids = seg[rows, tslice][0]
+            starts = torch.nonzero(ids[1:] != ids[:-1]).flatten() + 1
+            if starts.numel() > 0:
+                cu = torch.cat([starts.new_zeros(1), starts, starts.new_full((1,), ids.numel())]).to(torch.int32)
+                nseq = cu.numel() - 1
+                init_all = None
+                if init is not None:
+                    init_all = torch.cat([init, init.new_zeros(nseq - 1, *init.shape[1:])], dim=0)
+                o, final = ops.linear_attention(kind, ql, kl, vl, impl=impl, initial_state=init_all,
+                                                output_final_state=True, cu_seqlens=cu, **kw)
+                return o, final[-1:]
         if seg is not None:
             kw["segment_ids"] = seg[rows, tslice]
-        init = None if state is None else state[rows]
-        return ops.linear_attention(kind, q[rows, tslice], k[rows, tslice], v[rows, tslice], impl=impl,
-                                    initial_state=init, output_final_state=True, **kw)
+        return ops.linear_attention(kind, ql, kl, vl, impl=impl, initial_state=init, output_final_state=True, **kw)
     return call
 
 
