@@ -153,11 +153,14 @@ int jla_linear_attention_fwd_noalloc(const jla_problem* p, void* o, float* final
  * with JLA_FLAG_SAVE_RESIDUALS (meta .. vn) and into the backward scratch (dh .. dk_acc). Chunk slot c of head h:
  *   gates [c][h][128] f32 (G[64], beta[64])    runs [c][64] u8    t0, ag [c][h][64][64] dtype (ag = t0 * D * beta_j)
  *   h [c][h][K][V] dtype (state entering the chunk)    vn [c][h][64][V] dtype
- *   dh [c][h][K][V] dtype (gradient of the state leaving the chunk)    dvn [c][h][64][V] dtype */
+ *   dh [c][h][K][V] dtype (gradient of the state leaving the chunk)    dvn [c][h][64][V] dtype
+ * With K = V = 128 (the tcgen05 kernels; JLA_B200_LEGACY=1 in the environment turns them off) h, vn, dh and dvn are
+ * stored transposed ([V][K], [V][64]), and three more buffers exist: w [c][h][V][64] dtype (W^T = (V - cin Gamma K S)^T),
+ * dp [c][h] 64x64 dtype tiles in the 128-byte-swizzled shared-memory layout, dga [c][h][64] f32 (dG partial sums). */
 typedef struct jla_chunked_layout {
   int32_t num_chunk_slots;
-  size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, residual_bytes;
-  size_t dh, dvn, dq_acc, dk_acc, bwd_scratch_bytes;
+  size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, w, residual_bytes;
+  size_t dh, dvn, dq_acc, dk_acc, dp, dga, bwd_scratch_bytes;
 } jla_chunked_layout;
 int jla_chunked_get_layout(const jla_problem* p, jla_chunked_layout* out);
 

@@ -25,10 +25,14 @@ struct ChunkMeta {
 struct Plan {
   int rows, nc;       // rows; chunk slots (upper bound on the number of chunks)
   bool delta, l2norm, save;
-  size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, residual_bytes;  // residual buffer
+  size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, w, residual_bytes;  // residual buffer
   size_t fwd_scratch_bytes;                                                 // same layout without h, vn
-  size_t dh, dvn, dq_acc, dk_acc, bwd_scratch_bytes;                        // backward scratch
+  size_t dh, dvn, dq_acc, dk_acc, dp, dga, bwd_scratch_bytes;               // backward scratch
 };
+
+// The tcgen05 kernels cover K = V = 128 and keep the residuals h, Vn and W transposed ([V][K], [V][64]); other head
+// sizes, or JLA_B200_LEGACY=1 (A/B comparison), use the mma.sync kernels with row-major residuals.
+bool use_tc_kernels(const jla_problem& p);  // chunked_api.cu
 
 inline int elem_size(int dtype) { return dtype == JLA_DTYPE_F32 ? 4 : 2; }
 
@@ -61,6 +65,8 @@ inline Plan make_plan(const jla_problem& p) {
   pl.fwd_scratch_bytes = align_up(c.off);
   pl.h = off((size_t)pl.nc * p.H * p.K * p.V * es);
   pl.vn = off(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
+  const bool tc = use_tc_kernels(p);
+  pl.w = off(pl.delta && tc ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);  // W^T, for the key-side gradient kernel
   pl.residual_bytes = align_up(c.off);
   Carver b(nullptr);
   auto boff = [&](size_t bytes) {
@@ -74,6 +80,8 @@ inline Plan make_plan(const jla_problem& p) {
   pl.dvn = boff(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
   pl.dq_acc = boff(direct ? 0 : tokens * p.H * p.K * sizeof(float));
   pl.dk_acc = boff(direct ? 0 : tokens * p.H * p.K * sizeof(float));
+  pl.dp = boff(tc ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);       // dP tiles, query-side -> key-side gradient kernel
+  pl.dga = boff(tc ? (size_t)pl.nc * p.H * 64 * sizeof(float) : 0);  // dG partial sums, likewise
   pl.bwd_scratch_bytes = align_up(b.off);
   return pl;
 }
@@ -103,10 +111,6 @@ __device__ __forceinline__ float keep_gamma(const float* Gs, const unsigned char
 __device__ __forceinline__ float decay_ij(const float* Gs, const unsigned char* runs, int i, int j, float Gi, int runi) {
   return (j <= i && runs[j] == runi) ? __expf(Gi - Gs[j]) : 0.f;
 }
-
-// The tcgen05 kernels cover K = V = 128 and keep the residuals h and Vn transposed ([V][K], [V][64]); other head
-// sizes, or JLA_B200_LEGACY=1 (A/B comparison), use the mma.sync kernels with row-major residuals.
-bool use_tc_kernels(const jla_problem& p);  // chunked_api.cu
 
 // ---- launchers (chunked_*.cu) -----------------------------------------------------------------------------
 struct ChunkedCtx {

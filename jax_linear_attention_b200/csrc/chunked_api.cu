@@ -92,9 +92,9 @@ extern "C" int jla_chunked_get_layout(const jla_problem* p, jla_chunked_layout* 
   const jla::Plan pl = jla::make_plan(ps);
   out->num_chunk_slots = pl.nc;
   out->meta = pl.meta; out->row_chunks = pl.row_chunks; out->gates = pl.gates; out->runs = pl.runs;
-  out->t0 = pl.t0; out->ag = pl.ag; out->qn = pl.qn; out->kn = pl.kn; out->h = pl.h; out->vn = pl.vn;
+  out->t0 = pl.t0; out->ag = pl.ag; out->qn = pl.qn; out->kn = pl.kn; out->h = pl.h; out->vn = pl.vn; out->w = pl.w;
   out->residual_bytes = pl.residual_bytes;
-  out->dh = pl.dh; out->dvn = pl.dvn; out->dq_acc = pl.dq_acc; out->dk_acc = pl.dk_acc;
+  out->dh = pl.dh; out->dvn = pl.dvn; out->dq_acc = pl.dq_acc; out->dk_acc = pl.dk_acc; out->dp = pl.dp; out->dga = pl.dga;
   out->bwd_scratch_bytes = pl.bwd_scratch_bytes;
   return JLA_OK;
 }

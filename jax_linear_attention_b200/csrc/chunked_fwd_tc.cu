@@ -40,7 +40,7 @@ struct FwdTcParams {
   const float* h0;
   void* o;
   float* final_state;
-  void *hT_out, *vnT_out;  // residuals (nullptr when not saving)
+  void *hT_out, *vnT_out, *wT_out;  // residuals (nullptr when not saving)
   int H, Hk;
   float scale;
   int* status;
@@ -304,11 +304,18 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
             pk[i] = pack2<T>(w0, w1);
           }
           umma::st_32x32b_x16(tl + cWb + 16 * half, pk);
+          umma::wait_st();
+          umma::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + B_W);
+          if (p.wT_out) {  // residual for the key-side gradient kernel (dAg = dVn W^T)
+            T* wT = static_cast<T*>(p.wT_out) + (((long)c * p.H + h) * V + v) * 64 + j0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              *reinterpret_cast<uint4*>(wT + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+            }
+          }
         }
-        umma::wait_st();
-        umma::fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + B_W);
         // ---- Vn^T = W^T Ag^T
         ok = wait(bars + B_M2, ph, abort_flag);
         if (!ok) break;
@@ -499,7 +506,7 @@ int launch_one(const FwdTcMaps& maps, const FwdTcParams& fp, int blocks, cudaStr
 
 }  // namespace
 
-int* tc_status_ptr();  // chunked_bwd_tc.cu
+int* tc_status_ptr();  // chunked_grads_tc.cu
 
 // Same contract as launch_sg_fwd (chunked_fwd.cu) for K = V = 128; the residuals h and Vn are written transposed.
 int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) {
@@ -523,6 +530,7 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
   fp.final_state = io.final_state;
   fp.hT_out = pl.save ? c.res + pl.h : nullptr;
   fp.vnT_out = pl.save && pl.delta ? c.res + pl.vn : nullptr;
+  fp.wT_out = pl.save && pl.delta ? c.res + pl.w : nullptr;
   fp.H = p.H;
   fp.Hk = p.Hk;
   fp.scale = p.scale;

@@ -25,7 +25,7 @@ int g_launches[kProfKernels] = {};
 const char* const kNames[kProfKernels] = {
     "build_tables", "prep_gates", "l2norm_fwd", "kkt_inv", "sg_fwd", "sg_bwd_state", "sg_chunk_grads",
     "finalize_key_grad", "rec_fwd", "rec_bwd", "kda_prep", "kda_intra", "kda_fwd", "kda_bwd_state", "kda_chunk_grads",
-    "cp_correction"};
+    "cp_correction", "sg_grads_q", "sg_grads_k"};
 
 cudaEvent_t take_event() {
   if (!g_pool.empty()) {

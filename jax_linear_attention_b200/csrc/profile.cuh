@@ -7,7 +7,7 @@ namespace jla {
 enum {
   kProfTables = 0, kProfGates, kProfL2Norm, kProfKktInv, kProfSgFwd, kProfSgBwdState, kProfSgChunkGrads,
   kProfFinalize, kProfRecFwd, kProfRecBwd, kProfKdaPrep, kProfKdaIntra, kProfKdaFwd, kProfKdaBwdState,
-  kProfKdaChunkGrads, kProfCpCorrection, kProfKernels
+  kProfKdaChunkGrads, kProfCpCorrection, kProfSgGradsQ, kProfSgGradsK, kProfKernels
 };
 
 class ProfScope {

@@ -38,9 +38,18 @@ bool encode_3d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t mid,
   const cuuint64_t strides[2] = {inner * 2, inner * mid * 2};  // bytes, dims 1 and 2
   const cuuint32_t box[3] = {64, 1, box_rows};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&] {
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult rc = encode();
+  if (rc == CUDA_ERROR_INVALID_CONTEXT || rc == CUDA_ERROR_NOT_INITIALIZED) {
+    // A host thread that has made no runtime call yet (an autograd worker, say) has no current context for a driver
+    // call: a no-op runtime call binds the device's primary context to it.
+    cudaFree(nullptr);
+    rc = encode();
+  }
   if (rc != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed (%d) for dims {%llu, %llu, %llu}", (int)rc, (unsigned long long)inner,
               (unsigned long long)mid, (unsigned long long)outer);

@@ -41,6 +41,14 @@ __device__ __forceinline__ uint32_t load_tile(unsigned char* smem_tile, const CU
   return ROWS * COLS * 2;
 }
 
+// Untiled bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned) from global to shared memory.
+__device__ __forceinline__ void load_bulk(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   umma::smem_addr(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(umma::smem_addr(bar))
+               : "memory");
+}
+
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

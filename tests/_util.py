@@ -161,8 +161,8 @@ class ChunkedLayout:
 
         class Layout(C.Structure):
             _fields_ = [("num_chunk_slots", C.c_int32)] + [(n, C.c_size_t) for n in (
-                "meta", "row_chunks", "gates", "runs", "t0", "ag", "qn", "kn", "h", "vn", "residual_bytes", "dh", "dvn",
-                "dq_acc", "dk_acc", "bwd_scratch_bytes")]
+                "meta", "row_chunks", "gates", "runs", "t0", "ag", "qn", "kn", "h", "vn", "w", "residual_bytes", "dh", "dvn",
+                "dq_acc", "dk_acc", "dp", "dga", "bwd_scratch_bytes")]
 
         lay = Layout()
         lib = _lib.load()
@@ -207,6 +207,12 @@ class ChunkedLayout:
             x = self._view(self.res, self.lay.vn, (self.nc, self.p.H, self.p.V, 64), self.dtype)
             return self.chunked(x.transpose(-1, -2))
         return self.chunked(self._view(self.res, self.lay.vn, (self.nc, self.p.H, 64, self.p.V), self.dtype))
+
+    def w(self):
+        """W = V - cin Gamma (K S) per chunk; only the tcgen05 path keeps it (transposed)."""
+        assert self.transposed
+        x = self._view(self.res, self.lay.w, (self.nc, self.p.H, self.p.V, 64), self.dtype)
+        return self.chunked(x.transpose(-1, -2))
 
     def dh(self):
         if self.transposed:
