@@ -74,26 +74,27 @@ __device__ __forceinline__ void store_acc_swz(unsigned char* tile, int r0, int c
   }
 }
 
+// Reductions never use shared-memory float atomics (a compare-and-swap loop that serialises under contention):
+// row quantities are accumulated per thread in registers and reduced over the quad once, column sums are reduced
+// over the warp's 16 rows with shuffles and stored to a slot that only this warp writes.
 template <int NT>
-__device__ __forceinline__ void row_sums_add(const float (&x)[NT][4], float* vec, int r0, int lane, float sign) {
-  float a = 0.f, b = 0.f;
+__device__ __forceinline__ void row_sums_acc(const float (&x)[NT][4], float& a, float& b) {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     a += x[nt][0] + x[nt][1];
     b += x[nt][2] + x[nt][3];
   }
-  a += __shfl_xor_sync(0xffffffffu, a, 1);
-  a += __shfl_xor_sync(0xffffffffu, a, 2);
-  b += __shfl_xor_sync(0xffffffffu, b, 1);
-  b += __shfl_xor_sync(0xffffffffu, b, 2);
-  if ((lane & 3) == 0) {
-    atomicAdd(vec + r0 + (lane >> 2), sign * a);
-    atomicAdd(vec + r0 + (lane >> 2) + 8, sign * b);
-  }
 }
 
+__device__ __forceinline__ float quad_sum(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  return x;
+}
+
+// out[c0 + 8 nt + 2 t + {0, 1}] = sum over this warp's 16 rows of x (out is this warp's own slot)
 template <int NT>
-__device__ __forceinline__ void col_sums_add(const float (&x)[NT][4], float* vec, int c0, int lane, float sign) {
+__device__ __forceinline__ void col_sums_store(const float (&x)[NT][4], float* out, int c0, int lane) {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     float a = x[nt][0] + x[nt][2], b = x[nt][1] + x[nt][3];
@@ -102,21 +103,16 @@ __device__ __forceinline__ void col_sums_add(const float (&x)[NT][4], float* vec
       a += __shfl_xor_sync(0xffffffffu, a, off);
       b += __shfl_xor_sync(0xffffffffu, b, off);
     }
-    if (lane < 4) {
-      atomicAdd(vec + c0 + nt * 8 + 2 * lane, sign * a);
-      atomicAdd(vec + c0 + nt * 8 + 2 * lane + 1, sign * b);
-    }
+    if (lane < 4) *reinterpret_cast<float2*>(out + c0 + nt * 8 + 2 * lane) = make_float2(a, b);
   }
 }
 
-// sum_c x[i][c] * tile[i][c] over this warp's columns of a [64 x 128] swizzled 16-bit tile, reduced over the quad.
+// this thread's part of sum_c x[i][c] * tile[i][c] for its rows g and g + 8 ([64 x 128] swizzled 16-bit tile)
 template <typename T, int NT>
-__device__ __forceinline__ void row_dots_swz(const float (&x)[NT][4], const unsigned char* tile, int r0, int c0, int lane,
-                                             float& d0, float& d1) {
+__device__ __forceinline__ void row_dots_part(const float (&x)[NT][4], const unsigned char* tile, int r0, int c0, int lane,
+                                              float& d0, float& d1) {
   const T* src = reinterpret_cast<const T*>(tile);
   const int g = lane >> 2, t = lane & 3;
-  d0 = 0.f;
-  d1 = 0.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int col = c0 + nt * 8 + 2 * t;
@@ -125,10 +121,6 @@ __device__ __forceinline__ void row_dots_swz(const float (&x)[NT][4], const unsi
     d0 += x[nt][0] * a.x + x[nt][1] * a.y;
     d1 += x[nt][2] * b.x + x[nt][3] * b.y;
   }
-  d0 += __shfl_xor_sync(0xffffffffu, d0, 1);
-  d0 += __shfl_xor_sync(0xffffffffu, d0, 2);
-  d1 += __shfl_xor_sync(0xffffffffu, d1, 1);
-  d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
 }
 
 // writes this thread's fragment of a [64 x 128] gradient tile (rows i0, i0 + 8; columns c0 + 8 nt + 2t, +1)
@@ -160,7 +152,9 @@ __device__ __forceinline__ void cta_sync_tc() {
 
 // ---------------------------------------------------------------------------------------------------------------
 // Query side. Shared memory: dO [64][V], Vn^T [V][64] (or V [64][V] without the delta rule), S^T [V][K], q, k
-// [64][K], dP [64][64]. TMEM columns: [0,64) dO Vn^T, [64,128) Q K^T, then [0,128) dP K; [128,256) dO S^T.
+// [64][K], dP [64][64]. TMEM columns: [0,64) dO Vn^T, then [0,128) dP K; [128,256) dO S^T.
+// The gate gradient of the in-chunk scores needs no score matrix: with E = dP (Q K^T), rowsum_i(E) = q_i . (dP K)_i
+// and colsum_j(E) = k_j . (dP^T Q)_j, so this kernel contributes q_i . dq_i and the key side subtracts k_j . (dP^T Q)_j.
 struct SmemQ {
   static constexpr int kDo = 0;
   static constexpr int kVn = kDo + 64 * VD * 2;
@@ -168,8 +162,8 @@ struct SmemQ {
   static constexpr int kQ = kS + KD * VD * 2;
   static constexpr int kK = kQ + 64 * KD * 2;
   static constexpr int kXa = kK + 64 * KD * 2;
-  static constexpr int kVec = kXa + 8192;            // G, gam, dG: [64] f32 each; runs[64] u8
-  static constexpr int kBars = kVec + 3 * 256 + 64;  // 3 mbarriers, tmem slot
+  static constexpr int kVec = kXa + 8192;            // G, gam: [64] f32; rowG [2][64] f32; runs[64] u8
+  static constexpr int kBars = kVec + 4 * 256 + 64;  // 3 mbarriers, tmem slot
   static constexpr int kBytes = kBars + 3 * 8 + 8 + 1024;
   static_assert(kBars % 8 == 0, "mbarrier alignment");
   static_assert(2 * (kBytes + 1024) <= 233472, "two CTAs per SM");
@@ -198,12 +192,12 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   unsigned char* Xa = base + L::kXa;
   float* Gs = reinterpret_cast<float*>(base + L::kVec);
   float* gam = Gs + 64;
-  float* dGv = gam + 64;
-  unsigned char* runs = reinterpret_cast<unsigned char*>(dGv + 64);
+  float* rowG = gam + 64;  // [2][64]: q . dq over each column half
+  unsigned char* runs = reinterpret_cast<unsigned char*>(rowG + 128);
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::kBars);  // 0: loads, 1..2: MMA batches
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
-  const uint32_t aDo = umma::smem_addr(doS), aVn = umma::smem_addr(vnS), aS = umma::smem_addr(SS), aQ = umma::smem_addr(qS),
-                 aK = umma::smem_addr(kS), aXa = umma::smem_addr(Xa);
+  const uint32_t aDo = umma::smem_addr(doS), aVn = umma::smem_addr(vnS), aS = umma::smem_addr(SS), aK = umma::smem_addr(kS),
+                 aXa = umma::smem_addr(Xa);
   const int ch_off = c * p.H + h;
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) umma::mbar_init(bars + i, 1);
@@ -213,14 +207,13 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     if (DELTA) tma::load_tile<VD, 64>(vnS, &maps.vn, 0, 0, ch_off * VD, bars + 0);
     else tma::load_tile<64, VD>(vnS, &maps.v, 0, h, m.tok0, bars + 0);
     tma::load_tile<VD, KD>(SS, &maps.h, 0, 0, ch_off * VD, bars + 0);
-    tma::load_tile<64, KD>(qS, &maps.q, 0, hk, m.tok0, bars + 0);
     tma::load_tile<64, KD>(kS, &maps.k, 0, hk, m.tok0, bars + 0);
+    tma::load_tile<64, KD>(qS, &maps.q, 0, hk, m.tok0, bars + 0);
   }
   if (warp == 1) umma::tmem_alloc(tmem_slot, 256);
   if (tid < 64) {
     Gs[tid] = p.gates[(long)ch_off * 128 + tid];
     runs[tid] = p.runs[(long)c * 64 + tid];
-    dGv[tid] = 0.f;
   }
   __syncthreads();
   if (tid < 64) gam[tid] = row_scalars(Gs, runs, m.flags, tid).gam;
@@ -233,13 +226,12 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   cta_sync_tc();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tl = tmem + ((uint32_t)(32 * (warp & 3)) << 16);  // this warp's lane quadrant
-  constexpr uint32_t cP1 = 0, cP2 = 64, cT1 = 0, cQ = 128;
+  constexpr uint32_t cP1 = 0, cT1 = 0, cQ = 128;
 
-  // ---- batch 1: P1 = dO Vn^T, P2 = Q K^T, accQ = dO S^T ---------------------------------------------------------
+  // ---- batch 1: P1 = dO Vn^T, accQ = dO S^T ------------------------------------------------------------------------
   if (tid == 0 && ok) {
     if (DELTA) umma::gemm<64, 64, VD / 16, false, true, FMT>(tmem + cP1, aDo, 64, aVn, VD, false);
     else umma::gemm<64, 64, VD / 16, false, false, FMT>(tmem + cP1, aDo, 64, aVn, 64, false);
-    umma::gemm<64, 64, KD / 16, false, false, FMT>(tmem + cP2, aQ, 64, aK, 64, false);
     umma::commit(bars + 1);
     umma::gemm<64, KD, VD / 16, false, true, FMT>(tmem + cQ, aDo, 64, aS, VD, false);
     umma::commit(bars + 2);
@@ -248,13 +240,12 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   const int i0 = r0 + g, i1 = r0 + g + 8;
   const float G0 = Gs[i0], G1 = Gs[i1];
   const int run0 = runs[i0], run1 = runs[i1];
-  {  // epilogue 1: dP = scale (dO Vn^T) D ; E = dP (Q K^T)
+  {  // epilogue 1: dP = scale (dO Vn^T) D
     ok = ok && umma::mbar_wait(bars + 1, 0);
     umma::fence_after_sync();
     if (ok) {
-      float accP[4][4], accE[4][4];
+      float accP[4][4];
       umma::ld_16x256b<4>(accP, tl + cP1 + cc0);
-      umma::ld_16x256b<4>(accE, tl + cP2 + cc0);
       umma::wait_ld();
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
@@ -263,18 +254,13 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
           const int j = cc0 + nt * 8 + 2 * t + (e & 1);
           const float d = (e >> 1) ? decay_ij(Gs, runs, i1, j, G1, run1) : decay_ij(Gs, runs, i0, j, G0, run0);
           accP[nt][e] *= p.scale * d;
-          accE[nt][e] *= accP[nt][e];
         }
       }
-      row_sums_add<4>(accE, dGv, r0, lane, 1.f);
-      col_sums_add<4>(accE, dGv, cc0, lane, -1.f);
       store_acc_swz<T, 4>(Xa, r0, cc0, accP, lane);
     }
   }
   cta_sync_tc();
-  // ---- batch 2: T1 = dP K (over the two 64 x 64 tiles, which every warp has read) ----------------------------------
-  ok = ok && umma::mbar_wait(bars + 2, 0);  // (the commit of batch 2 below also covers it; this keeps `ok` uniform)
-  umma::fence_after_sync();
+  // ---- batch 2: T1 = dP K (over the 64 x 64 tile, which every warp has read) ---------------------------------------
   if (tid == 0 && ok) {
     umma::gemm<64, KD, 4, false, true, FMT>(tmem + cT1, aXa, 64, aK, 64, false);
     umma::commit(bars + 1);
@@ -286,8 +272,10 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     dst[tid] = src[tid];
     dst[tid + NTHREADS] = src[tid + NTHREADS];
   }
-  {  // epilogue 2: dq = scale (cin Gamma)(dO S^T) + dP K
+  {  // epilogue 2: dq = scale (cin Gamma)(dO S^T) + dP K ; dG partial = q . dq
     float accQ[8][4], accT[8][4];
+    ok = ok && umma::mbar_wait(bars + 2, 0);
+    umma::fence_after_sync();
     if (ok) {
       umma::ld_16x256b<8>(accQ, tl + cQ + kc0);
       umma::wait_ld();
@@ -298,12 +286,6 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
         accQ[nt][1] *= s0;
         accQ[nt][2] *= s1;
         accQ[nt][3] *= s1;
-      }
-      float d0, d1;
-      row_dots_swz<T, 8>(accQ, qS, r0, kc0, lane, d0, d1);
-      if (t == 0) {
-        atomicAdd(dGv + i0, d0);
-        atomicAdd(dGv + i1, d1);
       }
     }
     ok = ok && umma::mbar_wait(bars + 1, 1);
@@ -316,6 +298,14 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) accQ[nt][e] += accT[nt][e];
       }
+      float d0 = 0.f, d1 = 0.f;
+      row_dots_part<T, 8>(accQ, qS, r0, kc0, lane, d0, d1);
+      d0 = quad_sum(d0);
+      d1 = quad_sum(d1);
+      if (t == 0) {
+        rowG[cq * 64 + i0] = d0;
+        rowG[cq * 64 + i1] = d1;
+      }
       store_key_grad<T, 8>(accQ, p.dq_acc, p.dq, m.tok0, i0, m.len, kc0, t, p.H, h, p.Hk, hk);
     }
   }
@@ -326,7 +316,7 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     if (tid == 0) atomicExch(&g_tc_status, 1);
     return;
   }
-  if (tid < 64) p.dga[(size_t)ch_off * 64 + tid] = dGv[tid];
+  if (tid < 64) p.dga[(size_t)ch_off * 64 + tid] = rowG[tid] + rowG[64 + tid];
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -342,8 +332,9 @@ struct SmemK {
   static constexpr int kXb = kT0 + 8192;
   static constexpr int kDp = kXb + 8192;
   static constexpr int kEx = kDp + 8192;
-  static constexpr int kVec = kEx + 64 * VD * 2;        // G beta gam gamr dG dbeta: [64] f32 each; sdot[4]; runs[64] u8
-  static constexpr int kBars = kVec + 6 * 256 + 16 + 64;  // 8 mbarriers, tmem slot
+  // G beta gam gamr [64] f32; rowG rowB [2][64]; colF colB [4][64]; dG[64]; tot[8] sdot[8]; runs[64] u8
+  static constexpr int kVec = kEx + 64 * VD * 2;
+  static constexpr int kBars = kVec + 17 * 256 + 64 + 64;  // 8 mbarriers, tmem slot
   static constexpr int kBytes = kBars + 8 * 8 + 16 + 1024;
   static_assert(kBars % 8 == 0, "mbarrier alignment");
   static_assert(2 * (kBytes + 1024) <= 233472, "two CTAs per SM");
@@ -365,21 +356,25 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* kS = base + L::kK;
-  unsigned char* qS = base + L::kQ;     // later a 64-column half of S^T
-  unsigned char* wS = base + L::kW;     // W^T, later dW
-  unsigned char* dvnS = base + L::kDvn; // dVn^T, later Vn^T (V itself without the delta rule)
+  unsigned char* qS = base + L::kQ;      // later a 64-column half of S^T
+  unsigned char* wS = base + L::kW;      // W^T, later dW
+  unsigned char* dvnS = base + L::kDvn;  // dVn^T, later Vn^T (V itself without the delta rule)
   unsigned char* t0S = base + L::kT0;
-  unsigned char* Xb = base + L::kXb;    // dT0, later dA0 beta_i
-  unsigned char* dpS = base + L::kDp;   // dP, later M1
-  unsigned char* exS = base + L::kEx;   // a 64-column half of dS+^T
+  unsigned char* Xb = base + L::kXb;     // dT0, later dA0 beta_i
+  unsigned char* dpS = base + L::kDp;    // dP, later M1
+  unsigned char* exS = base + L::kEx;    // a 64-column half of dS+^T
   float* Gs = reinterpret_cast<float*>(base + L::kVec);
   float* betas = Gs + 64;
   float* gam = betas + 64;
   float* gamr = gam + 64;
-  float* dGv = gamr + 64;
-  float* dbv = dGv + 64;
-  float* sdot = dbv + 64;
-  unsigned char* runs = reinterpret_cast<unsigned char*>(sdot + 4);
+  float* rowG = gamr + 64;   // [2][64] row-wise dG terms of each column half
+  float* rowB = rowG + 128;  // [2][64] row-wise dbeta terms
+  float* colF = rowB + 128;  // [4][64] column sums of F over each row quadrant
+  float* colB = colF + 256;  // [4][64] column sums of dAg T0 D
+  float* dGv = colB + 256;   // [64]
+  float* tot = dGv + 64;     // [8] per warp: sum over rows of k . (tail Gamma_r)(Vn dS+^T)
+  float* sdot = tot + 8;     // [8] per warp: <S, dS+>
+  unsigned char* runs = reinterpret_cast<unsigned char*>(sdot + 8);
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + L::kBars);
   enum { L0 = 0, L1, L2, M0, M1, M2, M3, M4 };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
@@ -391,9 +386,6 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     for (int i = 0; i < 8; ++i) umma::mbar_init(bars + i, i == L1 ? 2 : 1);
     umma::mbar_init_fence();
     tma::expect_tx(bars + L0, 2 * 64 * KD * 2 + 8192 + (DELTA ? 2 * 64 * VD * 2 + 8192 : 64 * VD * 2));
-    tma::load_tile<64, KD>(kS, &maps.k, 0, hk, m.tok0, bars + L0);
-    tma::load_tile<64, KD>(qS, &maps.q, 0, hk, m.tok0, bars + L0);
-    tma::load_bulk(dpS, p.dp + (size_t)ch_off * 8192, 8192, bars + L0);
     if (DELTA) {
       tma::load_tile<VD, 64>(wS, &maps.w, 0, 0, ch_off * VD, bars + L0);
       tma::load_tile<VD, 64>(dvnS, &maps.dvn, 0, 0, ch_off * VD, bars + L0);
@@ -401,6 +393,9 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     } else {
       tma::load_tile<64, VD>(dvnS, &maps.v, 0, h, m.tok0, bars + L0);
     }
+    tma::load_tile<64, KD>(kS, &maps.k, 0, hk, m.tok0, bars + L0);
+    tma::load_tile<64, KD>(qS, &maps.q, 0, hk, m.tok0, bars + L0);
+    tma::load_bulk(dpS, p.dp + (size_t)ch_off * 8192, 8192, bars + L0);
     tma::expect_tx(bars + L1, VD * 64 * 2);  // first half of dS+^T: its tile is free from the start
     tma::load_3d(exS, &maps.dh, 0, 0, ch_off * VD, bars + L1);
   }
@@ -409,9 +404,6 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     Gs[tid] = p.gates[(long)ch_off * 128 + tid];
     betas[tid] = p.gates[(long)ch_off * 128 + 64 + tid];
     runs[tid] = p.runs[(long)c * 64 + tid];
-    dGv[tid] = p.dga[(size_t)ch_off * 64 + tid];
-    dbv[tid] = 0.f;
-    if (tid == 0) sdot[0] = 0.f;
   }
   __syncthreads();
   if (tid < 64) {
@@ -432,29 +424,35 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   const int i0 = r0 + g, i1 = r0 + g + 8;
   const float G0 = Gs[i0], G1 = Gs[i1];
   const int run0 = runs[i0], run1 = runs[i1];
+  float rG0 = 0.f, rG1 = 0.f;  // this thread's part of the row-wise dG terms of rows i0, i1
+  float rB0 = 0.f, rB1 = 0.f;  // likewise for dbeta
+  float tot_part = 0.f, sdot_part = 0.f;
 
-  // ---- batch 1: accK = dP^T Q ; P1 = dVn W^T ; P2 = K K^T ----------------------------------------------------------
+  // ---- batch 1: P1 = dVn W^T ; P2 = K K^T ; accK = dP^T Q ----------------------------------------------------------
   if (tid == 0 && ok) {
     if (DELTA) {
       umma::gemm<64, 64, VD / 16, true, true, FMT>(tmem + cP1, aDvn, VD, aW, VD, false);
+      umma::commit(bars + M0);
       umma::gemm<64, 64, KD / 16, false, false, FMT>(tmem + cP2, aK, 64, aK, 64, false);
     }
     umma::gemm<64, KD, 4, true, true, FMT>(tmem + cK, aDp, 64, aQ, 64, false);
-    umma::commit(bars + M0);
+    umma::commit(bars + M4);  // (M4 is reused by the second state half: its first phase ends here)
   }
   __syncwarp();
-  ok = ok && umma::mbar_wait(bars + M0, 0);
-  umma::fence_after_sync();
-  if (tid == 0 && ok) {  // q, dP, W^T, dVn^T are consumed: fetch the second-phase tiles over them
-    tma::expect_tx(bars + L1, VD * 64 * 2 + (DELTA ? 2 * 64 * VD * 2 : 0));
-    tma::load_3d(qS, &maps.h, 0, 0, ch_off * VD, bars + L1);
-    if (DELTA) {
-      tma::load_tile<64, VD>(wS, &maps.dv, 0, h, m.tok0, bars + L1);
-      tma::load_tile<VD, 64>(dvnS, &maps.vn, 0, 0, ch_off * VD, bars + L1);
-    }
-  }
-  __syncwarp();
+  // subtracts k_j . (dP^T Q)_j, the column sums of dP (Q K^T), from the dG rows; the accumulator must be read
+  // before the dA0 terms are added to it
+  auto key_score_dots = [&]() {
+    float accK[8][4];
+    umma::ld_16x256b<8>(accK, tl + cK + 64 * cq);
+    umma::wait_ld();
+    float d0 = 0.f, d1 = 0.f;
+    row_dots_part<T, 8>(accK, kS, r0, 64 * cq, lane, d0, d1);
+    rG0 -= d0;
+    rG1 -= d1;
+  };
   if (DELTA) {
+    ok = ok && umma::mbar_wait(bars + M0, 0);
+    umma::fence_after_sync();
     if (ok) {  // dAg = tril(dVn W^T); F = dAg Ag; dT0 = dAg D beta_j
       float accA[4][4], accF[4][4], accB[4][4];
       umma::ld_16x256b<4>(accA, tl + cP1 + cc0);
@@ -477,16 +475,25 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
           accA[nt][e] = dag * d * bj;
         }
       }
-      row_sums_add<4>(accF, dGv, r0, lane, 1.f);
-      col_sums_add<4>(accF, dGv, cc0, lane, -1.f);
-      col_sums_add<4>(accB, dbv, cc0, lane, 1.f);
       store_acc_swz<T, 4>(Xb, r0, cc0, accA, lane);
+      row_sums_acc<4>(accF, rG0, rG1);
+      col_sums_store<4>(accF, colF + (warp & 3) * 64, cc0, lane);
+      col_sums_store<4>(accB, colB + (warp & 3) * 64, cc0, lane);
     }
     cta_sync_tc();
     // ---- batch 2: M1 = dT0 T0^T ------------------------------------------------------------------------------------
     if (tid == 0 && ok) {
       umma::gemm<64, 64, 4, false, false, FMT>(tmem + cP1, aXb, 64, aT0, 64, false);
       umma::commit(bars + M1);
+    }
+    __syncwarp();
+    ok = ok && umma::mbar_wait(bars + M4, 0);  // dP^T Q: long done; q, dP, W^T, dVn^T are consumed
+    umma::fence_after_sync();
+    if (tid == 0 && ok) {  // fetch the second-phase tiles over them
+      tma::expect_tx(bars + L1, VD * 64 * 2 + 2 * 64 * VD * 2);
+      tma::load_3d(qS, &maps.h, 0, 0, ch_off * VD, bars + L1);
+      tma::load_tile<64, VD>(wS, &maps.dv, 0, h, m.tok0, bars + L1);
+      tma::load_tile<VD, 64>(dvnS, &maps.vn, 0, 0, ch_off * VD, bars + L1);
     }
     __syncwarp();
     ok = ok && umma::mbar_wait(bars + M1, 0);
@@ -504,6 +511,7 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
       umma::commit(bars + M2);
     }
     __syncwarp();
+    if (ok) key_score_dots();  // while the product runs
     ok = ok && umma::mbar_wait(bars + M2, 0);
     umma::fence_after_sync();
     if (ok) {  // dA0 = -strict(P1) same; dbeta_i += sum_j dA0_ij (k_i . k_j); Xb = dA0 beta_i
@@ -522,9 +530,18 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
           accA0[nt][e] = a * ((e >> 1) ? b1 : b0);
         }
       }
-      row_sums_add<4>(accKK, dbv, r0, lane, 1.f);
       store_acc_swz<T, 4>(Xb, r0, cc0, accA0, lane);
+      row_sums_acc<4>(accKK, rB0, rB1);
     }
+  } else {
+    ok = ok && umma::mbar_wait(bars + M4, 0);
+    umma::fence_after_sync();
+    if (tid == 0 && ok) {  // q and dP are consumed: fetch the first half of S^T over q
+      tma::expect_tx(bars + L1, VD * 64 * 2);
+      tma::load_3d(qS, &maps.h, 0, 0, ch_off * VD, bars + L1);
+    }
+    __syncwarp();
+    if (ok) key_score_dots();
   }
   ok = ok && umma::mbar_wait(bars + L1, 0);
   if (DELTA && m.len < 64) zero_tail_rows<T, VD>(wS, m.len, tid);  // dW rows past the end were never written
@@ -534,33 +551,34 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     // ---- state terms over key columns [64 hh, 64 hh + 64): P1 = dW S^T, P2 = Vn dS+^T (first pass also the dA0 terms)
     if (tid == 0 && ok) {
       if (DELTA) {
+        umma::gemm<64, 64, VD / 16, false, true, FMT>(tmem + cP1, aW, 64, aQ, VD, false);
+        umma::gemm<64, 64, VD / 16, true, true, FMT>(tmem + cP2, aDvn, VD, aEx, VD, false);
         if (hh == 0) {
           umma::gemm<64, KD, 4, false, true, FMT>(tmem + cK, aXb, 64, aK, 64, true);
           umma::gemm<64, KD, 4, true, true, FMT>(tmem + cK, aXb, 64, aK, 64, true);
         }
-        umma::gemm<64, 64, VD / 16, false, true, FMT>(tmem + cP1, aW, 64, aQ, VD, false);
-        umma::gemm<64, 64, VD / 16, true, true, FMT>(tmem + cP2, aDvn, VD, aEx, VD, false);
       } else {
         umma::gemm<64, 64, VD / 16, false, true, FMT>(tmem + cP2, aDvn, 64, aEx, VD, false);
       }
-      umma::commit(bars + M3 + hh);
+      umma::commit(bars + (hh == 0 ? M3 : M4));
     }
     __syncwarp();
     {  // keep gamma <S, dS+> over this half while the products run (both tiles share one layout)
-      float part = 0.f;
-      const uint32_t* a = reinterpret_cast<const uint32_t*>(qS);
-      const uint32_t* b = reinterpret_cast<const uint32_t*>(exS);
-#pragma unroll 4
-      for (int idx = tid; idx < VD * 64 / 2; idx += NTHREADS) {
-        const float2 x = unpack2<T>(a[idx]), y = unpack2<T>(b[idx]);
-        part += x.x * y.x + x.y * y.y;
-      }
+      const uint4* a = reinterpret_cast<const uint4*>(qS);
+      const uint4* b = reinterpret_cast<const uint4*>(exS);
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-      if (lane == 0) atomicAdd(sdot, part);
+      for (int it = 0; it < VD * 64 * 2 / 16 / NTHREADS; ++it) {
+        const uint4 x = a[tid + it * NTHREADS], y = b[tid + it * NTHREADS];
+        const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 u = unpack2<T>(xs[e]), v = unpack2<T>(ys[e]);
+          sdot_part += u.x * v.x + u.y * v.y;
+        }
+      }
     }
     if (hh == 0) __syncthreads();  // every thread is past its reads of the two half tiles
-    ok = ok && umma::mbar_wait(bars + M3 + hh, 0);
+    ok = ok && umma::mbar_wait(bars + (hh == 0 ? M3 : M4), hh);
     umma::fence_after_sync();
     if (hh == 0 && tid == 0 && ok) {  // the products are done with the half tiles too: fetch the second halves
       tma::expect_tx(bars + L2, 2 * VD * 64 * 2);
@@ -571,7 +589,6 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     if (ok) {  // dk columns and the state terms of dG
       const int kc = 64 * hh + cc0;
       float accK[4][4], accT[4][4];
-      float d0, d1;
       umma::ld_16x256b<4>(accK, tl + cK + kc);
       if (DELTA) {
         umma::ld_16x256b<4>(accT, tl + cP1 + cc0);
@@ -586,11 +603,10 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) accK[nt][e] -= accT[nt][e];
         }
-        row_dots_swz<T, 4>(accT, kS, r0, kc, lane, d0, d1);
-        if (t == 0) {
-          atomicAdd(dGv + i0, -d0);
-          atomicAdd(dGv + i1, -d1);
-        }
+        float d0 = 0.f, d1 = 0.f;
+        row_dots_part<T, 4>(accT, kS, r0, kc, lane, d0, d1);
+        rG0 -= d0;
+        rG1 -= d1;
       }
       umma::ld_16x256b<4>(accT, tl + cP2 + cc0);
       umma::wait_ld();
@@ -604,12 +620,11 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) accK[nt][e] += accT[nt][e];
       }
-      row_dots_swz<T, 4>(accT, kS, r0, kc, lane, d0, d1);
-      if (t == 0) {
-        atomicAdd(dGv + i0, -d0);
-        atomicAdd(dGv + i1, -d1);
-        atomicAdd(dGv + 63, d0 + d1);
-      }
+      float d0 = 0.f, d1 = 0.f;
+      row_dots_part<T, 4>(accT, kS, r0, kc, lane, d0, d1);
+      rG0 -= d0;
+      rG1 -= d1;
+      tot_part += d0 + d1;
       store_key_grad<T, 4>(accK, p.dk_acc, p.dk, m.tok0, i0, m.len, kc, t, p.H, h, p.Hk, hk);
     }
     if (hh == 0) {
@@ -619,6 +634,26 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
       umma::fence_after_sync();
     }
   }
+  // ---- fold the per-thread and per-warp partial sums ----------------------------------------------------------------
+  rG0 = quad_sum(rG0);
+  rG1 = quad_sum(rG1);
+  rB0 = quad_sum(rB0);
+  rB1 = quad_sum(rB1);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    tot_part += __shfl_xor_sync(0xffffffffu, tot_part, off);
+    sdot_part += __shfl_xor_sync(0xffffffffu, sdot_part, off);
+  }
+  if (t == 0) {
+    rowG[cq * 64 + i0] = rG0;
+    rowG[cq * 64 + i1] = rG1;
+    rowB[cq * 64 + i0] = rB0;
+    rowB[cq * 64 + i1] = rB1;
+  }
+  if (lane == 0) {
+    tot[warp] = tot_part;
+    sdot[warp] = sdot_part;
+  }
   umma::fence_before_sync();
   __syncthreads();
   if (warp == 1) umma::tmem_dealloc(tmem, 256);
@@ -626,13 +661,29 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     if (tid == 0) atomicExch(&g_tc_status, 1);
     return;
   }
+  if (tid < 64) {
+    float dG = p.dga[(size_t)ch_off * 64 + tid] + rowG[tid] + rowG[64 + tid];
+    if (DELTA) dG -= colF[tid] + colF[64 + tid] + colF[128 + tid] + colF[192 + tid];
+    if (tid == 63) {
+#pragma unroll
+      for (int w = 0; w < 8; ++w) dG += tot[w];
+    }
+    dGv[tid] = dG;
+  }
+  __syncthreads();
   if (tid < 64) {  // dg = reverse cumulative sum of dG over the chunk
     float acc = 0.f;
     for (int j = 63; j >= tid; --j) acc += dGv[j];
-    acc += keep_gamma(Gs, runs, m.flags) * sdot[0];
+    float sd = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sd += sdot[w];
+    acc += keep_gamma(Gs, runs, m.flags) * sd;
     if (tid < m.len) {
       if (p.dg) p.dg[((long)m.tok0 + tid) * p.H + h] = acc;
-      if (DELTA) p.dbeta[((long)m.tok0 + tid) * p.H + h] = dbv[tid];
+      if (DELTA) {
+        p.dbeta[((long)m.tok0 + tid) * p.H + h] =
+            rowB[tid] + rowB[64 + tid] + colB[tid] + colB[64 + tid] + colB[128 + tid] + colB[192 + tid];
+      }
     }
   }
 }

@@ -95,10 +95,13 @@ struct KktParams {
 
 // T0 for one (chunk, head). 4 warps: K K^T with mma.sync (each warp 16 rows x 64 columns), then the inverse of
 // the unit lower-triangular 64 x 64 matrix in fp32: the four 16 x 16 diagonal blocks by forward substitution
-// (one column per thread), then X21 = -X22 L21 X11 at block sizes 16 and 32.
+// (one column per thread), then X21 = -X22 L21 X11 at block sizes 16 and 32. The block products are bound by
+// shared-memory loads, so every thread computes a strip of four adjacent columns (one 16-byte load per operand row)
+// and, at block size 32, of two rows. The fp32 inverse X takes over the key tile once K K^T is in registers.
 template <typename T, int K>
 __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
-  constexpr int LDK = K + 8, LDA = 65, LDM = 33;
+  constexpr int LDK = K + 8, LDA = 68, LDM = 36;
+  constexpr int kFirst = 64 * LDK * (int)sizeof(T) > 64 * LDA * 4 ? 64 * LDK * (int)sizeof(T) : 64 * LDA * 4;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
   if (m.len == 0) return;
@@ -106,9 +109,9 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* ks = reinterpret_cast<T*>(smem_raw);
-  float* A = reinterpret_cast<float*>(ks + 64 * LDK);
-  float* X = A + 64 * LDA;
-  float* M = X + 64 * LDA;        // [32][33]
+  float* X = reinterpret_cast<float*>(smem_raw);  // [64][LDA], after the key tile is consumed
+  float* A = reinterpret_cast<float*>(smem_raw + kFirst);
+  float* M = A + 64 * LDA;        // [32][LDM]
   float* betas = M + 32 * LDM;    // [64]
   float* Gs = betas + 64;         // [64]
   int* run = reinterpret_cast<int*>(Gs + 64);
@@ -121,7 +124,6 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
     Gs[tid] = p.gates[((long)c * p.H + h) * 128 + tid];
     run[tid] = p.runs[(long)c * 64 + tid];
   }
-  for (int idx = tid; idx < 64 * LDA; idx += 128) X[idx] = 0.f;
   cp_async_wait<0>();
   __syncthreads();
 
@@ -129,13 +131,20 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
     float acc[8][4];
     zero_acc(acc);
     warp_gemm<T, 8, K / 16, A_ROW, B_NK>(acc, ks + warp * 16 * LDK, LDK, ks, LDK, lane);
+    __syncthreads();  // every warp has read the key tile: X may take its place
+    for (int idx = tid; idx < 64 * LDA / 4; idx += 128) reinterpret_cast<float4*>(X)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = warp * 16 + g + ((e >> 1) << 3), j = nt * 8 + 2 * t + (e & 1);
-        A[i * LDA + j] = (j < i && run[i] == run[j]) ? betas[i] * acc[nt][e] : 0.f;
+      for (int hh = 0; hh < 2; ++hh) {
+        const int i = warp * 16 + g + 8 * hh, j = nt * 8 + 2 * t;
+        const float bi = betas[i];
+        const int ri = run[i];
+        float2 v;
+        v.x = (j < i && ri == run[j]) ? bi * acc[nt][2 * hh] : 0.f;
+        v.y = (j + 1 < i && ri == run[j + 1]) ? bi * acc[nt][2 * hh + 1] : 0.f;
+        *reinterpret_cast<float2*>(A + i * LDA + j) = v;
       }
     }
   }
@@ -155,47 +164,71 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
   }
   __syncthreads();
 
-  // level 1: two problems (blocks 0-1 and 2-3), 16 x 16 each
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const int o = tid * 4 + e, pr = o >> 8, i = (o >> 4) & 15, j = o & 15;
+  {  // level 1: two problems (blocks 0-1 and 2-3), 16 x 16 each; thread = one row, four columns
+    const int pr = tid >> 6, i = (tid >> 2) & 15, j4 = (tid & 3) * 4;
     const int r0 = 32 * pr + 16, c0 = 32 * pr;
-    float s = 0.f;
-    for (int mm = 0; mm < 16; ++mm) s += A[(r0 + i) * LDA + c0 + mm] * X[(c0 + mm) * LDA + c0 + j];
-    M[(pr * 16 + i) * LDM + j] = s;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int mm = 0; mm < 16; ++mm) {
+      const float a = A[(r0 + i) * LDA + c0 + mm];
+      const float4 x = *reinterpret_cast<const float4*>(X + (c0 + mm) * LDA + c0 + j4);
+      s[0] += a * x.x;
+      s[1] += a * x.y;
+      s[2] += a * x.z;
+      s[3] += a * x.w;
+    }
+    *reinterpret_cast<float4*>(M + (pr * 16 + i) * LDM + j4) = make_float4(s[0], s[1], s[2], s[3]);
+    __syncthreads();
+    s[0] = s[1] = s[2] = s[3] = 0.f;
+#pragma unroll
+    for (int mm = 0; mm < 16; ++mm) {
+      const float a = X[(r0 + i) * LDA + r0 + mm];
+      const float4 x = *reinterpret_cast<const float4*>(M + (pr * 16 + mm) * LDM + j4);
+      s[0] += a * x.x;
+      s[1] += a * x.y;
+      s[2] += a * x.z;
+      s[3] += a * x.w;
+    }
+    *reinterpret_cast<float4*>(X + (r0 + i) * LDA + c0 + j4) = make_float4(-s[0], -s[1], -s[2], -s[3]);
   }
   __syncthreads();
+  {  // level 2: rows 32-63, columns 0-31; thread = rows i and i + 16, four columns
+    const int i = tid >> 3, j4 = (tid & 7) * 4;
+    float s[2][4] = {};
+#pragma unroll 8
+    for (int mm = 0; mm < 32; ++mm) {
+      const float a0 = A[(32 + i) * LDA + mm], a1 = A[(48 + i) * LDA + mm];
+      const float4 x = *reinterpret_cast<const float4*>(X + mm * LDA + j4);
+      s[0][0] += a0 * x.x;
+      s[0][1] += a0 * x.y;
+      s[0][2] += a0 * x.z;
+      s[0][3] += a0 * x.w;
+      s[1][0] += a1 * x.x;
+      s[1][1] += a1 * x.y;
+      s[1][2] += a1 * x.z;
+      s[1][3] += a1 * x.w;
+    }
+    // (the level-1 contents of M were consumed before the barrier above)
+    *reinterpret_cast<float4*>(M + i * LDM + j4) = make_float4(s[0][0], s[0][1], s[0][2], s[0][3]);
+    *reinterpret_cast<float4*>(M + (16 + i) * LDM + j4) = make_float4(s[1][0], s[1][1], s[1][2], s[1][3]);
+    __syncthreads();
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const int o = tid * 4 + e, pr = o >> 8, i = (o >> 4) & 15, j = o & 15;
-    const int r0 = 32 * pr + 16, c0 = 32 * pr;
-    float s = 0.f;
-    for (int mm = 0; mm < 16; ++mm) s += X[(r0 + i) * LDA + r0 + mm] * M[(pr * 16 + mm) * LDM + j];
-    X[(r0 + i) * LDA + c0 + j] = -s;
-  }
-  __syncthreads();
-  // level 2: rows 32-63, columns 0-31
-  float m2[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const int o = tid * 8 + e, i = o >> 5, j = o & 31;
-    float s = 0.f;
-    for (int mm = 0; mm < 32; ++mm) s += A[(32 + i) * LDA + mm] * X[mm * LDA + j];
-    m2[e] = s;
-  }
-  __syncthreads();  // level-1 M fully consumed before it is overwritten
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const int o = tid * 8 + e, i = o >> 5, j = o & 31;
-    M[i * LDM + j] = m2[e];
-  }
-  __syncthreads();
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const int o = tid * 8 + e, i = o >> 5, j = o & 31;
-    float s = 0.f;
-    for (int mm = 0; mm < 32; ++mm) s += X[(32 + i) * LDA + 32 + mm] * M[mm * LDM + j];
-    X[(32 + i) * LDA + j] = -s;
+    for (int e = 0; e < 4; ++e) s[0][e] = s[1][e] = 0.f;
+#pragma unroll 8
+    for (int mm = 0; mm < 32; ++mm) {
+      const float a0 = X[(32 + i) * LDA + 32 + mm], a1 = X[(48 + i) * LDA + 32 + mm];
+      const float4 x = *reinterpret_cast<const float4*>(M + mm * LDM + j4);
+      s[0][0] += a0 * x.x;
+      s[0][1] += a0 * x.y;
+      s[0][2] += a0 * x.z;
+      s[0][3] += a0 * x.w;
+      s[1][0] += a1 * x.x;
+      s[1][1] += a1 * x.y;
+      s[1][2] += a1 * x.z;
+      s[1][3] += a1 * x.w;
+    }
+    *reinterpret_cast<float4*>(X + (32 + i) * LDA + j4) = make_float4(-s[0][0], -s[0][1], -s[0][2], -s[0][3]);
+    *reinterpret_cast<float4*>(X + (48 + i) * LDA + j4) = make_float4(-s[1][0], -s[1][1], -s[1][2], -s[1][3]);
   }
   __syncthreads();
 
@@ -230,7 +263,8 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
 
 template <typename T, int K>
 int launch_kkt(const KktParams& kp, int blocks, cudaStream_t s) {
-  const size_t smem = 64 * (K + 8) * sizeof(T) + (2 * 64 * 65 + 32 * 33 + 128) * sizeof(float) + 64 * sizeof(int);
+  const size_t first = 64 * (K + 8) * sizeof(T) > 64 * 68 * sizeof(float) ? 64 * (K + 8) * sizeof(T) : 64 * 68 * sizeof(float);
+  const size_t smem = first + (64 * 68 + 32 * 36 + 128) * sizeof(float) + 64 * sizeof(int);
   auto* kern = kkt_inv_kernel<T, K>;
   if (smem > 48 * 1024) JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
