@@ -71,11 +71,17 @@ def kernel_model(K: int, V: int, delta: bool, save: bool) -> dict:
     gates = 128 * 4 + 64
     m = {}
     if delta:
-        m["kkt_inv"] = dict(bytes=qk + gates + cc, mac=64 * 64 * K)
-    m["sg_fwd"] = dict(bytes=2 * qk + vv + (cc if delta else 0) + gates + vv + (st + (vv if delta else 0) if save else 0),
+        m["kkt_inv"] = dict(bytes=qk + gates + 2 * cc, mac=64 * 64 * K)  # writes T0 and its gated form Ag
+    m["sg_fwd"] = dict(bytes=2 * qk + vv + (cc if delta else 0) + gates + vv + (st + (2 * vv if delta else 0) if save else 0),  # residuals h, Vn, W
                        mac=64 * 64 * K + 64 * 64 * V * (2 if delta else 1) + K * V * 64 * (3 if delta else 2))
     m["sg_bwd_state"] = dict(bytes=2 * qk + vv + (cc if delta else 0) + gates + st + vv + (vv if delta else 0),
                              mac=64 * K * V + 64 * 64 * V * (2 if delta else 1) + K * V * 64 * (2 if delta else 1))
+    # tcgen05 path (K = V = 128): the chunk gradients are two kernels, dP and a dG partial go through the scratch
+    m["sg_grads_q"] = dict(bytes=2 * vv + st + 2 * qk + gates + cc + qk + 256,
+                           mac=64 * 64 * V + 64 * K * V + 64 * 64 * K)
+    m["sg_grads_k"] = dict(
+        bytes=2 * qk + cc + 2 * st + gates + 256 + qk + ((4 * vv + cc) if delta else vv),
+        mac=64 * 64 * K + 64 * K * V + ((64 * 64 * V + 64 * 64 * K + 2 * 64 ** 3 + 2 * 64 * 64 * K + 64 * K * V) if delta else 0))
     m["sg_chunk_grads"] = dict(
         bytes=2 * qk + 2 * vv + 2 * st + gates + 2 * qk + ((cc + 3 * vv) if delta else 0),
         mac=64 * 64 * V + 64 * K * V + 64 * 64 * K * 2 + 64 * K * V + ((64 * 64 * V + 64 * K * V + 2 * 64 * 64 * K) if delta else 0))

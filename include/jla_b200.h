@@ -147,6 +147,23 @@ int jla_linear_attention_bwd(const jla_problem* p, const jla_bwd_io* io, jla_str
 size_t jla_noalloc_scratch_limit(void);
 int jla_linear_attention_fwd_noalloc(const jla_problem* p, void* o, float* final_state, jla_stream_t stream);
 
+/* Element-wise glue of the Mamba-2 SSD layer around the simple_gla kernels, fused so every [tokens, H, P] tensor is
+ * read and written once; replaces the XLA fusions around the kernel call in mamba2_ssd (src/jla/layers/ssm.py:207-229)
+ * and their transposes (ssm.py:76-84). 16-bit x, v, o, y and gradients; dt, A, D, g and their gradients f32;
+ * tokens = B * T; P a multiple of 8. dA and dD ([H]) are zeroed by the call before it accumulates into them.
+ *   inputs_fwd:  v = round(x * dt), g = dt * A
+ *   inputs_bwd:  dx = round(dv * dt), ddt = sum_p dv * x + dg * A, dA = sum_tokens dg * dt
+ *   output_fwd:  y = round(o + D * x)
+ *   output_bwd:  dx = round(D * dy), dD = sum_{tokens, p} dy * x      (do = dy needs no kernel) */
+int jla_ssd_inputs_fwd(int dtype, int64_t tokens, int H, int P, const void* x, const float* dt, const float* a, void* v,
+                       float* g, jla_stream_t stream);
+int jla_ssd_inputs_bwd(int dtype, int64_t tokens, int H, int P, const void* x, const float* dt, const float* a,
+                       const void* dv, const float* dg, void* dx, float* ddt, float* da, jla_stream_t stream);
+int jla_ssd_output_fwd(int dtype, int64_t tokens, int H, int P, const void* o, const void* x, const float* d, void* y,
+                       jla_stream_t stream);
+int jla_ssd_output_bwd(int dtype, int64_t tokens, int H, int P, const void* dy, const void* x, const float* d, void* dx,
+                       float* dd, jla_stream_t stream);
+
 /* Diagnostics: where the chunked path keeps its intermediates, so that tests can compare them stage by stage
  * with the CPU model (the reference checks its kernels per stage too:
  * tests/test_mosaic_gpu_gated_delta_rule.py:104-146). Byte offsets into the residual buffer written by a forward

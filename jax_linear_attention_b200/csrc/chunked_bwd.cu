@@ -219,6 +219,9 @@ __global__ void __launch_bounds__(256, 1) sg_bwd_state_kernel(BwdParams p) {
 // ---------------------------------------------------------------------------------------------------------
 // chunk-parallel gradients
 
+// Reductions avoid shared-memory float atomics (a compare-and-swap loop): every warp adds into slots that only it
+// writes (row sums: one slot array per column half; column sums: one per row quadrant), always from the same lane,
+// and the slots are summed once at the end.
 // vec[row] += sign * sum over this thread's columns, reduced over the 4 lanes of a quad.
 template <int NT>
 __device__ __forceinline__ void row_sums_add(const float (&x)[NT][4], float* vec, int r0, int lane, float sign) {
@@ -233,8 +236,8 @@ __device__ __forceinline__ void row_sums_add(const float (&x)[NT][4], float* vec
   b += __shfl_xor_sync(0xffffffffu, b, 1);
   b += __shfl_xor_sync(0xffffffffu, b, 2);
   if ((lane & 3) == 0) {
-    atomicAdd(vec + r0 + (lane >> 2), sign * a);
-    atomicAdd(vec + r0 + (lane >> 2) + 8, sign * b);
+    vec[r0 + (lane >> 2)] += sign * a;
+    vec[r0 + (lane >> 2) + 8] += sign * b;
   }
 }
 
@@ -250,8 +253,8 @@ __device__ __forceinline__ void col_sums_add(const float (&x)[NT][4], float* vec
       b += __shfl_xor_sync(0xffffffffu, b, off);
     }
     if (lane < 4) {
-      atomicAdd(vec + c0 + nt * 8 + 2 * lane, sign * a);
-      atomicAdd(vec + c0 + nt * 8 + 2 * lane + 1, sign * b);
+      vec[c0 + nt * 8 + 2 * lane] += sign * a;
+      vec[c0 + nt * 8 + 2 * lane + 1] += sign * b;
     }
   }
 }
@@ -281,7 +284,7 @@ struct GradSmem {
   static constexpr int LDK = K + 8, LDV = V + 8, LDC = 72;
   // k | q | do (q and do contiguous: later reused for dS+) | v (W, then dW) | Vn | S | T0, Xa, Xb, Xc | vectors
   static constexpr int kElems = 2 * 64 * LDK + 2 * 64 * LDV + (DELTA ? 64 * LDV : 0) + K * LDV + 4 * 64 * LDC;
-  static constexpr int kBytes = kElems * 2 + (128 + 64 + 64 + 4) * 4 + 64;
+  static constexpr int kBytes = kElems * 2 + (128 + 13 * 64 + 16) * 4 + 64;
   static_assert(K * LDV <= 64 * LDK + 64 * LDV, "dS+ must fit in the q | do region");
 };
 
@@ -311,10 +314,16 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
   T* Xc = Xb + 64 * LDC;
   float* Gs = reinterpret_cast<float*>(smem_raw + L::kElems * 2);
   float* betas = Gs + 64;
-  float* dGv = betas + 64;
-  float* dbv = dGv + 64;
-  float* sdot = dbv + 64;
-  unsigned char* runs = reinterpret_cast<unsigned char*>(sdot + 4);
+  float* dGrow = betas + 64;   // [2][64] row-wise dG terms per column half
+  float* dGcol = dGrow + 128;  // [4][64] column-wise dG terms per row quadrant
+  float* dbrow = dGcol + 256;  // [2][64]
+  float* dbcol = dbrow + 128;  // [4][64]
+  float* dGv = dbcol + 256;    // [64] folded dG
+  float* tot = dGv + 64;       // [8] per warp
+  float* sdot = tot + 8;       // [8] per warp
+  unsigned char* runs = reinterpret_cast<unsigned char*>(sdot + 8);
+  float tot_part = 0.f;
+  const int quad = warp & 3;
   T* dSS = qS;  // dS+ overlays q | do once both are dead
 
   const long ch_off = (long)c * p.H + h;
@@ -335,11 +344,7 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
   load_tile_async<T, 64, K>(qS, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * K, (long)p.Hk * K, m.len,
                             tid, 256);
   cp_async_commit();
-  if (tid < 64) {
-    dGv[tid] = 0.f;
-    dbv[tid] = 0.f;
-  }
-  if (tid == 0) sdot[0] = 0.f;
+  for (int idx = tid; idx < 12 * 64; idx += 256) dGrow[idx] = 0.f;
   cp_async_wait<1>();
   __syncthreads();
 
@@ -381,8 +386,8 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) accE[nt][e] *= accP[nt][e];
     }
-    row_sums_add<4>(accE, dGv, r0, lane, 1.f);
-    col_sums_add<4>(accE, dGv, cc0, lane, -1.f);
+    row_sums_add<4>(accE, dGrow + ch * 64, r0, lane, 1.f);
+    col_sums_add<4>(accE, dGcol + quad * 64, cc0, lane, -1.f);
     store_acc<T, 4>(Xa, LDC, r0, cc0, accP, lane);
   }
   float accQ[KNT][4];
@@ -400,8 +405,8 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
     float d0, d1;
     row_dots<T, KNT>(accQ, qS, LDK, r0, kc0, lane, d0, d1);
     if (t == 0) {
-      atomicAdd(dGv + r0 + g, d0);
-      atomicAdd(dGv + r0 + g + 8, d1);
+      dGrow[ch * 64 + r0 + g] += d0;
+      dGrow[ch * 64 + r0 + g + 8] += d1;
     }
   }
   __syncthreads();  // S2: Xa = dP complete
@@ -451,9 +456,9 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
           accA[nt][e] = dag * d * betas[j];     // dT0
         }
       }
-      row_sums_add<4>(accF, dGv, r0, lane, 1.f);
-      col_sums_add<4>(accF, dGv, cc0, lane, -1.f);
-      col_sums_add<4>(accB, dbv, cc0, lane, 1.f);
+      row_sums_add<4>(accF, dGrow + ch * 64, r0, lane, 1.f);
+      col_sums_add<4>(accF, dGcol + quad * 64, cc0, lane, -1.f);
+      col_sums_add<4>(accB, dbcol + quad * 64, cc0, lane, 1.f);
       store_acc<T, 4>(Xb, LDC, r0, cc0, accA, lane);
     }
     __syncthreads();  // S5: Xb = dT0 complete; W and dVn dead
@@ -485,7 +490,7 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
           accA0[nt][e] = a * betas[i];
         }
       }
-      row_sums_add<4>(accKK, dbv, r0, lane, 1.f);
+      row_sums_add<4>(accKK, dbrow + ch * 64, r0, lane, 1.f);
       store_acc<T, 4>(Xb, LDC, r0, cc0, accA0, lane);
     }
     __syncthreads();  // S7: Xb = dA0 beta_i complete
@@ -515,8 +520,8 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
       }
       row_dots<T, KNT>(accT, kS, LDK, r0, kc0, lane, d0, d1);
       if (t == 0) {
-        atomicAdd(dGv + r0 + g, -d0);
-        atomicAdd(dGv + r0 + g + 8, -d1);
+        dGrow[ch * 64 + r0 + g] -= d0;
+        dGrow[ch * 64 + r0 + g + 8] -= d1;
       }
     }
     zero_acc(accT);  // (tail Gamma_r)(Vn dS+^T)
@@ -532,9 +537,9 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
     }
     row_dots<T, KNT>(accT, kS, LDK, r0, kc0, lane, d0, d1);
     if (t == 0) {
-      atomicAdd(dGv + r0 + g, -d0);
-      atomicAdd(dGv + r0 + g + 8, -d1);
-      atomicAdd(dGv + 63, d0 + d1);
+      dGrow[ch * 64 + r0 + g] -= d0;
+      dGrow[ch * 64 + r0 + g + 8] -= d1;
+      tot_part += d0 + d1;
     }
     // keep gamma <S, dS+>
     float part = 0.f;
@@ -546,7 +551,7 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-    if (lane == 0) atomicAdd(sdot, part);
+    if (lane == 0) sdot[warp] = part;
     // dk out
     const long tok0 = (long)m.tok0 + r0 + g;
 #pragma unroll
@@ -565,15 +570,33 @@ __global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
       }
     }
   }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) tot_part += __shfl_xor_sync(0xffffffffu, tot_part, off);
+  if (lane == 0) tot[warp] = tot_part;
   __syncthreads();  // S9
+  if (tid < 64) {
+    float dG = dGrow[tid] + dGrow[64 + tid] + dGcol[tid] + dGcol[64 + tid] + dGcol[128 + tid] + dGcol[192 + tid];
+    if (tid == 63) {
+#pragma unroll
+      for (int w = 0; w < 8; ++w) dG += tot[w];
+    }
+    dGv[tid] = dG;
+  }
+  __syncthreads();
   if (tid < 64) {  // 7. dg = reverse cumulative sum of dG over the chunk
     float acc = 0.f;
     for (int j = 63; j >= tid; --j) acc += dGv[j];
     // the keep gamma <S, dS+> term belongs to the chunk's last position, so it is part of every suffix sum
-    acc += keep_gamma(Gs, runs, m.flags) * sdot[0];
+    float sd = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sd += sdot[w];
+    acc += keep_gamma(Gs, runs, m.flags) * sd;
     if (tid < m.len) {
       if (p.dg) p.dg[((long)m.tok0 + tid) * p.H + h] = acc;
-      if (DELTA) p.dbeta[((long)m.tok0 + tid) * p.H + h] = dbv[tid];
+      if (DELTA) {
+        p.dbeta[((long)m.tok0 + tid) * p.H + h] =
+            dbrow[tid] + dbrow[64 + tid] + dbcol[tid] + dbcol[64 + tid] + dbcol[128 + tid] + dbcol[192 + tid];
+      }
     }
   }
 }

@@ -6,15 +6,21 @@
 ``ops.linear_attention("simple_gla", q=C, k=B, v=dt*x, g=dt*A, scale=1.0)``: the grouped ``B, C`` go to the kernels
 un-repeated (value head ``h`` reads group ``h // (H / G)``; the kernels sum ``dB, dC`` over a group's heads in
 float32, as the reference does in ``scalar_gate_grouped.py``). The elementwise glue (``dt*x`` rounded to the
-activation dtype, ``dt*A`` in float32, ``+ D*x`` in float32) is plain torch, so autograd supplies the chain rule
-``dx = dv*dt + D*dy``, ``ddt = sum_p dv*x + dg*A``, ``dA = sum dg*dt``, ``dD = sum dy*x`` (``ssm.py:76-84``).
+activation dtype, ``dt*A`` in float32, ``+ D*x`` in float32) and its transpose ``dx = dv*dt + D*dy``,
+``ddt = sum_p dv*x + dg*A``, ``dA = sum dg*dt``, ``dD = sum dy*x`` (``ssm.py:76-84``) run as the fused
+``jla_ssd_*`` kernels for 16-bit activations (one pass over each ``[B, T, H, P]`` tensor); float32 activations, which
+take the token-scan kernels anyway, keep plain torch glue.
 """
 
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
-from .. import ops
+from .. import _lib, ops
+
+_DTYPES = {torch.bfloat16: 0, torch.float16: 1}
 
 
 def mamba2_ssd(x, dt, a, b, c, *, d=None, segment_ids=None, initial_state=None, output_final_state=False,
@@ -28,12 +34,69 @@ def mamba2_ssd(x, dt, a, b, c, *, d=None, segment_ids=None, initial_state=None, 
         raise ValueError(f"b, c must be [B, T, G, N] with H % G == 0; got {tuple(b.shape)}, {tuple(c.shape)}")
     if a.shape != (heads,):
         raise ValueError(f"a must be [H] = {(heads,)}; got {tuple(a.shape)}")
-    dt32 = dt.float()
-    v = (x.float() * dt32[..., None]).to(x.dtype).to(c.dtype)
-    g = dt32 * a.float()
+    fused = x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.shape[3] % 8 == 0
+    if fused:
+        v, g = _SsdInputs.apply(x.contiguous(), dt.float().contiguous(), a.float().contiguous())
+        v = v.to(c.dtype)
+    else:
+        dt32 = dt.float()
+        v = (x.float() * dt32[..., None]).to(x.dtype).to(c.dtype)
+        g = dt32 * a.float()
     y, state = ops.linear_attention("simple_gla", c, b.to(c.dtype), v, g=g, impl=impl, scale=1.0,
                                     chunk_size=chunk_size, segment_ids=segment_ids, initial_state=initial_state,
                                     output_final_state=output_final_state, precision=precision)
     if d is not None:
-        y = (y.float() + d.float()[:, None] * x.float()).to(y.dtype)
+        if fused and y.dtype == x.dtype:
+            y = _SsdOutput.apply(y, x.contiguous(), d.float().contiguous())
+        else:
+            y = (y.float() + d.float()[:, None] * x.float()).to(y.dtype)
     return y, state
+
+
+def _glue_call(name: str, x: torch.Tensor, *args):
+    lib = _lib.load()
+    tokens, heads, p = x.shape[0] * x.shape[1], x.shape[2], x.shape[3]
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    ptrs = [C.c_void_p(t.data_ptr()) for t in args]
+    with torch.cuda.device(x.device):
+        _lib.check(getattr(lib, name)(_DTYPES[x.dtype], C.c_int64(tokens), heads, p, *ptrs, C.c_void_p(stream)), name)
+
+
+class _SsdInputs(torch.autograd.Function):
+    """``(v, g) = (round(x * dt), dt * A)``."""
+
+    @staticmethod
+    def forward(ctx, x, dt, a):
+        v = torch.empty_like(x)
+        g = torch.empty_like(dt)
+        _glue_call("jla_ssd_inputs_fwd", x, x, dt, a, v, g)
+        ctx.save_for_backward(x, dt, a)
+        return v, g
+
+    @staticmethod
+    def backward(ctx, dv, dg):
+        x, dt, a = ctx.saved_tensors
+        dv = torch.zeros_like(x) if dv is None else dv.contiguous()
+        dg = torch.zeros_like(dt) if dg is None else dg.float().contiguous()
+        dx, ddt, da = torch.empty_like(x), torch.empty_like(dt), torch.empty_like(a)
+        _glue_call("jla_ssd_inputs_bwd", x, x, dt, a, dv, dg, dx, ddt, da)
+        return dx, ddt, da
+
+
+class _SsdOutput(torch.autograd.Function):
+    """``y = round(o + D * x)``."""
+
+    @staticmethod
+    def forward(ctx, o, x, d):
+        y = torch.empty_like(o)
+        _glue_call("jla_ssd_output_fwd", x, o, x, d, y)
+        ctx.save_for_backward(x, d)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, d = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx, dd = torch.empty_like(x), torch.empty_like(d)
+        _glue_call("jla_ssd_output_bwd", x, dy, x, d, dx, dd)
+        return dy, dx, dd
