@@ -415,7 +415,12 @@ def main() -> None:
                     ach = fl / (per_launch_ms * 1e-3) / 1e12
                     roof = dict(bound="tensor", achieved=ach, peak=pk["bf16_tflops"], unit="TFLOP/s",
                                 frac=ach / pk["bf16_tflops"])
-                roof.update(kernel=top, ms_per_launch=per_launch_ms, traffic=None, peak_source=pk["source"],
+                # DRAM bytes per unit from ncu captures of this workload (profiles/*.md); scaled by the units of a launch
+                ncu_bytes_per_unit = {"sg_grads_k": 805.7e6 / 4096, "sg_grads_q": 491.2e6 / 4096,
+                                      "sg_bwd_state": 454.0e6 / 4096, "kkt_inv": 92.9e6 / 4096}
+                traffic = ncu_bytes_per_unit.get(top) if args.workload == "gdn" else None
+                roof.update(kernel=top, ms_per_launch=per_launch_ms,
+                            traffic=None if traffic is None else traffic * units, peak_source=pk["source"],
                             algorithmic_bytes_per_launch=by, algorithmic_flops_per_launch=fl)
         # whole-step view against both rooflines (SURVEY accounting: 491,520 FLOP and 2,816 B per token and head)
         step_flops = 491520.0 * tokens * H if args.workload != "ssd" else 172032.0 * tokens * H
