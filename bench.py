@@ -205,8 +205,12 @@ def run_step(workload: str, dev: dict):
         else:
             from jax_linear_attention_b200.distributed import context_parallel_linear_attention
 
+            # documents (4 Ki .. 128 Ki tokens) are cut into about 32 pieces per rank so that the state passes
+            # fill the SMs instead of walking each document as one chain
+            t_local = dev["q"].shape[1]
+            piece_len = max(2048, (t_local // 32) // 64 * 64)
             o, _ = context_parallel_linear_attention("gated_deltanet", dev["q"], dev["k"], dev["v"], g=dev["g"],
-                                                     beta=dev["beta"], segment_ids=dev["seg"])
+                                                     beta=dev["beta"], segment_ids=dev["seg"], piece_len=piece_len)
     else:
         kind = "gated_deltanet" if workload == "gdn" else "kda"
         o, _ = ops.linear_attention(kind, dev["q"], dev["k"], dev["v"], g=dev["g"], beta=dev["beta"],
@@ -451,7 +455,9 @@ def main() -> None:
             dtype="bf16", data="synthetic",
             config=dict(workload=WORKLOADS[args.workload]["name"], per_gpu_batch=list(shape[:2]),
                         l2="inputs larger than L2 (hundreds of MB of q,k,v,dO + residuals per step)",
-                        parallelism=(f"sequence-parallel over {world} GPU(s), NCCL send/recv of the fp32 state" if longctx
+                        parallelism=(f"sequence-parallel over {world} GPUs: documents cut into pieces joined by affine "
+                                     "maps, NCCL send/recv of the fp32 state" if longctx and world > 1
+                                     else "one GPU, documents as cu_seqlens rows" if longctx
                                      else f"batch x heads, {world} GPU(s), no communication")),
             e2e=None if not e2e_steps else dict(
                 value=world * tokens / (e2e_ms / e2e_steps * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,

@@ -58,7 +58,14 @@ enum jla_path {
 
 enum jla_flags {
   JLA_FLAG_QK_L2NORM = 1,     /* normalise q and k over the head dim in fp32, eps 1e-6 (reference.py:65-69)   */
-  JLA_FLAG_SAVE_RESIDUALS = 2 /* forward: fill `residuals` for a later jla_linear_attention_bwd             */
+  JLA_FLAG_SAVE_RESIDUALS = 2, /* forward: fill `residuals` for a later jla_linear_attention_bwd             */
+  /* The two flags below serve callers that run several passes over the same tokens (documents cut into pieces
+   * joined by affine maps: src/jla/ops/mosaic_gpu/scalar_gate.py:129-148). Chunked path only; ignored elsewhere. */
+  JLA_FLAG_PREP_DONE = 4,      /* forward: the buffer passed as residuals (or scratch) already holds the chunk table,
+                                * gates, T0/Ag and normalised q/k of an earlier forward with the same k, g, beta,
+                                * segment_ids / cu_seqlens and (with the L2 norm) q: skip recomputing them          */
+  JLA_FLAG_STATE_GRADS_ONLY = 8 /* backward: run the reverse state pass only: dh0 and dv are written, dq, dk, dg and
+                                * dbeta are left untouched                                                          */
 };
 
 enum jla_status {

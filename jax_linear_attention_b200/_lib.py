@@ -15,6 +15,8 @@ KIND = {"simple_gla": 0, "deltanet": 1, "gated_deltanet": 2, "kda": 3}
 PATH = {"auto": 0, "recurrent": 1, "chunked": 2}
 FLAG_QK_L2NORM = 1
 FLAG_SAVE_RESIDUALS = 2
+FLAG_PREP_DONE = 4
+FLAG_STATE_GRADS_ONLY = 8
 OK, ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA = 0, -1, -2, -3, -4
 
 EXPORTS = (

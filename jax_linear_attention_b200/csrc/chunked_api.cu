@@ -60,8 +60,10 @@ int chunked_fwd(const jla_problem& p, const jla_fwd_io& io, cudaStream_t stream)
     res = static_cast<char*>(io.scratch);
   }
   const ChunkedCtx c = make_ctx(p, res);
-  int rc = launch_prep(c, stream);
-  if (rc != JLA_OK) return rc;
+  if (!(p.flags & JLA_FLAG_PREP_DONE)) {
+    const int rc = launch_prep(c, stream);
+    if (rc != JLA_OK) return rc;
+  }
   return use_tc_kernels(p) ? launch_sg_fwd_tc(c, io, stream) : launch_sg_fwd(c, io, stream);
 }
 

@@ -680,6 +680,7 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
     rc = pl.delta ? launch_kv<__half, true>(bp, p.K, p.V, rb, cb, legacy, s)
                   : launch_kv<__half, false>(bp, p.K, p.V, rb, cb, legacy, s);
   }
+  if (rc == JLA_OK && !legacy && (p.flags & JLA_FLAG_STATE_GRADS_ONLY)) return rc;
   if (rc == JLA_OK && !legacy) rc = launch_chunk_grads_tc(c, io, scratch, direct, s);
   if (rc != JLA_OK || direct) return rc;
   rc = finalize_key_grad(bp.dq_acc, p.q, io.dq, p.dtype, tokens, p.H, p.Hk, p.K, pl.l2norm, s);

@@ -20,6 +20,20 @@ every kind, including the delta rule, where the entering state acts through a K 
 applied as a decayed additive term.
 
 Document boundaries are read on the host (one small device-to-host copy per call) to size the prefixes.
+
+**Pieces** (``piece_len``, single packed row). The state passes of the kernels walk one document's chunks in order,
+so a long document is a long serial chain however many ranks there are. With ``piece_len`` set, every document is
+cut into pieces of at most that many tokens and each piece becomes an independent kernel row (``cu_seqlens``), the
+form of the reference's intra-GPU split (``src/jla/ops/mosaic_gpu/scalar_gate.py:129-148``, pieces joined by affine
+maps). A piece maps the state entering it affinely, ``S_out = M S_in + E``: ``E`` is the final state of the piece run
+from a zero state, and ``M`` (K x K per head) is the final state of the same piece run with zero values from an
+identity state of value width K (the recurrence is linear in the state, so its response to the identity is the map).
+Forward: pass E and pass M over all pieces in parallel, a scan of small matrix products over the pieces of each
+document (across ranks: one state hand-off, sent early when the shard's last document starts inside the shard), then
+the real pass with every piece's true entering state. Backward: the state gradients obey the transposed recursion
+``dS_in = e + M^T dS_out`` with ``e`` the entering-state gradient for a zero final-state cotangent, so one backward
+pass yields ``e``, a reverse scan yields every piece's ``dS_out``, and a second backward pass gives the gradients.
+Three forward and two backward passes instead of one each, but none of them is longer than a piece.
 """
 
 from __future__ import annotations
@@ -28,6 +42,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
+from ..ops.cuda import shared_prep, state_grads_only
 
 _GATES = {"simple_gla": ("g",), "deltanet": ("beta",), "gated_deltanet": ("g", "beta"), "kda": ("g", "beta")}
 
@@ -183,6 +198,171 @@ class _ContextParallel(torch.autograd.Function):
         return (None, None, None, None, None, *grads, d_h0)
 
 
+def _piece_table(ids, cont0: bool, piece_len: int):
+    """Cut points of the local row: document starts plus every ``piece_len`` tokens inside a document.
+    Returns (cu, cont): ``cu`` has P + 1 entries; ``cont[p]`` says piece p continues the document of piece p - 1
+    (for p = 0: of the previous rank's last token)."""
+    t_local = ids.numel()
+    change = torch.zeros(t_local, dtype=torch.bool)
+    change[1:] = ids[1:] != ids[:-1]
+    doc_starts = [0] + torch.nonzero(change).flatten().tolist() + [t_local]
+    cu, cont = [], []
+    for a, b in zip(doc_starts[:-1], doc_starts[1:]):
+        for s in range(a, b, piece_len):
+            cu.append(s)
+            cont.append(s != a)
+    cont[0] = cont0
+    cu.append(t_local)
+    return cu, cont
+
+
+class _PiecewiseContextParallel(torch.autograd.Function):
+    """One packed row per rank, cut into pieces joined by affine maps (see the module docstring)."""
+
+    @staticmethod
+    def forward(ctx, pcall, kind, group, seg, piece_len, *tensors):
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        ranks = dist.get_process_group_ranks(group)
+        prev_rank = ranks[rank - 1] if rank > 0 else None
+        next_rank = ranks[rank + 1] if rank < world - 1 else None
+        *xs, h0 = tensors
+        q, k, v, *gates = xs
+        t_local, heads, kd, vd = q.shape[1], v.shape[2], q.shape[3], v.shape[3]
+        dev = q.device
+        sdt = torch.float64 if q.dtype == torch.float64 else torch.float32
+
+        ids = torch.zeros(t_local, dtype=torch.int64) if seg is None else seg[0].cpu().to(torch.int64)
+        cont0 = rank > 0
+        if seg is not None and world > 1:  # does this shard's first token continue the previous rank's document?
+            last = seg[:, -1].contiguous()
+            recv = torch.empty_like(last)
+            reqs = []
+            if next_rank is not None:
+                reqs.append(dist.isend(last, next_rank, group=group))
+            if prev_rank is not None:
+                reqs.append(dist.irecv(recv, prev_rank, group=group))
+            for r in reqs:
+                r.wait()
+            cont0 = prev_rank is not None and int(recv.cpu()[0]) == int(ids[0])
+        cu, cont = _piece_table(ids, cont0, piece_len)
+        pieces = len(cont)
+        cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+        plain = [x.detach() for x in xs]
+        has_h0 = rank == 0 and h0 is not None
+
+        share = shared_prep()  # the three passes read the same keys and gates: one chunk table, one set of inverses
+        share.__enter__()
+        try:
+            with torch.no_grad():
+                init_e = None
+                if has_h0:
+                    init_e = torch.zeros(pieces, heads, kd, vd, dtype=sdt, device=dev)
+                    init_e[0] = h0[0].to(sdt)
+                _, e_state = pcall(kind, plain, cu_t, init_e)
+                m_map = None
+                if any(cont):
+                    eye = torch.eye(kd, dtype=sdt, device=dev).expand(pieces, heads, kd, kd).contiguous()
+                    vz = torch.zeros(1, t_local, heads, kd, dtype=v.dtype, device=dev)
+                    _, m_map = pcall(kind, [plain[0], plain[1], vz, *plain[3:]], cu_t, eye)
+                    m_map = m_map.to(sdt)
+                s_out = e_state.to(sdt).clone()
+                s_recv = torch.zeros(1, heads, kd, vd, dtype=sdt, device=dev)
+
+                def scan(p0, p1):  # S_out[p] = E[p] + M[p] S_out[p - 1] along a document's pieces
+                    for p in range(p0, p1):
+                        if cont[p]:
+                            torch.baddbmm(s_out[p], m_map[p], s_out[p - 1] if p > 0 else s_recv[0], out=s_out[p])
+
+                # the shard's last document starts at piece `tail`: its states do not depend on the received state
+                tail = max((p for p in range(pieces) if not cont[p]), default=0)
+                send_req = None
+                if not cont[tail]:
+                    scan(tail, pieces)
+                    if next_rank is not None:
+                        send_req = dist.isend(s_out[-1:].contiguous(), next_rank, group=group)
+                if prev_rank is not None:
+                    dist.recv(s_recv, prev_rank, group=group)
+                if cont[tail]:  # one document fills the whole shard
+                    scan(0, pieces)
+                    if next_rank is not None:
+                        send_req = dist.isend(s_out[-1:].contiguous(), next_rank, group=group)
+                else:
+                    scan(0, tail)
+                if send_req is not None:
+                    send_req.wait()
+                # entering states: the previous piece's final state where the document continues, else zero
+                s_in = torch.zeros(pieces, heads, kd, vd, dtype=sdt, device=dev)
+                idx = torch.tensor([p for p in range(1, pieces) if cont[p]], dtype=torch.long, device=dev)
+                if idx.numel():
+                    s_in[idx] = s_out[idx - 1]
+                if cont[0]:
+                    s_in[0] = s_recv[0]
+                if has_h0:
+                    s_in[0] = h0[0].to(sdt)
+
+            leaves = [x.detach().requires_grad_(True) for x in xs]
+            s_in_leaf = s_in.requires_grad_(True)
+            with torch.enable_grad():
+                o, f = pcall(kind, leaves, cu_t, s_in_leaf)
+        finally:
+            share.__exit__(None, None, None)
+        ctx.state = dict(leaves=leaves, s_in_leaf=s_in_leaf, o=o, f=f, m_map=m_map, cont=cont, group=group,
+                         prev_rank=prev_rank, next_rank=next_rank, has_h0=has_h0, h0_given=h0 is not None, sdt=sdt)
+        return o.detach(), f.detach()[-1:].to(sdt)
+
+    @staticmethod
+    def backward(ctx, d_o, d_f):
+        st = ctx.state
+        cont, m_map, group, sdt = st["cont"], st["m_map"], st["group"], st["sdt"]
+        leaves, s_in_leaf, o, f = st["leaves"], st["s_in_leaf"], st["o"], st["f"]
+        pieces = len(cont)
+        d_o = d_o.contiguous()
+        # entering-state gradients for a zero final-state cotangent
+        with state_grads_only():
+            (e_grad,) = torch.autograd.grad([o], [s_in_leaf], [d_o], retain_graph=True)
+        ds_in = e_grad.to(sdt).clone()
+        ds_out = torch.zeros_like(ds_in)
+        g_next = torch.zeros_like(ds_in[:1])
+        m_t = None if m_map is None else m_map.transpose(-1, -2)
+
+        def scan(p_hi, p_lo):  # pieces p_hi - 1 down to p_lo: dS_in[p] = e[p] + M[p]^T dS_out[p]
+            for p in range(p_hi - 1, p_lo - 1, -1):
+                if p == pieces - 1:
+                    ds_out[p] = g_next[0]
+                elif cont[p + 1]:
+                    ds_out[p] = ds_in[p + 1]
+                else:
+                    continue
+                if cont[p] and m_t is not None:
+                    torch.baddbmm(ds_in[p], m_t[p], ds_out[p], out=ds_in[p])
+
+        # the shard's first document ends before piece `head`: its gradients do not depend on the received one
+        head = min((p for p in range(1, pieces) if not cont[p]), default=pieces)
+        send_req = None
+        if head < pieces:
+            scan(head, 0)
+            if st["prev_rank"] is not None:
+                send_req = dist.isend(ds_in[:1].contiguous() if cont[0] else torch.zeros_like(ds_in[:1]),
+                                      st["prev_rank"], group=group)
+        if st["next_rank"] is not None:
+            dist.recv(g_next, st["next_rank"], group=group)
+        elif d_f is not None:
+            g_next = d_f.to(sdt).contiguous()
+        if head < pieces:
+            scan(pieces, head)
+        else:
+            scan(pieces, 0)
+            if st["prev_rank"] is not None:
+                send_req = dist.isend(ds_in[:1].contiguous() if cont[0] else torch.zeros_like(ds_in[:1]),
+                                      st["prev_rank"], group=group)
+        got = torch.autograd.grad([o, f], [*leaves, s_in_leaf], [d_o, ds_out.to(f.dtype)], allow_unused=True)
+        if send_req is not None:
+            send_req.wait()
+        grads = [x if x is not None else torch.zeros_like(l) for x, l in zip(got[:-1], leaves)]
+        d_h0 = got[-1][:1].to(sdt) if st["has_h0"] else None
+        return (None, None, None, None, None, *grads, d_h0)
+
+
 def _default_call(impl, options):
     """The op on (a slice of) the local shard. A single packed row is handed over as ``cu_seqlens`` (the document
     boundaries are on the host anyway), so that every document is an independent row for the kernels instead of
@@ -213,13 +393,29 @@ def _default_call(impl, options):
     return call
 
 
-def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: str = "auto", call=None, **inputs):
+def _default_piece_call(impl, options):
+    """The op over the local row cut into ``cu_seqlens`` pieces, each with its own entering state."""
+    def pcall(kind, leaves, cu, init):
+        q, k, v, *gates = leaves
+        kw = dict(options)
+        kw.update(dict(zip(_GATES[kind], gates)))
+        return ops.linear_attention(kind, q, k, v, impl=impl, initial_state=init, output_final_state=True,
+                                    cu_seqlens=cu, **kw)
+    return pcall
+
+
+def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: str = "auto", call=None,
+                                      piece_len: int | None = None, piece_call=None, **inputs):
     """``(o_local, final_state)`` for this rank's T-shard ``q, k, v [B, T/P, ...]`` (gates and ``segment_ids``
     sharded the same way). ``initial_state`` is read on the first rank; the final state of the whole sequence is
     returned on the last rank when ``output_final_state`` is set (``None`` elsewhere). ``cu_seqlens`` is not
     supported: pass ``segment_ids``, as in the reference's sequence-parallel op.
 
-    ``call(kind, leaves, state, seg, tslice, row)`` may replace the op (tests inject the CPU oracle).
+    ``piece_len`` (a multiple of the chunk size; batch 1 only) cuts documents into independent pieces joined by
+    affine maps, which is what lets a long document use more than one SM per head and more than one rank.
+
+    ``call(kind, leaves, state, seg, tslice, row)`` or, with pieces, ``piece_call(kind, leaves, cu, init)`` may
+    replace the op (tests inject the CPU oracle).
     """
     if kind not in _GATES:
         raise ValueError(f"unknown linear-attention kind {kind!r}; expected one of {sorted(_GATES)}")
@@ -234,7 +430,15 @@ def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: s
     h0 = inputs.pop("initial_state", None)
     want_final = bool(inputs.pop("output_final_state", False))
     seg = inputs.pop("segment_ids", None)
-    call = call or _default_call(impl, inputs)
-    o, f = _ContextParallel.apply(call, kind, group, seg, want_final, q, k, v, *gates, h0)
+    if piece_len is not None:
+        if q.shape[0] != 1:
+            raise ValueError(f"piece_len needs a single packed row (batch 1); got batch {q.shape[0]}")
+        if piece_len <= 0:
+            raise ValueError(f"piece_len must be positive; got {piece_len}")
+        pcall = piece_call or _default_piece_call(impl, inputs)
+        o, f = _PiecewiseContextParallel.apply(pcall, kind, group, seg, int(piece_len), q, k, v, *gates, h0)
+    else:
+        call = call or _default_call(impl, inputs)
+        o, f = _ContextParallel.apply(call, kind, group, seg, want_final, q, k, v, *gates, h0)
     last = dist.get_rank(group) == dist.get_world_size(group) - 1
     return o, (f if (want_final and last) else None)

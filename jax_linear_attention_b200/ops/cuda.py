@@ -110,6 +110,41 @@ def _supports(kind: str):
     return supports
 
 
+class _PassOptions:
+    """Process-wide switches for callers that run several passes over the same tokens (the piecewise
+    sequence-parallel form). Plain module state, not thread-local: autograd runs backward on its own thread."""
+    share = None              # dict(key=..., buffer=...) while shared_prep() is active
+    state_grads_only = False  # backward runs the reverse state pass only (dh0, dv)
+
+
+class shared_prep:
+    """``with shared_prep():`` lets successive forward calls on the same ``k``, gates and document layout (and, with
+    the in-op L2 norm, the same ``q``) share one residual-layout buffer, so that only the first of them computes the
+    chunk table, the gate cumsums and the triangular inverses. Every call overwrites the buffer's state residuals:
+    only the last call inside the block may be differentiated."""
+
+    def __enter__(self):
+        self._outer = _PassOptions.share
+        _PassOptions.share = dict(key=None, buffer=None)
+        return self
+
+    def __exit__(self, *exc):
+        _PassOptions.share = self._outer
+
+
+class state_grads_only:
+    """``with state_grads_only():`` backward calls compute only the gradient of the initial state (and ``dv``);
+    the gradients of q, k and the gates come back as zeros-shaped garbage and must be ignored."""
+
+    def __enter__(self):
+        self._outer = _PassOptions.state_grads_only
+        _PassOptions.state_grads_only = True
+        return self
+
+    def __exit__(self, *exc):
+        _PassOptions.state_grads_only = self._outer
+
+
 class _LinearAttention(torch.autograd.Function):
     """``(o, final) = op(q, k, v, g, beta, h0)``; the config rides in ``cfg``."""
 
@@ -130,9 +165,25 @@ class _LinearAttention(torch.autograd.Function):
         o = torch.empty_like(v)
         final = torch.empty(rows, H, K, V, dtype=torch.float32, device=dev) if cfg["output_final_state"] else None
         res_bytes = lib.jla_residual_bytes(C.byref(p)) if needs_grad else 0
-        residuals = torch.empty(res_bytes, dtype=torch.uint8, device=dev) if res_bytes else None
-        scr_bytes = lib.jla_fwd_scratch_bytes(C.byref(p))
-        scratch = torch.empty(scr_bytes, dtype=torch.uint8, device=dev) if scr_bytes else None
+        share = _PassOptions.share
+        if share is not None:  # one residual-layout buffer for a run of calls; the first one fills its tables
+            key = (k.data_ptr(), _ptr(g), _ptr(beta), _ptr(seg), _ptr(cu), q.data_ptr() if cfg["l2norm"] else 0,
+                   tuple(q.shape), tuple(v.shape[2:3]), q.dtype, cfg["kind"], cfg["l2norm"], cfg["precision"])
+            p.flags = flags | _lib.FLAG_SAVE_RESIDUALS
+            full = lib.jla_residual_bytes(C.byref(p))
+            if share["key"] == key and share["buffer"] is not None and share["buffer"].numel() >= full:
+                flags |= _lib.FLAG_PREP_DONE
+            else:
+                share["key"], share["buffer"] = key, torch.empty(full, dtype=torch.uint8, device=dev)
+            p.flags = flags
+            residuals = share["buffer"] if needs_grad else None
+            scratch = None if needs_grad else share["buffer"]
+            res_bytes = full if needs_grad else 0
+            scr_bytes = 0 if needs_grad else full
+        else:
+            residuals = torch.empty(res_bytes, dtype=torch.uint8, device=dev) if res_bytes else None
+            scr_bytes = lib.jla_fwd_scratch_bytes(C.byref(p))
+            scratch = torch.empty(scr_bytes, dtype=torch.uint8, device=dev) if scr_bytes else None
         io = _lib.FwdIO(_ptr(o), _ptr(final), _ptr(residuals), res_bytes, _ptr(scratch), scr_bytes)
         stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
@@ -150,7 +201,8 @@ class _LinearAttention(torch.autograd.Function):
         B, T, Hk, K = q.shape
         H, V = v.shape[2:]
         cu, seg = cfg["cu_seqlens"], cfg["segment_ids"]
-        p = _problem(cfg["kind"], q.dtype, B, T, H, Hk, K, V, 0 if cu is None else ctx.rows, cfg["scale"], ctx.flags,
+        flags = (ctx.flags & ~_lib.FLAG_PREP_DONE) | (_lib.FLAG_STATE_GRADS_ONLY if _PassOptions.state_grads_only else 0)
+        p = _problem(cfg["kind"], q.dtype, B, T, H, Hk, K, V, 0 if cu is None else ctx.rows, cfg["scale"], flags,
                      cfg["precision"])
         p.q, p.k, p.v, p.g, p.beta, p.h0 = (_ptr(x) for x in (q, k, v, g, beta, h0))
         p.segment_ids, p.cu_seqlens = _ptr(seg), _ptr(cu)

@@ -113,6 +113,77 @@ def test_context_parallel_matches_the_unsharded_run(tmp_path, world, docs, kind)
         assert max_rel(o_cut.detach().numpy(), want["o"]) > 1e-3
 
 
+def _oracle_piece_call(kind, leaves, cu, init):
+    q, k, v, *gates = leaves
+    fn, _ = recurrence.KIND_FUNCTIONS[kind]
+    return fn(q, k, v, *gates, initial_state=init, output_final_state=True, cu_seqlens=cu, dtype=F64)
+
+
+def _piece_worker(rank, world, port, kind, seg_np, piece_len, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from jax_linear_attention_b200.distributed import context_parallel_linear_attention
+
+    T = 96
+    case = make_case(kind, B=1, T=T, H=2, K=8, V=8, seed=43, h0=True)
+    tl = T // world
+    sl = slice(rank * tl, (rank + 1) * tl)
+    names = [n for n in ("q", "k", "v", "g", "beta") if n in case]
+    loc = {n: torch.tensor(case[n][:, sl], dtype=F64, requires_grad=True) for n in names}
+    h0 = torch.tensor(case["h0"], dtype=F64, requires_grad=True)
+    seg = None if seg_np is None else torch.tensor(seg_np[:1, sl])
+    gates = {n: loc[n] for n in ("g", "beta") if n in loc}
+    o, f = context_parallel_linear_attention(kind, loc["q"], loc["k"], loc["v"], piece_call=_oracle_piece_call,
+                                             piece_len=piece_len, segment_ids=seg,
+                                             initial_state=h0 if rank == 0 else None, output_final_state=True, **gates)
+    do = torch.tensor(case["do"][:, sl], dtype=F64)
+    outs, cots = [o], [do]
+    if f is not None:
+        outs.append(f)
+        cots.append(torch.tensor(case["dht"], dtype=F64))
+    wrt = [loc[n] for n in names] + ([h0] if rank == 0 else [])
+    grads = torch.autograd.grad(outs, wrt, cots, allow_unused=True)
+    res = {"o": o.detach().numpy()}
+    for n, gr in zip(names + (["h0"] if rank == 0 else []), grads):
+        res["d" + n] = gr.numpy()
+    if f is not None:
+        res["f"] = f.detach().numpy()
+    np.savez(os.path.join(out, f"rank{rank}.npz"), **res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,piece_len", [(2, 8), (3, 16)])
+@pytest.mark.parametrize("docs", ["none", "inside", "spanning_then_start"])
+@pytest.mark.parametrize("kind", ["gated_deltanet", "simple_gla"])
+def test_pieces_joined_by_affine_maps_match_the_unsharded_run(tmp_path, world, piece_len, docs, kind):
+    """Documents cut into independent pieces (``piece_len``): values and every gradient equal the plain run."""
+    T = 96
+    if docs == "none":
+        seg = None
+    elif docs == "inside":
+        seg = np.concatenate([np.zeros(20), np.ones(37), 2 * np.ones(3), 3 * np.ones(36)])[None].astype(np.int32)
+    else:  # one document over the first shards, a start only near the very end
+        seg = np.concatenate([np.zeros(90), np.ones(6)])[None].astype(np.int32)
+    mp.spawn(_piece_worker, args=(world, _free_port(), kind, seg, piece_len, str(tmp_path)), nprocs=world, join=True)
+    case = make_case(kind, B=1, T=T, H=2, K=8, V=8, seed=43, h0=True)
+    names = [n for n in ("q", "k", "v", "g", "beta") if n in case]
+    full = {n: torch.tensor(case[n], dtype=F64, requires_grad=True) for n in names + ["h0"]}
+    fn, gate_names = recurrence.KIND_FUNCTIONS[kind]
+    o, f = fn(full["q"], full["k"], full["v"], *[full[g] for g in gate_names], initial_state=full["h0"],
+              output_final_state=True, segment_ids=None if seg is None else torch.tensor(seg))
+    grads = torch.autograd.grad([o, f], [full[n] for n in names + ["h0"]],
+                                [torch.tensor(case["do"], dtype=F64), torch.tensor(case["dht"], dtype=F64)])
+    want = {"o": o.detach().numpy(), "f": f.detach().numpy()}
+    want.update({"d" + n: g.numpy() for n, g in zip(names + ["h0"], grads)})
+    parts = [dict(np.load(tmp_path / f"rank{r}.npz")) for r in range(world)]
+    for key in ["o"] + ["d" + n for n in names]:
+        got = np.concatenate([p[key] for p in parts], axis=1)
+        assert max_rel(got, want[key]) < 1e-9, key
+    assert max_rel(parts[-1]["f"], want["f"]) < 1e-9
+    assert max_rel(parts[0]["dh0"], want["dh0"]) < 1e-9
+
+
 def _shard_worker(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
