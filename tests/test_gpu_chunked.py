@@ -152,3 +152,38 @@ def test_baseline_config1_full_size_slices_and_properties():
         compare(got, want, TOL, f"config1 slice {b},{h}")
         alone = run_cuda("gated_deltanet", sl, scale=128 ** -0.5, dtype="bfloat16")
         assert np.array_equal(alone["o"], got["o"]) and np.array_equal(alone["dk"], got["dk"])
+
+
+def test_shared_prep_and_state_only_backward_match_the_plain_calls():
+    """Passes that share one chunk table (JLA_FLAG_PREP_DONE) and the reverse-state-pass-only backward
+    (JLA_FLAG_STATE_GRADS_ONLY) give the plain calls' results bit for bit."""
+    from jax_linear_attention_b200 import ops
+    from jax_linear_attention_b200.ops.cuda import shared_prep, state_grads_only
+
+    case = make_case("gated_deltanet", B=1, T=1500, H=4, K=128, V=128, seed=77, docs="mixed", h0=True)
+    dev = torch.device("cuda")
+    t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16 if n in "qkv" else torch.float32)
+         for n in ("q", "k", "v", "g", "beta")}
+    cu = torch.tensor([0, 300, 301, 900, 1500], dtype=torch.int32, device=dev)
+    h0 = torch.randn(4, 4, 128, 128, device=dev) * 0.1
+    do = torch.tensor(case["do"], device=dev, dtype=torch.bfloat16)
+
+    def run(v, init, grad):
+        leaf = init.clone().requires_grad_(grad)
+        o, f = ops.linear_attention("gated_deltanet", t["q"], t["k"], v, g=t["g"], beta=t["beta"], cu_seqlens=cu,
+                                    initial_state=leaf, output_final_state=True)
+        return o, f, leaf
+
+    o1, f1, _ = run(t["v"], h0, False)
+    o2, f2, leaf2 = run(t["v"] * 0.5, h0 * 2, True)
+    (want_dh0,) = torch.autograd.grad([o2], [leaf2], [do])
+    with shared_prep():
+        o1s, f1s, _ = run(t["v"], h0, False)
+        o2s, f2s, leaf2s = run(t["v"] * 0.5, h0 * 2, True)  # second call: tables reused, residuals saved
+    assert torch.equal(o1, o1s) and torch.equal(f1, f1s)
+    assert torch.equal(o2, o2s) and torch.equal(f2, f2s)
+    with state_grads_only():
+        (got_dh0,) = torch.autograd.grad([o2s], [leaf2s], [do], retain_graph=True)
+    assert torch.equal(got_dh0, want_dh0)
+    (full_dh0,) = torch.autograd.grad([o2s], [leaf2s], [do])
+    assert torch.equal(full_dh0, want_dh0)
