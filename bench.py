@@ -205,13 +205,13 @@ def run_step(workload: str, dev: dict):
         else:
             from jax_linear_attention_b200.distributed import context_parallel_linear_attention
 
-            # documents (4 Ki .. 128 Ki tokens) are cut into about 32 pieces per rank so that the state passes
-            # fill the SMs instead of walking each document as one chain
+            # documents (4 Ki .. 128 Ki tokens) are cut into about 64 pieces per rank (x 16 heads = some 7 waves of
+            # CTAs) so that the state passes fill the SMs instead of walking each document as one chain
             if "plan" not in dev:  # the document layout is fixed input metadata: cut it into pieces once
                 from jax_linear_attention_b200.distributed import plan_pieces
 
                 t_local = dev["q"].shape[1]
-                dev["plan"] = plan_pieces(dev["seg"], max(2048, (t_local // 32) // 64 * 64))
+                dev["plan"] = plan_pieces(dev["seg"], max(1024, (t_local // 64) // 64 * 64))
             o, _ = context_parallel_linear_attention("gated_deltanet", dev["q"], dev["k"], dev["v"], g=dev["g"],
                                                      beta=dev["beta"], segment_ids=dev["seg"], piece_len=dev["plan"])
     else:
