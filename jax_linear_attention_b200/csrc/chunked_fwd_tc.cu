@@ -21,8 +21,6 @@
 #include "umma.cuh"
 
 namespace jla {
-__device__ unsigned long long g_ftrace[8][8];
-#define FT(i) do { if (blockIdx.x == 3 && warp == 4 && lane == 0 && it >= 8 && it < 16) { unsigned long long t_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_)); g_ftrace[it - 8][i] = t_; } } while (0)
 namespace {
 
 using umma::swz_tile;
@@ -249,7 +247,6 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
       // ---- the state entering this chunk: 16-bit copy for the products, decayed fp32 copy for the update
       if (it > 0) {
         ok = wait(bars + B_M3, ph ^ 1, abort_flag);
-        FT(0);
         if (!ok) break;
         umma::fence_after_sync();
       }
@@ -280,7 +277,6 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
       umma::fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + B_ST);
-      FT(1);
       if (p.hT_out) {
         T* hT = static_cast<T*>(p.hT_out) + (((long)c * p.H + h) * V + v) * K + 64 * half;
 #pragma unroll
@@ -294,7 +290,6 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
       if (DELTA) {
         // ---- W^T = V^T - (cin Gamma)_j (S^T K^T)
         ok = wait(bars + B_M1, ph, abort_flag);
-        FT(2);
         if (!ok) break;
         umma::fence_after_sync();
         {
@@ -313,7 +308,6 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
           umma::fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bars + B_W);
-          FT(3);
           if (p.wT_out) {  // residual for the key-side gradient kernel (dAg = dVn W^T)
             T* wT = static_cast<T*>(p.wT_out) + (((long)c * p.H + h) * V + v) * 64 + j0;
 #pragma unroll
@@ -324,7 +318,6 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         }
         // ---- Vn^T = W^T Ag^T
         ok = wait(bars + B_M2, ph, abort_flag);
-        FT(4);
         if (!ok) break;
         umma::fence_after_sync();
         {
@@ -344,7 +337,6 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
           __syncwarp();
           if (lane == 0) {
             mbar_arrive(bars + B_VN);
-          FT(5);
             mbar_arrive(bars + NS + s);  // done with this stage's v and gate vectors
           }
           if (p.vnT_out) {
@@ -552,5 +544,3 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
 }
 
 }  // namespace jla
-
-extern "C" int jla_debug_fwd_trace(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, jla::g_ftrace, sizeof(jla::g_ftrace)); }
