@@ -171,6 +171,21 @@ int jla_ssd_output_fwd(int dtype, int64_t tokens, int H, int P, const void* o, c
 int jla_ssd_output_bwd(int dtype, int64_t tokens, int H, int P, const void* dy, const void* x, const float* d, void* dx,
                        float* dd, jla_stream_t stream);
 
+/* Gate activations in front of the kernels, forward and backward in one pass each; replaces the XLA fusions of
+ * _mamba_gate and _write_strength in the Gated DeltaNet and KDA mixers (src/jla/layers/linear_attention.py:84-86,
+ * 159-162, 295-297, 324-328):
+ *   g = -exp(A_log[h]) * softplus(a + dt_bias)      a [tokens, H, C] dtype (C = 1, or K for KDA), dt_bias [H, C] f32,
+ *                                                   A_log [H] f32, g [tokens, H, C] f32
+ *   beta = m * sigmoid(b), m = allow_neg_eigval ? 2 : 1     b [tokens, H] dtype (may be NULL), beta [tokens, H] f32
+ * Backward: da, db in dtype; dA_log [H] and ddt_bias [H, C] f32 are zeroed by the call and then accumulated.
+ * H * C / 8 (H * C itself when it is no multiple of 8) must divide 256 or be a multiple of it. */
+int jla_gate_prologue_fwd(int dtype, int64_t tokens, int H, int C, const void* a, const float* a_log,
+                          const float* dt_bias, const void* b, int allow_neg_eigval, float* g, float* beta,
+                          jla_stream_t stream);
+int jla_gate_prologue_bwd(int dtype, int64_t tokens, int H, int C, const void* a, const float* a_log,
+                          const float* dt_bias, const void* b, int allow_neg_eigval, const float* dg, const float* dbeta,
+                          void* da, void* db, float* da_log, float* ddt_bias, jla_stream_t stream);
+
 /* Diagnostics: where the chunked path keeps its intermediates, so that tests can compare them stage by stage
  * with the CPU model (the reference checks its kernels per stage too:
  * tests/test_mosaic_gpu_gated_delta_rule.py:104-146). Byte offsets into the residual buffer written by a forward

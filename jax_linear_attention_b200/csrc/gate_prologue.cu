@@ -1,0 +1,230 @@
+// Gate activations in front of the linear-attention kernels, fused forward and backward
+// (src/jla/layers/linear_attention.py:84-86 `_mamba_gate`, :159-162 `_write_strength`; used by the Gated DeltaNet
+// mixer :295-297 and the KDA mixer :324-328):
+//
+//   g    = -exp(A_log[h]) * softplus(a + dt_bias)        a [tokens, H, C] (C = 1: one decay per head; C = K: KDA),
+//                                                        dt_bias [H, C], A_log [H]; g float32
+//   beta = m * sigmoid(b),  m = 2 if allow_neg_eigval else 1      b [tokens, H]; beta float32
+//
+//   da = dg * (-exp(A_log)) * sigmoid(a + dt_bias);  dA_log[h] = sum dg * g;  ddt_bias[h, c] = sum_tokens da
+//   db = dbeta * beta * (1 - beta / m)
+//
+// HBM-bound element-wise work. A thread owns eight adjacent (h, c) columns and walks a tile of tokens, so the
+// parameter gradients are summed in registers and leave the thread as one atomic per output.
+#include "common.cuh"
+
+namespace jla {
+namespace {
+
+constexpr int THREADS = 256;
+
+struct GateParams {
+  long tokens;
+  int H, C;
+  const void *a, *b;            // activations (dtype), b may be null
+  const float *a_log, *dt_bias;
+  float mult;                   // 1 or 2
+  int tokens_per_lane;          // tokens one thread walks (set by the launcher)
+  float *g, *beta;              // forward outputs
+  const float *dg, *dbeta;      // backward inputs
+  void *da, *db;                // backward outputs (dtype)
+  float *da_log, *ddt_bias;     // [H], [H * C], accumulated with atomics (zeroed by the launcher)
+};
+
+__device__ __forceinline__ float softplus(float x) { return fmaxf(x, 0.f) + log1pf(__expf(-fabsf(x))); }
+__device__ __forceinline__ float sigmoid(float x) { return 1.f / (1.f + __expf(-x)); }
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, float (&f)[VEC]) {
+  if constexpr (VEC == 8 && sizeof(T) == 2) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
+  } else if constexpr (VEC == 8) {
+    const float4 x = *reinterpret_cast<const float4*>(p), y = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = to_f32(x.x), f[1] = to_f32(x.y), f[2] = to_f32(x.z), f[3] = to_f32(x.w);
+    f[4] = to_f32(y.x), f[5] = to_f32(y.y), f[6] = to_f32(y.z), f[7] = to_f32(y.w);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) f[i] = to_f32(p[i]);
+  }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T* p, const float (&f)[VEC]) {
+  if constexpr (VEC == 8 && sizeof(T) == 2) {
+    uint4 u;
+    T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e[i] = from_f32<T>(f[i]);
+    *reinterpret_cast<uint4*>(p) = u;
+  } else if constexpr (VEC == 8) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) p[i] = from_f32<T>(f[i]);
+  }
+}
+
+// A thread owns VEC adjacent (h, c) columns (one 16-byte load of 16-bit activations) and walks every `lanes_t`-th token
+// of its block's tile. Block layout: min(H * C / VEC, THREADS) column threads x the remaining threads as token lanes.
+template <typename T, bool BWD, int VEC>
+__global__ void __launch_bounds__(THREADS) gate_kernel(GateParams p) {
+  const int HC = p.H * p.C;
+  const int groups = HC / VEC;
+  const int cols = groups < THREADS ? groups : THREADS;
+  const int lanes_t = THREADS / cols;
+  const int ct = (int)(threadIdx.x % cols);
+  const int grp = blockIdx.x * cols + ct;
+  const int lt = threadIdx.x / cols;
+  const bool active = lt < lanes_t && grp < groups;
+  const int col = active ? grp * VEC : 0;
+  const long tile = (long)p.tokens_per_lane * lanes_t;
+  const long t0 = (long)blockIdx.y * tile;
+  const long t1 = t0 + tile < p.tokens ? t0 + tile : p.tokens;
+  float neg_a[VEC], bias[VEC], s_alog[VEC], s_bias[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    neg_a[i] = -expf(p.a_log[(col + i) / p.C]);
+    bias[i] = p.dt_bias[col + i];
+    s_alog[i] = s_bias[i] = 0.f;
+  }
+  const T* __restrict__ a = static_cast<const T*>(p.a);
+  const T* __restrict__ b = static_cast<const T*>(p.b);
+  for (long t = t0 + lt; active && t < t1; t += lanes_t) {
+    const long idx = t * HC + col;
+    float x[VEC], out[VEC];
+    load_vec<T, VEC>(a + idx, x);
+    if (!BWD) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) out[i] = neg_a[i] * softplus(x[i] + bias[i]);
+      store_vec<float, VEC>(p.g + idx, out);
+    } else {
+      float dg[VEC];
+      load_vec<float, VEC>(p.dg + idx, dg);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float xi = x[i] + bias[i];
+        out[i] = dg[i] * neg_a[i] * sigmoid(xi);
+        s_bias[i] += out[i];
+        s_alog[i] += dg[i] * neg_a[i] * softplus(xi);
+      }
+      store_vec<T, VEC>(static_cast<T*>(p.da) + idx, out);
+    }
+    if (b) {  // the thread that owns column c = 0 of a head handles that head's beta
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        if ((col + i) % p.C != 0) continue;
+        const long bi = t * p.H + (col + i) / p.C;
+        const float beta = p.mult * sigmoid(to_f32(b[bi]));
+        if (!BWD) p.beta[bi] = beta;
+        else static_cast<T*>(p.db)[bi] = from_f32<T>(p.dbeta[bi] * beta * (1.f - beta / p.mult));
+      }
+    }
+  }
+  if (BWD) {
+    // parameter gradients: first over the block's token lanes in shared memory, then one atomic per column and block
+    __shared__ float red_bias[THREADS * VEC], red_alog[THREADS * VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      red_bias[threadIdx.x * VEC + i] = s_bias[i];
+      red_alog[threadIdx.x * VEC + i] = s_alog[i];
+    }
+    __syncthreads();
+    if (active && lt == 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float sb = 0.f, sa = 0.f;
+        for (int l = 0; l < lanes_t; ++l) {
+          sb += red_bias[(l * cols + ct) * VEC + i];
+          sa += red_alog[(l * cols + ct) * VEC + i];
+        }
+        s_bias[i] = sb;
+        s_alog[i] = sa;
+        atomicAdd(p.ddt_bias + col + i, sb);
+      }
+      if (p.C % VEC == 0) {  // the thread's columns share one head
+        float sa = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) sa += s_alog[i];
+        atomicAdd(p.da_log + col / p.C, sa);
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) atomicAdd(p.da_log + (col + i) / p.C, s_alog[i]);
+      }
+    }
+  }
+}
+
+template <bool BWD, int VEC>
+int launch_vec(int dtype, const GateParams& gp, cudaStream_t s) {
+  const int groups = gp.H * gp.C / VEC;
+  if (groups >= THREADS ? groups % THREADS != 0 : THREADS % groups != 0) {
+    set_error("gate prologue: H * C / %d = %d must divide or be a multiple of %d", VEC, groups, THREADS);
+    return JLA_ERR_UNSUPPORTED;
+  }
+  // enough blocks to fill the GPU several times over, few enough that the per-block atomics stay cheap
+  const long lanes_t = groups < THREADS ? THREADS / groups : 1;
+  long per_lane = gp.tokens / (lanes_t * 1024);
+  per_lane = per_lane < 1 ? 1 : (per_lane > 32 ? 32 : per_lane);
+  const long tile = per_lane * lanes_t;
+  const long tiles = (gp.tokens + tile - 1) / tile;
+  if (tiles > 65535) {
+    set_error("gate prologue: more than %ld tokens per call", 65535 * tile);
+    return JLA_ERR_UNSUPPORTED;
+  }
+  GateParams q = gp;
+  q.tokens_per_lane = (int)per_lane;
+  const dim3 grid(groups < THREADS ? 1 : groups / THREADS, (unsigned)tiles);
+  switch (dtype) {
+    case JLA_DTYPE_BF16: gate_kernel<__nv_bfloat16, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
+    case JLA_DTYPE_F16: gate_kernel<__half, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
+    case JLA_DTYPE_F32: gate_kernel<float, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
+    default: set_error("gate prologue: unknown dtype %d", dtype); return JLA_ERR_BAD_ARGUMENT;
+  }
+  JLA_LAUNCH_OK();
+  return JLA_OK;
+}
+
+template <bool BWD>
+int launch(int dtype, const GateParams& gp, cudaStream_t s) {
+  if (gp.tokens < 0 || gp.H <= 0 || gp.C <= 0) {
+    set_error("gate prologue: need H > 0 and C > 0 (got H=%d, C=%d)", gp.H, gp.C);
+    return JLA_ERR_BAD_ARGUMENT;
+  }
+  if (BWD) {
+    JLA_CUDA_OK(cudaMemsetAsync(gp.da_log, 0, sizeof(float) * gp.H, s));
+    JLA_CUDA_OK(cudaMemsetAsync(gp.ddt_bias, 0, sizeof(float) * gp.H * gp.C, s));
+  }
+  if (gp.tokens == 0) return JLA_OK;
+  return (gp.H * gp.C) % 8 == 0 ? launch_vec<BWD, 8>(dtype, gp, s) : launch_vec<BWD, 1>(dtype, gp, s);
+}
+
+}  // namespace
+}  // namespace jla
+
+using namespace jla;
+
+extern "C" int jla_gate_prologue_fwd(int dtype, int64_t tokens, int H, int C, const void* a, const float* a_log,
+                                     const float* dt_bias, const void* b, int allow_neg_eigval, float* g, float* beta,
+                                     jla_stream_t stream) {
+  if (!a || !a_log || !dt_bias || !g || (b && !beta)) return JLA_ERR_BAD_ARGUMENT;
+  GateParams gp{};
+  gp.tokens = tokens, gp.H = H, gp.C = C, gp.a = a, gp.b = b, gp.a_log = a_log, gp.dt_bias = dt_bias;
+  gp.mult = allow_neg_eigval ? 2.f : 1.f, gp.g = g, gp.beta = beta;
+  return launch<false>(dtype, gp, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int jla_gate_prologue_bwd(int dtype, int64_t tokens, int H, int C, const void* a, const float* a_log,
+                                     const float* dt_bias, const void* b, int allow_neg_eigval, const float* dg,
+                                     const float* dbeta, void* da, void* db, float* da_log, float* ddt_bias,
+                                     jla_stream_t stream) {
+  if (!a || !a_log || !dt_bias || !dg || !da || !da_log || !ddt_bias || (b && (!dbeta || !db))) return JLA_ERR_BAD_ARGUMENT;
+  GateParams gp{};
+  gp.tokens = tokens, gp.H = H, gp.C = C, gp.a = a, gp.b = b, gp.a_log = a_log, gp.dt_bias = dt_bias;
+  gp.mult = allow_neg_eigval ? 2.f : 1.f, gp.dg = dg, gp.dbeta = dbeta, gp.da = da, gp.db = db;
+  gp.da_log = da_log, gp.ddt_bias = ddt_bias;
+  return launch<true>(dtype, gp, static_cast<cudaStream_t>(stream));
+}

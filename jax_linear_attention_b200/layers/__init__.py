@@ -1,2 +1,4 @@
-"""Callers of the hot path that the reference keeps in ``jla.layers``: the Mamba-2 SSD mapping."""
+"""Callers of the hot path that the reference keeps in ``jla.layers``: the Mamba-2 SSD mapping and the gate
+activations of the Gated DeltaNet / KDA mixers."""
+from .gates import gate_prologue  # noqa: F401
 from .ssm import mamba2_ssd  # noqa: F401

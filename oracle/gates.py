@@ -1,0 +1,26 @@
+"""CPU restatement of the mixers' gate activations (test infrastructure only; nothing under the package imports it).
+
+Follows ``src/jla/layers/linear_attention.py:84-86`` (``_mamba_gate``: ``-exp(A_log) * softplus(a + dt_bias)`` in
+float32, ``A_log`` broadcast per head) and ``:159-162`` (``_write_strength``: ``sigmoid``, doubled with
+``allow_neg_eigval``), in torch float64 so that autograd supplies the gradients. Parity: pinned by closed-form values
+(``tests/test_oracle.py``), the formulas having no free choices.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def mamba_gate(a, a_log, dt_bias):
+    a = a.double()
+    a_log = a_log.double()
+    dt_bias = dt_bias.double().reshape(a.shape[2:])
+    neg = -torch.exp(a_log)
+    if a.ndim == 4:
+        neg = neg[:, None]
+    return neg * torch.nn.functional.softplus(a + dt_bias)
+
+
+def write_strength(b, allow_neg_eigval: bool = False):
+    s = torch.sigmoid(b.double())
+    return 2.0 * s if allow_neg_eigval else s

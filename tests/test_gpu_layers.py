@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from oracle import ssd as oracle_ssd
-from oracle.cases import baseline_config, make_case, make_mamba2_case
+from oracle.cases import baseline_config, make_case, make_mamba2_case, rel_l2
 from tests._util import compare, run_cuda, run_oracle
 
 pytestmark = pytest.mark.gpu
@@ -85,3 +85,32 @@ def test_kda_default_dispatch_bf16(docs):
     want = run_oracle("kda", case, scale=case["meta"]["scale"], chunked=True)
     got = run_cuda("kda", case, scale=case["meta"]["scale"], dtype="bfloat16")
     compare(got, want, 1e-2, "kda")
+
+
+@pytest.mark.parametrize("width,dtype,neg", [(1, torch.bfloat16, False), (128, torch.bfloat16, True), (1, torch.float32, True)])
+def test_gate_prologue_matches_the_cpu_restatement(width, dtype, neg):
+    """g = -exp(A_log) softplus(a + dt_bias), beta = (2) sigmoid(b), and all their gradients."""
+    from jax_linear_attention_b200.layers import gate_prologue
+    from oracle import gates
+
+    torch.manual_seed(3)
+    B, T, H = 2, 300, 16
+    shape = (B, T, H) if width == 1 else (B, T, H, width)
+    dev = torch.device("cuda")
+    a = (torch.randn(shape) * 2).to(dtype)
+    b = torch.randn(B, T, H).to(dtype)
+    a_log = torch.randn(H) * 0.5
+    dt_bias = torch.randn(H * width).reshape(shape[2:]) - 1.0
+    dg = torch.randn(shape)
+    dbeta = torch.randn(B, T, H)
+    leaves = [x.to(dev).requires_grad_(True) for x in (a, a_log, dt_bias, b)]
+    g, beta = gate_prologue(leaves[0], leaves[1], leaves[2], leaves[3], allow_neg_eigval=neg)
+    got = torch.autograd.grad([g, beta], leaves, [dg.to(dev), dbeta.to(dev)])
+    ref = [x.double().requires_grad_(True) for x in (a, a_log, dt_bias, b)]
+    g64, b64 = gates.mamba_gate(ref[0], ref[1], ref[2]), gates.write_strength(ref[3], neg)
+    want = torch.autograd.grad([g64, b64], ref, [dg.double(), dbeta.double()])
+    tol = 1e-5 if dtype == torch.float32 else 6e-3  # 16-bit: da, db are rounded to the activation dtype
+    assert rel_l2(g.detach().cpu().numpy(), g64.detach().numpy()) < 1e-5
+    assert rel_l2(beta.detach().cpu().numpy(), b64.detach().numpy()) < 1e-5
+    for name, x, y in zip(("da", "dA_log", "ddt_bias", "db"), got, want):
+        assert rel_l2(x.float().cpu().numpy(), y.numpy()) < (tol if name in ("da", "db") else 1e-4), name

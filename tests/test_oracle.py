@@ -160,3 +160,22 @@ def test_shape_errors():
                               segment_ids=torch.zeros(1, 8, dtype=torch.int32))
     with pytest.raises(ValueError, match="q and k"):
         recurrence.simple_gla(q, q[..., :2], q, torch.zeros(2, 8, 2))
+
+
+def test_gate_activations_closed_form():
+    """``_mamba_gate`` and ``_write_strength`` (linear_attention.py:84-86, 159-162) at points with known values."""
+    import math
+
+    from oracle import gates
+
+    a = torch.tensor([[[0.0, 1.0], [-2.0, 30.0]]])           # [1, 2, 2]
+    a_log = torch.tensor([0.0, math.log(2.0)], dtype=torch.float64)
+    dt_bias = torch.tensor([0.0, -1.0])
+    g = gates.mamba_gate(a, a_log, dt_bias)
+    want = [[-math.log(2.0), -2 * math.log(2.0)], [-math.log1p(math.exp(-2.0)), -2 * (29.0 + math.log1p(math.exp(-29.0)))]]
+    assert torch.allclose(g[0], torch.tensor(want, dtype=torch.float64), rtol=1e-12)
+    b = torch.tensor([0.0, math.log(3.0)], dtype=torch.float64)
+    assert torch.allclose(gates.write_strength(b), torch.tensor([0.5, 0.75], dtype=torch.float64))
+    assert torch.allclose(gates.write_strength(b, True), torch.tensor([1.0, 1.5], dtype=torch.float64))
+    k = gates.mamba_gate(torch.zeros(1, 1, 2, 3), a_log, torch.zeros(2, 3))  # per-channel form: A_log per head
+    assert torch.allclose(k[0, 0], torch.tensor([[-math.log(2.0)] * 3, [-2 * math.log(2.0)] * 3], dtype=torch.float64))
