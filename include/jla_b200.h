@@ -64,8 +64,10 @@ enum jla_flags {
   JLA_FLAG_PREP_DONE = 4,      /* forward: the buffer passed as residuals (or scratch) already holds the chunk table,
                                 * gates, T0/Ag and normalised q/k of an earlier forward with the same k, g, beta,
                                 * segment_ids / cu_seqlens and (with the L2 norm) q: skip recomputing them          */
-  JLA_FLAG_STATE_GRADS_ONLY = 8 /* backward: run the reverse state pass only: dh0 and dv are written, dq, dk, dg and
-                                * dbeta are left untouched                                                          */
+  JLA_FLAG_STATE_GRADS_ONLY = 8, /* backward: run the reverse state pass only: dh0 and dv are written, dq, dk, dg and
+                                 * dbeta are left untouched                                                         */
+  JLA_FLAG_STATE_ONLY = 16      /* forward: only final_state (and residuals) are wanted; o may be left unwritten
+                                 * (the tcgen05 forward then skips the score and output products)                  */
 };
 
 enum jla_status {

@@ -17,6 +17,7 @@ FLAG_QK_L2NORM = 1
 FLAG_SAVE_RESIDUALS = 2
 FLAG_PREP_DONE = 4
 FLAG_STATE_GRADS_ONLY = 8
+FLAG_STATE_ONLY = 16
 OK, ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA = 0, -1, -2, -3, -4
 
 EXPORTS = (

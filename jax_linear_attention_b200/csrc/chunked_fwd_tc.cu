@@ -44,6 +44,7 @@ struct FwdTcParams {
   int H, Hk;
   float scale;
   int* status;
+  int state_only;  // final state (and residuals) only: no scores, no outputs
 };
 
 struct Smem {
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         umma::commit(bars + B_PDONE);
         return true;
       };
-      bool okm = n > 0 ? issue_p(0) : true;
+      bool okm = n > 0 && !p.state_only ? issue_p(0) : true;
       for (int it = 0; it < n && okm; ++it) {
         const int s = it % NS;
         const uint32_t ph = it & 1;
@@ -197,13 +198,15 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
           umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, ak, 64, false);  // S^T K^T
           umma::commit(bars + B_M1);
         }
-        if (it + 1 < n && !issue_p(it + 1)) break;
-        // q has been scaled by (cin Gamma)_i in place by the score group (part of "PA ready")
-        if (!wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
-        if (!wait(bars + B_OFREE0 + (it & 1), ((it >> 1) & 1) ^ 1, abort_flag)) break;
-        umma::fence_after_sync();
         const uint32_t co = cO + (it & 1) * 64;
-        umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + co, tmem + cSb, aq, 64, false);  // S^T ((cin Gamma) Q)^T
+        if (!p.state_only) {
+          if (it + 1 < n && !issue_p(it + 1)) break;
+          // q has been scaled by (cin Gamma)_i in place by the score group (part of "PA ready")
+          if (!wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
+          if (!wait(bars + B_OFREE0 + (it & 1), ((it >> 1) & 1) ^ 1, abort_flag)) break;
+          umma::fence_after_sync();
+          umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + co, tmem + cSb, aq, 64, false);  // S^T ((cin Gamma) Q)^T
+        }
         if (DELTA) {
           if (!wait(bars + B_W, ph, abort_flag)) break;
           umma::fence_after_sync();
@@ -214,8 +217,10 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         umma::fence_after_sync();
         umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cVg, ak, 64, true);  // S^T += (Gamma_r Vn)^T K
         umma::commit(bars + B_M3);
-        umma::gemm_ts<128, 64, 4, false, FMT>(tmem + co, tmem + cWb, umma::smem_addr(Pb + (it & 1) * 8192), 64,
-                                              true);  // += Vn^T P^T
+        if (!p.state_only) {
+          umma::gemm_ts<128, 64, 4, false, FMT>(tmem + co, tmem + cWb, umma::smem_addr(Pb + (it & 1) * 8192), 64,
+                                                true);  // += Vn^T P^T
+        }
         umma::commit(bars + B_ODONE);
         umma::commit(bars + NS + s);
       }
@@ -448,10 +453,19 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
       if (lane == 0) mbar_arrive(bars + B_PA0 + buf);
       return true;
     };
-    if (n > 0) ok = build(0);
-    for (int it = 0; it < n && ok; ++it) {
+    if (p.state_only) {  // nothing to build or to write: only release the stages
+      for (int it = 0; it < n && ok; ++it) {
+        const int s = it % NS;
+        ok = wait(bars + s, (it / NS) & 1, abort_flag);
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(bars + NS + s);
+      }
+    }
+    const int n_out = p.state_only ? 0 : n;
+    if (n_out > 0) ok = build(0);
+    for (int it = 0; it < n_out && ok; ++it) {
       const int s = it % NS;
-      if (it + 1 < n) {
+      if (it + 1 < n_out) {
         ok = build(it + 1);
         if (!ok) break;
       }
@@ -535,6 +549,7 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
   fp.Hk = p.Hk;
   fp.scale = p.scale;
   fp.status = tc_status_ptr();
+  fp.state_only = (p.flags & JLA_FLAG_STATE_ONLY) != 0;
   if (!fp.status) return JLA_ERR_CUDA;
   const int blocks = pl.rows * p.H;
   if (p.dtype == JLA_DTYPE_BF16) {

@@ -42,7 +42,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
-from ..ops.cuda import shared_prep, state_grads_only
+from ..ops.cuda import final_state_only, shared_prep, state_grads_only
 
 _GATES = {"simple_gla": ("g",), "deltanet": ("beta",), "gated_deltanet": ("g", "beta"), "kda": ("g", "beta")}
 
@@ -283,7 +283,7 @@ class _PiecewiseContextParallel(torch.autograd.Function):
         share = shared_prep()  # the three passes read the same keys and gates: one chunk table, one set of inverses
         share.__enter__()
         try:
-            with torch.no_grad():
+            with torch.no_grad(), final_state_only():
                 init_e = None
                 if has_h0:
                     init_e = torch.zeros(pieces, heads, kd, vd, dtype=sdt, device=dev)

@@ -115,6 +115,7 @@ class _PassOptions:
     sequence-parallel form). Plain module state, not thread-local: autograd runs backward on its own thread."""
     share = None              # dict(key=..., buffer=...) while shared_prep() is active
     state_grads_only = False  # backward runs the reverse state pass only (dh0, dv)
+    final_state_only = False  # forward computes the final state only (o is left unwritten)
 
 
 class shared_prep:
@@ -130,6 +131,19 @@ class shared_prep:
 
     def __exit__(self, *exc):
         _PassOptions.share = self._outer
+
+
+class final_state_only:
+    """``with final_state_only():`` forward calls return a valid final state and an ``o`` that must be ignored
+    (the kernels skip the score and output products)."""
+
+    def __enter__(self):
+        self._outer = _PassOptions.final_state_only
+        _PassOptions.final_state_only = True
+        return self
+
+    def __exit__(self, *exc):
+        _PassOptions.final_state_only = self._outer
 
 
 class state_grads_only:
@@ -155,6 +169,8 @@ class _LinearAttention(torch.autograd.Function):
         H, V = v.shape[2:]
         needs_grad = any(x is not None and x.requires_grad for x in (q, k, v, g, beta, h0))
         flags = (_lib.FLAG_QK_L2NORM if cfg["l2norm"] else 0) | (_lib.FLAG_SAVE_RESIDUALS if needs_grad else 0)
+        if _PassOptions.final_state_only and not needs_grad:
+            flags |= _lib.FLAG_STATE_ONLY
         cu, seg = cfg["cu_seqlens"], cfg["segment_ids"]
         rows = B if cu is None else cu.numel() - 1
         p = _problem(cfg["kind"], q.dtype, B, T, H, Hk, K, V, 0 if cu is None else rows, cfg["scale"], flags,

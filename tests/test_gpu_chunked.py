@@ -155,10 +155,11 @@ def test_baseline_config1_full_size_slices_and_properties():
 
 
 def test_shared_prep_and_state_only_backward_match_the_plain_calls():
-    """Passes that share one chunk table (JLA_FLAG_PREP_DONE) and the reverse-state-pass-only backward
-    (JLA_FLAG_STATE_GRADS_ONLY) give the plain calls' results bit for bit."""
+    """Passes that share one chunk table (JLA_FLAG_PREP_DONE), the reverse-state-pass-only backward
+    (JLA_FLAG_STATE_GRADS_ONLY) and the state-only forward (JLA_FLAG_STATE_ONLY) give the plain calls' results bit
+    for bit."""
     from jax_linear_attention_b200 import ops
-    from jax_linear_attention_b200.ops.cuda import shared_prep, state_grads_only
+    from jax_linear_attention_b200.ops.cuda import final_state_only, shared_prep, state_grads_only
 
     case = make_case("gated_deltanet", B=1, T=1500, H=4, K=128, V=128, seed=77, docs="mixed", h0=True)
     dev = torch.device("cuda")
@@ -187,3 +188,6 @@ def test_shared_prep_and_state_only_backward_match_the_plain_calls():
     assert torch.equal(got_dh0, want_dh0)
     (full_dh0,) = torch.autograd.grad([o2s], [leaf2s], [do])
     assert torch.equal(full_dh0, want_dh0)
+    with final_state_only():  # JLA_FLAG_STATE_ONLY: the outputs are skipped, the state pass is the same
+        _, f1o, _ = run(t["v"], h0, False)
+    assert torch.equal(f1o, f1)
