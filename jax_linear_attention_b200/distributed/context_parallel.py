@@ -223,6 +223,10 @@ class PiecePlan:
     def __init__(self, cu, cont, cu_device):
         self.cu, self.cont, self.cu_device = cu, cont, cu_device
         self.buffers = {}  # constant operands of the map pass (identity states, zero values), kept between calls
+        # pieces (other than the first) that continue a document, as a device index: building it per call would
+        # cost a synchronous host-to-device copy in the middle of the step
+        self.cont_index = torch.tensor([p for p in range(1, len(cont)) if cont[p]], dtype=torch.long,
+                                       device=cu_device.device)
 
 
 def plan_pieces(segment_ids, piece_len: int, *, group=None, t_local: int | None = None, device=None) -> PiecePlan:
@@ -326,7 +330,7 @@ class _PiecewiseContextParallel(torch.autograd.Function):
                     send_req.wait()
                 # entering states: the previous piece's final state where the document continues, else zero
                 s_in = torch.zeros(pieces, heads, kd, vd, dtype=sdt, device=dev)
-                idx = torch.tensor([p for p in range(1, pieces) if cont[p]], dtype=torch.long, device=dev)
+                idx = plan.cont_index
                 if idx.numel():
                     s_in[idx] = s_out[idx - 1]
                 if cont[0]:
