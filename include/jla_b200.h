@@ -188,6 +188,18 @@ int jla_gate_prologue_bwd(int dtype, int64_t tokens, int H, int C, const void* a
                           const float* dt_bias, const void* b, int allow_neg_eigval, const float* dg, const float* dbeta,
                           void* da, void* db, float* da_log, float* ddt_bias, jla_stream_t stream);
 
+/* Gated RMS norm behind the kernels (the mixers' output norm; with norm_before_gate = 0 the Mamba-2 norm), forward
+ * and backward in one pass each; replaces GatedRMSNorm.__call__ (src/jla/layers/norm.py:60-112) and its transpose.
+ *   gate = silu(z), or sigmoid(z) with sigmoid_gate;  u = x (norm_before_gate) or x * gate;
+ *   y = u * rsqrt(mean over each group of `group` channels of u^2 + eps) * weight (* gate with norm_before_gate)
+ * x, z, y, dy, dx, dz [rows, dim] dtype; weight, dweight [dim] f32 (dweight is zeroed by the call, then accumulated).
+ * `group` divides dim and is 8 times a power of two, at most 8192. */
+int jla_gated_rmsnorm_fwd(int dtype, int64_t rows, int dim, int group, const void* x, const void* z, const float* weight,
+                          float eps, int sigmoid_gate, int norm_before_gate, void* y, jla_stream_t stream);
+int jla_gated_rmsnorm_bwd(int dtype, int64_t rows, int dim, int group, const void* x, const void* z, const float* weight,
+                          float eps, int sigmoid_gate, int norm_before_gate, const void* dy, void* dx, void* dz,
+                          float* dweight, jla_stream_t stream);
+
 /* Diagnostics: where the chunked path keeps its intermediates, so that tests can compare them stage by stage
  * with the CPU model (the reference checks its kernels per stage too:
  * tests/test_mosaic_gpu_gated_delta_rule.py:104-146). Byte offsets into the residual buffer written by a forward

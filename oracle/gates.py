@@ -24,3 +24,19 @@ def mamba_gate(a, a_log, dt_bias):
 def write_strength(b, allow_neg_eigval: bool = False):
     s = torch.sigmoid(b.double())
     return 2.0 * s if allow_neg_eigval else s
+
+
+def gated_rms_norm(x, z, weight, *, eps=1e-6, activation="silu", norm_before_gate=True, group_size=None):
+    """``GatedRMSNorm.__call__`` (``src/jla/layers/norm.py:96-109``) in float64."""
+    x64, z64 = x.double(), z.double()
+    gate = torch.nn.functional.silu(z64) if activation == "silu" else torch.sigmoid(z64)
+    if not norm_before_gate:
+        x64 = x64 * gate
+    dim = x.shape[-1]
+    group = group_size or dim
+    grouped = x64.reshape(*x.shape[:-1], dim // group, group)
+    y = grouped * torch.rsqrt((grouped * grouped).mean(-1, keepdim=True) + eps)
+    y = y.reshape(x.shape) * weight.double()
+    if norm_before_gate:
+        y = y * gate
+    return y

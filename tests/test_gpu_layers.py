@@ -114,3 +114,31 @@ def test_gate_prologue_matches_the_cpu_restatement(width, dtype, neg):
     assert rel_l2(beta.detach().cpu().numpy(), b64.detach().numpy()) < 1e-5
     for name, x, y in zip(("da", "dA_log", "ddt_bias", "db"), got, want):
         assert rel_l2(x.float().cpu().numpy(), y.numpy()) < (tol if name in ("da", "db") else 1e-4), name
+
+
+@pytest.mark.parametrize("shape,group,act,nbg,dtype", [
+    ((2, 300, 16, 128), None, "silu", True, torch.bfloat16),      # Gated DeltaNet output norm: one group per head
+    ((2, 300, 16, 128), None, "sigmoid", True, torch.bfloat16),   # KDA
+    ((3, 70, 4096), 4096, "silu", False, torch.bfloat16),         # Mamba-2, one group over d_inner (block-wide sum)
+    ((3, 70, 1024), 64, "silu", False, torch.float32),            # grouped norm, float32
+])
+def test_gated_rms_norm_matches_the_cpu_restatement(shape, group, act, nbg, dtype):
+    from jax_linear_attention_b200.layers import gated_rms_norm
+    from oracle import gates
+
+    torch.manual_seed(5)
+    dev = torch.device("cuda")
+    x = torch.randn(shape).to(dtype)
+    z = torch.randn(shape).to(dtype)
+    w = 1.0 + 0.1 * torch.randn(shape[-1])
+    dy = torch.randn(shape).to(dtype)
+    leaves = [t.to(dev).requires_grad_(True) for t in (x, z, w)]
+    y = gated_rms_norm(leaves[0], leaves[1], leaves[2], eps=1e-5, activation=act, norm_before_gate=nbg, group_size=group)
+    got = torch.autograd.grad([y], leaves, [dy.to(dev)])
+    ref = [t.double().requires_grad_(True) for t in (x, z, w)]
+    y64 = gates.gated_rms_norm(ref[0], ref[1], ref[2], eps=1e-5, activation=act, norm_before_gate=nbg, group_size=group)
+    want = torch.autograd.grad([y64], ref, [dy.double()])
+    tol = 1e-5 if dtype == torch.float32 else 6e-3  # 16-bit: y, dx, dz are rounded to the activation dtype
+    assert rel_l2(y.detach().float().cpu().numpy(), y64.detach().numpy()) < tol
+    for name, a, b in zip(("dx", "dz", "dweight"), got, want):
+        assert rel_l2(a.float().cpu().numpy(), b.numpy()) < (tol if name != "dweight" else 1e-4), name

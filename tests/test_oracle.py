@@ -179,3 +179,23 @@ def test_gate_activations_closed_form():
     assert torch.allclose(gates.write_strength(b, True), torch.tensor([1.0, 1.5], dtype=torch.float64))
     k = gates.mamba_gate(torch.zeros(1, 1, 2, 3), a_log, torch.zeros(2, 3))  # per-channel form: A_log per head
     assert torch.allclose(k[0, 0], torch.tensor([[-math.log(2.0)] * 3, [-2 * math.log(2.0)] * 3], dtype=torch.float64))
+
+
+def test_gated_rms_norm_closed_form():
+    """``GatedRMSNorm`` (norm.py:96-109): a constant row has unit RMS; both gate placements; groups."""
+    import math
+
+    from oracle import gates
+
+    x = torch.full((1, 4), 3.0, dtype=torch.float64)
+    z = torch.zeros(1, 4, dtype=torch.float64)          # silu(0) = 0, sigmoid(0) = 0.5
+    w = torch.tensor([1.0, 2.0, 3.0, 4.0], dtype=torch.float64)
+    assert torch.allclose(gates.gated_rms_norm(x, z, w, eps=0.0, activation="sigmoid"), 0.5 * w[None])
+    assert torch.allclose(gates.gated_rms_norm(x, z, w, eps=0.0, activation="sigmoid", norm_before_gate=False), w[None])
+    assert torch.allclose(gates.gated_rms_norm(x, z, w, eps=0.0), torch.zeros(1, 4, dtype=torch.float64))
+    x2 = torch.tensor([[1.0, 1.0, 3.0, 3.0]], dtype=torch.float64)
+    z2 = torch.full((1, 4), 50.0, dtype=torch.float64)  # silu(50) = 50 to 1e-20
+    got = gates.gated_rms_norm(x2, z2, torch.ones(4, dtype=torch.float64), eps=0.0, group_size=2)
+    assert torch.allclose(got, torch.full((1, 4), 50.0, dtype=torch.float64), rtol=1e-12)
+    whole = gates.gated_rms_norm(x2, z2, torch.ones(4, dtype=torch.float64), eps=0.0)
+    assert torch.allclose(whole, 50.0 * x2 / math.sqrt(5.0), rtol=1e-12)
