@@ -180,7 +180,7 @@ int jla_ssd_output_bwd(int dtype, int64_t tokens, int H, int P, const void* dy, 
  *                                                   A_log [H] f32, g [tokens, H, C] f32
  *   beta = m * sigmoid(b), m = allow_neg_eigval ? 2 : 1     b [tokens, H] dtype (may be NULL), beta [tokens, H] f32
  * Backward: da, db in dtype; dA_log [H] and ddt_bias [H, C] f32 are zeroed by the call and then accumulated.
- * H * C / 8 (H * C itself when it is no multiple of 8) must divide 256 or be a multiple of it. */
+ * H * C / 8 (H * C itself when it is no multiple of 8) must divide 32 or be a multiple of it. */
 int jla_gate_prologue_fwd(int dtype, int64_t tokens, int H, int C, const void* a, const float* a_log,
                           const float* dt_bias, const void* b, int allow_neg_eigval, float* g, float* beta,
                           jla_stream_t stream);

@@ -16,7 +16,7 @@
 namespace jla {
 namespace {
 
-constexpr int THREADS = 256;
+constexpr int THREADS = 512;
 
 struct GateParams {
   long tokens;
@@ -25,6 +25,7 @@ struct GateParams {
   const float *a_log, *dt_bias;
   float mult;                   // 1 or 2
   int tokens_per_lane;          // tokens one thread walks (set by the launcher)
+  int cols;                     // column threads of a block; the other threads are token lanes
   float *g, *beta;              // forward outputs
   const float *dg, *dbeta;      // backward inputs
   void *da, *db;                // backward outputs (dtype)
@@ -74,8 +75,8 @@ template <typename T, bool BWD, int VEC>
 __global__ void __launch_bounds__(THREADS) gate_kernel(GateParams p) {
   const int HC = p.H * p.C;
   const int groups = HC / VEC;
-  const int cols = groups < THREADS ? groups : THREADS;
-  const int lanes_t = THREADS / cols;
+  const int cols = p.cols;
+  const int lanes_t = blockDim.x / cols;
   const int ct = (int)(threadIdx.x % cols);
   const int grp = blockIdx.x * cols + ct;
   const int lt = threadIdx.x / cols;
@@ -161,14 +162,16 @@ __global__ void __launch_bounds__(THREADS) gate_kernel(GateParams p) {
 template <bool BWD, int VEC>
 int launch_vec(int dtype, const GateParams& gp, cudaStream_t s) {
   const int groups = gp.H * gp.C / VEC;
-  if (groups >= THREADS ? groups % THREADS != 0 : THREADS % groups != 0) {
-    set_error("gate prologue: H * C / %d = %d must divide or be a multiple of %d", VEC, groups, THREADS);
+  // a warp covers up to 32 adjacent column groups of one token; the block's other warps are token lanes, so that
+  // many tokens fold into one set of parameter-gradient atomics
+  const int cols = groups < 32 ? groups : 32;
+  if (groups % cols != 0 || THREADS % cols != 0) {
+    set_error("gate prologue: H * C / %d = %d must divide 32 or be a multiple of it", VEC, groups);
     return JLA_ERR_UNSUPPORTED;
   }
-  // enough blocks to fill the GPU several times over, few enough that the per-block atomics stay cheap
-  const long lanes_t = groups < THREADS ? THREADS / groups : 1;
-  long per_lane = gp.tokens / (lanes_t * 1024);
-  per_lane = per_lane < 1 ? 1 : (per_lane > 32 ? 32 : per_lane);
+  const long lanes_t = THREADS / cols;
+  long per_lane = gp.tokens / (lanes_t * 64);
+  per_lane = per_lane < 1 ? 1 : (per_lane > 16 ? 16 : per_lane);
   const long tile = per_lane * lanes_t;
   const long tiles = (gp.tokens + tile - 1) / tile;
   if (tiles > 65535) {
@@ -177,7 +180,8 @@ int launch_vec(int dtype, const GateParams& gp, cudaStream_t s) {
   }
   GateParams q = gp;
   q.tokens_per_lane = (int)per_lane;
-  const dim3 grid(groups < THREADS ? 1 : groups / THREADS, (unsigned)tiles);
+  q.cols = cols;
+  const dim3 grid(groups / cols, (unsigned)tiles);
   switch (dtype) {
     case JLA_DTYPE_BF16: gate_kernel<__nv_bfloat16, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
     case JLA_DTYPE_F16: gate_kernel<__half, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
