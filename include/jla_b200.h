@@ -188,6 +188,22 @@ int jla_gate_prologue_bwd(int dtype, int64_t tokens, int H, int C, const void* a
                           const float* dt_bias, const void* b, int allow_neg_eigval, const float* dg, const float* dbeta,
                           void* da, void* db, float* da_log, float* ddt_bias, jla_stream_t stream);
 
+/* Short causal depthwise convolution (+ SiLU) (+ per-head L2 norm), the q / k prologue of the delta-rule mixers,
+ * forward and backward in one pass each; replaces ShortConv.__call__ (src/jla/layers/conv.py:97-142) followed by the
+ * op's use_qk_l2norm, i.e. the fused kernels of src/jla/ops/mosaic_gpu/short_conv_l2norm.py.
+ *   x, y, dy, dx [B, T, C] dtype; weight, dweight [C, K] f32 (1 <= K <= 4); bias, dbias [C] f32 or NULL;
+ *   segment_ids [B, T] int32 or NULL (taps into an earlier document contribute zero); state, dstate [B, K - 1, C]
+ *   dtype or NULL (the inputs before t = 0; they count as the first token's document); head_dim > 0 normalises each
+ *   head_dim consecutive channels to unit L2 norm (eps 1e-6) in float32 before the single rounding; 0 = no norm.
+ * dweight and dbias are zeroed by the call, then accumulated. The state after the call (the last K - 1 inputs) is
+ * input data and is assembled by the host. */
+int jla_short_conv_fwd(int dtype, int B, int T, int C, int K, int head_dim, int activation, const void* x,
+                       const float* weight, const float* bias, const int32_t* segment_ids, const void* state, void* y,
+                       jla_stream_t stream);
+int jla_short_conv_bwd(int dtype, int B, int T, int C, int K, int head_dim, int activation, const void* x,
+                       const float* weight, const float* bias, const int32_t* segment_ids, const void* state,
+                       const void* dy, void* dx, float* dweight, float* dbias, void* dstate, jla_stream_t stream);
+
 /* Gated RMS norm behind the kernels (the mixers' output norm; with norm_before_gate = 0 the Mamba-2 norm), forward
  * and backward in one pass each; replaces GatedRMSNorm.__call__ (src/jla/layers/norm.py:60-112) and its transpose.
  *   gate = silu(z), or sigmoid(z) with sigmoid_gate;  u = x (norm_before_gate) or x * gate;

@@ -40,3 +40,37 @@ def gated_rms_norm(x, z, weight, *, eps=1e-6, activation="silu", norm_before_gat
     if norm_before_gate:
         y = y * gate
     return y
+
+
+def short_conv(x, weight, bias=None, *, activation=True, head_dim=None, segment_ids=None, state=None):
+    """``ShortConv.__call__`` (``src/jla/layers/conv.py:97-142``) followed by the per-head ``l2norm`` of
+    ``src/jla/ops/reference.py:65-69`` (as the fused ``short_conv_l2norm`` does, without rounding in between), in
+    float64. Returns ``(y, new_state)``."""
+    B, T, Cn = x.shape
+    K = weight.shape[1]
+    x64 = x.double()
+    st = x64.new_zeros(B, K - 1, Cn) if state is None else state.double()
+    x_ext = torch.cat([st, x64], dim=1)
+    seg_ext = None
+    if segment_ids is not None:
+        seg_ext = torch.cat([segment_ids[:, :1].expand(B, K - 1), segment_ids], dim=1)
+    y = x64.new_zeros(B, T, Cn)
+    if bias is not None:
+        y = y + bias.double()
+    w = weight.double()
+    for i in range(K):
+        tap = x_ext[:, i:i + T] * w[:, i]
+        if seg_ext is not None and i < K - 1:
+            same = seg_ext[:, i:i + T] == segment_ids
+            tap = torch.where(same[..., None], tap, torch.zeros((), dtype=tap.dtype))
+        y = y + tap
+    if activation:
+        y = torch.nn.functional.silu(y)
+    if head_dim:
+        yh = y.reshape(B, T, Cn // head_dim, head_dim)
+        y = (yh * torch.rsqrt((yh * yh).sum(-1, keepdim=True) + 1e-6)).reshape(B, T, Cn)
+    new_state = x_ext[:, T:]
+    if seg_ext is not None and K > 1:
+        keep = seg_ext[:, T:] == segment_ids[:, -1:]
+        new_state = torch.where(keep[..., None], new_state, torch.zeros((), dtype=new_state.dtype))
+    return y, new_state

@@ -142,3 +142,43 @@ def test_gated_rms_norm_matches_the_cpu_restatement(shape, group, act, nbg, dtyp
     assert rel_l2(y.detach().float().cpu().numpy(), y64.detach().numpy()) < tol
     for name, a, b in zip(("dx", "dz", "dweight"), got, want):
         assert rel_l2(a.float().cpu().numpy(), b.numpy()) < (tol if name != "dweight" else 1e-4), name
+
+
+@pytest.mark.parametrize("K,head_dim,act,docs,with_state,bias,dtype", [
+    (4, 128, True, True, True, False, torch.bfloat16),    # the q / k prologue of the mixers
+    (4, 64, True, False, False, True, torch.bfloat16),
+    (4, None, True, True, True, True, torch.float32),     # plain ShortConv
+    (2, 128, False, True, True, False, torch.float32),
+    (3, None, True, False, True, False, torch.bfloat16),
+])
+def test_short_conv_matches_the_cpu_restatement(K, head_dim, act, docs, with_state, bias, dtype):
+    from jax_linear_attention_b200.layers import short_conv
+    from oracle import gates
+
+    torch.manual_seed(11)
+    B, T, Cn = 2, 333, 512
+    dev = torch.device("cuda")
+    x = torch.randn(B, T, Cn).to(dtype)
+    w = torch.randn(Cn, K) * 0.5
+    bb = torch.randn(Cn) * 0.3 if bias else None
+    st = torch.randn(B, K - 1, Cn).to(dtype) if with_state else None
+    seg = None
+    if docs:  # documents of 1 .. 90 tokens, one starting at the first token after the state
+        cuts = torch.sort(torch.randint(1, T, (B, 9)), dim=1).values
+        seg = (torch.arange(T)[None, None] >= cuts[..., None]).sum(1).to(torch.int32)
+    dy = torch.randn(B, T, Cn).to(dtype)
+    names = ["x", "weight"] + (["bias"] if bias else []) + (["state"] if with_state else [])
+    vals = {"x": x, "weight": w, "bias": bb, "state": st}
+    leaves = {n: vals[n].to(dev).requires_grad_(True) for n in names}
+    y, new_state = short_conv(leaves["x"], leaves["weight"], leaves.get("bias"), activation=act, head_dim=head_dim,
+                              segment_ids=None if seg is None else seg.to(dev), state=leaves.get("state"))
+    got = torch.autograd.grad([y], [leaves[n] for n in names], [dy.to(dev)])
+    ref = {n: vals[n].double().requires_grad_(True) for n in names}
+    y64, st64 = gates.short_conv(ref["x"], ref["weight"], ref.get("bias"), activation=act, head_dim=head_dim,
+                                 segment_ids=seg, state=ref.get("state"))
+    want = torch.autograd.grad([y64], [ref[n] for n in names], [dy.double()])
+    tol = 1e-5 if dtype == torch.float32 else 6e-3
+    assert rel_l2(y.detach().float().cpu().numpy(), y64.detach().numpy()) < tol
+    assert torch.equal(new_state.detach().double().cpu(), st64.detach())
+    for n, a, b in zip(names, got, want):
+        assert rel_l2(a.float().cpu().numpy(), b.numpy()) < (tol if n in ("x", "state") else 2e-4), n

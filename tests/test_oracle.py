@@ -199,3 +199,25 @@ def test_gated_rms_norm_closed_form():
     assert torch.allclose(got, torch.full((1, 4), 50.0, dtype=torch.float64), rtol=1e-12)
     whole = gates.gated_rms_norm(x2, z2, torch.ones(4, dtype=torch.float64), eps=0.0)
     assert torch.allclose(whole, 50.0 * x2 / math.sqrt(5.0), rtol=1e-12)
+
+
+def test_short_conv_closed_form():
+    """``ShortConv`` (conv.py:97-142): identity taps, the causal shift, document masking, the carried state."""
+    from oracle import gates
+
+    x = torch.arange(1.0, 7.0, dtype=torch.float64).reshape(1, 6, 1)          # tokens 1..6, one channel
+    ident = torch.tensor([[0.0, 0.0, 0.0, 1.0]], dtype=torch.float64)
+    y, st = gates.short_conv(x, ident, activation=False)
+    assert torch.equal(y, x) and torch.equal(st[0, :, 0], torch.tensor([4.0, 5.0, 6.0], dtype=torch.float64))
+    shift = torch.tensor([[0.0, 0.0, 1.0, 0.0]], dtype=torch.float64)         # y_t = x_{t-1}
+    y, _ = gates.short_conv(x, shift, activation=False)
+    assert torch.equal(y[0, :, 0], torch.tensor([0.0, 1.0, 2.0, 3.0, 4.0, 5.0], dtype=torch.float64))
+    seg = torch.tensor([[0, 0, 0, 1, 1, 1]])
+    y, st = gates.short_conv(x, shift, activation=False, segment_ids=seg)     # token 4 starts a document: no tap into 3
+    assert torch.equal(y[0, :, 0], torch.tensor([0.0, 1.0, 2.0, 0.0, 4.0, 5.0], dtype=torch.float64))
+    state = torch.tensor([[[7.0], [8.0], [9.0]]], dtype=torch.float64)
+    y, _ = gates.short_conv(x, shift, activation=False, state=state)
+    assert y[0, 0, 0] == 9.0
+    two = torch.tensor([[3.0, 4.0]], dtype=torch.float64).reshape(1, 1, 2)    # head of two channels: unit norm
+    y, _ = gates.short_conv(two, torch.tensor([[1.0], [1.0]], dtype=torch.float64), activation=False, head_dim=2)
+    assert torch.allclose(y[0, 0], torch.tensor([0.6, 0.8], dtype=torch.float64), atol=1e-7)
