@@ -9,11 +9,8 @@
 //   dy = inv (dn - n sum_head(dn n));  dpre = dy silu'(pre);  dx_ext[s] = sum_i w[:, i] dpre[s - i + K - 1] (same
 //   document);  dw[:, i] = sum dpre_t x_ext[t + i];  dbias = sum dpre_t
 //
-// HBM-bound. A thread owns eight adjacent channels and a tile of consecutive tokens of one batch row and slides a
-// window of the last K - 1 inputs (forward) or of the next K - 1 pre-activation gradients (backward, walking the
-// tile from its end; the K - 1 tokens behind the tile are recomputed) through registers, so every input row is
-// loaded once per tile. A head's sum is a butterfly over the head_dim / 8 threads that hold it. The conv output
-// stays in float32 until the norm has been applied and is rounded once.
+// HBM-bound. The conv output stays in float32 until the norm has been applied and is rounded once. (Block and
+// thread layout: see the kernel.)
 #include "common.cuh"
 
 namespace jla {
@@ -34,7 +31,6 @@ struct ConvParams {
   void* dx;
   float *dw, *dbias;
   void* dstate;
-  int cols, tile;  // column threads per block (8 channels each); tokens per thread
 };
 
 template <typename T>
@@ -69,50 +65,80 @@ __device__ __forceinline__ float head_sum(float v, int lanes) {
   return v;
 }
 
-// Row t of x_ext's token axis for batch row b: t >= 0 reads x, t < 0 the carried state (zeros without one).
-template <typename T>
-__device__ __forceinline__ void load_row(const ConvParams& p, int b, int t, int col, bool live, float (&f)[8]) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = 0.f;
-  if (!live || t >= p.T) return;
-  if (t >= 0) {
-    load8<T>(static_cast<const T*>(p.x) + ((long)b * p.T + t) * p.C + col, f);
-  } else if (p.state && t >= -(p.K - 1)) {
-    load8<T>(static_cast<const T*>(p.state) + ((long)b * (p.K - 1) + (p.K - 1 + t)) * p.C + col, f);
-  }
-}
+// A block owns TT consecutive tokens of one batch row and 32 adjacent channel vectors (256 channels: one or several
+// whole heads). The inputs it needs (the tile plus K - 1 rows in front, in the backward also K - 1 behind) are staged
+// once in shared memory; a warp then handles one token at a time (lane = channel vector), so the head sums are warp
+// butterflies and nothing is walked serially.
+constexpr int TT = 64;
+constexpr int COLS = 32;
+constexpr int ROW_LANES = THREADS / COLS;  // 8 tokens in flight per block
+
+struct Tile {
+  int b, t0, t1;
+};
 
 __device__ __forceinline__ int seg_at(const ConvParams& p, int b, int t) {
   if (!p.seg) return 0;
   return p.seg[(long)b * p.T + (t < 0 ? 0 : (t >= p.T ? p.T - 1 : t))];
 }
 
-// Pre-activation, activation and norm of one token from its window (win[j] = x_ext token t - (K - 1) + j, j < K).
-// Returns the quantities the backward needs: y (normalised when head_dim > 0), sig = sigmoid(pre), inv.
+// Stages rows [r0, r0 + rows) of x_ext (state rows for t < 0, zeros outside) as float32: xs[row][COLS * 8], and their
+// document ids (state rows: the first token's).
+template <typename T>
+__device__ __forceinline__ void stage_rows(const ConvParams& p, int b, int r0, int rows, int col0, int cv, int vec0,
+                                           float* xs, int* ss) {
+  for (int idx = threadIdx.x; idx < rows * COLS; idx += THREADS) {
+    const int r = idx / COLS, c = idx % COLS, t = r0 + r;
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    if (vec0 + c < cv && t < p.T) {
+      if (t >= 0) load8<T>(static_cast<const T*>(p.x) + ((long)b * p.T + t) * p.C + col0 + c * 8, f);
+      else if (p.state && t >= -(p.K - 1))
+        load8<T>(static_cast<const T*>(p.state) + ((long)b * (p.K - 1) + (p.K - 1 + t)) * p.C + col0 + c * 8, f);
+    }
+    float4* dst = reinterpret_cast<float4*>(xs + (size_t)r * COLS * 8 + c * 8);
+    dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+    dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+  for (int r = threadIdx.x; r < rows; r += THREADS) ss[r] = seg_at(p, b, r0 + r);
+}
+
+// Pre-activation, activation and norm of the token whose window starts at staged row `r` (rows r .. r + K - 1, the
+// last one being the token itself). y is normalised when head_dim > 0.
 struct TokenOut {
-  float y[8], pre[8], inv;
+  float y[8], pre[8], sg[8], inv;  // sg = sigmoid(pre) when the activation is on
 };
 
 template <int K>
 __device__ __forceinline__ void conv_token(const ConvParams& p, const float (&w)[KMAX][8], const float (&bias)[8],
-                                           const float (&win)[KMAX][8], const int (&sw)[KMAX], int lanes, TokenOut& o) {
-  const int sc = sw[K - 1];
-  float ss = 0.f;
+                                           const float* xs, const int* ss, int r, int ct, int lanes, TokenOut& o) {
+  const int sc = ss[r + K - 1];
+  float acc[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc[c] = bias[c];
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    if (j == K - 1 || ss[r + j] == sc) {
+      const float4* src = reinterpret_cast<const float4*>(xs + (size_t)(r + j) * COLS * 8 + ct * 8);
+      const float4 a = src[0], b4 = src[1];
+      const float v[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[c] += w[j][c] * v[c];
+    }
+  }
+  float sq = 0.f;
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
-    float acc = bias[c];
-#pragma unroll
-    for (int j = 0; j < KMAX; ++j) {
-      if (j < K && (j == K - 1 || sw[j] == sc)) acc += w[j][c] * win[j][c];
-    }
-    o.pre[c] = acc;
-    const float y = p.activation ? acc / (1.f + __expf(-acc)) : acc;
+    o.pre[c] = acc[c];
+    o.sg[c] = __frcp_rn(1.f + __expf(-acc[c]));
+    const float y = p.activation ? acc[c] * o.sg[c] : acc[c];
     o.y[c] = y;
-    ss += y * y;
+    sq += y * y;
   }
   o.inv = 1.f;
   if (p.head_dim > 0) {
-    o.inv = rsqrtf(head_sum(ss, lanes) + kL2Eps);
+    o.inv = rsqrtf(head_sum(sq, lanes) + kL2Eps);
 #pragma unroll
     for (int c = 0; c < 8; ++c) o.y[c] *= o.inv;
   }
@@ -120,20 +146,17 @@ __device__ __forceinline__ void conv_token(const ConvParams& p, const float (&w)
 
 template <typename T, bool BWD, int K>
 __global__ void __launch_bounds__(THREADS) short_conv_kernel(ConvParams p) {
-  extern __shared__ float fold[];  // backward: [row lanes][cols * 8 * (K + 1)]
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int cv = p.C / 8;
-  const int cols = p.cols, lanes_r = blockDim.x / cols;
-  const int ct = threadIdx.x % cols, lr = threadIdx.x / cols;
-  const int vec = blockIdx.x * cols + ct;
-  const bool live = vec < cv;
-  const int col = (live ? vec : 0) * 8;
+  const int ct = threadIdx.x % COLS, lr = threadIdx.x / COLS;
+  const int vec0 = blockIdx.x * COLS;
+  const bool live = vec0 + ct < cv;
+  const int col0 = vec0 * 8, col = (live ? vec0 + ct : 0) * 8;
   const int lanes = p.head_dim > 0 ? p.head_dim / 8 : 1;
-  const int tiles_per_row = (p.T + p.tile - 1) / p.tile;
-  const long tile_id = (long)blockIdx.y * lanes_r + lr;
-  const bool has_tile = tile_id < (long)p.B * tiles_per_row;
-  const int b = has_tile ? (int)(tile_id / tiles_per_row) : 0;
-  const int t0 = has_tile ? (int)(tile_id % tiles_per_row) * p.tile : 0;
-  const int t1 = has_tile ? (t0 + p.tile < p.T ? t0 + p.tile : p.T) : 0;
+  const int tiles_per_row = (p.T + TT - 1) / TT;
+  const int b = blockIdx.y / tiles_per_row;
+  const int t0 = (blockIdx.y % tiles_per_row) * TT;
+  const int t1 = t0 + TT < p.T ? t0 + TT : p.T;
   float w[KMAX][8], bias[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
@@ -143,168 +166,124 @@ __global__ void __launch_bounds__(THREADS) short_conv_kernel(ConvParams p) {
   }
 
   if constexpr (!BWD) {
-    float win[KMAX][8];
-    int sw[KMAX];
-#pragma unroll
-    for (int j = 0; j < KMAX; ++j) {  // tokens t0 - (K - 1) + j, j < K - 1, sit in win[j]; win[K - 1] is the token itself
-      if (j < K - 1) {
-        load_row<T>(p, b, t0 - (K - 1) + j, col, live && has_tile, win[j]);
-        sw[j] = seg_at(p, b, t0 - (K - 1) + j);
-      } else {
-        sw[j] = 0;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) win[j][c] = 0.f;
-      }
-    }
-    for (int t = t0; t < t0 + p.tile; ++t) {  // uniform trip count: the head sums shuffle across the warp
-      const bool on = live && has_tile && t < t1;
-      load_row<T>(p, b, t, col, on, win[K - 1]);
-      sw[K - 1] = seg_at(p, b, t);
+    constexpr int ROWS = TT + K - 1;  // staged rows: tokens t0 - (K - 1) .. t1 - 1
+    float* xs = reinterpret_cast<float*>(smem_raw);
+    int* ss = reinterpret_cast<int*>(xs + ROWS * COLS * 8);
+    stage_rows<T>(p, b, t0 - (K - 1), ROWS, col0, cv, vec0, xs, ss);
+    __syncthreads();
+    for (int i = lr; i < TT; i += ROW_LANES) {  // token t0 + i: its window starts at staged row i
       TokenOut o;
-      conv_token<K>(p, w, bias, win, sw, lanes, o);
-      if (on) store8<T>(static_cast<T*>(p.y) + ((long)b * p.T + t) * p.C + col, o.y);
-#pragma unroll
-      for (int j = 0; j < KMAX - 1; ++j) {
-        if (j < K - 1) {
-          sw[j] = sw[j + 1];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) win[j][c] = win[j + 1][c];
-        }
-      }
+      conv_token<K>(p, w, bias, xs, ss, i, ct, lanes, o);
+      if (live && t0 + i < t1) store8<T>(static_cast<T*>(p.y) + ((long)b * p.T + t0 + i) * p.C + col, o.y);
     }
   } else {
-  // ---------------------------------------------------------------------------------------------- backward
-  float dwacc[KMAX][8], dbacc[8];
+    // staged inputs: tokens t0 - (K - 1) .. t1 + (K - 1) - 1 (the K - 1 tokens behind the tile are recomputed: their
+    // pre-activation gradients reach back into the tile); dps[i] = dpre of token t0 + i, i < TT + K - 1
+    constexpr int ROWS = TT + 2 * (K - 1), DROWS = TT + K - 1;
+    float* xs = reinterpret_cast<float*>(smem_raw);
+    float* dps = xs + ROWS * COLS * 8;
+    float* fold = xs;  // [ROW_LANES][COLS * 8 * (K + 1)], over the staged rows once they are dead
+    static_assert(ROW_LANES * (K + 1) <= ROWS + DROWS, "the fold buffer fits over the staged rows");
+    int* ss = reinterpret_cast<int*>(dps + DROWS * COLS * 8);
+    stage_rows<T>(p, b, t0 - (K - 1), ROWS, col0, cv, vec0, xs, ss);
+    __syncthreads();
+    float dwacc[KMAX][8], dbacc[8];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    dbacc[c] = 0.f;
+    for (int c = 0; c < 8; ++c) {
+      dbacc[c] = 0.f;
 #pragma unroll
-    for (int j = 0; j < KMAX; ++j) dwacc[j][c] = 0.f;
-  }
-  // dp[l - 1] = dpre of token t + l (l = 1 .. K - 1) while the walk stands at token t; sp its document id
-  float dp[KMAX][8];
-  int sp[KMAX];
-#pragma unroll
-  for (int j = 0; j < KMAX; ++j) {
-    sp[j] = -1;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) dp[j][c] = 0.f;
-  }
-  // the walk starts K - 1 tokens behind the tile (their dpre feed the tile's dx) and ends K - 1 rows into the state
-  const int t_hi = t1 + (K - 1) - 1;                      // first token visited
-  const int t_lo = (t0 == 0 && p.dstate) ? -(K - 1) : t0;  // last row visited (state rows only for the row's first tile)
-  float win[KMAX][8];
-  int sw[KMAX];
-#pragma unroll
-  for (int j = 0; j < KMAX; ++j) {
-    if (j < K) {
-      load_row<T>(p, b, t_hi - (K - 1) + j, col, live && has_tile, win[j]);
-      sw[j] = seg_at(p, b, t_hi - (K - 1) + j);
-    } else {
-      sw[j] = 0;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) win[j][c] = 0.f;
+      for (int j = 0; j < KMAX; ++j) dwacc[j][c] = 0.f;
     }
-  }
-  const int steps = p.tile + 2 * (K - 1);  // uniform trip count
-  for (int s = 0; s < steps; ++s) {
-    const int t = t_hi - s;
-    const bool visit = has_tile && t >= t_lo;
-    const bool token = visit && t >= 0 && t < p.T;       // a real token: it has a dpre of its own
-    const bool mine = token && t >= t0 && t < t1;        // inside the tile: dx, dw, dbias are this thread's to write
-    float dpre[8];
+    for (int i = lr; i < DROWS; i += ROW_LANES) {  // a warp handles one token at a time (i depends on the warp only)
+      const int t = t0 + i;
+      const bool token = t < p.T;
+      TokenOut o;
+      conv_token<K>(p, w, bias, xs, ss, i, ct, lanes, o);
+      float dnv[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) dpre[c] = 0.f;
-    TokenOut o;
-    conv_token<K>(p, w, bias, win, sw, lanes, o);        // every thread of the warp takes part in the head sums
-    float dnv[8];
+      for (int c = 0; c < 8; ++c) dnv[c] = 0.f;
+      if (token && live) load8<T>(static_cast<const T*>(p.dy) + ((long)b * p.T + t) * p.C + col, dnv);
+      float dot = 0.f;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) dnv[c] = 0.f;
-    if (token && live) load8<T>(static_cast<const T*>(p.dy) + ((long)b * p.T + t) * p.C + col, dnv);
-    float dot = 0.f;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) dot += dnv[c] * o.y[c];
-    if (p.head_dim > 0) dot = head_sum(dot, lanes);
-    if (token && live) {
+      for (int c = 0; c < 8; ++c) dot += dnv[c] * o.y[c];
+      if (p.head_dim > 0) dot = head_sum(dot, lanes);
+      float dpre[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const float dy = p.head_dim > 0 ? o.inv * (dnv[c] - o.y[c] * dot) : dnv[c];
-        const float sg = 1.f / (1.f + __expf(-o.pre[c]));
-        dpre[c] = p.activation ? dy * sg * (1.f + o.pre[c] * (1.f - sg)) : dy;
+        const float sg = o.sg[c];
+        dpre[c] = !token ? 0.f : (p.activation ? dy * sg * (1.f + o.pre[c] * (1.f - sg)) : dy);
       }
-    }
-    const int sc = sw[K - 1];  // document of row t (state rows: the first token's)
-    if (visit && live && (mine || t < 0)) {
-      // dx_ext[t] = w[:, K - 1] dpre_t + sum_l w[:, K - 1 - l] dpre_{t + l} for later tokens of the same document
-      float dxv[8];
+      float4* dst = reinterpret_cast<float4*>(dps + (size_t)i * COLS * 8 + ct * 8);
+      dst[0] = make_float4(dpre[0], dpre[1], dpre[2], dpre[3]);
+      dst[1] = make_float4(dpre[4], dpre[5], dpre[6], dpre[7]);
+      if (t < t1) {  // inside the tile: this token's share of the parameter gradients
+        const int sc = ss[i + K - 1];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float acc = w[K - 1][c] * dpre[c];
+        for (int j = 0; j < K; ++j) {
+          if (j == K - 1 || ss[i + j] == sc) {
+            const float4* src = reinterpret_cast<const float4*>(xs + (size_t)(i + j) * COLS * 8 + ct * 8);
+            const float4 a = src[0], b4 = src[1];
+            const float v[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-        for (int l = 1; l < KMAX; ++l) {
-          if (l < K && sp[l - 1] == sc) acc += w[K - 1 - l][c] * dp[l - 1][c];
+            for (int c = 0; c < 8; ++c) dwacc[j][c] += dpre[c] * v[c];
+          }
         }
-        dxv[c] = acc;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) dbacc[c] += dpre[c];
       }
-      if (t >= 0) store8<T>(static_cast<T*>(p.dx) + ((long)b * p.T + t) * p.C + col, dxv);
-      else store8<T>(static_cast<T*>(p.dstate) + ((long)b * (K - 1) + (K - 1 + t)) * p.C + col, dxv);
     }
-    if (mine && live) {
+    __syncthreads();
+    // dx_ext[s] = sum_{l < K} w[:, K - 1 - l] dpre[s + l] over the later tokens of the same document (l = 0: the token
+    // itself). Rows s = t0 .. t1 - 1, and for the row's first tile also the K - 1 state rows in front.
+    const int first = (t0 == 0 && p.dstate) ? -(K - 1) : 0;
+    for (int i = first + lr; i < TT; i += ROW_LANES) {
+      const int srow = t0 + i;
+      if (srow >= t1 || !live) continue;
+      const int sc = ss[i + K - 1];  // staged row of token t0 + i is i + K - 1
+      float acc[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        dbacc[c] += dpre[c];
+      for (int c = 0; c < 8; ++c) acc[c] = 0.f;
 #pragma unroll
-        for (int j = 0; j < KMAX; ++j) {
-          if (j < K && (j == K - 1 || sw[j] == sc)) dwacc[j][c] += dpre[c] * win[j][c];
+      for (int l = 0; l < K; ++l) {
+        const int u = i + l;  // dps index of token srow + l
+        if (u < 0 || u >= DROWS) continue;
+        if (l == 0 ? srow >= 0 : ss[u + K - 1] == sc) {
+          const float4* src = reinterpret_cast<const float4*>(dps + (size_t)u * COLS * 8 + ct * 8);
+          const float4 a = src[0], b4 = src[1];
+          const float v[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[c] += w[K - 1 - l][c] * v[c];
         }
       }
+      if (srow >= 0) store8<T>(static_cast<T*>(p.dx) + ((long)b * p.T + srow) * p.C + col, acc);
+      else store8<T>(static_cast<T*>(p.dstate) + ((long)b * (K - 1) + (K - 1 + srow)) * p.C + col, acc);
     }
-    // slide: dpre_t becomes the nearest later token; the input window moves one row down
-#pragma unroll
-    for (int l = KMAX - 1; l > 0; --l) {
-      sp[l] = sp[l - 1];
-#pragma unroll
-      for (int c = 0; c < 8; ++c) dp[l][c] = dp[l - 1][c];
-    }
-    sp[0] = token ? sc : -1;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) dp[0][c] = dpre[c];
-#pragma unroll
-    for (int j = KMAX - 1; j > 0; --j) {
-      if (j < K) {
-        sw[j] = sw[j - 1];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) win[j][c] = win[j - 1][c];
-      }
-    }
-    load_row<T>(p, b, t - 1 - (K - 1), col, live && has_tile && s + 1 < steps, win[0]);
-    sw[0] = seg_at(p, b, t - 1 - (K - 1));
-  }
-  // parameter gradients: fold the block's row lanes, then one atomic per entry and block
-  const int per = 8 * (KMAX + 1);
-  float* mine_f = fold + (size_t)(lr * cols + ct) * per;
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    mine_f[c] = dbacc[c];
-#pragma unroll
-    for (int j = 0; j < KMAX; ++j) mine_f[8 * (j + 1) + c] = dwacc[j][c];
-  }
-  __syncthreads();
-  if (lr == 0 && live) {
+    __syncthreads();  // every warp is done with the staged rows: the fold buffer takes their place
+    // parameter gradients: fold the block's token lanes, then one atomic per entry and block
+    constexpr int PER = 8 * (K + 1);
+    float* mine_f = fold + (size_t)(lr * COLS + ct) * PER;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      float sb = 0.f;
-      for (int l = 0; l < lanes_r; ++l) sb += fold[(size_t)(l * cols + ct) * per + c];
-      if (p.dbias) atomicAdd(p.dbias + col + c, sb);
+      mine_f[c] = dbacc[c];
 #pragma unroll
-      for (int j = 0; j < KMAX; ++j) {
-        if (j >= K) continue;
-        float sw_ = 0.f;
-        for (int l = 0; l < lanes_r; ++l) sw_ += fold[(size_t)(l * cols + ct) * per + 8 * (j + 1) + c];
-        atomicAdd(p.dw + (long)(col + c) * K + j, sw_);
+      for (int j = 0; j < K; ++j) mine_f[8 * (j + 1) + c] = dwacc[j][c];
+    }
+    __syncthreads();
+    if (lr == 0 && live) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float sb = 0.f;
+        for (int l = 0; l < ROW_LANES; ++l) sb += fold[(size_t)(l * COLS + ct) * PER + c];
+        if (p.dbias) atomicAdd(p.dbias + col + c, sb);
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+          float sw_ = 0.f;
+          for (int l = 0; l < ROW_LANES; ++l) sw_ += fold[(size_t)(l * COLS + ct) * PER + 8 * (j + 1) + c];
+          atomicAdd(p.dw + (long)(col + c) * K + j, sw_);
+        }
       }
     }
-  }
   }
 }
 
@@ -325,29 +304,37 @@ int launch(int dtype, ConvParams cp, cudaStream_t s) {
   }
   if (cp.B == 0 || cp.T == 0) return JLA_OK;
   const int cv = cp.C / 8;
-  int cols = cv < 32 ? cv : 32;
-  if (cols % lanes) cols = lanes;  // a head never straddles two blocks' column ranges
-  if (cv % cols) {
-    set_error("short conv: C / 8 = %d must be a multiple of %d", cv, cols);
-    return JLA_ERR_UNSUPPORTED;
-  }
-  const int threads = cols * (THREADS / cols);
-  const int lanes_r = threads / cols;
-  cp.cols = cols;
-  // tokens per thread: long enough to amortise the K - 1 recomputed tokens and 2 (K - 1) extra steps of the backward
-  cp.tile = cp.T >= 1024 ? 64 : (cp.T >= 256 ? 32 : 16);
-  const long tiles = (long)cp.B * ((cp.T + cp.tile - 1) / cp.tile);
-  const long gy = (tiles + lanes_r - 1) / lanes_r;
-  if (gy > 65535) {
-    set_error("short conv: more than %ld token tiles per call", 65535L * lanes_r);
-    return JLA_ERR_UNSUPPORTED;
-  }
-  const dim3 grid(cv / cols, (unsigned)gy);
-  const size_t smem = BWD ? sizeof(float) * threads * 8 * (KMAX + 1) : 0;
+  const dim3 grid((cv + COLS - 1) / COLS, 1, 1);
+  const int K = cp.K;
+  const size_t smem = BWD ? sizeof(float) * COLS * 8 * ((TT + 2 * (K - 1)) + (TT + K - 1)) + sizeof(int) * (TT + 2 * (K - 1))
+                          : sizeof(float) * COLS * 8 * (TT + K - 1) + sizeof(int) * (TT + K - 1);
   auto go = [&](auto kern) -> int {
     if (smem > 48 * 1024) JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, threads, smem, s>>>(cp);
-    JLA_LAUNCH_OK();
+    // the token-tile index lives in gridDim.y (<= 65535): larger problems go in slices of batch rows
+    const int tiles_per_row = (cp.T + TT - 1) / TT;
+    const int rows_per_launch = tiles_per_row > 65535 ? 0 : 65535 / tiles_per_row;
+    if (rows_per_launch == 0) {
+      set_error("short conv: more than %d tokens per batch row", 65535 * TT);
+      return JLA_ERR_UNSUPPORTED;
+    }
+    for (int b0 = 0; b0 < cp.B; b0 += rows_per_launch) {
+      ConvParams q = cp;
+      const int nb = cp.B - b0 < rows_per_launch ? cp.B - b0 : rows_per_launch;
+      const size_t es = dtype == JLA_DTYPE_F32 ? 4 : 2;
+      auto adv = [&](const void* ptr, size_t per_row) {
+        return ptr ? static_cast<const void*>(static_cast<const char*>(ptr) + (size_t)b0 * per_row) : nullptr;
+      };
+      q.B = nb;
+      q.x = adv(cp.x, (size_t)cp.T * cp.C * es);
+      q.y = const_cast<void*>(adv(cp.y, (size_t)cp.T * cp.C * es));
+      q.dy = adv(cp.dy, (size_t)cp.T * cp.C * es);
+      q.dx = const_cast<void*>(adv(cp.dx, (size_t)cp.T * cp.C * es));
+      q.state = adv(cp.state, (size_t)(K - 1) * cp.C * es);
+      q.dstate = const_cast<void*>(adv(cp.dstate, (size_t)(K - 1) * cp.C * es));
+      q.seg = static_cast<const int32_t*>(adv(cp.seg, (size_t)cp.T * sizeof(int32_t)));
+      kern<<<dim3(grid.x, (unsigned)(nb * tiles_per_row)), THREADS, smem, s>>>(q);
+      JLA_LAUNCH_OK();
+    }
     return JLA_OK;
   };
   auto by_k = [&](auto tag) -> int {
