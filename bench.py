@@ -452,7 +452,8 @@ def main() -> None:
                 roof.update(kernel=top, ms_per_launch=per_launch_ms,
                             traffic=None if traffic is None else traffic * units, peak_source=pk["source"],
                             algorithmic_bytes_per_launch=by, algorithmic_flops_per_launch=fl)
-        # whole-step view against both rooflines (SURVEY accounting: 491,520 FLOP and 2,816 B per token and head)
+        # whole-step view against both rooflines (dense 64x64 tiles, no recompute, inverse excluded: 491,520 FLOP and
+        # 2,816 B per token and head for the delta-rule kinds)
         step_flops = 491520.0 * tokens * H if args.workload != "ssd" else 172032.0 * tokens * H
         step_bytes = 2816.0 * tokens * H
         sec = ms_per_step * 1e-3

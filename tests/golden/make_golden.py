@@ -103,7 +103,7 @@ def draw_kda(c: dict, seed: int) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of jla-org/jax-linear-attention")
     ap.add_argument("--out", default=HERE)
     args = ap.parse_args()
     bench_dir = os.path.join(args.reference, "benchmarks")
