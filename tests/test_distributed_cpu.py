@@ -233,3 +233,16 @@ def test_shard_plans():
     assert shard_slices(p, 3, 1, 8, 2) == (slice(0, 1), slice(6, 8), slice(1, 2))
     with pytest.raises(ValueError, match="cannot split"):
         plan_shards(3, 5, 5, 4)
+
+
+def test_piece_table_cuts_documents_and_marks_continuations():
+    from jax_linear_attention_b200.distributed.context_parallel import _piece_table
+
+    ids = torch.tensor([0] * 10 + [1] * 3 + [2] * 9)
+    cu, cont = _piece_table(ids, cont0=True, piece_len=4)
+    assert cu == [0, 4, 8, 10, 13, 17, 21, 22]
+    assert cont == [True, True, True, False, False, True, True]      # piece 0 continues the previous rank's document
+    cu, cont = _piece_table(ids, cont0=False, piece_len=100)          # nothing longer than a piece: one per document
+    assert cu == [0, 10, 13, 22] and cont == [False, False, False]
+    cu, cont = _piece_table(torch.zeros(7, dtype=torch.int64), cont0=True, piece_len=7)
+    assert cu == [0, 7] and cont == [True]
