@@ -27,9 +27,12 @@ int chunked_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t stream)
 
 namespace {
 
-int resolve_path(const jla_problem& p) {
+// The KDA backward is always the token scan (it recomputes what it needs from the inputs, so the chunked KDA forward
+// keeps no residuals).
+int resolve_path(const jla_problem& p, bool bwd = false) {
+  if (bwd && p.kind == JLA_KIND_KDA) return JLA_PATH_RECURRENT;
   if (p.path == JLA_PATH_AUTO) {
-    // f32 tensors run the exact token scan; so does KDA until its chunked kernels exist (chunked_unsupported()).
+    // f32 tensors run the exact token scan; so does whatever the chunked kernels do not cover (chunked_unsupported()).
     if (p.dtype == JLA_DTYPE_F32 || chunked_unsupported(p) != nullptr) {
       return recurrent_unsupported(p) == nullptr || p.dtype == JLA_DTYPE_F32 ? JLA_PATH_RECURRENT : JLA_PATH_CHUNKED;
     }
@@ -112,7 +115,7 @@ const char* jla_last_error(void) { return g_error; }
 const char* jla_unsupported_reason(const jla_problem* p) { return p ? unsupported(*p) : "null problem"; }
 
 size_t jla_residual_bytes(const jla_problem* p) {
-  if (!p || unsupported(*p)) return 0;
+  if (!p || unsupported(*p) || p->kind == JLA_KIND_KDA) return 0;
   return resolve_path(*p) == JLA_PATH_RECURRENT ? 0 : chunked_residual_bytes(*p);
 }
 
@@ -123,7 +126,7 @@ size_t jla_fwd_scratch_bytes(const jla_problem* p) {
 
 size_t jla_bwd_scratch_bytes(const jla_problem* p) {
   if (!p || unsupported(*p)) return 0;
-  return resolve_path(*p) == JLA_PATH_RECURRENT ? recurrent_bwd_scratch_bytes(*p) : chunked_bwd_scratch_bytes(*p);
+  return resolve_path(*p, true) == JLA_PATH_RECURRENT ? recurrent_bwd_scratch_bytes(*p) : chunked_bwd_scratch_bytes(*p);
 }
 
 int jla_linear_attention_fwd(const jla_problem* p, const jla_fwd_io* io, jla_stream_t stream) {
@@ -150,7 +153,7 @@ int jla_linear_attention_bwd(const jla_problem* p, const jla_bwd_io* io, jla_str
     return JLA_ERR_BAD_ARGUMENT;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return resolve_path(*p) == JLA_PATH_RECURRENT ? recurrent_bwd(*p, *io, s) : chunked_bwd(*p, *io, s);
+  return resolve_path(*p, true) == JLA_PATH_RECURRENT ? recurrent_bwd(*p, *io, s) : chunked_bwd(*p, *io, s);
 }
 
 }  // extern "C"

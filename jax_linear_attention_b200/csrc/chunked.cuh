@@ -26,6 +26,7 @@ struct Plan {
   int rows, nc;       // rows; chunk slots (upper bound on the number of chunks)
   bool delta, l2norm, save;
   size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, w, residual_bytes;  // residual buffer
+  size_t kda_q, kda_kr, kda_kw, kda_p, kda_d;  // KDA: gate-folded operands per chunk slot (see chunked_kda_prep.cu)
   size_t fwd_scratch_bytes;                                                 // same layout without h, vn
   size_t dh, dvn, dq_acc, dk_acc, dp, dga, bwd_scratch_bytes;               // backward scratch
 };
@@ -44,7 +45,8 @@ inline Plan make_plan(const jla_problem& p) {
   pl.nc = varlen ? per_row + p.num_seqs : p.B * per_row;
   pl.delta = p.kind != JLA_KIND_SIMPLE_GLA;
   pl.l2norm = (p.flags & JLA_FLAG_QK_L2NORM) != 0;
-  pl.save = (p.flags & JLA_FLAG_SAVE_RESIDUALS) != 0;
+  const bool kda = p.kind == JLA_KIND_KDA;  // forward only: its backward is the token scan, which keeps no residuals
+  pl.save = (p.flags & JLA_FLAG_SAVE_RESIDUALS) != 0 && !kda;
   const size_t es = elem_size(p.dtype);
   const size_t tokens = (size_t)p.B * p.T;
   Carver c(nullptr);
@@ -58,15 +60,21 @@ inline Plan make_plan(const jla_problem& p) {
   pl.row_chunks = off((size_t)(pl.rows + 1) * 2 * sizeof(int));
   pl.gates = off((size_t)pl.nc * p.H * 128 * sizeof(float));  // per (chunk, head): G[64] then beta[64]
   pl.runs = off((size_t)pl.nc * 64);
-  pl.t0 = off(pl.delta ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
+  pl.t0 = off(pl.delta && !kda ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
   pl.ag = off(pl.delta ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);  // Ag = T0 * D * beta_j (gated), for the forward
   pl.qn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
   pl.kn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
+  const size_t slot_tile = kda ? (size_t)pl.nc * p.H * 64 * p.K * es : 0;
+  pl.kda_q = off(slot_tile);
+  pl.kda_kr = off(slot_tile);
+  pl.kda_kw = off(slot_tile);
+  pl.kda_p = off(kda ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
+  pl.kda_d = off(kda ? (size_t)pl.nc * p.H * p.K * sizeof(float) : 0);
   pl.fwd_scratch_bytes = align_up(c.off);
-  pl.h = off((size_t)pl.nc * p.H * p.K * p.V * es);
-  pl.vn = off(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
+  pl.h = off(kda ? 0 : (size_t)pl.nc * p.H * p.K * p.V * es);
+  pl.vn = off(pl.delta && !kda ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
   const bool tc = use_tc_kernels(p);
-  pl.w = off(pl.delta && tc ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);  // W^T, for the key-side gradient kernel
+  pl.w = off(pl.delta && tc && !kda ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);  // W^T, for the key-side gradient kernel
   pl.residual_bytes = align_up(c.off);
   Carver b(nullptr);
   auto boff = [&](size_t bytes) {
@@ -122,6 +130,7 @@ struct ChunkedCtx {
 };
 
 int launch_prep(const ChunkedCtx& c, cudaStream_t s);                           // tables, G/beta/runs, T0, l2norm
+int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s);                       // KDA: gate-folded operands, P, Ag
 int launch_sg_fwd(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s);
 int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s);
 int l2norm_fwd(const void* x, void* y, int dtype, long rows, int K, cudaStream_t stream);

@@ -26,16 +26,19 @@ namespace {
 using umma::swz_tile;
 
 constexpr int K = 128, V = 128;
-constexpr int NS = 3;  // stages of the input ring
+constexpr int kBarBase = 6;  // full / empty barriers of the ring (at most 3 stages) come first
 
+// VG (per-channel gates, KDA): the tiles come gate-folded from kda_prep_kernel, one set per chunk slot:
+// q -> cin q exp(G), k -> cin k exp(G) (recall), k2 -> tail k exp(G_63 - G) (write), p -> the masked score tile,
+// ag -> T beta_j, and the G/beta vector of the stage carries the decay exp(G_63) of the K state columns instead.
 struct FwdTcMaps {
-  CUtensorMap q, k, v, ag;
+  CUtensorMap q, k, v, ag, k2, p;
 };
 
 struct FwdTcParams {
   const ChunkMeta* meta;
   const int2* row_chunks;
-  const float* gates;
+  const float* gates;  // VG: the per-slot decay vectors [K]
   const unsigned char* runs;
   const float* h0;
   void* o;
@@ -47,21 +50,24 @@ struct FwdTcParams {
   int state_only;  // final state (and residuals) only: no scores, no outputs
 };
 
-struct Smem {
-  static constexpr int kStage = 64 * K * 2 * 2 + 64 * V * 2 + 8192;  // q, k, v, T0
+template <bool VG>
+struct SmemT {
+  static constexpr int NS = VG ? 2 : 3;  // stages of the input ring
+  // q, k, v, T0 (Ag); VG adds the write-side keys and the score tile
+  static constexpr int kStage = 64 * K * 2 * 2 + 64 * V * 2 + 8192 + (VG ? 64 * K * 2 + 8192 : 0);
   static constexpr int kTiles = NS * kStage;
   static constexpr int kPb = kTiles;            // P tiles [2][64x64]
-  static constexpr int kAgb = kPb + 2 * 8192;   // Ag tiles [2][64x64]
-  static constexpr int kGates = kAgb + 2 * 8192;         // per stage: G[64], beta[64] f32 (512 B) + runs (64 B) + meta (16 B)
+  static constexpr int kAgb = kPb + (VG ? 0 : 2 * 8192);   // Ag tiles [2][64x64]
+  static constexpr int kGates = kAgb + (VG ? 0 : 2 * 8192);  // per stage: G[64], beta[64] f32 (512 B) + runs (64 B) + meta (16 B)
   static constexpr int kGateStride = 640;
   static constexpr int kScal = kGates + NS * kGateStride;  // per stage and warp: gam[64], gamr[64] (state group); gam[64] (score group)
   static constexpr int kBars = kScal + NS * 4096;
-  static constexpr int kNumBars = 2 * NS + 16;
+  static constexpr int kNumBars = kBarBase + 16;
   static constexpr int kBytes = kBars + kNumBars * 8 + 64 + 1024;
 };
 
-enum {  // mbarrier indices after the 2 * NS full / empty barriers
-  B_PDONE = 2 * NS, B_PFREE, B_PA0, B_PA1, B_ST, B_M1, B_W, B_M2, B_VN, B_M3, B_ODONE, B_OFREE0, B_OFREE1
+enum {  // mbarrier indices after the full / empty barriers
+  B_PDONE = kBarBase, B_PFREE, B_PA0, B_PA1, B_ST, B_M1, B_W, B_M2, B_VN, B_M3, B_ODONE, B_OFREE0, B_OFREE1
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -100,8 +106,11 @@ __device__ __forceinline__ void ld_row32(float (&v)[32], uint32_t taddr) {
   umma::wait_ld();
 }
 
-template <typename T, bool DELTA>
+template <typename T, bool DELTA, bool VG>
 __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant__ FwdTcMaps maps, FwdTcParams p) {
+  static_assert(DELTA || !VG, "per-channel gates come with the delta rule");
+  using Smem = SmemT<VG>;
+  constexpr int NS = Smem::NS;
   constexpr int FMT = umma::Fmt<T>::value;
   const int row = blockIdx.x / p.H, h = blockIdx.x - row * p.H;
   const int hk = h / (p.H / p.Hk);
@@ -115,6 +124,8 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
   auto st_k = [&](int s) { return st_q(s) + 64 * K * 2; };
   auto st_v = [&](int s) { return st_k(s) + 64 * K * 2; };
   auto st_t0 = [&](int s) { return st_v(s) + 64 * V * 2; };
+  auto st_k2 = [&](int s) { return st_t0(s) + 8192; };      // VG only
+  auto st_p = [&](int s) { return st_k2(s) + 64 * K * 2; };  // VG only
   auto st_G = [&](int s) { return reinterpret_cast<float*>(base + Smem::kGates + s * Smem::kGateStride); };
   auto st_runs = [&](int s) { return reinterpret_cast<unsigned char*>(st_G(s) + 128); };
   auto st_meta = [&](int s) { return reinterpret_cast<volatile int*>(st_runs(s) + 64); };
@@ -164,12 +175,20 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         ms[0] = m.tok0;
         ms[1] = m.len;
         ms[2] = m.flags;
-        const uint32_t bytes = 64 * K * 2 * 2 + 64 * V * 2 + (DELTA ? 8192 : 0) + 512 + 64;
+        const uint32_t bytes = 64 * K * 2 * 2 + 64 * V * 2 + (DELTA ? 8192 : 0) + (VG ? 64 * K * 2 + 8192 : 0) + 512 + 64;
         tma::expect_tx(bars + s, bytes);
-        tma::load_tile<64, K>(st_k(s), &maps.k, 0, hk, m.tok0, bars + s);
-        tma::load_tile<64, K>(st_q(s), &maps.q, 0, hk, m.tok0, bars + s);
+        const int slot_row = (c * p.H + h) * 64;
+        if (VG) {
+          tma::load_tile<64, K>(st_k(s), &maps.k, 0, 0, slot_row, bars + s);
+          tma::load_tile<64, K>(st_q(s), &maps.q, 0, 0, slot_row, bars + s);
+          tma::load_tile<64, K>(st_k2(s), &maps.k2, 0, 0, slot_row, bars + s);
+          tma::load_tile<64, 64>(st_p(s), &maps.p, 0, 0, slot_row, bars + s);
+        } else {
+          tma::load_tile<64, K>(st_k(s), &maps.k, 0, hk, m.tok0, bars + s);
+          tma::load_tile<64, K>(st_q(s), &maps.q, 0, hk, m.tok0, bars + s);
+        }
         tma::load_tile<64, V>(st_v(s), &maps.v, 0, h, m.tok0, bars + s);
-        if (DELTA) tma::load_tile<64, 64>(st_t0(s), &maps.ag, 0, 0, (c * p.H + h) * 64, bars + s);
+        if (DELTA) tma::load_tile<64, 64>(st_t0(s), &maps.ag, 0, 0, slot_row, bars + s);
         bulk_copy(st_G(s), p.gates + ((long)c * p.H + h) * 128, 512, bars + s);
         bulk_copy(st_runs(s), p.runs + (long)c * 64, 64, bars + s);
       }
@@ -187,7 +206,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         umma::commit(bars + B_PDONE);
         return true;
       };
-      bool okm = n > 0 && !p.state_only ? issue_p(0) : true;
+      bool okm = n > 0 && !p.state_only && !VG ? issue_p(0) : true;
       for (int it = 0; it < n && okm; ++it) {
         const int s = it % NS;
         const uint32_t ph = it & 1;
@@ -200,9 +219,11 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         }
         const uint32_t co = cO + (it & 1) * 64;
         if (!p.state_only) {
-          if (it + 1 < n && !issue_p(it + 1)) break;
-          // q has been scaled by (cin Gamma)_i in place by the score group (part of "PA ready")
-          if (!wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
+          if (!VG) {
+            if (it + 1 < n && !issue_p(it + 1)) break;
+            // q has been scaled by (cin Gamma)_i in place by the score group (part of "PA ready")
+            if (!wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
+          }
           if (!wait(bars + B_OFREE0 + (it & 1), ((it >> 1) & 1) ^ 1, abort_flag)) break;
           umma::fence_after_sync();
           umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + co, tmem + cSb, aq, 64, false);  // S^T ((cin Gamma) Q)^T
@@ -215,11 +236,12 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         }
         if (!wait(bars + B_VN, ph, abort_flag)) break;
         umma::fence_after_sync();
-        umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cVg, ak, 64, true);  // S^T += (Gamma_r Vn)^T K
+        umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cVg, VG ? umma::smem_addr(st_k2(s)) : ak, 64,
+                                              true);  // S^T += (Gamma_r Vn)^T K
         umma::commit(bars + B_M3);
         if (!p.state_only) {
-          umma::gemm_ts<128, 64, 4, false, FMT>(tmem + co, tmem + cWb, umma::smem_addr(Pb + (it & 1) * 8192), 64,
-                                                true);  // += Vn^T P^T
+          const uint32_t ap = VG ? umma::smem_addr(st_p(s)) : umma::smem_addr(Pb + (it & 1) * 8192);
+          umma::gemm_ts<128, 64, 4, false, FMT>(tmem + co, tmem + cWb, ap, 64, true);  // += Vn^T P^T
         }
         umma::commit(bars + B_ODONE);
         umma::commit(bars + NS + s);
@@ -243,12 +265,17 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) {
         const int j = lane + 32 * jj;
-        const RowScalars rs = row_scalars(Gs, runs, flags, j);
-        gam[j] = rs.gam;
-        gamr[j] = (j < len) ? rs.gamr : 0.f;  // tokens past a partial chunk must not write the state
+        if (VG) {  // the masks and decays are folded into the operands
+          gam[j] = 1.f;
+          gamr[j] = 1.f;
+        } else {
+          const RowScalars rs = row_scalars(Gs, runs, flags, j);
+          gam[j] = rs.gam;
+          gamr[j] = (j < len) ? rs.gamr : 0.f;  // tokens past a partial chunk must not write the state
+        }
       }
       __syncwarp();
-      const float kg = keep_gamma(Gs, runs, flags);
+      const float kg = VG ? 0.f : keep_gamma(Gs, runs, flags);
       // ---- the state entering this chunk: 16-bit copy for the products, decayed fp32 copy for the update
       if (it > 0) {
         ok = wait(bars + B_M3, ph ^ 1, abort_flag);
@@ -275,7 +302,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         }
         umma::st_32x32b_x16(tl + cSb + blk * 16, pk);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] *= kg;
+        for (int i = 0; i < 32; ++i) x[i] *= VG ? Gs[blk * 32 + i] : kg;  // VG: exp(G_63) of key channel blk * 32 + i
         umma::st_32x32b_x32(tl + cS + blk * 32, x);
       }
       umma::wait_st();
@@ -462,10 +489,10 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
       }
     }
     const int n_out = p.state_only ? 0 : n;
-    if (n_out > 0) ok = build(0);
+    if (n_out > 0 && !VG) ok = build(0);
     for (int it = 0; it < n_out && ok; ++it) {
       const int s = it % NS;
-      if (it + 1 < n_out) {
+      if (it + 1 < n_out && !VG) {
         ok = build(it + 1);
         if (!ok) break;
       }
@@ -506,13 +533,13 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
   if (tid == 0 && *abort_flag) atomicExch(p.status, 2);
 }
 
-template <typename T, bool DELTA>
+template <typename T, bool DELTA, bool VG = false>
 int launch_one(const FwdTcMaps& maps, const FwdTcParams& fp, int blocks, cudaStream_t s) {
-  auto* kern = sg_fwd_tc_kernel<T, DELTA>;
-  JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+  auto* kern = sg_fwd_tc_kernel<T, DELTA, VG>;
+  JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemT<VG>::kBytes));
   {
     ProfScope ps(kProfSgFwd, s);
-    kern<<<blocks, 640, Smem::kBytes, s>>>(maps, fp);
+    kern<<<blocks, 640, SmemT<VG>::kBytes, s>>>(maps, fp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
@@ -528,16 +555,25 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
   const Plan& pl = c.plan;
   if (pl.rows == 0) return JLA_OK;
   const uint64_t tokens = (uint64_t)p.B * p.T, slots = (uint64_t)pl.nc * p.H;
+  const bool vg = p.kind == JLA_KIND_KDA;
   FwdTcMaps maps;
-  bool ok = tma::encode_3d(&maps.q, c.q_eff, p.K, p.Hk, tokens, 64) && tma::encode_3d(&maps.k, c.k_eff, p.K, p.Hk, tokens, 64) &&
-            tma::encode_3d(&maps.v, p.v, p.V, p.H, tokens, 64);
+  bool ok = tma::encode_3d(&maps.v, p.v, p.V, p.H, tokens, 64);
+  if (vg) {  // gate-folded operands, one [64 x K] tile per chunk slot
+    ok = ok && tma::encode_3d(&maps.q, c.res + pl.kda_q, p.K, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.k, c.res + pl.kda_kr, p.K, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.k2, c.res + pl.kda_kw, p.K, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.p, c.res + pl.kda_p, 64, 1, slots * 64, 64);
+  } else {
+    ok = ok && tma::encode_3d(&maps.q, c.q_eff, p.K, p.Hk, tokens, 64) && tma::encode_3d(&maps.k, c.k_eff, p.K, p.Hk, tokens, 64);
+  }
   if (ok && pl.delta) ok = tma::encode_3d(&maps.ag, c.res + pl.ag, 64, 1, slots * 64, 64);
   if (ok && !pl.delta) maps.ag = maps.v;
   if (!ok) return JLA_ERR_CUDA;
+  if (!vg) maps.k2 = maps.p = maps.v;  // unused
   FwdTcParams fp{};
   fp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
   fp.row_chunks = reinterpret_cast<const int2*>(c.res + pl.row_chunks);
-  fp.gates = reinterpret_cast<const float*>(c.res + pl.gates);
+  fp.gates = reinterpret_cast<const float*>(c.res + (vg ? pl.kda_d : pl.gates));
   fp.runs = reinterpret_cast<const unsigned char*>(c.res + pl.runs);
   fp.h0 = p.h0;
   fp.o = io.o;
@@ -552,6 +588,13 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
   fp.state_only = (p.flags & JLA_FLAG_STATE_ONLY) != 0;
   if (!fp.status) return JLA_ERR_CUDA;
   const int blocks = pl.rows * p.H;
+  if (vg) {
+    if (p.dtype != JLA_DTYPE_BF16) {
+      set_error("chunked KDA: bf16 tensors only");
+      return JLA_ERR_UNSUPPORTED;
+    }
+    return launch_one<__nv_bfloat16, true, true>(maps, fp, blocks, s);
+  }
   if (p.dtype == JLA_DTYPE_BF16) {
     return pl.delta ? launch_one<__nv_bfloat16, true>(maps, fp, blocks, s) : launch_one<__nv_bfloat16, false>(maps, fp, blocks, s);
   }

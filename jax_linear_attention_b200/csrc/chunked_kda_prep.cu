@@ -1,0 +1,260 @@
+// Prologue of the chunked KDA forward (per-channel gates, reference: src/jla/ops/mosaic_gpu/vector_gate.py:226-303
+// cumsum, :559-769 intra-chunk scores, :849-870 solve, :873-949 gate-folded operands). One CTA per (chunk, head).
+//
+// With G_i[c] the chunk-local cumulative log decay of channel c (token i sees exp(G_i) of the entering state), the
+// chunk step of the delta rule is
+//   Aqk_ij = sum_c q_ic k_jc exp(G_ic - G_jc)  (j <= i)        Akk_ij = beta_i sum_c k_ic k_jc exp(G_ic - G_jc)  (j < i)
+//   T = (I + Akk)^-1,  Ag = T beta_j,  W = V - (k exp(G)) S,  Vn = Ag W,
+//   O = scale [(q exp(G)) S + Aqk Vn],  S+ = diag(exp(G_63)) S + (k exp(G_63 - G))^T Vn.
+// Everything that touches a gate is done here, in parallel over the chunks, so that the serial state pass
+// (sg_fwd_tc_kernel, VG variant) is a gate-free delta rule on folded operands:
+//   qs = cin   * q exp(G)          [64 x K]  reads the entering state        (cin: token still sees it)
+//   kr = cin   * k exp(G)          [64 x K]  recalls from the entering state
+//   kw = tail  * k exp(G_63 - G)   [64 x K]  writes into the leaving state   (tail: token reaches it)
+//   d  = keep  * exp(G_63)         [K]       decay of the entering state
+//   P  = Aqk, Ag                   [64 x 64] with the document mask applied
+// All exponents above are <= 0, so these never overflow. The two score matrices need exp(G_i - G_j) per channel
+// inside a contraction; they are factored through the per-channel mid point R = G_63 / 2,
+//   (q exp(G - R)) (k exp(R - G))^T,   |G - R| <= |G_63| / 2,
+// and run on the tensor cores when no channel decays by more than exp(-kBoundedLog) over the chunk. Chunks with a
+// stronger decay take the exact fp32 loop over (i, j, c) instead, so the result never depends on the bound.
+#include "chunked.cuh"
+#include "profile.cuh"
+#include "mma.cuh"
+#include "tri_inverse.cuh"
+
+namespace jla {
+namespace {
+
+constexpr int KD = 128;
+constexpr float kBoundedLog = 60.f;  // exp(+-30) factors: far inside the bf16 / fp32 exponent range
+
+struct KdaPrepParams {
+  const ChunkMeta* meta;
+  const void *q, *k;   // [tokens, Hk, K] (after the optional L2 norm)
+  const float* g;      // [tokens, H, K]
+  const float* gates;  // per (chunk, head): G[64] (zero here), beta[64]
+  const unsigned char* runs;
+  void *qs, *kr, *kw;  // [slot][64][K]
+  void *ptile, *ag;    // [slot][64][64]
+  float* dvec;         // [slot][K]
+  int H, Hk;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
+  constexpr int LDK = KD + 8, LDA = kTriLda, LDM = kTriLdm, LDP = 72;
+  const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
+  const ChunkMeta m = p.meta[c];
+  if (m.len == 0) return;
+  const int hk = h / (p.H / p.Hk);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long slot = (long)c * p.H + h;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* tq = reinterpret_cast<T*>(smem_raw);        // q, then q exp(G - R); the inverse X takes its place afterwards
+  T* tk = tq + 64 * LDK;                         // k, then k exp(G - R)
+  T* tb = tk + 64 * LDK;                         // k exp(R - G); later the staged P tile [64][LDP]
+  float* Gm = reinterpret_cast<float*>(tb + 64 * LDK);  // [64][KD]
+  float* A = Gm + 64 * KD;                       // [64][LDA]
+  float* M = A + 64 * LDA;                       // [32][LDM]
+  float* betas = M + 32 * LDM;                   // [64]
+  float* Glast = betas + 64;                     // [KD]
+  int* run = reinterpret_cast<int*>(Glast + KD); // [64]
+  float* X = reinterpret_cast<float*>(smem_raw);
+  static_assert(64 * LDK * sizeof(T) >= 64 * LDA * sizeof(float), "X overlays the q tile");
+  T* pst = tb;
+
+  const long kstride = (long)p.Hk * KD;
+  load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
+  load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
+  cp_async_commit();
+  if (tid < 64) {
+    betas[tid] = p.gates[slot * 128 + 64 + tid];
+    run[tid] = p.runs[(long)c * 64 + tid];
+  }
+  // ---- cumulative log decay per channel (thread = channel); padding tokens add nothing
+  int unbounded;
+  {
+    const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + tid;
+    const long gstride = (long)p.H * KD;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < 64; ++i) {
+      if (i < m.len) acc += gp[i * gstride];
+      Gm[i * KD + tid] = acc;
+    }
+    Glast[tid] = acc;
+    cp_async_wait<0>();
+    unbounded = __syncthreads_or(!(fabsf(acc) <= kBoundedLog));
+  }
+  const bool entering = !(m.flags & 1);
+  const int run_last = run[63];
+
+  // ---- the state-side operands and the decay vector
+  {
+    T* qs = static_cast<T*>(p.qs) + slot * 64 * KD;
+    T* kr = static_cast<T*>(p.kr) + slot * 64 * KD;
+    T* kw = static_cast<T*>(p.kw) + slot * 64 * KD;
+    for (int idx = tid; idx < 64 * (KD / 8); idx += 128) {
+      const int i = idx >> 4, c8 = (idx & 15) * 8;
+      const bool cin = entering && run[i] == 0;
+      const bool tail = i < m.len && run[i] == run_last;
+      const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
+      const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
+      const uint32_t* kwd = reinterpret_cast<const uint32_t*>(&kv);
+      uint4 oq, or_, ow;
+      uint32_t* oqw = reinterpret_cast<uint32_t*>(&oq);
+      uint32_t* orw = reinterpret_cast<uint32_t*>(&or_);
+      uint32_t* oww = reinterpret_cast<uint32_t*>(&ow);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]);
+        const float g0 = Gm[i * KD + c8 + 2 * e], g1 = Gm[i * KD + c8 + 2 * e + 1];
+        const float e0 = cin ? __expf(g0) : 0.f, e1 = cin ? __expf(g1) : 0.f;
+        const float w0 = tail ? __expf(Glast[c8 + 2 * e] - g0) : 0.f, w1 = tail ? __expf(Glast[c8 + 2 * e + 1] - g1) : 0.f;
+        oqw[e] = pack2<T>(qf.x * e0, qf.y * e1);
+        orw[e] = pack2<T>(kf.x * e0, kf.y * e1);
+        oww[e] = pack2<T>(kf.x * w0, kf.y * w1);
+      }
+      *reinterpret_cast<uint4*>(qs + i * KD + c8) = oq;
+      *reinterpret_cast<uint4*>(kr + i * KD + c8) = or_;
+      *reinterpret_cast<uint4*>(kw + i * KD + c8) = ow;
+    }
+    p.dvec[slot * KD + tid] = (entering && run_last == 0) ? __expf(Glast[tid]) : 0.f;
+  }
+
+  if (!unbounded) {
+    // ---- factored operands in place, then both score matrices on the tensor cores
+    __syncthreads();  // the raw tiles have been read
+    for (int idx = tid; idx < 64 * (KD / 8); idx += 128) {
+      const int i = idx >> 4, c8 = (idx & 15) * 8;
+      uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
+      uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      uint4 bv;
+      uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
+      uint32_t* kwd = reinterpret_cast<uint32_t*>(&kv);
+      uint32_t* bw = reinterpret_cast<uint32_t*>(&bv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]);
+        const float d0 = Gm[i * KD + c8 + 2 * e] - 0.5f * Glast[c8 + 2 * e];
+        const float d1 = Gm[i * KD + c8 + 2 * e + 1] - 0.5f * Glast[c8 + 2 * e + 1];
+        const float u0 = __expf(d0), u1 = __expf(d1), n0 = __expf(-d0), n1 = __expf(-d1);
+        qw[e] = pack2<T>(qf.x * u0, qf.y * u1);
+        kwd[e] = pack2<T>(kf.x * u0, kf.y * u1);
+        bw[e] = pack2<T>(kf.x * n0, kf.y * n1);
+      }
+      *reinterpret_cast<uint4*>(tq + i * LDK + c8) = qv;
+      *reinterpret_cast<uint4*>(tk + i * LDK + c8) = kv;
+      *reinterpret_cast<uint4*>(tb + i * LDK + c8) = bv;
+    }
+    __syncthreads();
+    float accP[8][4], accA[8][4];
+    zero_acc(accP);
+    zero_acc(accA);
+    warp_gemm<T, 8, KD / 16, A_ROW, B_NK>(accP, tq + warp * 16 * LDK, LDK, tb, LDK, lane);
+    warp_gemm<T, 8, KD / 16, A_ROW, B_NK>(accA, tk + warp * 16 * LDK, LDK, tb, LDK, lane);
+    __syncthreads();  // every warp has read the tiles: X and the staged P may take their place
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int i = warp * 16 + g + 8 * hh, j = nt * 8 + 2 * t;
+        const float bi = betas[i];
+        const int ri = run[i];
+        const bool s0 = ri == run[j], s1 = ri == run[j + 1];
+        float2 v;
+        v.x = (j < i && s0) ? bi * accA[nt][2 * hh] : 0.f;
+        v.y = (j + 1 < i && s1) ? bi * accA[nt][2 * hh + 1] : 0.f;
+        *reinterpret_cast<float2*>(A + i * LDA + j) = v;
+        const float p0 = (j <= i && s0) ? accP[nt][2 * hh] : 0.f;
+        const float p1 = (j + 1 <= i && s1) ? accP[nt][2 * hh + 1] : 0.f;
+        *reinterpret_cast<uint32_t*>(pst + i * LDP + j) = pack2<T>(p0, p1);
+      }
+    }
+  } else {
+    // ---- exact path: every pair (i, j <= i) of one document, fp32 with the true exponent per channel
+    __syncthreads();
+    for (int idx = tid; idx < 64 * 64; idx += 128) {
+      const int i = idx >> 6, j = idx & 63;
+      float sq = 0.f, sk = 0.f;
+      if (j <= i && run[i] == run[j]) {
+        for (int cc = 0; cc < KD; ++cc) {
+          const int ch = (cc + lane) & (KD - 1);  // lanes of a warp share i: spread the channels over the banks
+          const float e = __expf(Gm[i * KD + ch] - Gm[j * KD + ch]);
+          const float kj = to_f32(tk[j * LDK + ch]) * e;
+          sq += to_f32(tq[i * LDK + ch]) * kj;
+          sk += to_f32(tk[i * LDK + ch]) * kj;
+        }
+      }
+      A[i * LDA + j] = j < i ? betas[i] * sk : 0.f;
+      pst[i * LDP + j] = from_f32<T>(sq);
+    }
+    __syncthreads();  // the raw tiles have been read: X may take their place
+  }
+  for (int idx = tid; idx < 64 * LDA / 4; idx += 128) reinterpret_cast<float4*>(X)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncthreads();
+
+  invert_unit_lower_64(A, X, M, tid);
+
+  T* outp = static_cast<T*>(p.ptile) + slot * 64 * 64;
+  T* outg = static_cast<T*>(p.ag) + slot * 64 * 64;
+  for (int idx = tid; idx < 64 * 8; idx += 128) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    *reinterpret_cast<uint4*>(outp + r * 64 + c8) = *reinterpret_cast<const uint4*>(pst + r * LDP + c8);
+    float a[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int j = c8 + e;
+      a[e] = (j <= r && run[j] == run[r]) ? X[r * LDA + j] * betas[j] : 0.f;
+    }
+    uint4 v;
+    v.x = pack2<T>(a[0], a[1]);
+    v.y = pack2<T>(a[2], a[3]);
+    v.z = pack2<T>(a[4], a[5]);
+    v.w = pack2<T>(a[6], a[7]);
+    *reinterpret_cast<uint4*>(outg + r * 64 + c8) = v;
+  }
+}
+
+}  // namespace
+
+int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
+  const jla_problem& p = c.p;
+  const Plan& pl = c.plan;
+  KdaPrepParams kp{};
+  kp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
+  kp.q = c.q_eff;
+  kp.k = c.k_eff;
+  kp.g = p.g;
+  kp.gates = reinterpret_cast<const float*>(c.res + pl.gates);
+  kp.runs = reinterpret_cast<const unsigned char*>(c.res + pl.runs);
+  kp.qs = c.res + pl.kda_q;
+  kp.kr = c.res + pl.kda_kr;
+  kp.kw = c.res + pl.kda_kw;
+  kp.ptile = c.res + pl.kda_p;
+  kp.ag = c.res + pl.ag;
+  kp.dvec = reinterpret_cast<float*>(c.res + pl.kda_d);
+  kp.H = p.H;
+  kp.Hk = p.Hk;
+  if (p.dtype != JLA_DTYPE_BF16 || p.K != KD) {
+    set_error("chunked KDA: bf16 tensors with K = 128 only");
+    return JLA_ERR_UNSUPPORTED;
+  }
+  using T = __nv_bfloat16;
+  const size_t smem = 3 * 64 * (KD + 8) * sizeof(T) + (64 * KD + 64 * kTriLda + 32 * kTriLdm + 64 + KD) * sizeof(float) +
+                      64 * sizeof(int);
+  auto* kern = kda_prep_kernel<T>;
+  JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  {
+    ProfScope ps(kProfKktInv, s);
+    kern<<<pl.nc * p.H, 128, smem, s>>>(kp);
+  }
+  JLA_LAUNCH_OK();
+  return JLA_OK;
+}
+
+}  // namespace jla

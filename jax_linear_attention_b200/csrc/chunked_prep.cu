@@ -4,6 +4,7 @@
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
+#include "tri_inverse.cuh"
 
 namespace jla {
 namespace {
@@ -100,7 +101,7 @@ struct KktParams {
 // and, at block size 32, of two rows. The fp32 inverse X takes over the key tile once K K^T is in registers.
 template <typename T, int K>
 __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
-  constexpr int LDK = K + 8, LDA = 68, LDM = 36;
+  constexpr int LDK = K + 8, LDA = kTriLda, LDM = kTriLdm;
   constexpr int kFirst = 64 * LDK * (int)sizeof(T) > 64 * LDA * 4 ? 64 * LDK * (int)sizeof(T) : 64 * LDA * 4;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
@@ -150,87 +151,7 @@ __global__ void __launch_bounds__(128) kkt_inv_kernel(KktParams p) {
   }
   __syncthreads();
 
-  if (tid < 64) {  // diagonal 16 x 16 blocks: column `col` of the inverse of block `b`
-    const int b = tid >> 4, col = tid & 15;
-    float x[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float s = (i == col) ? 1.f : 0.f;
-#pragma unroll
-      for (int mm = 0; mm < i; ++mm) s -= A[(16 * b + i) * LDA + 16 * b + mm] * x[mm];
-      x[i] = s;
-      X[(16 * b + i) * LDA + 16 * b + col] = s;
-    }
-  }
-  __syncthreads();
-
-  {  // level 1: two problems (blocks 0-1 and 2-3), 16 x 16 each; thread = one row, four columns
-    const int pr = tid >> 6, i = (tid >> 2) & 15, j4 = (tid & 3) * 4;
-    const int r0 = 32 * pr + 16, c0 = 32 * pr;
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int mm = 0; mm < 16; ++mm) {
-      const float a = A[(r0 + i) * LDA + c0 + mm];
-      const float4 x = *reinterpret_cast<const float4*>(X + (c0 + mm) * LDA + c0 + j4);
-      s[0] += a * x.x;
-      s[1] += a * x.y;
-      s[2] += a * x.z;
-      s[3] += a * x.w;
-    }
-    *reinterpret_cast<float4*>(M + (pr * 16 + i) * LDM + j4) = make_float4(s[0], s[1], s[2], s[3]);
-    __syncthreads();
-    s[0] = s[1] = s[2] = s[3] = 0.f;
-#pragma unroll
-    for (int mm = 0; mm < 16; ++mm) {
-      const float a = X[(r0 + i) * LDA + r0 + mm];
-      const float4 x = *reinterpret_cast<const float4*>(M + (pr * 16 + mm) * LDM + j4);
-      s[0] += a * x.x;
-      s[1] += a * x.y;
-      s[2] += a * x.z;
-      s[3] += a * x.w;
-    }
-    *reinterpret_cast<float4*>(X + (r0 + i) * LDA + c0 + j4) = make_float4(-s[0], -s[1], -s[2], -s[3]);
-  }
-  __syncthreads();
-  {  // level 2: rows 32-63, columns 0-31; thread = rows i and i + 16, four columns
-    const int i = tid >> 3, j4 = (tid & 7) * 4;
-    float s[2][4] = {};
-#pragma unroll 8
-    for (int mm = 0; mm < 32; ++mm) {
-      const float a0 = A[(32 + i) * LDA + mm], a1 = A[(48 + i) * LDA + mm];
-      const float4 x = *reinterpret_cast<const float4*>(X + mm * LDA + j4);
-      s[0][0] += a0 * x.x;
-      s[0][1] += a0 * x.y;
-      s[0][2] += a0 * x.z;
-      s[0][3] += a0 * x.w;
-      s[1][0] += a1 * x.x;
-      s[1][1] += a1 * x.y;
-      s[1][2] += a1 * x.z;
-      s[1][3] += a1 * x.w;
-    }
-    // (the level-1 contents of M were consumed before the barrier above)
-    *reinterpret_cast<float4*>(M + i * LDM + j4) = make_float4(s[0][0], s[0][1], s[0][2], s[0][3]);
-    *reinterpret_cast<float4*>(M + (16 + i) * LDM + j4) = make_float4(s[1][0], s[1][1], s[1][2], s[1][3]);
-    __syncthreads();
-#pragma unroll
-    for (int e = 0; e < 4; ++e) s[0][e] = s[1][e] = 0.f;
-#pragma unroll 8
-    for (int mm = 0; mm < 32; ++mm) {
-      const float a0 = X[(32 + i) * LDA + 32 + mm], a1 = X[(48 + i) * LDA + 32 + mm];
-      const float4 x = *reinterpret_cast<const float4*>(M + mm * LDM + j4);
-      s[0][0] += a0 * x.x;
-      s[0][1] += a0 * x.y;
-      s[0][2] += a0 * x.z;
-      s[0][3] += a0 * x.w;
-      s[1][0] += a1 * x.x;
-      s[1][1] += a1 * x.y;
-      s[1][2] += a1 * x.z;
-      s[1][3] += a1 * x.w;
-    }
-    *reinterpret_cast<float4*>(X + (32 + i) * LDA + j4) = make_float4(-s[0][0], -s[0][1], -s[0][2], -s[0][3]);
-    *reinterpret_cast<float4*>(X + (48 + i) * LDA + j4) = make_float4(-s[1][0], -s[1][1], -s[1][2], -s[1][3]);
-  }
-  __syncthreads();
+  invert_unit_lower_64(A, X, M, tid);
 
   T* out = static_cast<T*>(p.t0) + ((long)c * p.H + h) * 64 * 64;
   for (int idx = tid; idx < 64 * 8; idx += 128) {
@@ -293,7 +214,8 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
   JLA_LAUNCH_OK();
   {
     ProfScope ps(kProfGates, s);
-    prep_gates_kernel<<<pl.nc, 64, 0, s>>>(rows, p.H, p.g, p.beta, meta, gates, runs);
+    // KDA gates are per channel: its own prologue folds them into the operands; here G stays zero
+    prep_gates_kernel<<<pl.nc, 64, 0, s>>>(rows, p.H, p.kind == JLA_KIND_KDA ? nullptr : p.g, p.beta, meta, gates, runs);
   }
   JLA_LAUNCH_OK();
   if (pl.l2norm) {
@@ -304,6 +226,7 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
     if (rc != JLA_OK) return rc;
   }
   if (!pl.delta) return JLA_OK;
+  if (p.kind == JLA_KIND_KDA) return launch_kda_prep(c, s);
   KktParams kp{meta, c.k_eff, gates, runs, c.res + pl.t0, c.res + pl.ag, p.H, p.Hk};
   const int blocks = pl.nc * p.H;
   if (p.dtype == JLA_DTYPE_BF16) {

@@ -187,15 +187,18 @@ class _LinearAttention(torch.autograd.Function):
                    tuple(q.shape), tuple(v.shape[2:3]), q.dtype, cfg["kind"], cfg["l2norm"], cfg["precision"])
             p.flags = flags | _lib.FLAG_SAVE_RESIDUALS
             full = lib.jla_residual_bytes(C.byref(p))
+            as_residuals = needs_grad and full > 0
+            if full == 0:  # a forward that keeps no residuals (KDA): the buffer is its scratch
+                full = lib.jla_fwd_scratch_bytes(C.byref(p))
             if share["key"] == key and share["buffer"] is not None and share["buffer"].numel() >= full:
                 flags |= _lib.FLAG_PREP_DONE
             else:
                 share["key"], share["buffer"] = key, torch.empty(full, dtype=torch.uint8, device=dev)
             p.flags = flags
-            residuals = share["buffer"] if needs_grad else None
-            scratch = None if needs_grad else share["buffer"]
-            res_bytes = full if needs_grad else 0
-            scr_bytes = 0 if needs_grad else full
+            residuals = share["buffer"] if as_residuals else None
+            scratch = None if as_residuals else share["buffer"]
+            res_bytes = full if as_residuals else 0
+            scr_bytes = 0 if as_residuals else full
         else:
             residuals = torch.empty(res_bytes, dtype=torch.uint8, device=dev) if res_bytes else None
             scr_bytes = lib.jla_fwd_scratch_bytes(C.byref(p))

@@ -1,0 +1,106 @@
+"""Chunked KDA forward (per-channel gates) on the tensor cores against the CPU oracle and against the library's
+own fp32 token scan. The gradients of a bf16 KDA call come from the token-scan backward and are checked too.
+Tolerance: relative L2 <= 1e-2 (bf16 tensors, fp32 state), as for the reference's kernels
+(tests/test_mosaic_gpu_kda.py:98-130 of the reference)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.cases import baseline_config, make_case, rel_l2
+from tests._util import compare, run_cuda, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _forward(case, *, precision=None, cu=None, l2norm=False, h0=True):
+    from jax_linear_attention_b200 import ops
+
+    dev = "cuda"
+    t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16) for n in ("q", "k", "v")}
+    g = torch.tensor(case["g"], device=dev)
+    beta = torch.tensor(case["beta"], device=dev)
+    opts = dict(scale=case["meta"]["scale"], output_final_state=True, precision=precision, use_qk_l2norm=l2norm)
+    if h0 and "h0" in case:
+        opts["initial_state"] = torch.tensor(case["h0"], device=dev)
+    if "seg" in case and cu is None:
+        opts["segment_ids"] = torch.tensor(case["seg"], device=dev)
+    if cu is not None:
+        opts["cu_seqlens"] = torch.tensor(cu, device=dev, dtype=torch.int32)
+    with torch.no_grad():
+        o, ht = ops.linear_attention("kda", t["q"], t["k"], t["v"], g=g, beta=beta, impl="cuda", **opts)
+    torch.cuda.synchronize()
+    return o.float().cpu().numpy(), ht.float().cpu().numpy()
+
+
+def test_the_bf16_forward_takes_the_chunked_path():
+    from jax_linear_attention_b200 import _lib
+    from jax_linear_attention_b200.ops.cuda import _problem
+
+    import ctypes as C
+
+    lib = _lib.load()
+    p = _problem("kda", torch.bfloat16, 2, 256, 4, 4, 128, 128, 0, 1.0, 0, None)
+    assert lib.jla_fwd_scratch_bytes(C.byref(p)) > 0      # only the chunked path needs a forward scratch
+    assert lib.jla_residual_bytes(C.byref(p)) == 0        # the backward is the token scan: nothing is kept
+    p64 = _problem("kda", torch.bfloat16, 2, 256, 4, 4, 64, 64, 0, 1.0, 0, None)
+    assert lib.jla_fwd_scratch_bytes(C.byref(p64)) == 0   # other head sizes stay on the token scan
+
+
+@pytest.mark.parametrize("docs", [None, "uniform", "mixed"])
+@pytest.mark.parametrize("T", [64, 200, 1024])
+def test_forward_matches_the_oracle(docs, T):
+    case = make_case("kda", B=2, T=T, H=4, K=128, V=128, seed=21 + T, gates="kda_baseline", docs=docs, h0=True,
+                     doc_range=(16, max(T // 2, 17)))
+    want = run_oracle("kda", case, scale=case["meta"]["scale"], grads=False)
+    o, ht = _forward(case)
+    compare({"o": o, "ht": ht}, want, 1e-2, f"kda T={T} docs={docs}")
+
+
+def test_plain_gates_and_grouped_key_heads():
+    """Gates of the scalar-gate tests' size per channel (decay up to e^-5 per token in places) and Hk < H."""
+    case = make_case("kda", B=1, T=500, H=4, Hk=2, K=128, V=128, seed=5, gates="plain", h0=True)
+    want = run_oracle("kda", case, scale=case["meta"]["scale"], grads=False)
+    o, ht = _forward(case)
+    compare({"o": o, "ht": ht}, want, 1e-2, "kda plain gates")
+
+
+def test_strong_decay_takes_the_exact_score_path():
+    """Channels that decay by e^-80 at one token in ten: the factored tensor-core scores would overflow, so these
+    chunks run the exact fp32 score loop; beta hits 0 and 1."""
+    case = make_case("kda", B=1, T=320, H=2, K=128, V=128, seed=6, gates="extreme", docs="mixed", h0=True)
+    assert float(np.abs(case["g"]).max()) >= 80.0
+    want = run_oracle("kda", case, scale=case["meta"]["scale"], grads=False)
+    o, ht = _forward(case)
+    assert np.isfinite(o).all() and np.isfinite(ht).all()
+    compare({"o": o, "ht": ht}, want, 1e-2, "kda extreme gates")
+
+
+def test_packed_sequences_with_l2norm_match_the_token_scan():
+    """cu_seqlens rows with ragged lengths (partial chunks in every row) and the in-op L2 norm: the chunked forward
+    against the library's own fp32-arithmetic scan on the same bf16 tensors."""
+    case = make_case("kda", B=1, T=1500, H=4, K=128, V=128, seed=8, gates="kda_baseline", l2norm=True)
+    cu = [0, 1, 65, 300, 777, 1500]
+    rng = np.random.default_rng(3)
+    case["h0"] = (rng.standard_normal((len(cu) - 1, 4, 128, 128)) * 0.5).astype(np.float32)
+    o, ht = _forward(case, cu=cu, l2norm=True)
+    o_ref, ht_ref = _forward(case, cu=cu, l2norm=True, precision="highest")
+    assert rel_l2(o, o_ref) <= 1e-2 and rel_l2(ht, ht_ref) <= 1e-2, (rel_l2(o, o_ref), rel_l2(ht, ht_ref))
+
+
+def test_gradients_of_a_bf16_call_come_from_the_scan_backward():
+    case = make_case("kda", B=1, T=300, H=2, K=128, V=128, seed=12, gates="kda_baseline", docs="uniform", h0=True,
+                     doc_range=(50, 200))
+    want = run_oracle("kda", case, scale=case["meta"]["scale"])
+    got = run_cuda("kda", case, scale=case["meta"]["scale"], dtype="bfloat16")
+    compare(got, want, 1e-2, "kda fwd+bwd")
+
+
+def test_config3_full_size_matches_the_token_scan():
+    """The KDA benchmark shape (B4 T4096 H16 d128, packed documents): chunked forward against the token scan."""
+    case = baseline_config(3)
+    o, ht = _forward(case, h0=False)
+    o_ref, ht_ref = _forward(case, h0=False, precision="highest")
+    assert np.isfinite(o).all()
+    assert rel_l2(o, o_ref) <= 1e-2 and rel_l2(ht, ht_ref) <= 1e-2, (rel_l2(o, o_ref), rel_l2(ht, ht_ref))
