@@ -19,6 +19,7 @@ void set_error(const char* fmt, ...) {
 
 const char* recurrent_unsupported(const jla_problem& p);
 const char* chunked_unsupported(const jla_problem& p);
+bool kda_scan_backward();
 size_t chunked_residual_bytes(const jla_problem& p);
 size_t chunked_fwd_scratch_bytes(const jla_problem& p);
 size_t chunked_bwd_scratch_bytes(const jla_problem& p);
@@ -27,10 +28,10 @@ int chunked_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t stream)
 
 namespace {
 
-// The KDA backward is always the token scan (it recomputes what it needs from the inputs, so the chunked KDA forward
-// keeps no residuals).
+// With JLA_B200_KDA_SCAN_BWD=1 the KDA backward is the token scan (it recomputes what it needs from the inputs, so the
+// chunked KDA forward then keeps no residuals).
 int resolve_path(const jla_problem& p, bool bwd = false) {
-  if (bwd && p.kind == JLA_KIND_KDA) return JLA_PATH_RECURRENT;
+  if (bwd && p.kind == JLA_KIND_KDA && kda_scan_backward()) return JLA_PATH_RECURRENT;
   if (p.path == JLA_PATH_AUTO) {
     // f32 tensors run the exact token scan; so does whatever the chunked kernels do not cover (chunked_unsupported()).
     if (p.dtype == JLA_DTYPE_F32 || chunked_unsupported(p) != nullptr) {
@@ -115,7 +116,7 @@ const char* jla_last_error(void) { return g_error; }
 const char* jla_unsupported_reason(const jla_problem* p) { return p ? unsupported(*p) : "null problem"; }
 
 size_t jla_residual_bytes(const jla_problem* p) {
-  if (!p || unsupported(*p) || p->kind == JLA_KIND_KDA) return 0;
+  if (!p || unsupported(*p) || (p->kind == JLA_KIND_KDA && kda_scan_backward())) return 0;
   return resolve_path(*p) == JLA_PATH_RECURRENT ? 0 : chunked_residual_bytes(*p);
 }
 

@@ -27,6 +27,7 @@ struct Plan {
   bool delta, l2norm, save;
   size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, w, residual_bytes;  // residual buffer
   size_t kda_q, kda_kr, kda_kw, kda_p, kda_d;  // KDA: gate-folded operands per chunk slot (see chunked_kda_prep.cu)
+  size_t kda_dag, kda_dqs, kda_dks, kda_dku, kda_dd;  // KDA backward scratch (see chunked_kda_bwd.cu)
   size_t fwd_scratch_bytes;                                                 // same layout without h, vn
   size_t dh, dvn, dq_acc, dk_acc, dp, dga, bwd_scratch_bytes;               // backward scratch
 };
@@ -34,6 +35,8 @@ struct Plan {
 // The tcgen05 kernels cover K = V = 128 and keep the residuals h, Vn and W transposed ([V][K], [V][64]); other head
 // sizes, or JLA_B200_LEGACY=1 (A/B comparison), use the mma.sync kernels with row-major residuals.
 bool use_tc_kernels(const jla_problem& p);  // chunked_api.cu
+// JLA_B200_KDA_SCAN_BWD=1: the KDA backward runs the fp32 token scan instead of the chunked kernels (A/B comparison).
+bool kda_scan_backward();  // chunked_api.cu
 
 inline int elem_size(int dtype) { return dtype == JLA_DTYPE_F32 ? 4 : 2; }
 
@@ -45,8 +48,9 @@ inline Plan make_plan(const jla_problem& p) {
   pl.nc = varlen ? per_row + p.num_seqs : p.B * per_row;
   pl.delta = p.kind != JLA_KIND_SIMPLE_GLA;
   pl.l2norm = (p.flags & JLA_FLAG_QK_L2NORM) != 0;
-  const bool kda = p.kind == JLA_KIND_KDA;  // forward only: its backward is the token scan, which keeps no residuals
-  pl.save = (p.flags & JLA_FLAG_SAVE_RESIDUALS) != 0 && !kda;
+  const bool kda = p.kind == JLA_KIND_KDA;
+  // with the token-scan backward (kda_scan_backward()) the KDA forward keeps no residuals
+  pl.save = (p.flags & JLA_FLAG_SAVE_RESIDUALS) != 0 && !(kda && kda_scan_backward());
   const size_t es = elem_size(p.dtype);
   const size_t tokens = (size_t)p.B * p.T;
   Carver c(nullptr);
@@ -60,7 +64,7 @@ inline Plan make_plan(const jla_problem& p) {
   pl.row_chunks = off((size_t)(pl.rows + 1) * 2 * sizeof(int));
   pl.gates = off((size_t)pl.nc * p.H * 128 * sizeof(float));  // per (chunk, head): G[64] then beta[64]
   pl.runs = off((size_t)pl.nc * 64);
-  pl.t0 = off(pl.delta && !kda ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
+  pl.t0 = off(pl.delta ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
   pl.ag = off(pl.delta ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);  // Ag = T0 * D * beta_j (gated), for the forward
   pl.qn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
   pl.kn = off(pl.l2norm ? tokens * p.Hk * p.K * es : 0);
@@ -71,10 +75,10 @@ inline Plan make_plan(const jla_problem& p) {
   pl.kda_p = off(kda ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
   pl.kda_d = off(kda ? (size_t)pl.nc * p.H * p.K * sizeof(float) : 0);
   pl.fwd_scratch_bytes = align_up(c.off);
-  pl.h = off(kda ? 0 : (size_t)pl.nc * p.H * p.K * p.V * es);
-  pl.vn = off(pl.delta && !kda ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
+  pl.h = off((size_t)pl.nc * p.H * p.K * p.V * es);
+  pl.vn = off(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
   const bool tc = use_tc_kernels(p);
-  pl.w = off(pl.delta && tc && !kda ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);  // W^T, for the key-side gradient kernel
+  pl.w = off(pl.delta && tc ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);  // W^T, for the key-side gradient kernel
   pl.residual_bytes = align_up(c.off);
   Carver b(nullptr);
   auto boff = [&](size_t bytes) {
@@ -83,13 +87,19 @@ inline Plan make_plan(const jla_problem& p) {
     b.off += bytes;
     return o;
   };
-  const bool direct = p.H == p.Hk && !pl.l2norm;  // dq, dk written straight in the tensor dtype
+  const bool direct = p.H == p.Hk && !pl.l2norm && !kda;  // dq, dk written straight in the tensor dtype
   pl.dh = boff((size_t)pl.nc * p.H * p.K * p.V * es);
   pl.dvn = boff(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
   pl.dq_acc = boff(direct ? 0 : tokens * p.H * p.K * sizeof(float));
   pl.dk_acc = boff(direct ? 0 : tokens * p.H * p.K * sizeof(float));
   pl.dp = boff(tc ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);       // dP tiles, query-side -> key-side gradient kernel
   pl.dga = boff(tc ? (size_t)pl.nc * p.H * 64 * sizeof(float) : 0);  // dG partial sums, likewise
+  const size_t slot_f32 = kda ? (size_t)pl.nc * p.H * 64 * p.K * sizeof(float) : 0;
+  pl.kda_dag = boff(kda ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);  // dAg tiles
+  pl.kda_dqs = boff(slot_f32);                                      // gradients of the folded state-side operands
+  pl.kda_dks = boff(slot_f32);
+  pl.kda_dku = boff(slot_f32);
+  pl.kda_dd = boff(kda ? (size_t)pl.nc * p.H * p.K * sizeof(float) : 0);  // gradient of the state decay vector
   pl.bwd_scratch_bytes = align_up(b.off);
   return pl;
 }
@@ -131,6 +141,7 @@ struct ChunkedCtx {
 
 int launch_prep(const ChunkedCtx& c, cudaStream_t s);                           // tables, G/beta/runs, T0, l2norm
 int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s);                       // KDA: gate-folded operands, P, Ag
+int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s);  // after the reverse pass
 int launch_sg_fwd(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s);
 int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s);
 int l2norm_fwd(const void* x, void* y, int dtype, long rows, int K, cudaStream_t stream);

@@ -24,6 +24,14 @@ bool use_tc_kernels(const jla_problem& p) {
   return !legacy && p.K == 128 && p.V == 128 && p.dtype != JLA_DTYPE_F32;
 }
 
+bool kda_scan_backward() {
+  static const bool scan = [] {
+    const char* e = getenv("JLA_B200_KDA_SCAN_BWD");
+    return e && e[0] == '1';
+  }();
+  return scan;
+}
+
 size_t chunked_residual_bytes(const jla_problem& p) { return make_plan(p).residual_bytes; }
 
 size_t chunked_fwd_scratch_bytes(const jla_problem& p) {

@@ -641,7 +641,8 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
   const Plan& pl = c.plan;
   const long tokens = (long)p.B * p.T;
   if (pl.rows == 0) return JLA_OK;
-  const bool direct = p.H == p.Hk && !pl.l2norm;
+  const bool kda = p.kind == JLA_KIND_KDA;
+  const bool direct = p.H == p.Hk && !pl.l2norm && !kda;
   BwdParams bp{};
   bp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
   bp.row_chunks = reinterpret_cast<const int2*>(c.res + pl.row_chunks);
@@ -681,7 +682,7 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
                   : launch_kv<__half, false>(bp, p.K, p.V, rb, cb, legacy, s);
   }
   if (rc == JLA_OK && !legacy && (p.flags & JLA_FLAG_STATE_GRADS_ONLY)) return rc;
-  if (rc == JLA_OK && !legacy) rc = launch_chunk_grads_tc(c, io, scratch, direct, s);
+  if (rc == JLA_OK && !legacy) rc = kda ? launch_kda_grads(c, io, scratch, s) : launch_chunk_grads_tc(c, io, scratch, direct, s);
   if (rc != JLA_OK || direct) return rc;
   rc = finalize_key_grad(bp.dq_acc, p.q, io.dq, p.dtype, tokens, p.H, p.Hk, p.K, pl.l2norm, s);
   if (rc != JLA_OK) return rc;

@@ -22,10 +22,13 @@ namespace {
 using umma::swz_tile;
 
 constexpr int K = 128, V = 128;
-constexpr int NS = 3;
+constexpr int kBarBase = 6;  // full / empty barriers of the ring (at most 3 stages) come first
 
+// VG (per-channel gates, KDA): gate-folded tiles per chunk slot as in the forward (chunked_kda_prep.cu):
+// q -> cin q exp(G), k -> cin k exp(G), k2 -> tail k exp(G_63 - G), p -> the masked score tile, ag -> T beta_j; the
+// gate vector of the stage carries exp(G_63) per key channel.
 struct BwdTcMaps {
-  CUtensorMap q, k, d_o, ag;
+  CUtensorMap q, k, d_o, ag, k2, p;
 };
 
 struct BwdTcParams {
@@ -42,18 +45,20 @@ struct BwdTcParams {
   int* status;
 };
 
-struct Smem {
-  static constexpr int kStage = 64 * K * 2 * 2 + 64 * V * 2 + 8192;  // q, k, dO, Ag
+template <bool VG>
+struct SmemT {
+  static constexpr int NS = VG ? 2 : 3;
+  static constexpr int kStage = 64 * K * 2 * 2 + 64 * V * 2 + 8192 + (VG ? 64 * K * 2 + 8192 : 0);  // q, k, dO, Ag (+ k2, P)
   static constexpr int kPb = NS * kStage;                // scale P tiles [2][64x64]
-  static constexpr int kGates = kPb + 2 * 8192;
+  static constexpr int kGates = kPb + (VG ? 0 : 2 * 8192);
   static constexpr int kGateStride = 640;
   static constexpr int kScal = kGates + NS * kGateStride;  // per stage and state warp: gam[64], gamr[64]
   static constexpr int kBars = kScal + NS * 4096;
-  static constexpr int kNumBars = 2 * NS + 12;
+  static constexpr int kNumBars = kBarBase + 12;
   static constexpr int kBytes = kBars + kNumBars * 8 + 64 + 1024;
 };
 
-enum { B_PDONE = 2 * NS, B_PFREE, B_PA0, B_PA1, B_ST, B_MA, B_DV, B_MB, B_DW, B_MC };
+enum { B_PDONE = kBarBase, B_PFREE, B_PA0, B_PA1, B_ST, B_MA, B_DV, B_MB, B_DW, B_MC };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(bar)) : "memory");
@@ -89,8 +94,11 @@ __device__ __forceinline__ void ld_row32(float (&v)[32], uint32_t taddr) {
   umma::wait_ld();
 }
 
-template <typename T, bool DELTA>
+template <typename T, bool DELTA, bool VG>
 __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_constant__ BwdTcMaps maps, BwdTcParams p) {
+  static_assert(DELTA || !VG, "per-channel gates come with the delta rule");
+  using Smem = SmemT<VG>;
+  constexpr int NS = Smem::NS;
   constexpr int FMT = umma::Fmt<T>::value;
   const int row = blockIdx.x / p.H, h = blockIdx.x - row * p.H;
   const int hk = h / (p.H / p.Hk);
@@ -104,6 +112,8 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
   auto st_k = [&](int s) { return st_q(s) + 64 * K * 2; };
   auto st_do = [&](int s) { return st_k(s) + 64 * K * 2; };
   auto st_ag = [&](int s) { return st_do(s) + 64 * V * 2; };
+  auto st_k2 = [&](int s) { return st_ag(s) + 8192; };       // VG only
+  auto st_p = [&](int s) { return st_k2(s) + 64 * K * 2; };  // VG only
   auto st_G = [&](int s) { return reinterpret_cast<float*>(base + Smem::kGates + s * Smem::kGateStride); };
   auto st_runs = [&](int s) { return reinterpret_cast<unsigned char*>(st_G(s) + 128); };
   auto st_meta = [&](int s) { return reinterpret_cast<volatile int*>(st_runs(s) + 64); };
@@ -150,12 +160,20 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
         ms[0] = m.tok0;
         ms[1] = m.len;
         ms[2] = m.flags;
-        const uint32_t bytes = 64 * K * 2 * 2 + 64 * V * 2 + (DELTA ? 8192 : 0) + 512 + 64;
+        const uint32_t bytes = 64 * K * 2 * 2 + 64 * V * 2 + (DELTA ? 8192 : 0) + (VG ? 64 * K * 2 + 8192 : 0) + 512 + 64;
         tma::expect_tx(bars + s, bytes);
-        tma::load_tile<64, K>(st_k(s), &maps.k, 0, hk, m.tok0, bars + s);
-        tma::load_tile<64, K>(st_q(s), &maps.q, 0, hk, m.tok0, bars + s);
+        const int slot_row = (c * p.H + h) * 64;
+        if (VG) {
+          tma::load_tile<64, K>(st_k(s), &maps.k, 0, 0, slot_row, bars + s);
+          tma::load_tile<64, K>(st_q(s), &maps.q, 0, 0, slot_row, bars + s);
+          tma::load_tile<64, K>(st_k2(s), &maps.k2, 0, 0, slot_row, bars + s);
+          tma::load_tile<64, 64>(st_p(s), &maps.p, 0, 0, slot_row, bars + s);
+        } else {
+          tma::load_tile<64, K>(st_k(s), &maps.k, 0, hk, m.tok0, bars + s);
+          tma::load_tile<64, K>(st_q(s), &maps.q, 0, hk, m.tok0, bars + s);
+        }
         tma::load_tile<64, V>(st_do(s), &maps.d_o, 0, h, m.tok0, bars + s);
-        if (DELTA) tma::load_tile<64, 64>(st_ag(s), &maps.ag, 0, 0, (c * p.H + h) * 64, bars + s);
+        if (DELTA) tma::load_tile<64, 64>(st_ag(s), &maps.ag, 0, 0, slot_row, bars + s);
         bulk_copy(st_G(s), p.gates + ((long)c * p.H + h) * 128, 512, bars + s);
         bulk_copy(st_runs(s), p.runs + (long)c * 64, 64, bars + s);
       }
@@ -172,19 +190,21 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
         umma::commit(bars + B_PDONE);
         return true;
       };
-      bool okm = n > 0 ? issue_p(0) : true;
+      bool okm = n > 0 && !VG ? issue_p(0) : true;
       for (int it = 0; it < n && okm; ++it) {
         const int s = it % NS;
         const uint32_t ph = it & 1;
         const uint32_t aq = umma::smem_addr(st_q(s)), ak = umma::smem_addr(st_k(s)), ado = umma::smem_addr(st_do(s));
         if (!wait(bars + B_ST, ph, abort_flag)) break;
         umma::fence_after_sync();
-        umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, ak, 64, false);  // dS+^T K^T
-        if (!wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
+        umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, VG ? umma::smem_addr(st_k2(s)) : ak, 64,
+                                                   false);  // dS+^T K^T
+        if (!VG && !wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
         // dO^T (scale P): A = dO tile read MN-major (M = value index), B = P tile read MN-major (rows i)
-        umma::gemm<128, 64, 4, true, true, FMT>(tmem + cA2, ado, 64, umma::smem_addr(Pb + (it & 1) * 8192), 64, false);
+        umma::gemm<128, 64, 4, true, true, FMT>(tmem + cA2, ado, 64,
+                                                VG ? umma::smem_addr(st_p(s)) : umma::smem_addr(Pb + (it & 1) * 8192), 64, false);
         umma::commit(bars + B_MA);
-        if (it + 1 < n && !issue_p(it + 1)) break;
+        if (!VG && it + 1 < n && !issue_p(it + 1)) break;
         if (DELTA) {
           if (!wait(bars + B_DV, ph, abort_flag)) break;
           umma::fence_after_sync();
@@ -216,12 +236,18 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) {
         const int j = lane + 32 * jj;
-        const RowScalars rs = row_scalars(Gs, runs, flags, j);
-        gam[j] = rs.gam;
-        gamr[j] = rs.gamr;
+        if (VG) {  // masks and decays are folded into the operands
+          gam[j] = 1.f;
+          gamr[j] = 1.f;
+        } else {
+          const RowScalars rs = row_scalars(Gs, runs, flags, j);
+          gam[j] = rs.gam;
+          gamr[j] = rs.gamr;
+        }
       }
       __syncwarp();
-      const float kg = keep_gamma(Gs, runs, flags);
+      const float kg = VG ? 0.f : keep_gamma(Gs, runs, flags);
+      const float pscale = VG ? p.scale : 1.f;  // VG: the score tile comes unscaled
       const int j0 = 32 * half;
       // ---- dS+ of this chunk: 16-bit copy, residual, decayed fp32 copy
       if (it > 0) {
@@ -249,7 +275,7 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
         }
         umma::st_32x32b_x16(tl + cSb + blk * 16, pk);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] *= kg;
+        for (int i = 0; i < 32; ++i) x[i] *= VG ? Gs[blk * 32 + i] : kg;  // VG: exp(G_63) of key channel blk * 32 + i
         umma::st_32x32b_x32(tl + cS + blk * 32, x);
       }
       // ---- scale (cin Gamma)_i dO^T as a 16-bit A operand (tokens i of this warp's half)
@@ -290,8 +316,8 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
         for (int i = 0; i < 16; ++i) {
           const int j = j0 + 2 * i;
           // columns of tokens past a partial chunk are forced to zero (their inputs are other rows' data)
-          dvn[i] = pack2<T>(j < len ? y[2 * i] + gamr[j] * x[2 * i] : 0.f,
-                            j + 1 < len ? y[2 * i + 1] + gamr[j + 1] * x[2 * i + 1] : 0.f);
+          dvn[i] = pack2<T>(j < len ? pscale * y[2 * i] + gamr[j] * x[2 * i] : 0.f,
+                            j + 1 < len ? pscale * y[2 * i + 1] + gamr[j + 1] * x[2 * i + 1] : 0.f);
         }
       }
       T* stg = reinterpret_cast<T*>(st_do(s)) + (warp - 4) * 32 * 32;  // [32 tokens][32 values]: dv staging (dO is dead)
@@ -380,6 +406,11 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
       const int s = it % NS, buf = it & 1;
       ok = wait(bars + s, (it / NS) & 1, abort_flag);
       if (!ok) break;
+      if (VG) {  // the score tile arrives with the stage: nothing to build
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + NS + s);
+        continue;
+      }
       const float* Gs = st_G(s);
       const unsigned char* runs = st_runs(s);
       ok = wait(bars + B_PDONE, it & 1, abort_flag);
@@ -420,13 +451,13 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
   if (tid == 0 && *abort_flag) atomicExch(p.status, 3);
 }
 
-template <typename T, bool DELTA>
+template <typename T, bool DELTA, bool VG = false>
 int launch_one(const BwdTcMaps& maps, const BwdTcParams& bp, int blocks, cudaStream_t s) {
-  auto* kern = sg_bwd_state_tc_kernel<T, DELTA>;
-  JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+  auto* kern = sg_bwd_state_tc_kernel<T, DELTA, VG>;
+  JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemT<VG>::kBytes));
   {
     ProfScope ps(kProfSgBwdState, s);
-    kern<<<blocks, 640, Smem::kBytes, s>>>(maps, bp);
+    kern<<<blocks, 640, SmemT<VG>::kBytes, s>>>(maps, bp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
@@ -442,16 +473,25 @@ int launch_sg_bwd_state_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scra
   const Plan& pl = c.plan;
   if (pl.rows == 0) return JLA_OK;
   const uint64_t tokens = (uint64_t)p.B * p.T, slots = (uint64_t)pl.nc * p.H;
+  const bool vg = p.kind == JLA_KIND_KDA;
   BwdTcMaps maps;
-  bool ok = tma::encode_3d(&maps.q, c.q_eff, p.K, p.Hk, tokens, 64) && tma::encode_3d(&maps.k, c.k_eff, p.K, p.Hk, tokens, 64) &&
-            tma::encode_3d(&maps.d_o, io.d_o, p.V, p.H, tokens, 64);
+  bool ok = tma::encode_3d(&maps.d_o, io.d_o, p.V, p.H, tokens, 64);
+  if (vg) {
+    ok = ok && tma::encode_3d(&maps.q, c.res + pl.kda_q, p.K, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.k, c.res + pl.kda_kr, p.K, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.k2, c.res + pl.kda_kw, p.K, 1, slots * 64, 64) &&
+         tma::encode_3d(&maps.p, c.res + pl.kda_p, 64, 1, slots * 64, 64);
+  } else {
+    ok = ok && tma::encode_3d(&maps.q, c.q_eff, p.K, p.Hk, tokens, 64) && tma::encode_3d(&maps.k, c.k_eff, p.K, p.Hk, tokens, 64);
+  }
   if (ok && pl.delta) ok = tma::encode_3d(&maps.ag, c.res + pl.ag, 64, 1, slots * 64, 64);
   if (ok && !pl.delta) maps.ag = maps.d_o;
   if (!ok) return JLA_ERR_CUDA;
+  if (!vg) maps.k2 = maps.p = maps.d_o;  // unused
   BwdTcParams bp{};
   bp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
   bp.row_chunks = reinterpret_cast<const int2*>(c.res + pl.row_chunks);
-  bp.gates = reinterpret_cast<const float*>(c.res + pl.gates);
+  bp.gates = reinterpret_cast<const float*>(c.res + (vg ? pl.kda_d : pl.gates));
   bp.runs = reinterpret_cast<const unsigned char*>(c.res + pl.runs);
   bp.d_final = io.d_final;
   bp.dv = io.dv;
@@ -464,6 +504,7 @@ int launch_sg_bwd_state_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scra
   bp.status = tc_status_ptr();
   if (!bp.status) return JLA_ERR_CUDA;
   const int blocks = pl.rows * p.H;
+  if (vg) return launch_one<__nv_bfloat16, true, true>(maps, bp, blocks, s);
   if (p.dtype == JLA_DTYPE_BF16) {
     return pl.delta ? launch_one<__nv_bfloat16, true>(maps, bp, blocks, s) : launch_one<__nv_bfloat16, false>(maps, bp, blocks, s);
   }

@@ -1,0 +1,449 @@
+// Chunk-parallel gradients of the chunked KDA path (per-channel gates), after the reverse state pass
+// (sg_bwd_state_tc_kernel, VG variant) has produced dS+ per chunk, dVn and dW = dv. Reference:
+// src/jla/ops/mosaic_gpu/vector_gate_bwd.py:278-447 (state-side and WY gradients), :450-492 (dAkk), :528-799 (scores).
+//
+// In the gate-folded form of chunked_kda_prep.cu the chunk step is a gate-free delta rule
+//   W = V - Ks S,  Vn = Ag W,  O = scale (Qs S + P Vn),  S+ = diag(d) S + Ku^T Vn,
+// so the first kernel needs no gate at all (one CTA per chunk and head, all operands as the forward left them):
+//   dQs = scale dO S^T    dKs = -dW S^T    dKu = Vn dS+^T    dP = scale dO Vn^T    dAg = dVn W^T    dd = rowsum(dS+ * S)
+// The second kernel takes these back through the triangular solve and the decayed scores and unfolds the gates:
+//   dT = dAg beta_j,  dbeta_j += sum_i dAg_ij T_ij,  dA = -strict(T^T dT T^T),  dbeta_i += sum_j dA_ij Akk_ij,
+//   dAkk = beta_i dA,   dq^ = dP k~,  dk^ = dAkk k~,  dk~ = dP^T q^ + dAkk^T k^      (q^, k^, k~: mid-point factors)
+//   dq = dq^ e^(G-R) + dQs cin e^G          dk = [dk^ e^(G-R) + dKs cin e^G] + [dk~ e^(R-G) + dKu tail e^(G63-G)]
+//   dG_i = q dq + k (read-side dk - write-side dk);   dG_63 += sum_i k dKu tail e^(G63-G) + d dd
+//   dg_t = sum_(i >= t) dG_i + dG_63        (G is a running sum over the chunk's tokens)
+// Chunks whose decay is too strong for the factored scores take exact fp32 loops, as in the forward.
+#include "chunked.cuh"
+#include "profile.cuh"
+#include "mma.cuh"
+
+namespace jla {
+namespace {
+
+constexpr int KD = 128, VD = 128;
+constexpr float kBoundedLog = 60.f;  // the same bound as chunked_kda_prep.cu
+
+struct KdaGradParams {
+  const ChunkMeta* meta;
+  const void *q, *k;   // [tokens, Hk, K]
+  const float* g;      // [tokens, H, K]
+  const float* gates;  // per (chunk, head): G (zero), beta[64]
+  const unsigned char* runs;
+  const void *d_o, *dw;              // [tokens, H, V]
+  const void *hT, *dhT;              // [slot][V][K]
+  const void *vnT, *dvnT, *wT;       // [slot][V][64]
+  const void *t0;                    // [slot][64][64]  T = (I + Akk)^-1
+  void *dp, *dag;                    // [slot][64][64]
+  float *dqs, *dks, *dku;            // [slot][64][K]
+  float* dd;                         // [slot][K]
+  float *dq_acc, *dk_acc;            // [tokens, H, K]
+  float *dg, *dbeta;
+  int H, Hk;
+  float scale;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256, 1) kda_state_grads_kernel(KdaGradParams p) {
+  constexpr int LDV = VD + 8, LDK = KD + 8, LDC = 72;
+  const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
+  const ChunkMeta m = p.meta[c];
+  if (m.len == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int r0 = 16 * (warp & 3), ch = warp >> 2, kc0 = (KD / 2) * ch, cc0 = 32 * ch;
+  const long slot = (long)c * p.H + h;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* dOs = reinterpret_cast<T*>(smem_raw);  // [64][LDV]
+  T* dWs = dOs + 64 * LDV;                  // [64][LDV]
+  T* hS = dWs + 64 * LDV;                   // [V][LDK]   S^T
+  T* dhS = hS + VD * LDK;                   // [V][LDK]   dS+^T
+  T* vnS = dhS + VD * LDK;                  // [V][LDC]   Vn^T
+  T* dvnS = vnS + VD * LDC;                 // [V][LDC]   dVn^T
+  T* wS = dvnS + VD * LDC;                  // [V][LDC]   W^T
+  float* ddp = reinterpret_cast<float*>(wS + VD * LDC);  // [2][KD]
+
+  const long vstride = (long)p.H * VD;
+  load_tile_async<T, 64, VD>(dOs, LDV, static_cast<const T*>(p.d_o) + ((long)m.tok0 * p.H + h) * VD, vstride, m.len, tid, 256);
+  load_tile_async<T, 64, VD>(dWs, LDV, static_cast<const T*>(p.dw) + ((long)m.tok0 * p.H + h) * VD, vstride, m.len, tid, 256);
+  load_tile_async<T, VD, KD>(hS, LDK, static_cast<const T*>(p.hT) + slot * VD * KD, KD, VD, tid, 256);
+  load_tile_async<T, VD, KD>(dhS, LDK, static_cast<const T*>(p.dhT) + slot * VD * KD, KD, VD, tid, 256);
+  load_tile_async<T, VD, 64>(vnS, LDC, static_cast<const T*>(p.vnT) + slot * VD * 64, 64, VD, tid, 256);
+  load_tile_async<T, VD, 64>(dvnS, LDC, static_cast<const T*>(p.dvnT) + slot * VD * 64, 64, VD, tid, 256);
+  load_tile_async<T, VD, 64>(wS, LDC, static_cast<const T*>(p.wT) + slot * VD * 64, 64, VD, tid, 256);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  auto store_f32 = [&](float* dst, const float (&acc)[8][4], float s) {  // [64][K] tile, this warp's 16 x 64 block
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int col = kc0 + nt * 8 + 2 * t;
+      *reinterpret_cast<float2*>(dst + (r0 + g) * KD + col) = make_float2(s * acc[nt][0], s * acc[nt][1]);
+      *reinterpret_cast<float2*>(dst + (r0 + g + 8) * KD + col) = make_float2(s * acc[nt][2], s * acc[nt][3]);
+    }
+  };
+  {
+    float acc[8][4];
+    zero_acc(acc);  // dQs = scale dO S^T
+    warp_gemm<T, 8, VD / 16, A_ROW, B_KN>(acc, dOs + r0 * LDV, LDV, hS + kc0, LDK, lane);
+    store_f32(p.dqs + slot * 64 * KD, acc, p.scale);
+    zero_acc(acc);  // dKs = -dW S^T
+    warp_gemm<T, 8, VD / 16, A_ROW, B_KN>(acc, dWs + r0 * LDV, LDV, hS + kc0, LDK, lane);
+    store_f32(p.dks + slot * 64 * KD, acc, -1.f);
+    zero_acc(acc);  // dKu = Vn dS+^T
+    warp_gemm<T, 8, VD / 16, A_COL, B_KN>(acc, vnS + r0, LDC, dhS + kc0, LDK, lane);
+    store_f32(p.dku + slot * 64 * KD, acc, 1.f);
+  }
+  {
+    float acc[4][4];
+    zero_acc(acc);  // dP = scale dO Vn^T
+    warp_gemm<T, 4, VD / 16, A_ROW, B_KN>(acc, dOs + r0 * LDV, LDV, vnS + cc0, LDC, lane);
+    store_acc<T, 4>(static_cast<T*>(p.dp) + slot * 4096, 64, r0, cc0, acc, lane, p.scale, p.scale);
+    zero_acc(acc);  // dAg = dVn W^T
+    warp_gemm<T, 4, VD / 16, A_COL, B_KN>(acc, dvnS + r0, LDC, wS + cc0, LDC, lane);
+    store_acc<T, 4>(static_cast<T*>(p.dag) + slot * 4096, 64, r0, cc0, acc, lane);
+  }
+  {  // dd[c] = sum_v dS+[c][v] S[c][v]
+    const int col = tid & (KD - 1), half = tid >> 7;
+    float s = 0.f;
+    for (int v = 64 * half; v < 64 * half + 64; ++v) s += to_f32(dhS[v * LDK + col]) * to_f32(hS[v * LDK + col]);
+    ddp[half * KD + col] = s;
+    __syncthreads();
+    if (tid < KD) p.dd[slot * KD + tid] = ddp[tid] + ddp[KD + tid];
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// sum over the 8 row groups of a warp for one accumulator column pair; valid in lanes 0..3 (t = lane)
+__device__ __forceinline__ float col_reduce(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  x += __shfl_xor_sync(0xffffffffu, x, 8);
+  x += __shfl_xor_sync(0xffffffffu, x, 16);
+  return x;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128, 1) kda_intra_grads_kernel(KdaGradParams p) {
+  constexpr int LDK = KD + 8, LDC = 72;
+  const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
+  const ChunkMeta m = p.meta[c];
+  if (m.len == 0) return;
+  const int hk = h / (p.H / p.Hk);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int r0 = 16 * warp;
+  const long slot = (long)c * p.H + h;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* tq = reinterpret_cast<T*>(smem_raw);  // raw q
+  T* tk = tq + 64 * LDK;                   // raw k
+  T* tqh = tk + 64 * LDK;                  // q exp(G - R)
+  T* tkh = tqh + 64 * LDK;                 // k exp(G - R)
+  T* tb = tkh + 64 * LDK;                  // k exp(R - G)
+  T* Tt = tb + 64 * LDK;                   // [64][LDC] T
+  T* Xd = Tt + 64 * LDC;                   // dT, later dAkk
+  T* Xm = Xd + 64 * LDC;                   // dAg, later M1 = dT T^T
+  T* Xp = Xm + 64 * LDC;                   // dP
+  float* Gm = reinterpret_cast<float*>(Xp + 64 * LDC);  // [64][KD]
+  float* dGt = Gm + 64 * KD;               // [64][KD] per-token dG; the exact path keeps the write-side dk here first
+  float* part = dGt + 64 * KD;             // [4][KD] column sums per warp
+  float* betas = part + 4 * KD;            // [64]
+  float* Glast = betas + 64;               // [KD]
+  float* dbrow = Glast + KD;               // [64]
+  float* dbcol = dbrow + 64;               // [64]
+  int* run = reinterpret_cast<int*>(dbcol + 64);  // [64]
+
+  const long kstride = (long)p.Hk * KD;
+  load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
+  load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
+  load_tile_async<T, 64, 64>(Tt, LDC, static_cast<const T*>(p.t0) + slot * 4096, 64, 64, tid, 128);
+  load_tile_async<T, 64, 64>(Xm, LDC, static_cast<const T*>(p.dag) + slot * 4096, 64, 64, tid, 128);
+  load_tile_async<T, 64, 64>(Xp, LDC, static_cast<const T*>(p.dp) + slot * 4096, 64, 64, tid, 128);
+  cp_async_commit();
+  if (tid < 64) {
+    betas[tid] = p.gates[slot * 128 + 64 + tid];
+    run[tid] = p.runs[(long)c * 64 + tid];
+  }
+  int unbounded;
+  {
+    const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + tid;
+    const long gstride = (long)p.H * KD;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < 64; ++i) {
+      if (i < m.len) acc += gp[i * gstride];
+      Gm[i * KD + tid] = acc;
+    }
+    Glast[tid] = acc;
+    cp_async_wait<0>();
+    unbounded = __syncthreads_or(!(fabsf(acc) <= kBoundedLog));
+  }
+  const bool entering = !(m.flags & 1);
+  const int run_last = run[63];
+
+  // ---- dT = dAg beta_j (same document, j <= i); dbeta_j += sum_i dAg_ij T_ij; the same mask on dP
+  for (int idx = tid; idx < 64 * 64; idx += 128) {
+    const int i = idx >> 6, j = idx & 63;
+    const bool ok = j <= i && run[i] == run[j];
+    Xd[i * LDC + j] = from_f32<T>(ok ? to_f32(Xm[i * LDC + j]) * betas[j] : 0.f);
+    if (!ok) Xp[i * LDC + j] = from_f32<T>(0.f);  // dP arrives unmasked: only pairs of one document with j <= i count
+  }
+  if (tid < 64) {
+    const int j = tid;
+    float s = 0.f;
+    for (int i = j; i < 64; ++i) {
+      if (run[i] == run[j]) s += to_f32(Xm[i * LDC + j]) * to_f32(Tt[i * LDC + j]);
+    }
+    dbcol[j] = s;
+  }
+  __syncthreads();
+  // ---- dA = -strict(T^T (dT T^T)), this warp's 16 rows
+  float accA[8][4];
+  {
+    float accM[8][4];
+    zero_acc(accM);
+    warp_gemm<T, 8, 4, A_ROW, B_NK>(accM, Xd + r0 * LDC, LDC, Tt, LDC, lane);
+    __syncthreads();  // dAg (Xm) and dT (Xd) have been read by every warp
+    store_acc<T, 8>(Xm, LDC, r0, 0, accM, lane);
+  }
+  __syncthreads();
+  zero_acc(accA);
+  warp_gemm<T, 8, 4, A_COL, B_KN>(accA, Tt + r0, LDC, Xm, LDC, lane);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = r0 + g + ((e >> 1) << 3), j = nt * 8 + 2 * t + (e & 1);
+      accA[nt][e] = (j < i && run[i] == run[j]) ? -accA[nt][e] : 0.f;
+    }
+  }
+  store_acc<T, 8>(Xd, LDC, r0, 0, accA, lane, betas[r0 + g], betas[r0 + g + 8]);  // dAkk = beta_i dA
+  const long tokbase = ((long)m.tok0 * p.H + h) * KD;
+  const long tstride = (long)p.H * KD;
+  const float* dqs = p.dqs + slot * 64 * KD;
+  const float* dks = p.dks + slot * 64 * KD;
+  const float* dku = p.dku + slot * 64 * KD;
+
+  if (!unbounded) {
+    // ---- the factored operands
+    for (int idx = tid; idx < 64 * (KD / 8); idx += 128) {
+      const int i = idx >> 4, c8 = (idx & 15) * 8;
+      const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
+      const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      uint4 oq, ok, ob;
+      const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
+      const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv);
+      uint32_t* oqw = reinterpret_cast<uint32_t*>(&oq);
+      uint32_t* okw = reinterpret_cast<uint32_t*>(&ok);
+      uint32_t* obw = reinterpret_cast<uint32_t*>(&ob);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kw[e]);
+        const float d0 = Gm[i * KD + c8 + 2 * e] - 0.5f * Glast[c8 + 2 * e];
+        const float d1 = Gm[i * KD + c8 + 2 * e + 1] - 0.5f * Glast[c8 + 2 * e + 1];
+        const float u0 = __expf(d0), u1 = __expf(d1), n0 = __expf(-d0), n1 = __expf(-d1);
+        oqw[e] = pack2<T>(qf.x * u0, qf.y * u1);
+        okw[e] = pack2<T>(kf.x * u0, kf.y * u1);
+        obw[e] = pack2<T>(kf.x * n0, kf.y * n1);
+      }
+      *reinterpret_cast<uint4*>(tqh + i * LDK + c8) = oq;
+      *reinterpret_cast<uint4*>(tkh + i * LDK + c8) = ok;
+      *reinterpret_cast<uint4*>(tb + i * LDK + c8) = ob;
+    }
+    uint32_t afrag[4][4];
+    acc_to_afrag<T, 4>(afrag, accA);
+    __syncthreads();  // factored tiles and dAkk (Xd) complete
+    float db0 = 0.f, db1 = 0.f;
+    const int i0 = r0 + g, i1 = r0 + g + 8;
+    const bool cin0 = entering && run[i0] == 0, cin1 = entering && run[i1] == 0;
+    const bool tl0 = i0 < m.len && run[i0] == run_last, tl1 = i1 < m.len && run[i1] == run_last;
+    const float b0 = betas[i0], b1 = betas[i1];
+#pragma unroll 1
+    for (int hf = 0; hf < 2; ++hf) {
+      const int kc0 = 64 * hf;
+      float accU[8][4], accQ[8][4], accW[8][4];
+      zero_acc(accU);
+      zero_acc(accQ);
+      zero_acc(accW);
+      warp_gemm_ra<T, 8, 4, B_KN>(accU, afrag, tb + kc0, LDK, lane);                          // dA k~
+      warp_gemm<T, 8, 4, A_ROW, B_KN>(accQ, Xp + r0 * LDC, LDC, tb + kc0, LDK, lane);         // dP k~
+      warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xp + r0, LDC, tqh + kc0, LDK, lane);              // dP^T q^
+      warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xd + r0, LDC, tkh + kc0, LDK, lane);              // + dAkk^T k^
+      float colsum[8][2];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        colsum[nt][0] = colsum[nt][1] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int hi = e >> 1, i = hi ? i1 : i0, col = kc0 + nt * 8 + 2 * t + (e & 1);
+          const bool cin = hi ? cin1 : cin0, tail = hi ? tl1 : tl0;
+          const float Gi = Gm[i * KD + col], Gl = Glast[col];
+          const float d = Gi - 0.5f * Gl;
+          const float eu = __expf(d), en = __expf(-d);
+          const float eg = cin ? __expf(Gi) : 0.f, ew = tail ? __expf(Gl - Gi) : 0.f;
+          const float kh = to_f32(tkh[i * LDK + col]);
+          if (hi) db1 += kh * accU[nt][e]; else db0 += kh * accU[nt][e];
+          const float dq = accQ[nt][e] * eu + dqs[i * KD + col] * eg;
+          const float dkr = (hi ? b1 : b0) * accU[nt][e] * eu + dks[i * KD + col] * eg;
+          const float kuw = dku[i * KD + col] * ew;
+          const float dkw = accW[nt][e] * en + kuw;
+          const float qr = to_f32(tq[i * LDK + col]), kr = to_f32(tk[i * LDK + col]);
+          dGt[i * KD + col] = qr * dq + kr * (dkr - dkw);
+          colsum[nt][e & 1] += kr * kuw;
+          if (i < m.len) {
+            p.dq_acc[tokbase + i * tstride + col] = dq;
+            p.dk_acc[tokbase + i * tstride + col] = dkr + dkw;
+          }
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const float a = col_reduce(colsum[nt][0]), b = col_reduce(colsum[nt][1]);
+        if (lane < 4) {
+          part[warp * KD + kc0 + nt * 8 + 2 * lane] = a;
+          part[warp * KD + kc0 + nt * 8 + 2 * lane + 1] = b;
+        }
+      }
+    }
+    db0 += __shfl_xor_sync(0xffffffffu, db0, 1);
+    db0 += __shfl_xor_sync(0xffffffffu, db0, 2);
+    db1 += __shfl_xor_sync(0xffffffffu, db1, 1);
+    db1 += __shfl_xor_sync(0xffffffffu, db1, 2);
+    if (t == 0) {
+      dbrow[i0] = db0;
+      dbrow[i1] = db1;
+    }
+  } else {
+    // ---- exact path: thread = key channel, fp32 with the true exponent of every pair of one document.
+    // dA (unscaled) goes to Xm for the beta gradient; the write-side dk accumulates in dGt[j][ch].
+    __syncthreads();  // M1 (Xm) has been read by every warp
+    store_acc<T, 8>(Xm, LDC, r0, 0, accA, lane);
+    for (int i = 0; i < 64; ++i) dGt[i * KD + tid] = 0.f;
+    if (tid < 64) dbrow[tid] = 0.f;
+    __syncthreads();
+    const int ch = tid;
+    float colsum = 0.f;
+    for (int i = 0; i < 64; ++i) {
+      const float Gi = Gm[i * KD + ch];
+      const float qi = to_f32(tq[i * LDK + ch]), ki = to_f32(tk[i * LDK + ch]);
+      float dq = 0.f, u = 0.f;
+      for (int j = 0; j <= i; ++j) {
+        if (run[j] != run[i]) continue;
+        const float e = __expf(Gi - Gm[j * KD + ch]);
+        const float kj = to_f32(tk[j * LDK + ch]) * e;
+        const float dp = to_f32(Xp[i * LDC + j]), dakk = to_f32(Xd[i * LDC + j]);
+        dq += dp * kj;
+        u += to_f32(Xm[i * LDC + j]) * kj;
+        dGt[j * KD + ch] += (dp * qi + dakk * ki) * e;
+      }
+      // dbeta_i += sum over channels of k_i u_i
+      float x = ki * u;
+      for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+      if (lane == 0) part[warp * KD + i] = x;
+      // the read-side parts are final now; stash them in registers-free form: q dq and k dkr go to global / dGt later
+      const bool cin = entering && run[i] == 0;
+      const float eg = cin ? __expf(Gi) : 0.f;
+      const float dqf = dq + dqs[i * KD + ch] * eg;
+      const float dkr = betas[i] * u + dks[i * KD + ch] * eg;
+      if (i < m.len) {
+        p.dq_acc[tokbase + i * tstride + ch] = dqf;
+        p.dk_acc[tokbase + i * tstride + ch] = dkr;  // the write side is added below
+      }
+      // keep q dq + k dkr for the gate gradient in the (dead) factored tile region as fp32
+      reinterpret_cast<float*>(tqh)[i * KD + ch] = qi * dqf + ki * dkr;
+    }
+    __syncthreads();
+    if (tid < 64) dbrow[tid] = part[tid] + part[KD + tid] + part[2 * KD + tid] + part[3 * KD + tid];
+    for (int i = 0; i < 64; ++i) {
+      const float Gi = Gm[i * KD + ch];
+      const bool tail = i < m.len && run[i] == run_last;
+      const float ki = to_f32(tk[i * LDK + ch]);
+      const float kuw = dku[i * KD + ch] * (tail ? __expf(Glast[ch] - Gi) : 0.f);
+      const float dkw = dGt[i * KD + ch] + kuw;
+      dGt[i * KD + ch] = reinterpret_cast<float*>(tqh)[i * KD + ch] - ki * dkw;
+      colsum += ki * kuw;
+      if (i < m.len) p.dk_acc[tokbase + i * tstride + ch] += dkw;
+    }
+    __syncthreads();  // part[] has been read
+    part[ch] = colsum;
+    part[KD + ch] = part[2 * KD + ch] = part[3 * KD + ch] = 0.f;
+  }
+  __syncthreads();
+
+  // ---- dg: suffix sums over the chunk's tokens plus the terms that act through G_63; dbeta
+  {
+    const int ch = tid;
+    const float keep_d = (entering && run_last == 0) ? __expf(Glast[ch]) : 0.f;
+    float acc = part[ch] + part[KD + ch] + part[2 * KD + ch] + part[3 * KD + ch] + keep_d * p.dd[slot * KD + ch];
+    for (int i = 63; i >= 0; --i) {
+      acc += dGt[i * KD + ch];
+      if (i < m.len) p.dg[tokbase + i * tstride + ch] = acc;
+    }
+    if (tid < m.len) p.dbeta[(long)(m.tok0 + tid) * p.H + h] = dbrow[tid] + dbcol[tid];
+  }
+}
+
+template <typename T>
+int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
+  const size_t smem_a = (2 * 64 * (VD + 8) + 2 * VD * (KD + 8) + 3 * VD * 72) * sizeof(T) + 2 * KD * sizeof(float);
+  const size_t smem_b = (5 * 64 * (KD + 8) + 4 * 64 * 72) * sizeof(T) +
+                        (2 * 64 * KD + 4 * KD + 64 + KD + 64 + 64) * sizeof(float) + 64 * sizeof(int);
+  auto* ka = kda_state_grads_kernel<T>;
+  auto* kb = kda_intra_grads_kernel<T>;
+  JLA_CUDA_OK(cudaFuncSetAttribute(ka, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
+  JLA_CUDA_OK(cudaFuncSetAttribute(kb, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b));
+  {
+    ProfScope ps(kProfSgGradsQ, s);
+    ka<<<blocks, 256, smem_a, s>>>(gp);
+  }
+  JLA_LAUNCH_OK();
+  {
+    ProfScope ps(kProfSgGradsK, s);
+    kb<<<blocks, 128, smem_b, s>>>(gp);
+  }
+  JLA_LAUNCH_OK();
+  return JLA_OK;
+}
+
+}  // namespace
+
+int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s) {
+  const jla_problem& p = c.p;
+  const Plan& pl = c.plan;
+  if (p.dtype != JLA_DTYPE_BF16 || p.K != KD || p.V != VD) {
+    set_error("chunked KDA backward: bf16 tensors with K = V = 128 only");
+    return JLA_ERR_UNSUPPORTED;
+  }
+  KdaGradParams gp{};
+  gp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
+  gp.q = c.q_eff;
+  gp.k = c.k_eff;
+  gp.g = p.g;
+  gp.gates = reinterpret_cast<const float*>(c.res + pl.gates);
+  gp.runs = reinterpret_cast<const unsigned char*>(c.res + pl.runs);
+  gp.d_o = io.d_o;
+  gp.dw = io.dv;
+  gp.hT = c.res + pl.h;
+  gp.dhT = scratch + pl.dh;
+  gp.vnT = c.res + pl.vn;
+  gp.dvnT = scratch + pl.dvn;
+  gp.wT = c.res + pl.w;
+  gp.t0 = c.res + pl.t0;
+  gp.dp = scratch + pl.dp;
+  gp.dag = scratch + pl.kda_dag;
+  gp.dqs = reinterpret_cast<float*>(scratch + pl.kda_dqs);
+  gp.dks = reinterpret_cast<float*>(scratch + pl.kda_dks);
+  gp.dku = reinterpret_cast<float*>(scratch + pl.kda_dku);
+  gp.dd = reinterpret_cast<float*>(scratch + pl.kda_dd);
+  gp.dq_acc = reinterpret_cast<float*>(scratch + pl.dq_acc);
+  gp.dk_acc = reinterpret_cast<float*>(scratch + pl.dk_acc);
+  gp.dg = io.dg;
+  gp.dbeta = io.dbeta;
+  gp.H = p.H;
+  gp.Hk = p.Hk;
+  gp.scale = p.scale;
+  return launch_grads<__nv_bfloat16>(gp, pl.nc * p.H, s);
+}
+
+}  // namespace jla

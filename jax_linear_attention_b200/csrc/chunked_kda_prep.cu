@@ -37,6 +37,7 @@ struct KdaPrepParams {
   const unsigned char* runs;
   void *qs, *kr, *kw;  // [slot][64][K]
   void *ptile, *ag;    // [slot][64][64]
+  void* t0;            // [slot][64][64] T itself, for the backward (nullptr: not kept)
   float* dvec;         // [slot][K]
   int H, Hk;
 };
@@ -202,14 +203,16 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
 
   T* outp = static_cast<T*>(p.ptile) + slot * 64 * 64;
   T* outg = static_cast<T*>(p.ag) + slot * 64 * 64;
+  T* outt = p.t0 ? static_cast<T*>(p.t0) + slot * 64 * 64 : nullptr;
   for (int idx = tid; idx < 64 * 8; idx += 128) {
     const int r = idx >> 3, c8 = (idx & 7) * 8;
     *reinterpret_cast<uint4*>(outp + r * 64 + c8) = *reinterpret_cast<const uint4*>(pst + r * LDP + c8);
-    float a[8];
+    float a[8], x[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const int j = c8 + e;
-      a[e] = (j <= r && run[j] == run[r]) ? X[r * LDA + j] * betas[j] : 0.f;
+      x[e] = (j <= r && run[j] == run[r]) ? X[r * LDA + j] : 0.f;
+      a[e] = x[e] * betas[j];
     }
     uint4 v;
     v.x = pack2<T>(a[0], a[1]);
@@ -217,6 +220,13 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
     v.z = pack2<T>(a[4], a[5]);
     v.w = pack2<T>(a[6], a[7]);
     *reinterpret_cast<uint4*>(outg + r * 64 + c8) = v;
+    if (outt) {
+      v.x = pack2<T>(x[0], x[1]);
+      v.y = pack2<T>(x[2], x[3]);
+      v.z = pack2<T>(x[4], x[5]);
+      v.w = pack2<T>(x[6], x[7]);
+      *reinterpret_cast<uint4*>(outt + r * 64 + c8) = v;
+    }
   }
 }
 
@@ -237,6 +247,7 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
   kp.kw = c.res + pl.kda_kw;
   kp.ptile = c.res + pl.kda_p;
   kp.ag = c.res + pl.ag;
+  kp.t0 = pl.save ? c.res + pl.t0 : nullptr;
   kp.dvec = reinterpret_cast<float*>(c.res + pl.kda_d);
   kp.H = p.H;
   kp.Hk = p.Hk;
