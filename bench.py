@@ -85,6 +85,16 @@ def kernel_model(K: int, V: int, delta: bool, save: bool) -> dict:
     m["sg_chunk_grads"] = dict(
         bytes=2 * qk + 2 * vv + 2 * st + gates + 2 * qk + ((cc + 3 * vv) if delta else 0),
         mac=64 * 64 * V + 64 * K * V + 64 * 64 * K * 2 + 64 * K * V + ((64 * 64 * V + 64 * K * V + 2 * 64 * 64 * K) if delta else 0))
+    # KDA (per-channel gates): the gate-folded operands go through HBM between the prologue and the state passes, and
+    # the gradients of the folded state-side operands between the two gradient kernels (fp32)
+    f32 = 64 * K * 4
+    m["kda_prep"] = dict(bytes=2 * qk + f32 + 3 * qk + 3 * cc + K * 4 + gates, mac=2 * 64 * 64 * K)
+    m["kda_fwd"] = dict(bytes=3 * qk + 2 * cc + vv + K * 4 + vv + (st + 2 * vv if save else 0),
+                        mac=64 * 64 * V * 2 + K * V * 64 * 3)
+    m["kda_bwd_state"] = dict(bytes=3 * qk + 2 * cc + vv + K * 4 + st + 2 * vv, mac=64 * K * V + 64 * 64 * V * 2 + K * V * 64 * 2)
+    m["kda_chunk_grads"] = dict(bytes=2 * vv + 2 * st + 3 * vv + 3 * f32 + 2 * cc + K * 4, mac=3 * 64 * K * V + 2 * 64 * 64 * V)
+    m["kda_intra"] = dict(bytes=2 * qk + f32 + 3 * cc + 3 * f32 + K * 4 + 3 * f32 + 64 * 4,
+                          mac=2 * 64 ** 3 + 4 * 64 * 64 * K)
     return m
 
 

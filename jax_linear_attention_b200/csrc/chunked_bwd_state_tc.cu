@@ -456,7 +456,7 @@ int launch_one(const BwdTcMaps& maps, const BwdTcParams& bp, int blocks, cudaStr
   auto* kern = sg_bwd_state_tc_kernel<T, DELTA, VG>;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemT<VG>::kBytes));
   {
-    ProfScope ps(kProfSgBwdState, s);
+    ProfScope ps(VG ? kProfKdaBwdState : kProfSgBwdState, s);
     kern<<<blocks, 640, SmemT<VG>::kBytes, s>>>(maps, bp);
   }
   JLA_LAUNCH_OK();

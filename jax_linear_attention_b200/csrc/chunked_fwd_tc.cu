@@ -538,7 +538,7 @@ int launch_one(const FwdTcMaps& maps, const FwdTcParams& fp, int blocks, cudaStr
   auto* kern = sg_fwd_tc_kernel<T, DELTA, VG>;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemT<VG>::kBytes));
   {
-    ProfScope ps(kProfSgFwd, s);
+    ProfScope ps(VG ? kProfKdaFwd : kProfSgFwd, s);
     kern<<<blocks, 640, SmemT<VG>::kBytes, s>>>(maps, fp);
   }
   JLA_LAUNCH_OK();

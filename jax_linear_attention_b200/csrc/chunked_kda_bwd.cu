@@ -394,12 +394,12 @@ int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
   JLA_CUDA_OK(cudaFuncSetAttribute(ka, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
   JLA_CUDA_OK(cudaFuncSetAttribute(kb, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b));
   {
-    ProfScope ps(kProfSgGradsQ, s);
+    ProfScope ps(kProfKdaChunkGrads, s);
     ka<<<blocks, 256, smem_a, s>>>(gp);
   }
   JLA_LAUNCH_OK();
   {
-    ProfScope ps(kProfSgGradsK, s);
+    ProfScope ps(kProfKdaIntra, s);
     kb<<<blocks, 128, smem_b, s>>>(gp);
   }
   JLA_LAUNCH_OK();

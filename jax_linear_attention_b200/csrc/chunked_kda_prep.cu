@@ -261,7 +261,7 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
   auto* kern = kda_prep_kernel<T>;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
-    ProfScope ps(kProfKktInv, s);
+    ProfScope ps(kProfKdaPrep, s);
     kern<<<pl.nc * p.H, 128, smem, s>>>(kp);
   }
   JLA_LAUNCH_OK();
