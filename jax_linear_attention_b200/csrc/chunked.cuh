@@ -87,7 +87,7 @@ inline Plan make_plan(const jla_problem& p) {
     b.off += bytes;
     return o;
   };
-  const bool direct = p.H == p.Hk && !pl.l2norm && !kda;  // dq, dk written straight in the tensor dtype
+  const bool direct = p.H == p.Hk && !pl.l2norm;  // dq, dk written straight in the tensor dtype
   pl.dh = boff((size_t)pl.nc * p.H * p.K * p.V * es);
   pl.dvn = boff(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);
   pl.dq_acc = boff(direct ? 0 : tokens * p.H * p.K * sizeof(float));

@@ -642,7 +642,7 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
   const long tokens = (long)p.B * p.T;
   if (pl.rows == 0) return JLA_OK;
   const bool kda = p.kind == JLA_KIND_KDA;
-  const bool direct = p.H == p.Hk && !pl.l2norm && !kda;
+  const bool direct = p.H == p.Hk && !pl.l2norm;
   BwdParams bp{};
   bp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
   bp.row_chunks = reinterpret_cast<const int2*>(c.res + pl.row_chunks);

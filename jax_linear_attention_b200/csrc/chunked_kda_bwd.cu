@@ -36,7 +36,8 @@ struct KdaGradParams {
   void *dp, *dag;                    // [slot][64][64]
   float *dqs, *dks, *dku;            // [slot][64][K]
   float* dd;                         // [slot][K]
-  float *dq_acc, *dk_acc;            // [tokens, H, K]
+  float *dq_acc, *dk_acc;            // [tokens, H, K] f32, when key heads are grouped or the op normalised q, k
+  void *dq, *dk;                     // [tokens, Hk, K] tensor dtype, written directly otherwise (else nullptr)
   float *dg, *dbeta;
   int H, Hk;
   float scale;
@@ -125,14 +126,15 @@ __device__ __forceinline__ float col_reduce(float x) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128, 1) kda_intra_grads_kernel(KdaGradParams p) {
-  constexpr int LDK = KD + 8, LDC = 72;
+__global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p) {
+  constexpr int LDK = KD + 8, LDC = 72, NT = 256;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
   if (m.len == 0) return;
   const int hk = h / (p.H / p.Hk);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int r0 = 16 * warp;
+  const int rw = warp & 3, hf = warp >> 2;  // row block of 16 tokens; column half (of 64 x 64 tiles and of the K channels)
+  const int r0 = 16 * rw;
   const long slot = (long)c * p.H + h;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -142,48 +144,58 @@ __global__ void __launch_bounds__(128, 1) kda_intra_grads_kernel(KdaGradParams p
   T* tkh = tqh + 64 * LDK;                 // k exp(G - R)
   T* tb = tkh + 64 * LDK;                  // k exp(R - G)
   T* Tt = tb + 64 * LDK;                   // [64][LDC] T
-  T* Xd = Tt + 64 * LDC;                   // dT, later dAkk
-  T* Xm = Xd + 64 * LDC;                   // dAg, later M1 = dT T^T
+  T* Xd = Tt + 64 * LDC;                   // dT, later dAkk = beta_i dA
+  T* Xm = Xd + 64 * LDC;                   // dAg, then M1 = dT T^T, then dA
   T* Xp = Xm + 64 * LDC;                   // dP
   float* Gm = reinterpret_cast<float*>(Xp + 64 * LDC);  // [64][KD]
   float* dGt = Gm + 64 * KD;               // [64][KD] per-token dG; the exact path keeps the write-side dk here first
-  float* part = dGt + 64 * KD;             // [4][KD] column sums per warp
+  float* part = dGt + 64 * KD;             // [4][KD] column sums per row block (also scratch of the gate cumsum)
   float* betas = part + 4 * KD;            // [64]
   float* Glast = betas + 64;               // [KD]
-  float* dbrow = Glast + KD;               // [64]
-  float* dbcol = dbrow + 64;               // [64]
+  float* dbrow = Glast + KD;               // [2][64] per column half
+  float* dbcol = dbrow + 128;              // [64]
   int* run = reinterpret_cast<int*>(dbcol + 64);  // [64]
 
   const long kstride = (long)p.Hk * KD;
-  load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
-  load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
-  load_tile_async<T, 64, 64>(Tt, LDC, static_cast<const T*>(p.t0) + slot * 4096, 64, 64, tid, 128);
-  load_tile_async<T, 64, 64>(Xm, LDC, static_cast<const T*>(p.dag) + slot * 4096, 64, 64, tid, 128);
-  load_tile_async<T, 64, 64>(Xp, LDC, static_cast<const T*>(p.dp) + slot * 4096, 64, 64, tid, 128);
+  load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
+  load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
+  load_tile_async<T, 64, 64>(Tt, LDC, static_cast<const T*>(p.t0) + slot * 4096, 64, 64, tid, NT);
+  load_tile_async<T, 64, 64>(Xm, LDC, static_cast<const T*>(p.dag) + slot * 4096, 64, 64, tid, NT);
+  load_tile_async<T, 64, 64>(Xp, LDC, static_cast<const T*>(p.dp) + slot * 4096, 64, 64, tid, NT);
   cp_async_commit();
   if (tid < 64) {
     betas[tid] = p.gates[slot * 128 + 64 + tid];
     run[tid] = p.runs[(long)c * 64 + tid];
   }
+  // ---- cumulative log decay per channel: two threads per channel, 32 tokens each, then the second half is offset
   int unbounded;
   {
-    const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + tid;
+    const int ch = tid & (KD - 1), hh = tid >> 7;
+    const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + ch;
     const long gstride = (long)p.H * KD;
     float acc = 0.f;
 #pragma unroll 8
-    for (int i = 0; i < 64; ++i) {
+    for (int i = 32 * hh; i < 32 * hh + 32; ++i) {
       if (i < m.len) acc += gp[i * gstride];
-      Gm[i * KD + tid] = acc;
+      Gm[i * KD + ch] = acc;
     }
-    Glast[tid] = acc;
+    if (hh == 0) part[ch] = acc;
     cp_async_wait<0>();
-    unbounded = __syncthreads_or(!(fabsf(acc) <= kBoundedLog));
+    __syncthreads();
+    float total = acc;
+    if (hh == 1) {
+      const float off = part[ch];
+      for (int i = 32; i < 64; ++i) Gm[i * KD + ch] += off;
+      total = acc + off;
+      Glast[ch] = total;
+    }
+    unbounded = __syncthreads_or(hh == 1 && !(fabsf(total) <= kBoundedLog));
   }
   const bool entering = !(m.flags & 1);
   const int run_last = run[63];
 
   // ---- dT = dAg beta_j (same document, j <= i); dbeta_j += sum_i dAg_ij T_ij; the same mask on dP
-  for (int idx = tid; idx < 64 * 64; idx += 128) {
+  for (int idx = tid; idx < 64 * 64; idx += NT) {
     const int i = idx >> 6, j = idx & 63;
     const bool ok = j <= i && run[i] == run[j];
     Xd[i * LDC + j] = from_f32<T>(ok ? to_f32(Xm[i * LDC + j]) * betas[j] : 0.f);
@@ -198,36 +210,39 @@ __global__ void __launch_bounds__(128, 1) kda_intra_grads_kernel(KdaGradParams p
     dbcol[j] = s;
   }
   __syncthreads();
-  // ---- dA = -strict(T^T (dT T^T)), this warp's 16 rows
-  float accA[8][4];
+  // ---- dA = -strict(T^T (dT T^T)): this warp's 16 rows x 32 columns
   {
-    float accM[8][4];
+    float accM[4][4], accA[4][4];
     zero_acc(accM);
-    warp_gemm<T, 8, 4, A_ROW, B_NK>(accM, Xd + r0 * LDC, LDC, Tt, LDC, lane);
+    warp_gemm<T, 4, 4, A_ROW, B_NK>(accM, Xd + r0 * LDC, LDC, Tt + 32 * hf * LDC, LDC, lane);
     __syncthreads();  // dAg (Xm) and dT (Xd) have been read by every warp
-    store_acc<T, 8>(Xm, LDC, r0, 0, accM, lane);
-  }
-  __syncthreads();
-  zero_acc(accA);
-  warp_gemm<T, 8, 4, A_COL, B_KN>(accA, Tt + r0, LDC, Xm, LDC, lane);
+    store_acc<T, 4>(Xm, LDC, r0, 32 * hf, accM, lane);
+    __syncthreads();
+    zero_acc(accA);
+    warp_gemm<T, 4, 4, A_COL, B_KN>(accA, Tt + r0, LDC, Xm + 32 * hf, LDC, lane);
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = r0 + g + ((e >> 1) << 3), j = nt * 8 + 2 * t + (e & 1);
-      accA[nt][e] = (j < i && run[i] == run[j]) ? -accA[nt][e] : 0.f;
+      for (int e = 0; e < 4; ++e) {
+        const int i = r0 + g + ((e >> 1) << 3), j = 32 * hf + nt * 8 + 2 * t + (e & 1);
+        accA[nt][e] = (j < i && run[i] == run[j]) ? -accA[nt][e] : 0.f;
+      }
     }
+    __syncthreads();  // M1 (Xm) has been read by every warp
+    store_acc<T, 4>(Xm, LDC, r0, 32 * hf, accA, lane);                                      // dA
+    store_acc<T, 4>(Xd, LDC, r0, 32 * hf, accA, lane, betas[r0 + g], betas[r0 + g + 8]);    // dAkk = beta_i dA
   }
-  store_acc<T, 8>(Xd, LDC, r0, 0, accA, lane, betas[r0 + g], betas[r0 + g + 8]);  // dAkk = beta_i dA
   const long tokbase = ((long)m.tok0 * p.H + h) * KD;
   const long tstride = (long)p.H * KD;
+  T* dq16 = p.dq ? static_cast<T*>(p.dq) + ((long)m.tok0 * p.Hk + hk) * KD : nullptr;  // direct stores (H == Hk)
+  T* dk16 = p.dk ? static_cast<T*>(p.dk) + ((long)m.tok0 * p.Hk + hk) * KD : nullptr;
   const float* dqs = p.dqs + slot * 64 * KD;
   const float* dks = p.dks + slot * 64 * KD;
   const float* dku = p.dku + slot * 64 * KD;
 
   if (!unbounded) {
     // ---- the factored operands
-    for (int idx = tid; idx < 64 * (KD / 8); idx += 128) {
+    for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
       const int i = idx >> 4, c8 = (idx & 15) * 8;
       const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
@@ -251,59 +266,68 @@ __global__ void __launch_bounds__(128, 1) kda_intra_grads_kernel(KdaGradParams p
       *reinterpret_cast<uint4*>(tkh + i * LDK + c8) = ok;
       *reinterpret_cast<uint4*>(tb + i * LDK + c8) = ob;
     }
-    uint32_t afrag[4][4];
-    acc_to_afrag<T, 4>(afrag, accA);
-    __syncthreads();  // factored tiles and dAkk (Xd) complete
+    __syncthreads();  // factored tiles, dA (Xm) and dAkk (Xd) complete
     float db0 = 0.f, db1 = 0.f;
     const int i0 = r0 + g, i1 = r0 + g + 8;
     const bool cin0 = entering && run[i0] == 0, cin1 = entering && run[i1] == 0;
     const bool tl0 = i0 < m.len && run[i0] == run_last, tl1 = i1 < m.len && run[i1] == run_last;
     const float b0 = betas[i0], b1 = betas[i1];
-#pragma unroll 1
-    for (int hf = 0; hf < 2; ++hf) {
-      const int kc0 = 64 * hf;
-      float accU[8][4], accQ[8][4], accW[8][4];
-      zero_acc(accU);
-      zero_acc(accQ);
-      zero_acc(accW);
-      warp_gemm_ra<T, 8, 4, B_KN>(accU, afrag, tb + kc0, LDK, lane);                          // dA k~
-      warp_gemm<T, 8, 4, A_ROW, B_KN>(accQ, Xp + r0 * LDC, LDC, tb + kc0, LDK, lane);         // dP k~
-      warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xp + r0, LDC, tqh + kc0, LDK, lane);              // dP^T q^
-      warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xd + r0, LDC, tkh + kc0, LDK, lane);              // + dAkk^T k^
-      float colsum[8][2];
+    const int kc0 = 64 * hf;  // this warp's 64 key channels
+    float accU[8][4], accQ[8][4], accW[8][4];
+    zero_acc(accU);
+    zero_acc(accQ);
+    zero_acc(accW);
+    warp_gemm<T, 8, 4, A_ROW, B_KN>(accU, Xm + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dA k~
+    warp_gemm<T, 8, 4, A_ROW, B_KN>(accQ, Xp + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dP k~
+    warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xp + r0, LDC, tqh + kc0, LDK, lane);        // dP^T q^
+    warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xd + r0, LDC, tkh + kc0, LDK, lane);        // + dAkk^T k^
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        colsum[nt][0] = colsum[nt][1] = 0.f;
+    for (int nt = 0; nt < 8; ++nt) {
+      float colsum[2] = {0.f, 0.f};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int hi = e >> 1, i = hi ? i1 : i0, col = kc0 + nt * 8 + 2 * t + (e & 1);
-          const bool cin = hi ? cin1 : cin0, tail = hi ? tl1 : tl0;
-          const float Gi = Gm[i * KD + col], Gl = Glast[col];
+      for (int hi = 0; hi < 2; ++hi) {
+        const int i = hi ? i1 : i0, col = kc0 + nt * 8 + 2 * t;
+        const bool cin = hi ? cin1 : cin0, tail = hi ? tl1 : tl0;
+        const float2 qs2 = *reinterpret_cast<const float2*>(dqs + i * KD + col);
+        const float2 ks2 = *reinterpret_cast<const float2*>(dks + i * KD + col);
+        const float2 ku2 = *reinterpret_cast<const float2*>(dku + i * KD + col);
+        const float2 qr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tq + i * LDK + col));
+        const float2 kr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tk + i * LDK + col));
+        const float2 kh2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tkh + i * LDK + col));
+        float dqv[2], dkv[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int e = 2 * hi + x;
+          const float Gi = Gm[i * KD + col + x], Gl = Glast[col + x];
           const float d = Gi - 0.5f * Gl;
           const float eu = __expf(d), en = __expf(-d);
           const float eg = cin ? __expf(Gi) : 0.f, ew = tail ? __expf(Gl - Gi) : 0.f;
-          const float kh = to_f32(tkh[i * LDK + col]);
+          const float kh = x ? kh2.y : kh2.x;
           if (hi) db1 += kh * accU[nt][e]; else db0 += kh * accU[nt][e];
-          const float dq = accQ[nt][e] * eu + dqs[i * KD + col] * eg;
-          const float dkr = (hi ? b1 : b0) * accU[nt][e] * eu + dks[i * KD + col] * eg;
-          const float kuw = dku[i * KD + col] * ew;
+          const float dq = accQ[nt][e] * eu + (x ? qs2.y : qs2.x) * eg;
+          const float dkr = (hi ? b1 : b0) * accU[nt][e] * eu + (x ? ks2.y : ks2.x) * eg;
+          const float kuw = (x ? ku2.y : ku2.x) * ew;
           const float dkw = accW[nt][e] * en + kuw;
-          const float qr = to_f32(tq[i * LDK + col]), kr = to_f32(tk[i * LDK + col]);
-          dGt[i * KD + col] = qr * dq + kr * (dkr - dkw);
-          colsum[nt][e & 1] += kr * kuw;
-          if (i < m.len) {
-            p.dq_acc[tokbase + i * tstride + col] = dq;
-            p.dk_acc[tokbase + i * tstride + col] = dkr + dkw;
+          const float qr = x ? qr2.y : qr2.x, kr = x ? kr2.y : kr2.x;
+          dGt[i * KD + col + x] = qr * dq + kr * (dkr - dkw);
+          colsum[x] += kr * kuw;
+          dqv[x] = dq;
+          dkv[x] = dkr + dkw;
+        }
+        if (i < m.len) {
+          if (dq16) {
+            *reinterpret_cast<uint32_t*>(dq16 + (long)i * kstride + col) = pack2<T>(dqv[0], dqv[1]);
+            *reinterpret_cast<uint32_t*>(dk16 + (long)i * kstride + col) = pack2<T>(dkv[0], dkv[1]);
+          } else {
+            *reinterpret_cast<float2*>(p.dq_acc + tokbase + i * tstride + col) = make_float2(dqv[0], dqv[1]);
+            *reinterpret_cast<float2*>(p.dk_acc + tokbase + i * tstride + col) = make_float2(dkv[0], dkv[1]);
           }
         }
       }
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const float a = col_reduce(colsum[nt][0]), b = col_reduce(colsum[nt][1]);
-        if (lane < 4) {
-          part[warp * KD + kc0 + nt * 8 + 2 * lane] = a;
-          part[warp * KD + kc0 + nt * 8 + 2 * lane + 1] = b;
-        }
+      const float a = col_reduce(colsum[0]), b = col_reduce(colsum[1]);
+      if (lane < 4) {
+        part[rw * KD + kc0 + nt * 8 + 2 * lane] = a;
+        part[rw * KD + kc0 + nt * 8 + 2 * lane + 1] = b;
       }
     }
     db0 += __shfl_xor_sync(0xffffffffu, db0, 1);
@@ -311,68 +335,79 @@ __global__ void __launch_bounds__(128, 1) kda_intra_grads_kernel(KdaGradParams p
     db1 += __shfl_xor_sync(0xffffffffu, db1, 1);
     db1 += __shfl_xor_sync(0xffffffffu, db1, 2);
     if (t == 0) {
-      dbrow[i0] = db0;
-      dbrow[i1] = db1;
+      dbrow[hf * 64 + i0] = db0;
+      dbrow[hf * 64 + i1] = db1;
     }
   } else {
-    // ---- exact path: thread = key channel, fp32 with the true exponent of every pair of one document.
-    // dA (unscaled) goes to Xm for the beta gradient; the write-side dk accumulates in dGt[j][ch].
-    __syncthreads();  // M1 (Xm) has been read by every warp
-    store_acc<T, 8>(Xm, LDC, r0, 0, accA, lane);
-    for (int i = 0; i < 64; ++i) dGt[i * KD + tid] = 0.f;
-    if (tid < 64) dbrow[tid] = 0.f;
-    __syncthreads();
-    const int ch = tid;
-    float colsum = 0.f;
-    for (int i = 0; i < 64; ++i) {
-      const float Gi = Gm[i * KD + ch];
-      const float qi = to_f32(tq[i * LDK + ch]), ki = to_f32(tk[i * LDK + ch]);
-      float dq = 0.f, u = 0.f;
-      for (int j = 0; j <= i; ++j) {
-        if (run[j] != run[i]) continue;
-        const float e = __expf(Gi - Gm[j * KD + ch]);
-        const float kj = to_f32(tk[j * LDK + ch]) * e;
-        const float dp = to_f32(Xp[i * LDC + j]), dakk = to_f32(Xd[i * LDC + j]);
-        dq += dp * kj;
-        u += to_f32(Xm[i * LDC + j]) * kj;
-        dGt[j * KD + ch] += (dp * qi + dakk * ki) * e;
+    // ---- exact path: thread = key channel (threads 0..127), fp32 with the true exponent of every pair of one
+    // document. The write-side dk accumulates in dGt[j][ch]; q dq + k dk_read and dk_read are parked in the factored
+    // tiles, which this path does not build.
+    __syncthreads();  // dA (Xm) and dAkk (Xd) complete
+    const int ch = tid & (KD - 1);
+    const bool active = tid < KD;
+    float* keep = reinterpret_cast<float*>(tqh);  // [64][KD] fp32 over tqh | tkh
+    if (active) {
+      for (int i = 0; i < 64; ++i) dGt[i * KD + ch] = 0.f;
+      for (int i = 0; i < 64; ++i) {
+        const float Gi = Gm[i * KD + ch];
+        const float qi = to_f32(tq[i * LDK + ch]), ki = to_f32(tk[i * LDK + ch]);
+        float dq = 0.f, u = 0.f;
+        for (int j = 0; j <= i; ++j) {
+          if (run[j] != run[i]) continue;
+          const float e = __expf(Gi - Gm[j * KD + ch]);
+          const float kj = to_f32(tk[j * LDK + ch]) * e;
+          const float dp = to_f32(Xp[i * LDC + j]), dakk = to_f32(Xd[i * LDC + j]);
+          dq += dp * kj;
+          u += to_f32(Xm[i * LDC + j]) * kj;
+          dGt[j * KD + ch] += (dp * qi + dakk * ki) * e;
+        }
+        float x = ki * u;  // dbeta_i += sum over channels of k_i u_i
+        for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+        if (lane == 0) part[warp * KD + i] = x;
+        const bool cin = entering && run[i] == 0;
+        const float eg = cin ? __expf(Gi) : 0.f;
+        const float dqf = dq + dqs[i * KD + ch] * eg;
+        const float dkr = betas[i] * u + dks[i * KD + ch] * eg;
+        if (i < m.len) {
+          if (dq16) dq16[(long)i * kstride + ch] = from_f32<T>(dqf);
+          else p.dq_acc[tokbase + i * tstride + ch] = dqf;
+        }
+        keep[i * KD + ch] = qi * dqf + ki * dkr;
+        tb[i * LDK + ch] = from_f32<T>(dkr);  // the read-side dk waits here for the write side (tb is unused on this path)
       }
-      // dbeta_i += sum over channels of k_i u_i
-      float x = ki * u;
-      for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-      if (lane == 0) part[warp * KD + i] = x;
-      // the read-side parts are final now; stash them in registers-free form: q dq and k dkr go to global / dGt later
-      const bool cin = entering && run[i] == 0;
-      const float eg = cin ? __expf(Gi) : 0.f;
-      const float dqf = dq + dqs[i * KD + ch] * eg;
-      const float dkr = betas[i] * u + dks[i * KD + ch] * eg;
-      if (i < m.len) {
-        p.dq_acc[tokbase + i * tstride + ch] = dqf;
-        p.dk_acc[tokbase + i * tstride + ch] = dkr;  // the write side is added below
-      }
-      // keep q dq + k dkr for the gate gradient in the (dead) factored tile region as fp32
-      reinterpret_cast<float*>(tqh)[i * KD + ch] = qi * dqf + ki * dkr;
     }
     __syncthreads();
-    if (tid < 64) dbrow[tid] = part[tid] + part[KD + tid] + part[2 * KD + tid] + part[3 * KD + tid];
-    for (int i = 0; i < 64; ++i) {
-      const float Gi = Gm[i * KD + ch];
-      const bool tail = i < m.len && run[i] == run_last;
-      const float ki = to_f32(tk[i * LDK + ch]);
-      const float kuw = dku[i * KD + ch] * (tail ? __expf(Glast[ch] - Gi) : 0.f);
-      const float dkw = dGt[i * KD + ch] + kuw;
-      dGt[i * KD + ch] = reinterpret_cast<float*>(tqh)[i * KD + ch] - ki * dkw;
-      colsum += ki * kuw;
-      if (i < m.len) p.dk_acc[tokbase + i * tstride + ch] += dkw;
+    if (tid < 64) {
+      dbrow[tid] = part[tid] + part[KD + tid] + part[2 * KD + tid] + part[3 * KD + tid];
+      dbrow[64 + tid] = 0.f;
+    }
+    float colsum = 0.f;
+    if (active) {
+      for (int i = 0; i < 64; ++i) {
+        const float Gi = Gm[i * KD + ch];
+        const bool tail = i < m.len && run[i] == run_last;
+        const float ki = to_f32(tk[i * LDK + ch]);
+        const float kuw = dku[i * KD + ch] * (tail ? __expf(Glast[ch] - Gi) : 0.f);
+        const float dkw = dGt[i * KD + ch] + kuw;
+        dGt[i * KD + ch] = keep[i * KD + ch] - ki * dkw;
+        colsum += ki * kuw;
+        if (i < m.len) {
+          const float dk = to_f32(tb[i * LDK + ch]) + dkw;
+          if (dk16) dk16[(long)i * kstride + ch] = from_f32<T>(dk);
+          else p.dk_acc[tokbase + i * tstride + ch] = dk;
+        }
+      }
     }
     __syncthreads();  // part[] has been read
-    part[ch] = colsum;
-    part[KD + ch] = part[2 * KD + ch] = part[3 * KD + ch] = 0.f;
+    if (active) {
+      part[ch] = colsum;
+      part[KD + ch] = part[2 * KD + ch] = part[3 * KD + ch] = 0.f;
+    }
   }
   __syncthreads();
 
   // ---- dg: suffix sums over the chunk's tokens plus the terms that act through G_63; dbeta
-  {
+  if (tid < KD) {
     const int ch = tid;
     const float keep_d = (entering && run_last == 0) ? __expf(Glast[ch]) : 0.f;
     float acc = part[ch] + part[KD + ch] + part[2 * KD + ch] + part[3 * KD + ch] + keep_d * p.dd[slot * KD + ch];
@@ -380,7 +415,9 @@ __global__ void __launch_bounds__(128, 1) kda_intra_grads_kernel(KdaGradParams p
       acc += dGt[i * KD + ch];
       if (i < m.len) p.dg[tokbase + i * tstride + ch] = acc;
     }
-    if (tid < m.len) p.dbeta[(long)(m.tok0 + tid) * p.H + h] = dbrow[tid] + dbcol[tid];
+  } else if (tid - KD < m.len) {
+    const int i = tid - KD;
+    p.dbeta[(long)(m.tok0 + i) * p.H + h] = dbrow[i] + dbrow[64 + i] + dbcol[i];
   }
 }
 
@@ -388,7 +425,7 @@ template <typename T>
 int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
   const size_t smem_a = (2 * 64 * (VD + 8) + 2 * VD * (KD + 8) + 3 * VD * 72) * sizeof(T) + 2 * KD * sizeof(float);
   const size_t smem_b = (5 * 64 * (KD + 8) + 4 * 64 * 72) * sizeof(T) +
-                        (2 * 64 * KD + 4 * KD + 64 + KD + 64 + 64) * sizeof(float) + 64 * sizeof(int);
+                        (2 * 64 * KD + 4 * KD + 64 + KD + 128 + 64) * sizeof(float) + 64 * sizeof(int);
   auto* ka = kda_state_grads_kernel<T>;
   auto* kb = kda_intra_grads_kernel<T>;
   JLA_CUDA_OK(cudaFuncSetAttribute(ka, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
@@ -400,7 +437,7 @@ int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
   JLA_LAUNCH_OK();
   {
     ProfScope ps(kProfKdaIntra, s);
-    kb<<<blocks, 128, smem_b, s>>>(gp);
+    kb<<<blocks, 256, smem_b, s>>>(gp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
@@ -436,8 +473,11 @@ int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, c
   gp.dks = reinterpret_cast<float*>(scratch + pl.kda_dks);
   gp.dku = reinterpret_cast<float*>(scratch + pl.kda_dku);
   gp.dd = reinterpret_cast<float*>(scratch + pl.kda_dd);
-  gp.dq_acc = reinterpret_cast<float*>(scratch + pl.dq_acc);
-  gp.dk_acc = reinterpret_cast<float*>(scratch + pl.dk_acc);
+  const bool direct = p.H == p.Hk && !pl.l2norm;
+  gp.dq_acc = direct ? nullptr : reinterpret_cast<float*>(scratch + pl.dq_acc);
+  gp.dk_acc = direct ? nullptr : reinterpret_cast<float*>(scratch + pl.dk_acc);
+  gp.dq = direct ? io.dq : nullptr;
+  gp.dk = direct ? io.dk : nullptr;
   gp.dg = io.dg;
   gp.dbeta = io.dbeta;
   gp.H = p.H;
