@@ -43,8 +43,8 @@ struct KdaPrepParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
-  constexpr int LDK = KD + 8, LDA = kTriLda, LDM = kTriLdm, LDP = 72;
+__global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
+  constexpr int LDK = KD + 8, LDA = kTriLda, LDM = kTriLdm, LDP = 72, NT = 256;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
   if (m.len == 0) return;
@@ -67,27 +67,37 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
   T* pst = tb;
 
   const long kstride = (long)p.Hk * KD;
-  load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
-  load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, 128);
+  load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
+  load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
   cp_async_commit();
   if (tid < 64) {
     betas[tid] = p.gates[slot * 128 + 64 + tid];
     run[tid] = p.runs[(long)c * 64 + tid];
   }
-  // ---- cumulative log decay per channel (thread = channel); padding tokens add nothing
+  // ---- cumulative log decay per channel: two threads per channel, 32 tokens each, then the second half is offset;
+  // padding tokens add nothing
   int unbounded;
   {
-    const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + tid;
+    const int ch = tid & (KD - 1), hh = tid >> 7;
+    const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + ch;
     const long gstride = (long)p.H * KD;
     float acc = 0.f;
 #pragma unroll 8
-    for (int i = 0; i < 64; ++i) {
+    for (int i = 32 * hh; i < 32 * hh + 32; ++i) {
       if (i < m.len) acc += gp[i * gstride];
-      Gm[i * KD + tid] = acc;
+      Gm[i * KD + ch] = acc;
     }
-    Glast[tid] = acc;
+    if (hh == 0) M[ch] = acc;  // scratch of the inverse, free until then
     cp_async_wait<0>();
-    unbounded = __syncthreads_or(!(fabsf(acc) <= kBoundedLog));
+    __syncthreads();
+    float total = acc;
+    if (hh == 1) {
+      const float off = M[ch];
+      for (int i = 32; i < 64; ++i) Gm[i * KD + ch] += off;
+      total = acc + off;
+      Glast[ch] = total;
+    }
+    unbounded = __syncthreads_or(hh == 1 && !(fabsf(total) <= kBoundedLog));
   }
   const bool entering = !(m.flags & 1);
   const int run_last = run[63];
@@ -97,7 +107,7 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
     T* qs = static_cast<T*>(p.qs) + slot * 64 * KD;
     T* kr = static_cast<T*>(p.kr) + slot * 64 * KD;
     T* kw = static_cast<T*>(p.kw) + slot * 64 * KD;
-    for (int idx = tid; idx < 64 * (KD / 8); idx += 128) {
+    for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
       const int i = idx >> 4, c8 = (idx & 15) * 8;
       const bool cin = entering && run[i] == 0;
       const bool tail = i < m.len && run[i] == run_last;
@@ -123,13 +133,13 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
       *reinterpret_cast<uint4*>(kr + i * KD + c8) = or_;
       *reinterpret_cast<uint4*>(kw + i * KD + c8) = ow;
     }
-    p.dvec[slot * KD + tid] = (entering && run_last == 0) ? __expf(Glast[tid]) : 0.f;
+    if (tid < KD) p.dvec[slot * KD + tid] = (entering && run_last == 0) ? __expf(Glast[tid]) : 0.f;
   }
 
   if (!unbounded) {
     // ---- factored operands in place, then both score matrices on the tensor cores
     __syncthreads();  // the raw tiles have been read
-    for (int idx = tid; idx < 64 * (KD / 8); idx += 128) {
+    for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
       const int i = idx >> 4, c8 = (idx & 15) * 8;
       uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
@@ -152,34 +162,38 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
       *reinterpret_cast<uint4*>(tb + i * LDK + c8) = bv;
     }
     __syncthreads();
-    float accP[8][4], accA[8][4];
-    zero_acc(accP);
-    zero_acc(accA);
-    warp_gemm<T, 8, KD / 16, A_ROW, B_NK>(accP, tq + warp * 16 * LDK, LDK, tb, LDK, lane);
-    warp_gemm<T, 8, KD / 16, A_ROW, B_NK>(accA, tk + warp * 16 * LDK, LDK, tb, LDK, lane);
+    // warps 0-3: q^ k~^T (the score tile), warps 4-7: k^ k~^T (the solve matrix); 16 rows each
+    const int rw = warp & 3;
+    const bool score = warp < 4;
+    float acc[8][4];
+    zero_acc(acc);
+    warp_gemm<T, 8, KD / 16, A_ROW, B_NK>(acc, (score ? tq : tk) + rw * 16 * LDK, LDK, tb, LDK, lane);
     __syncthreads();  // every warp has read the tiles: X and the staged P may take their place
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        const int i = warp * 16 + g + 8 * hh, j = nt * 8 + 2 * t;
-        const float bi = betas[i];
+        const int i = rw * 16 + g + 8 * hh, j = nt * 8 + 2 * t;
         const int ri = run[i];
         const bool s0 = ri == run[j], s1 = ri == run[j + 1];
-        float2 v;
-        v.x = (j < i && s0) ? bi * accA[nt][2 * hh] : 0.f;
-        v.y = (j + 1 < i && s1) ? bi * accA[nt][2 * hh + 1] : 0.f;
-        *reinterpret_cast<float2*>(A + i * LDA + j) = v;
-        const float p0 = (j <= i && s0) ? accP[nt][2 * hh] : 0.f;
-        const float p1 = (j + 1 <= i && s1) ? accP[nt][2 * hh + 1] : 0.f;
-        *reinterpret_cast<uint32_t*>(pst + i * LDP + j) = pack2<T>(p0, p1);
+        if (score) {
+          const float p0 = (j <= i && s0) ? acc[nt][2 * hh] : 0.f;
+          const float p1 = (j + 1 <= i && s1) ? acc[nt][2 * hh + 1] : 0.f;
+          *reinterpret_cast<uint32_t*>(pst + i * LDP + j) = pack2<T>(p0, p1);
+        } else {
+          const float bi = betas[i];
+          float2 v;
+          v.x = (j < i && s0) ? bi * acc[nt][2 * hh] : 0.f;
+          v.y = (j + 1 < i && s1) ? bi * acc[nt][2 * hh + 1] : 0.f;
+          *reinterpret_cast<float2*>(A + i * LDA + j) = v;
+        }
       }
     }
   } else {
     // ---- exact path: every pair (i, j <= i) of one document, fp32 with the true exponent per channel
     __syncthreads();
-    for (int idx = tid; idx < 64 * 64; idx += 128) {
+    for (int idx = tid; idx < 64 * 64; idx += NT) {
       const int i = idx >> 6, j = idx & 63;
       float sq = 0.f, sk = 0.f;
       if (j <= i && run[i] == run[j]) {
@@ -196,7 +210,7 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
     }
     __syncthreads();  // the raw tiles have been read: X may take their place
   }
-  for (int idx = tid; idx < 64 * LDA / 4; idx += 128) reinterpret_cast<float4*>(X)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int idx = tid; idx < 64 * LDA / 4; idx += NT) reinterpret_cast<float4*>(X)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
   __syncthreads();
 
   invert_unit_lower_64(A, X, M, tid);
@@ -204,7 +218,7 @@ __global__ void __launch_bounds__(128) kda_prep_kernel(KdaPrepParams p) {
   T* outp = static_cast<T*>(p.ptile) + slot * 64 * 64;
   T* outg = static_cast<T*>(p.ag) + slot * 64 * 64;
   T* outt = p.t0 ? static_cast<T*>(p.t0) + slot * 64 * 64 : nullptr;
-  for (int idx = tid; idx < 64 * 8; idx += 128) {
+  for (int idx = tid; idx < 64 * 8; idx += NT) {
     const int r = idx >> 3, c8 = (idx & 7) * 8;
     *reinterpret_cast<uint4*>(outp + r * 64 + c8) = *reinterpret_cast<const uint4*>(pst + r * LDP + c8);
     float a[8], x[8];
@@ -262,7 +276,7 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
     ProfScope ps(kProfKdaPrep, s);
-    kern<<<pl.nc * p.H, 128, smem, s>>>(kp);
+    kern<<<pl.nc * p.H, 256, smem, s>>>(kp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
