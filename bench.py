@@ -459,7 +459,9 @@ def main() -> None:
                 # DRAM bytes per unit from ncu captures of this workload (profiles/*.md); scaled by the units of a launch
                 ncu_bytes_per_unit = {"sg_grads_k": 805.7e6 / 4096, "sg_grads_q": 491.2e6 / 4096,
                                       "sg_bwd_state": 454.0e6 / 4096, "kkt_inv": 92.9e6 / 4096}
-                traffic = ncu_bytes_per_unit.get(top) if args.workload == "gdn" else None
+                ncu_kda = {"kda_intra": 1023.5e6 / 4208, "kda_prep": 524.4e6 / 4208, "kda_chunk_grads": 1038.4e6 / 4208}
+                traffic = (ncu_bytes_per_unit.get(top) if args.workload == "gdn"
+                           else ncu_kda.get(top) if args.workload == "kda" else None)
                 roof.update(kernel=top, ms_per_launch=per_launch_ms,
                             traffic=None if traffic is None else traffic * units, peak_source=pk["source"],
                             algorithmic_bytes_per_launch=by, algorithmic_flops_per_launch=fl)
