@@ -167,10 +167,6 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     betas[tid] = p.gates[slot * 128 + 64 + tid];
     run[tid] = p.runs[(long)c * 64 + tid];
   }
-  if (tid >= 64 && tid < 67) {  // the fold reads these three fp32 tiles in fragment order: have them in L2 by then
-    const float* src = (tid == 64 ? p.dqs : tid == 65 ? p.dks : p.dku) + slot * 64 * KD;
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(64 * KD * 4) : "memory");
-  }
   // ---- cumulative log decay per channel: two threads per channel, 32 tokens each, then the second half is offset
   int unbounded;
   {
@@ -178,7 +174,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + ch;
     const long gstride = (long)p.H * KD;
     float acc = 0.f;
-#pragma unroll 16
+#pragma unroll 8
     for (int i = 32 * hh; i < 32 * hh + 32; ++i) {
       if (i < m.len) acc += gp[i * gstride];
       Gm[i * KD + ch] = acc;

@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
     const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + ch;
     const long gstride = (long)p.H * KD;
     float acc = 0.f;
-#pragma unroll 16
+#pragma unroll 8
     for (int i = 32 * hh; i < 32 * hh + 32; ++i) {
       if (i < m.len) acc += gp[i * gstride];
       Gm[i * KD + ch] = acc;
