@@ -37,7 +37,7 @@ struct KdaPrepParams {
   const unsigned char* runs;
   void *qs, *kr, *kw;  // [slot][64][K]
   void *ptile, *ag;    // [slot][64][64]
-  void* t0;            // [slot][64][64] T itself, for the backward (nullptr: not kept)
+  void* t0;            // [slot][64][64] T itself, for the backward
   float* dvec;         // [slot][K]
   int H, Hk;
 };
@@ -261,7 +261,7 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
   kp.kw = c.res + pl.kda_kw;
   kp.ptile = c.res + pl.kda_p;
   kp.ag = c.res + pl.ag;
-  kp.t0 = pl.save ? c.res + pl.t0 : nullptr;
+  kp.t0 = c.res + pl.t0;  // always: a later pass that shares this prologue (JLA_FLAG_PREP_DONE) may be differentiated
   kp.dvec = reinterpret_cast<float*>(c.res + pl.kda_d);
   kp.H = p.H;
   kp.Hk = p.Hk;

@@ -154,14 +154,16 @@ def test_baseline_config1_full_size_slices_and_properties():
         assert np.array_equal(alone["o"], got["o"]) and np.array_equal(alone["dk"], got["dk"])
 
 
-def test_shared_prep_and_state_only_backward_match_the_plain_calls():
+@pytest.mark.parametrize("kind", ["gated_deltanet", "kda"])
+def test_shared_prep_and_state_only_backward_match_the_plain_calls(kind):
     """Passes that share one chunk table (JLA_FLAG_PREP_DONE), the reverse-state-pass-only backward
     (JLA_FLAG_STATE_GRADS_ONLY) and the state-only forward (JLA_FLAG_STATE_ONLY) give the plain calls' results bit
-    for bit."""
+    for bit; for KDA the shared buffer also carries the gate-folded operands."""
     from jax_linear_attention_b200 import ops
     from jax_linear_attention_b200.ops.cuda import final_state_only, shared_prep, state_grads_only
 
-    case = make_case("gated_deltanet", B=1, T=1500, H=4, K=128, V=128, seed=77, docs="mixed", h0=True)
+    case = make_case(kind, B=1, T=1500, H=4, K=128, V=128, seed=77, docs="mixed", h0=True,
+                     gates="kda_baseline" if kind == "kda" else "plain")
     dev = torch.device("cuda")
     t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16 if n in "qkv" else torch.float32)
          for n in ("q", "k", "v", "g", "beta")}
@@ -169,15 +171,17 @@ def test_shared_prep_and_state_only_backward_match_the_plain_calls():
     h0 = torch.randn(4, 4, 128, 128, device=dev) * 0.1
     do = torch.tensor(case["do"], device=dev, dtype=torch.bfloat16)
 
+    kleaf = t["k"].clone().requires_grad_(True)
+
     def run(v, init, grad):
         leaf = init.clone().requires_grad_(grad)
-        o, f = ops.linear_attention("gated_deltanet", t["q"], t["k"], v, g=t["g"], beta=t["beta"], cu_seqlens=cu,
+        o, f = ops.linear_attention(kind, t["q"], kleaf if grad else t["k"], v, g=t["g"], beta=t["beta"], cu_seqlens=cu,
                                     initial_state=leaf, output_final_state=True)
         return o, f, leaf
 
     o1, f1, _ = run(t["v"], h0, False)
     o2, f2, leaf2 = run(t["v"] * 0.5, h0 * 2, True)
-    (want_dh0,) = torch.autograd.grad([o2], [leaf2], [do])
+    want_dh0, want_dk = torch.autograd.grad([o2], [leaf2, kleaf], [do])
     with shared_prep():
         o1s, f1s, _ = run(t["v"], h0, False)
         o2s, f2s, leaf2s = run(t["v"] * 0.5, h0 * 2, True)  # second call: tables reused, residuals saved
@@ -186,8 +190,10 @@ def test_shared_prep_and_state_only_backward_match_the_plain_calls():
     with state_grads_only():
         (got_dh0,) = torch.autograd.grad([o2s], [leaf2s], [do], retain_graph=True)
     assert torch.equal(got_dh0, want_dh0)
-    (full_dh0,) = torch.autograd.grad([o2s], [leaf2s], [do])
+    full_dh0, full_dk = torch.autograd.grad([o2s], [leaf2s, kleaf], [do])
     assert torch.equal(full_dh0, want_dh0)
+    # everything the backward reads from the shared prologue was written by its first (forward-only) call
+    assert torch.equal(full_dk, want_dk)
     with final_state_only():  # JLA_FLAG_STATE_ONLY: the outputs are skipped, the state pass is the same
         _, f1o, _ = run(t["v"], h0, False)
     assert torch.equal(f1o, f1)

@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _cp_worker(rank, world, port, out, piece_len=None):
+def _cp_worker(rank, world, port, out, piece_len=None, kind="gated_deltanet"):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -28,8 +28,8 @@ def _cp_worker(rank, world, port, out, piece_len=None):
     from jax_linear_attention_b200.distributed import context_parallel_linear_attention
 
     T = 4096
-    case = make_case("gated_deltanet", B=2 if piece_len is None else 1, T=T, H=4, K=128, V=128, seed=50, h0=True,
-                     docs="uniform", doc_range=(300, 3000))
+    case = make_case(kind, B=2 if piece_len is None else 1, T=T, H=4, K=128, V=128, seed=50, h0=True,
+                     docs="uniform", doc_range=(300, 3000), gates="kda_baseline" if kind == "kda" else "plain")
     tl = T // world
     sl = slice(rank * tl, (rank + 1) * tl)
     dev = torch.device("cuda", rank)
@@ -37,7 +37,7 @@ def _cp_worker(rank, world, port, out, piece_len=None):
                            requires_grad=True) for n in ("q", "k", "v", "g", "beta")}
     h0 = torch.tensor(case["h0"], device=dev, requires_grad=True)
     seg = torch.tensor(case["seg"][:, sl], device=dev)
-    o, f = context_parallel_linear_attention("gated_deltanet", loc["q"], loc["k"], loc["v"], g=loc["g"],
+    o, f = context_parallel_linear_attention(kind, loc["q"], loc["k"], loc["v"], g=loc["g"],
                                              beta=loc["beta"], segment_ids=seg, piece_len=piece_len,
                                              initial_state=h0 if rank == 0 else None, output_final_state=True)
     do = torch.tensor(case["do"][:, sl], device=dev, dtype=torch.bfloat16)
@@ -79,17 +79,18 @@ def test_context_parallel_two_gpus_matches_one_gpu(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_pieces_two_gpus_match_one_gpu(tmp_path):
+@pytest.mark.parametrize("kind", ["gated_deltanet", "kda"])
+def test_pieces_two_gpus_match_one_gpu(tmp_path, kind):
     """Documents cut into 512-token pieces joined by affine maps, over two ranks, against the plain one-GPU call."""
     import torch.multiprocessing as mp
 
     from tests._util import run_cuda
 
     world = 2
-    mp.spawn(_cp_worker, args=(world, _free_port(), str(tmp_path), 512), nprocs=world, join=True)
-    case = make_case("gated_deltanet", B=1, T=4096, H=4, K=128, V=128, seed=50, h0=True, docs="uniform",
-                     doc_range=(300, 3000))
-    want = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="bfloat16")
+    mp.spawn(_cp_worker, args=(world, _free_port(), str(tmp_path), 512, kind), nprocs=world, join=True)
+    case = make_case(kind, B=1, T=4096, H=4, K=128, V=128, seed=50, h0=True, docs="uniform",
+                     doc_range=(300, 3000), gates="kda_baseline" if kind == "kda" else "plain")
+    want = run_cuda(kind, case, scale=case["meta"]["scale"], dtype="bfloat16")
     parts = [dict(np.load(tmp_path / f"rank{r}.npz")) for r in range(world)]
     for key in ("o", "dq", "dk", "dv", "dg", "dbeta"):
         got = np.concatenate([p[key] for p in parts], axis=1)
