@@ -126,14 +126,14 @@ __device__ __forceinline__ float col_reduce(float x) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p) {
-  constexpr int LDK = KD + 8, LDC = 72, NT = 256;
+__global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p) {
+  constexpr int LDK = KD + 8, LDC = 72, NT = 512;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
   if (m.len == 0) return;
   const int hk = h / (p.H / p.Hk);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int rw = warp & 3, hf = warp >> 2;  // row block of 16 tokens; column half (of 64 x 64 tiles and of the K channels)
+  const int rw = warp & 3, cq = warp >> 2;  // row block of 16 tokens; column quarter (of 64 x 64 tiles and of the K channels)
   const int r0 = 16 * rw;
   const long slot = (long)c * p.H + h;
 
@@ -152,8 +152,8 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
   float* part = dGt + 64 * KD;             // [4][KD] column sums per row block (also scratch of the gate cumsum)
   float* betas = part + 4 * KD;            // [64]
   float* Glast = betas + 64;               // [KD]
-  float* dbrow = Glast + KD;               // [2][64] per column half
-  float* dbcol = dbrow + 128;              // [64]
+  float* dbrow = Glast + KD;               // [4][64] per column quarter
+  float* dbcol = dbrow + 256;              // [64]
   int* run = reinterpret_cast<int*>(dbcol + 64);  // [64]
 
   const long kstride = (long)p.Hk * KD;
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     betas[tid] = p.gates[slot * 128 + 64 + tid];
     run[tid] = p.runs[(long)c * 64 + tid];
   }
-  // ---- cumulative log decay per channel: two threads per channel, 32 tokens each, then the second half is offset
+  // ---- cumulative log decay per channel: four threads per channel, 16 tokens each, then offset by the totals before
   int unbounded;
   {
     const int ch = tid & (KD - 1), hh = tid >> 7;
@@ -175,21 +175,21 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     const long gstride = (long)p.H * KD;
     float acc = 0.f;
 #pragma unroll 8
-    for (int i = 32 * hh; i < 32 * hh + 32; ++i) {
+    for (int i = 16 * hh; i < 16 * hh + 16; ++i) {
       if (i < m.len) acc += gp[i * gstride];
       Gm[i * KD + ch] = acc;
     }
-    if (hh == 0) part[ch] = acc;
+    part[hh * KD + ch] = acc;
     cp_async_wait<0>();
     __syncthreads();
-    float total = acc;
-    if (hh == 1) {
-      const float off = part[ch];
-      for (int i = 32; i < 64; ++i) Gm[i * KD + ch] += off;
-      total = acc + off;
-      Glast[ch] = total;
+    float off = 0.f;
+    for (int b = 0; b < hh; ++b) off += part[b * KD + ch];
+    if (hh > 0) {
+      for (int i = 16 * hh; i < 16 * hh + 16; ++i) Gm[i * KD + ch] += off;
     }
-    unbounded = __syncthreads_or(hh == 1 && !(fabsf(total) <= kBoundedLog));
+    const float total = acc + off;
+    if (hh == 3) Glast[ch] = total;
+    unbounded = __syncthreads_or(hh == 3 && !(fabsf(total) <= kBoundedLog));
   }
   const bool entering = !(m.flags & 1);
   const int run_last = run[63];
@@ -210,27 +210,27 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     dbcol[j] = s;
   }
   __syncthreads();
-  // ---- dA = -strict(T^T (dT T^T)): this warp's 16 rows x 32 columns
+  // ---- dA = -strict(T^T (dT T^T)): this warp's 16 rows x 16 columns
   {
-    float accM[4][4], accA[4][4];
+    float accM[2][4], accA[2][4];
     zero_acc(accM);
-    warp_gemm<T, 4, 4, A_ROW, B_NK>(accM, Xd + r0 * LDC, LDC, Tt + 32 * hf * LDC, LDC, lane);
+    warp_gemm<T, 2, 4, A_ROW, B_NK>(accM, Xd + r0 * LDC, LDC, Tt + 16 * cq * LDC, LDC, lane);
     __syncthreads();  // dAg (Xm) and dT (Xd) have been read by every warp
-    store_acc<T, 4>(Xm, LDC, r0, 32 * hf, accM, lane);
+    store_acc<T, 2>(Xm, LDC, r0, 16 * cq, accM, lane);
     __syncthreads();
     zero_acc(accA);
-    warp_gemm<T, 4, 4, A_COL, B_KN>(accA, Tt + r0, LDC, Xm + 32 * hf, LDC, lane);
+    warp_gemm<T, 2, 4, A_COL, B_KN>(accA, Tt + r0, LDC, Xm + 16 * cq, LDC, lane);
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int i = r0 + g + ((e >> 1) << 3), j = 32 * hf + nt * 8 + 2 * t + (e & 1);
+        const int i = r0 + g + ((e >> 1) << 3), j = 16 * cq + nt * 8 + 2 * t + (e & 1);
         accA[nt][e] = (j < i && run[i] == run[j]) ? -accA[nt][e] : 0.f;
       }
     }
     __syncthreads();  // M1 (Xm) has been read by every warp
-    store_acc<T, 4>(Xm, LDC, r0, 32 * hf, accA, lane);                                      // dA
-    store_acc<T, 4>(Xd, LDC, r0, 32 * hf, accA, lane, betas[r0 + g], betas[r0 + g + 8]);    // dAkk = beta_i dA
+    store_acc<T, 2>(Xm, LDC, r0, 16 * cq, accA, lane);                                      // dA
+    store_acc<T, 2>(Xd, LDC, r0, 16 * cq, accA, lane, betas[r0 + g], betas[r0 + g + 8]);    // dAkk = beta_i dA
   }
   const long tokbase = ((long)m.tok0 * p.H + h) * KD;
   const long tstride = (long)p.H * KD;
@@ -272,17 +272,17 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     const bool cin0 = entering && run[i0] == 0, cin1 = entering && run[i1] == 0;
     const bool tl0 = i0 < m.len && run[i0] == run_last, tl1 = i1 < m.len && run[i1] == run_last;
     const float b0 = betas[i0], b1 = betas[i1];
-    const int kc0 = 64 * hf;  // this warp's 64 key channels
-    float accU[8][4], accQ[8][4], accW[8][4];
+    const int kc0 = 32 * cq;  // this warp's 32 key channels
+    float accU[4][4], accQ[4][4], accW[4][4];
     zero_acc(accU);
     zero_acc(accQ);
     zero_acc(accW);
-    warp_gemm<T, 8, 4, A_ROW, B_KN>(accU, Xm + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dA k~
-    warp_gemm<T, 8, 4, A_ROW, B_KN>(accQ, Xp + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dP k~
-    warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xp + r0, LDC, tqh + kc0, LDK, lane);        // dP^T q^
-    warp_gemm<T, 8, 4, A_COL, B_KN>(accW, Xd + r0, LDC, tkh + kc0, LDK, lane);        // + dAkk^T k^
+    warp_gemm<T, 4, 4, A_ROW, B_KN>(accU, Xm + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dA k~
+    warp_gemm<T, 4, 4, A_ROW, B_KN>(accQ, Xp + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dP k~
+    warp_gemm<T, 4, 4, A_COL, B_KN>(accW, Xp + r0, LDC, tqh + kc0, LDK, lane);        // dP^T q^
+    warp_gemm<T, 4, 4, A_COL, B_KN>(accW, Xd + r0, LDC, tkh + kc0, LDK, lane);        // + dAkk^T k^
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < 4; ++nt) {
       float colsum[2] = {0.f, 0.f};
 #pragma unroll
       for (int hi = 0; hi < 2; ++hi) {
@@ -335,8 +335,8 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     db1 += __shfl_xor_sync(0xffffffffu, db1, 1);
     db1 += __shfl_xor_sync(0xffffffffu, db1, 2);
     if (t == 0) {
-      dbrow[hf * 64 + i0] = db0;
-      dbrow[hf * 64 + i1] = db1;
+      dbrow[cq * 64 + i0] = db0;
+      dbrow[cq * 64 + i1] = db1;
     }
   } else {
     // ---- exact path: thread = key channel (threads 0..127), fp32 with the true exponent of every pair of one
@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     __syncthreads();
     if (tid < 64) {
       dbrow[tid] = part[tid] + part[KD + tid] + part[2 * KD + tid] + part[3 * KD + tid];
-      dbrow[64 + tid] = 0.f;
+      dbrow[64 + tid] = dbrow[128 + tid] = dbrow[192 + tid] = 0.f;
     }
     float colsum = 0.f;
     if (active) {
@@ -417,7 +417,7 @@ __global__ void __launch_bounds__(256, 1) kda_intra_grads_kernel(KdaGradParams p
     }
   } else if (tid - KD < m.len) {
     const int i = tid - KD;
-    p.dbeta[(long)(m.tok0 + i) * p.H + h] = dbrow[i] + dbrow[64 + i] + dbcol[i];
+    p.dbeta[(long)(m.tok0 + i) * p.H + h] = dbrow[i] + dbrow[64 + i] + dbrow[128 + i] + dbrow[192 + i] + dbcol[i];
   }
 }
 
@@ -425,7 +425,7 @@ template <typename T>
 int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
   const size_t smem_a = (2 * 64 * (VD + 8) + 2 * VD * (KD + 8) + 3 * VD * 72) * sizeof(T) + 2 * KD * sizeof(float);
   const size_t smem_b = (5 * 64 * (KD + 8) + 4 * 64 * 72) * sizeof(T) +
-                        (2 * 64 * KD + 4 * KD + 64 + KD + 128 + 64) * sizeof(float) + 64 * sizeof(int);
+                        (2 * 64 * KD + 4 * KD + 64 + KD + 256 + 64) * sizeof(float) + 64 * sizeof(int);
   auto* ka = kda_state_grads_kernel<T>;
   auto* kb = kda_intra_grads_kernel<T>;
   JLA_CUDA_OK(cudaFuncSetAttribute(ka, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
@@ -437,7 +437,7 @@ int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
   JLA_LAUNCH_OK();
   {
     ProfScope ps(kProfKdaIntra, s);
-    kb<<<blocks, 256, smem_b, s>>>(gp);
+    kb<<<blocks, 512, smem_b, s>>>(gp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
