@@ -67,6 +67,9 @@ KDA_SPECS = {
                                  l2norm=True),
     "kda_extreme": dict(B=1, T=160, H=2, K=32, V=32, gate="extreme", h0=True),
     "kda_grouped": dict(B=1, T=100, H=1, HV=2, K=32, V=32, gate="plain", h0=True),
+    # the head size of the chunked tensor-core kernels (K = V = 128): packed rows with partial chunks, and extreme gates
+    "kda_d128_packed_h0": dict(B=1, T=200, H=2, K=128, V=128, gate="plain", cu=(0, 64, 65, 192, 200), h0=True),
+    "kda_d128_extreme": dict(B=1, T=160, H=2, K=128, V=128, gate="extreme", h0=True),
 }
 
 

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from oracle.cases import baseline_config, make_case, rel_l2
-from tests._util import compare, run_cuda, run_oracle
+from tests._util import compare, load_golden, run_cuda, run_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -125,3 +125,17 @@ def test_config3_full_size_matches_the_token_scan():
     o_ref, ht_ref = _forward(case, h0=False, precision="highest")
     assert np.isfinite(o).all()
     assert rel_l2(o, o_ref) <= 1e-2 and rel_l2(ht, ht_ref) <= 1e-2, (rel_l2(o, o_ref), rel_l2(ht, ht_ref))
+
+
+@pytest.mark.parametrize("name", ["kda_d128_packed_h0", "kda_d128_extreme"])
+def test_chunked_forward_against_the_reference_float64_oracle(name):
+    """The committed outputs of the reference's own float64 KDA oracle (benchmarks/diff_vector_gate.py:209-250, run on
+    bf16-representable inputs; tests/golden/make_golden.py) at the head size of the chunked kernels: packed rows with
+    partial chunks and an initial state, and gates down to e^-1000 per token."""
+    meta, ins, want = load_golden(name)
+    if "cu" in meta:  # the reference's KDA harness turns cu into one row of segment ids
+        cu = np.asarray(meta["cu"])
+        ins["seg"] = np.searchsorted(cu[1:], np.arange(meta["T"]), side="right")[None].astype(np.int32)
+    got = run_cuda("kda", ins, scale=meta["scale"], dtype="bfloat16", grads=False)
+    assert np.isfinite(got["o"]).all() and np.isfinite(got["ht"]).all()
+    compare(got, {"o": want["o"], "ht": want["final"]}, 1e-2, name)

@@ -16,7 +16,8 @@ TOL = 1e-5
 
 SCALAR = ["gdn_dense_h0", "gdn_docs_gqa", "gdn_extreme", "gdn_l2norm", "gdn_beta2", "gdn_f32", "dn_docs",
           "dn_l2norm_dense", "sgla_docs_gqa", "sgla_extreme"]
-KDA = ["kda_dense_h0", "kda_packed", "kda_packed_h0_l2norm", "kda_extreme", "kda_grouped"]
+KDA = ["kda_dense_h0", "kda_packed", "kda_packed_h0_l2norm", "kda_extreme", "kda_grouped", "kda_d128_packed_h0",
+       "kda_d128_extreme"]
 
 
 @pytest.mark.parametrize("name", SCALAR)
