@@ -284,6 +284,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       float colsum[2] = {0.f, 0.f};
+      const float eR[2] = {__expf(0.5f * Glast[kc0 + nt * 8 + 2 * t]), __expf(0.5f * Glast[kc0 + nt * 8 + 2 * t + 1])};
 #pragma unroll
       for (int hi = 0; hi < 2; ++hi) {
         const int i = hi ? i1 : i0, col = kc0 + nt * 8 + 2 * t;
@@ -301,7 +302,8 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
           const float Gi = Gm[i * KD + col + x], Gl = Glast[col + x];
           const float d = Gi - 0.5f * Gl;
           const float eu = __expf(d), en = __expf(-d);
-          const float eg = cin ? __expf(Gi) : 0.f, ew = tail ? __expf(Gl - Gi) : 0.f;
+          // exp(G_i) = exp(d) exp(R) and exp(G_63 - G_i) = exp(-d) exp(R) with R = G_63 / 2 (|R| <= 30 on this path)
+          const float eg = cin ? eu * eR[x] : 0.f, ew = tail ? en * eR[x] : 0.f;
           const float kh = x ? kh2.y : kh2.x;
           if (hi) db1 += kh * accU[nt][e]; else db0 += kh * accU[nt][e];
           const float dq = accQ[nt][e] * eu + (x ? qs2.y : qs2.x) * eg;
