@@ -102,61 +102,50 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
   const bool entering = !(m.flags & 1);
   const int run_last = run[63];
 
-  // ---- the state-side operands and the decay vector
-  {
-    T* qs = static_cast<T*>(p.qs) + slot * 64 * KD;
-    T* kr = static_cast<T*>(p.kr) + slot * 64 * KD;
-    T* kw = static_cast<T*>(p.kw) + slot * 64 * KD;
+  T* qs = static_cast<T*>(p.qs) + slot * 64 * KD;
+  T* kr = static_cast<T*>(p.kr) + slot * 64 * KD;
+  T* kw = static_cast<T*>(p.kw) + slot * 64 * KD;
+  if (tid < KD) p.dvec[slot * KD + tid] = (entering && run_last == 0) ? __expf(Glast[tid]) : 0.f;
+
+  if (!unbounded) {
+    // ---- one pass over the tiles: the state-side operands to global memory and the factored operands in place.
+    // With d = G - R, R = G_63 / 2 (|d|, |R| <= kBoundedLog / 2 here): exp(G) = exp(d) exp(R) and
+    // exp(G_63 - G) = exp(-d) exp(R), so two exponentials per element serve all five operands.
+    float* eRs = M + KD;  // exp(R) per channel (scratch of the inverse, free until then)
+    if (tid < KD) eRs[tid] = __expf(0.5f * Glast[tid]);
+    __syncthreads();
     for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
       const int i = idx >> 4, c8 = (idx & 15) * 8;
       const bool cin = entering && run[i] == 0;
       const bool tail = i < m.len && run[i] == run_last;
-      const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
-      const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
-      const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
-      const uint32_t* kwd = reinterpret_cast<const uint32_t*>(&kv);
-      uint4 oq, or_, ow;
+      uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
+      uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      uint4 bv, oq, or_, ow;
+      uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
+      uint32_t* kwd = reinterpret_cast<uint32_t*>(&kv);
+      uint32_t* bw = reinterpret_cast<uint32_t*>(&bv);
       uint32_t* oqw = reinterpret_cast<uint32_t*>(&oq);
       uint32_t* orw = reinterpret_cast<uint32_t*>(&or_);
       uint32_t* oww = reinterpret_cast<uint32_t*>(&ow);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]);
-        const float g0 = Gm[i * KD + c8 + 2 * e], g1 = Gm[i * KD + c8 + 2 * e + 1];
-        const float e0 = cin ? __expf(g0) : 0.f, e1 = cin ? __expf(g1) : 0.f;
-        const float w0 = tail ? __expf(Glast[c8 + 2 * e] - g0) : 0.f, w1 = tail ? __expf(Glast[c8 + 2 * e + 1] - g1) : 0.f;
-        oqw[e] = pack2<T>(qf.x * e0, qf.y * e1);
-        orw[e] = pack2<T>(kf.x * e0, kf.y * e1);
-        oww[e] = pack2<T>(kf.x * w0, kf.y * w1);
-      }
-      *reinterpret_cast<uint4*>(qs + i * KD + c8) = oq;
-      *reinterpret_cast<uint4*>(kr + i * KD + c8) = or_;
-      *reinterpret_cast<uint4*>(kw + i * KD + c8) = ow;
-    }
-    if (tid < KD) p.dvec[slot * KD + tid] = (entering && run_last == 0) ? __expf(Glast[tid]) : 0.f;
-  }
-
-  if (!unbounded) {
-    // ---- factored operands in place, then both score matrices on the tensor cores
-    __syncthreads();  // the raw tiles have been read
-    for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
-      const int i = idx >> 4, c8 = (idx & 15) * 8;
-      uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
-      uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
-      uint4 bv;
-      uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
-      uint32_t* kwd = reinterpret_cast<uint32_t*>(&kv);
-      uint32_t* bw = reinterpret_cast<uint32_t*>(&bv);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]);
         const float d0 = Gm[i * KD + c8 + 2 * e] - 0.5f * Glast[c8 + 2 * e];
         const float d1 = Gm[i * KD + c8 + 2 * e + 1] - 0.5f * Glast[c8 + 2 * e + 1];
         const float u0 = __expf(d0), u1 = __expf(d1), n0 = __expf(-d0), n1 = __expf(-d1);
+        const float r0 = eRs[c8 + 2 * e], r1 = eRs[c8 + 2 * e + 1];
+        const float e0 = cin ? u0 * r0 : 0.f, e1 = cin ? u1 * r1 : 0.f;
+        const float w0 = tail ? n0 * r0 : 0.f, w1 = tail ? n1 * r1 : 0.f;
+        oqw[e] = pack2<T>(qf.x * e0, qf.y * e1);
+        orw[e] = pack2<T>(kf.x * e0, kf.y * e1);
+        oww[e] = pack2<T>(kf.x * w0, kf.y * w1);
         qw[e] = pack2<T>(qf.x * u0, qf.y * u1);
         kwd[e] = pack2<T>(kf.x * u0, kf.y * u1);
         bw[e] = pack2<T>(kf.x * n0, kf.y * n1);
       }
+      *reinterpret_cast<uint4*>(qs + i * KD + c8) = oq;
+      *reinterpret_cast<uint4*>(kr + i * KD + c8) = or_;
+      *reinterpret_cast<uint4*>(kw + i * KD + c8) = ow;
       *reinterpret_cast<uint4*>(tq + i * LDK + c8) = qv;
       *reinterpret_cast<uint4*>(tk + i * LDK + c8) = kv;
       *reinterpret_cast<uint4*>(tb + i * LDK + c8) = bv;
@@ -191,7 +180,34 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
       }
     }
   } else {
-    // ---- exact path: every pair (i, j <= i) of one document, fp32 with the true exponent per channel
+    // ---- exact path. The state-side operands with their own (always non-positive) exponents:
+    for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
+      const int i = idx >> 4, c8 = (idx & 15) * 8;
+      const bool cin = entering && run[i] == 0;
+      const bool tail = i < m.len && run[i] == run_last;
+      const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
+      const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
+      const uint32_t* kwd = reinterpret_cast<const uint32_t*>(&kv);
+      uint4 oq, or_, ow;
+      uint32_t* oqw = reinterpret_cast<uint32_t*>(&oq);
+      uint32_t* orw = reinterpret_cast<uint32_t*>(&or_);
+      uint32_t* oww = reinterpret_cast<uint32_t*>(&ow);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]);
+        const float g0 = Gm[i * KD + c8 + 2 * e], g1 = Gm[i * KD + c8 + 2 * e + 1];
+        const float e0 = cin ? __expf(g0) : 0.f, e1 = cin ? __expf(g1) : 0.f;
+        const float w0 = tail ? __expf(Glast[c8 + 2 * e] - g0) : 0.f, w1 = tail ? __expf(Glast[c8 + 2 * e + 1] - g1) : 0.f;
+        oqw[e] = pack2<T>(qf.x * e0, qf.y * e1);
+        orw[e] = pack2<T>(kf.x * e0, kf.y * e1);
+        oww[e] = pack2<T>(kf.x * w0, kf.y * w1);
+      }
+      *reinterpret_cast<uint4*>(qs + i * KD + c8) = oq;
+      *reinterpret_cast<uint4*>(kr + i * KD + c8) = or_;
+      *reinterpret_cast<uint4*>(kw + i * KD + c8) = ow;
+    }
+    // every pair (i, j <= i) of one document, fp32 with the true exponent per channel
     __syncthreads();
     for (int idx = tid; idx < 64 * 64; idx += NT) {
       const int i = idx >> 6, j = idx & 63;
