@@ -51,7 +51,19 @@ static ChunkedCtx make_ctx(const jla_problem& p, char* res) {
   return c;
 }
 
+// A call without tokens launches no chunk kernel: the state passes through unchanged.
+static int copy_state(float* dst, const float* src, const jla_problem& p, cudaStream_t stream) {
+  if (!dst) return JLA_OK;
+  const size_t rows = p.num_seqs > 0 ? p.num_seqs : p.B;
+  const size_t bytes = rows * p.H * p.K * p.V * sizeof(float);
+  if (bytes == 0) return JLA_OK;
+  if (src) JLA_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream));
+  else JLA_CUDA_OK(cudaMemsetAsync(dst, 0, bytes, stream));
+  return JLA_OK;
+}
+
 int chunked_fwd(const jla_problem& p, const jla_fwd_io& io, cudaStream_t stream) {
+  if ((long)p.B * p.T == 0) return copy_state(io.final_state, p.h0, p, stream);
   const Plan pl = make_plan(p);
   char* res;
   if (pl.save) {
@@ -78,6 +90,7 @@ int chunked_fwd(const jla_problem& p, const jla_fwd_io& io, cudaStream_t stream)
 }
 
 int chunked_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t stream) {
+  if ((long)p.B * p.T == 0) return copy_state(io.dh0, io.d_final, p, stream);
   jla_problem ps = p;
   ps.flags |= JLA_FLAG_SAVE_RESIDUALS;
   const Plan pl = make_plan(ps);

@@ -450,6 +450,7 @@ int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
 int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s) {
   const jla_problem& p = c.p;
   const Plan& pl = c.plan;
+  if (pl.nc == 0) return JLA_OK;  // no tokens: nothing to differentiate through
   if (p.dtype != JLA_DTYPE_BF16 || p.K != KD || p.V != VD) {
     set_error("chunked KDA backward: bf16 tensors with K = V = 128 only");
     return JLA_ERR_UNSUPPORTED;

@@ -197,3 +197,23 @@ def test_shared_prep_and_state_only_backward_match_the_plain_calls(kind):
     with final_state_only():  # JLA_FLAG_STATE_ONLY: the outputs are skipped, the state pass is the same
         _, f1o, _ = run(t["v"], h0, False)
     assert torch.equal(f1o, f1)
+
+
+@pytest.mark.parametrize("kind", ["gated_deltanet", "kda"])
+def test_a_call_without_tokens_passes_the_state_through(kind):
+    """T = 0 (an empty shard): no chunk kernel runs; the final state is the initial state and its gradient is the
+    upstream gradient of the final state."""
+    from jax_linear_attention_b200 import ops
+
+    dev = torch.device("cuda")
+    B, H, K, V = 2, 2, 128, 128
+    q = torch.zeros(B, 0, H, K, device=dev, dtype=torch.bfloat16)
+    v = torch.zeros(B, 0, H, V, device=dev, dtype=torch.bfloat16)
+    g = torch.zeros((B, 0, H, K) if kind == "kda" else (B, 0, H), device=dev)
+    beta = torch.zeros(B, 0, H, device=dev)
+    h0 = torch.randn(B, H, K, V, device=dev, requires_grad=True)
+    o, f = ops.linear_attention(kind, q, q, v, g=g, beta=beta, initial_state=h0, output_final_state=True)
+    assert o.shape == v.shape and torch.equal(f, h0.detach())
+    dht = torch.randn_like(f)
+    (dh0,) = torch.autograd.grad([f], [h0], [dht])
+    assert torch.equal(dh0, dht)
