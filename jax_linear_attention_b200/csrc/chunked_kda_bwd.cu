@@ -65,15 +65,17 @@ __global__ void __launch_bounds__(256, 1) kda_state_grads_kernel(KdaGradParams p
   float* ddp = reinterpret_cast<float*>(wS + VD * LDC);  // [2][KD]
 
   const long vstride = (long)p.H * VD;
+  // two load groups: the products of the first run while the second is still in flight
   load_tile_async<T, 64, VD>(dOs, LDV, static_cast<const T*>(p.d_o) + ((long)m.tok0 * p.H + h) * VD, vstride, m.len, tid, 256);
   load_tile_async<T, 64, VD>(dWs, LDV, static_cast<const T*>(p.dw) + ((long)m.tok0 * p.H + h) * VD, vstride, m.len, tid, 256);
   load_tile_async<T, VD, KD>(hS, LDK, static_cast<const T*>(p.hT) + slot * VD * KD, KD, VD, tid, 256);
-  load_tile_async<T, VD, KD>(dhS, LDK, static_cast<const T*>(p.dhT) + slot * VD * KD, KD, VD, tid, 256);
   load_tile_async<T, VD, 64>(vnS, LDC, static_cast<const T*>(p.vnT) + slot * VD * 64, 64, VD, tid, 256);
+  cp_async_commit();
+  load_tile_async<T, VD, KD>(dhS, LDK, static_cast<const T*>(p.dhT) + slot * VD * KD, KD, VD, tid, 256);
   load_tile_async<T, VD, 64>(dvnS, LDC, static_cast<const T*>(p.dvnT) + slot * VD * 64, 64, VD, tid, 256);
   load_tile_async<T, VD, 64>(wS, LDC, static_cast<const T*>(p.wT) + slot * VD * 64, 64, VD, tid, 256);
   cp_async_commit();
-  cp_async_wait<0>();
+  cp_async_wait<1>();
   __syncthreads();
 
   auto store_f32 = [&](float* dst, const float (&acc)[8][4], float s) {  // [64][K] tile, this warp's 16 x 64 block
@@ -92,15 +94,23 @@ __global__ void __launch_bounds__(256, 1) kda_state_grads_kernel(KdaGradParams p
     zero_acc(acc);  // dKs = -dW S^T
     warp_gemm<T, 8, VD / 16, A_ROW, B_KN>(acc, dWs + r0 * LDV, LDV, hS + kc0, LDK, lane);
     store_f32(p.dks + slot * 64 * KD, acc, -1.f);
-    zero_acc(acc);  // dKu = Vn dS+^T
-    warp_gemm<T, 8, VD / 16, A_COL, B_KN>(acc, vnS + r0, LDC, dhS + kc0, LDK, lane);
-    store_f32(p.dku + slot * 64 * KD, acc, 1.f);
   }
   {
     float acc[4][4];
     zero_acc(acc);  // dP = scale dO Vn^T
     warp_gemm<T, 4, VD / 16, A_ROW, B_KN>(acc, dOs + r0 * LDV, LDV, vnS + cc0, LDC, lane);
     store_acc<T, 4>(static_cast<T*>(p.dp) + slot * 4096, 64, r0, cc0, acc, lane, p.scale, p.scale);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  {
+    float acc[8][4];
+    zero_acc(acc);  // dKu = Vn dS+^T
+    warp_gemm<T, 8, VD / 16, A_COL, B_KN>(acc, vnS + r0, LDC, dhS + kc0, LDK, lane);
+    store_f32(p.dku + slot * 64 * KD, acc, 1.f);
+  }
+  {
+    float acc[4][4];
     zero_acc(acc);  // dAg = dVn W^T
     warp_gemm<T, 4, VD / 16, A_COL, B_KN>(acc, dvnS + r0, LDC, wS + cc0, LDC, lane);
     store_acc<T, 4>(static_cast<T*>(p.dag) + slot * 4096, 64, r0, cc0, acc, lane);
