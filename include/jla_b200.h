@@ -152,7 +152,9 @@ int jla_linear_attention_bwd(const jla_problem* p, const jla_bwd_io* io, jla_str
  *   - The first call on a device looks up the array's device address (one cudaGetSymbolAddress, with that device
  *     current); make that first call before any stream capture begins.
  *   - All calls on a device share the array: calls that may overlap on the GPU (different streams) race on it.
- *     Keep them on one stream or order them with events. Nothing needs clearing between calls. */
+ *     Keep them on one stream or order them with events. Nothing needs clearing between calls.
+ *   - JLA_FLAG_SAVE_RESIDUALS and JLA_FLAG_PREP_DONE are rejected (JLA_ERR_BAD_ARGUMENT): the array belongs to the
+ *     library, so no caller can know that an earlier call's tables are still in it. */
 size_t jla_noalloc_scratch_limit(void);
 int jla_linear_attention_fwd_noalloc(const jla_problem* p, void* o, float* final_state, jla_stream_t stream);
 
@@ -248,6 +250,20 @@ int jla_profile_read(int kernel_id, double* total_ms, int* launches);
  * Shapes: (64,128,128), (64,64,64), (64,64,128), (128,128,64). No counterpart in the reference. */
 int jla_selftest_umma(int m, int n, int kd, int a_mn_major, int b_mn_major, const void* a, const void* b, float* c,
                       int* status, jla_stream_t stream);
+
+/* Failure status of the tensor-core kernels. Every wait inside them (on a TMA copy, an MMA completion or another
+ * warp role) is bounded: a wait that runs out makes the kernel return normally with a non-zero code in a status
+ * word that lives on the GPU (one word per GPU that loads the library), and the results of that launch are
+ * undefined. jla_device_status() waits for `stream`, copies the word of the CURRENT device to *out and clears it:
+ * 0 = every launch since the last query completed its waits; 1 = a chunk-gradient kernel, 2 = a forward state
+ * pass, 3 = a reverse state pass gave up; 9 = jla_selftest_bounded_wait. It blocks the host (diagnostic call; the
+ * compute entry points never do). No counterpart in the reference, whose Pallas kernels wait without a bound. */
+int jla_device_status(int* out, jla_stream_t stream);
+
+/* Diagnostics: launches one small CTA whose bounded wait on a barrier nobody arrives on gives up after
+ * `spin_limit` polls (1 .. 2^20), records status 9 and exits normally -- the path a lost arrival takes in the real
+ * kernels, exercised without a fault or a hang. No counterpart in the reference. */
+int jla_selftest_bounded_wait(uint32_t spin_limit, jla_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -76,8 +76,21 @@ def load() -> C.CDLL:
     lib.jla_linear_attention_fwd.argtypes = [C.POINTER(Problem), C.POINTER(FwdIO), C.c_void_p]
     lib.jla_linear_attention_bwd.restype = C.c_int
     lib.jla_linear_attention_bwd.argtypes = [C.POINTER(Problem), C.POINTER(BwdIO), C.c_void_p]
+    lib.jla_device_status.restype = C.c_int
+    lib.jla_device_status.argtypes = [C.POINTER(C.c_int), C.c_void_p]
+    lib.jla_selftest_bounded_wait.restype = C.c_int
+    lib.jla_selftest_bounded_wait.argtypes = [C.c_uint32, C.c_void_p]
     _lib = lib
     return lib
+
+
+def device_status(stream: int | None = None) -> int:
+    """Waits for ``stream`` (the default stream if None), returns the current device's status word and clears it:
+    0 unless a bounded wait inside a tensor-core kernel gave up since the last query (then that launch's results
+    are undefined; the codes are listed at ``jla_device_status`` in the header)."""
+    out = C.c_int(0)
+    check(load().jla_device_status(C.byref(out), C.c_void_p(stream)), "device status")
+    return out.value
 
 
 def unsupported_reason(problem: Problem) -> str | None:

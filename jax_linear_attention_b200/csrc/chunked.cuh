@@ -148,6 +148,6 @@ int l2norm_fwd(const void* x, void* y, int dtype, long rows, int K, cudaStream_t
 int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s);
 int launch_sg_bwd_state_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s);
 int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, bool direct, cudaStream_t s);
-int read_tc_status(int* out);  // non-zero once a bounded tensor-core wait has given up
+int* tc_status_ptr();  // status.cu: the current device's status word (set non-zero when a bounded wait gave up)
 
 }  // namespace jla

@@ -465,8 +465,6 @@ int launch_one(const BwdTcMaps& maps, const BwdTcParams& bp, int blocks, cudaStr
 
 }  // namespace
 
-int* tc_status_ptr();
-
 // The reverse state pass of launch_sg_bwd for K = V = 128; dh and dVn are written transposed.
 int launch_sg_bwd_state_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s) {
   const jla_problem& p = c.p;

@@ -547,8 +547,6 @@ int launch_one(const FwdTcMaps& maps, const FwdTcParams& fp, int blocks, cudaStr
 
 }  // namespace
 
-int* tc_status_ptr();  // chunked_grads_tc.cu
-
 // Same contract as launch_sg_fwd (chunked_fwd.cu) for K = V = 128; the residuals h and Vn are written transposed.
 int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) {
   const jla_problem& p = c.p;

@@ -25,8 +25,6 @@
 
 namespace jla {
 
-__device__ int g_tc_status = 0;  // set to a non-zero code when a bounded wait gave up
-
 namespace {
 
 using umma::swz_tile;
@@ -46,6 +44,7 @@ struct GradParams {
   int H, Hk;
   float scale;
   int nitems;  // chunk slots x heads
+  int* status;  // device status word: set non-zero when a bounded wait gave up
 };
 
 struct GradMaps {
@@ -362,7 +361,7 @@ sg_grads_q_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   if (!ok) {  // let requested copies land before the shared memory goes away (bounded waits)
     if (x_inflight) umma::mbar_wait(bars + LX, 0), umma::mbar_wait(bars + LX, 1);
     if (y_inflight) umma::mbar_wait(bars + LY, 0), umma::mbar_wait(bars + LY, 1);
-    if (tid == 0) atomicExch(&g_tc_status, 1);
+    if (tid == 0) atomicExch(p.status, 1);
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -783,7 +782,7 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
       if (!k_inflight && tid == 0) load_k(next_live(item + gridDim.x));  // complete the byte count of the phase
       umma::mbar_wait(bars + L0, 0), umma::mbar_wait(bars + L0, 1);
     }
-    if (tid == 0) atomicExch(&g_tc_status, 1);
+    if (tid == 0) atomicExch(p.status, 1);
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -855,29 +854,13 @@ int launch_chunk_grads_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scrat
   gp.Hk = p.Hk;
   gp.scale = p.scale;
   gp.nitems = pl.nc * p.H;
+  gp.status = tc_status_ptr();
+  if (!gp.status) return JLA_ERR_CUDA;
   const int blocks = pl.nc * p.H;
   if (p.dtype == JLA_DTYPE_BF16) {
     return pl.delta ? launch_pair<__nv_bfloat16, true>(maps, gp, blocks, s) : launch_pair<__nv_bfloat16, false>(maps, gp, blocks, s);
   }
   return pl.delta ? launch_pair<__half, true>(maps, gp, blocks, s) : launch_pair<__half, false>(maps, gp, blocks, s);
-}
-
-int* tc_status_ptr() {
-  static int* ptr = nullptr;
-  if (!ptr) {
-    void* q = nullptr;
-    if (cudaGetSymbolAddress(&q, g_tc_status) != cudaSuccess) return nullptr;
-    ptr = static_cast<int*>(q);
-  }
-  return ptr;
-}
-
-int read_tc_status(int* out) {
-  int v = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
-  if (e != cudaSuccess) return JLA_ERR_CUDA;
-  *out = v;
-  return JLA_OK;
 }
 
 }  // namespace jla

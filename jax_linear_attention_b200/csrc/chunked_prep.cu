@@ -28,12 +28,18 @@ __global__ void build_tables_kernel(Rows rows, int nc, ChunkMeta* meta, int2* ro
     }
     return;
   }
+  // cu_seqlens is device data nobody has looked at: a table that is not monotonic, leaves [0, T] or would need more
+  // slots than the buffers hold must not send any later kernel to an out-of-range token. Such a row is treated as
+  // empty (its tokens are skipped); a well-formed table takes none of these branches.
+  auto row_range = [&](int r, int& tok0, int& len) { rows.range(r, tok0, len); };  // clamps to [0, B * T]
   __shared__ int total;
   if (tid == 0) {
     int acc = 0;
     for (int r = 0; r < nrows; ++r) {
-      const int len = rows.cu[r + 1] - rows.cu[r];
-      const int cnt = (len + kChunk - 1) / kChunk;
+      int tok0, len;
+      row_range(r, tok0, len);
+      int cnt = (len + kChunk - 1) / kChunk;
+      if (acc + cnt > nc) cnt = nc - acc;  // never more slots than the buffers were sized for
       row_chunks[r] = make_int2(acc, cnt);
       acc += cnt;
     }
@@ -43,7 +49,8 @@ __global__ void build_tables_kernel(Rows rows, int nc, ChunkMeta* meta, int2* ro
   __syncthreads();
   for (int r = tid; r < nrows; r += nt) {
     const int2 rc = row_chunks[r];
-    const int tok0 = rows.cu[r], len = rows.cu[r + 1] - tok0;
+    int tok0, len;
+    row_range(r, tok0, len);
     for (int i = 0; i < rc.y; ++i) {
       ChunkMeta m;
       m.tok0 = tok0 + i * kChunk;

@@ -36,9 +36,11 @@ struct Rows {
 
   __host__ __device__ int count() const { return cu ? num_seqs : B; }
   __device__ __forceinline__ void range(int r, int& tok0, int& len) const {
-    if (cu) {
-      tok0 = cu[r];
-      len = cu[r + 1] - tok0;
+    if (cu) {  // device data: a range that is not inside [0, B * T] counts as an empty row, never as an address
+      const int a = cu[r], b = cu[r + 1];
+      const bool good = a >= 0 && b >= a && b <= B * T;
+      tok0 = good ? a : 0;
+      len = good ? b - a : 0;
     } else {
       tok0 = r * T;
       len = T;

@@ -65,6 +65,11 @@ int jla_linear_attention_fwd_noalloc(const jla_problem* p, void* o, float* final
     set_error("the no-allocation entry point runs the forward only: clear JLA_FLAG_SAVE_RESIDUALS");
     return JLA_ERR_BAD_ARGUMENT;
   }
+  if (p->flags & JLA_FLAG_PREP_DONE) {
+    set_error("the no-allocation entry point shares its scratch with every other call on the device: "
+              "JLA_FLAG_PREP_DONE cannot be honoured, clear it");
+    return JLA_ERR_BAD_ARGUMENT;
+  }
   jla_fwd_io io{};
   io.o = o;
   io.final_state = final_state;

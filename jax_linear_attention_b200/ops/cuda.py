@@ -183,17 +183,20 @@ class _LinearAttention(torch.autograd.Function):
         res_bytes = lib.jla_residual_bytes(C.byref(p)) if needs_grad else 0
         share = _PassOptions.share
         if share is not None:  # one residual-layout buffer for a run of calls; the first one fills its tables
-            key = (k.data_ptr(), _ptr(g), _ptr(beta), _ptr(seg), _ptr(cu), q.data_ptr() if cfg["l2norm"] else 0,
-                   tuple(q.shape), tuple(v.shape[2:3]), q.dtype, cfg["kind"], cfg["l2norm"], cfg["precision"])
+            # identity and version of the tensors the CALLER passed (not of the float32 / int32 / contiguous copies
+            # made on the way here, whose addresses can be reused by the allocator inside one shared_prep block)
+            key = (cfg["prep_identity"], tuple(q.shape), tuple(v.shape[2:3]), q.dtype, cfg["kind"], cfg["l2norm"],
+                   cfg["precision"])
             p.flags = flags | _lib.FLAG_SAVE_RESIDUALS
             full = lib.jla_residual_bytes(C.byref(p))
             as_residuals = needs_grad and full > 0
-            if full == 0:  # a forward that keeps no residuals (KDA): the buffer is its scratch
+            if full == 0:  # a forward that keeps no residuals (KDA with the token-scan backward): the buffer is its scratch
                 full = lib.jla_fwd_scratch_bytes(C.byref(p))
             if share["key"] == key and share["buffer"] is not None and share["buffer"].numel() >= full:
                 flags |= _lib.FLAG_PREP_DONE
             else:
                 share["key"], share["buffer"] = key, torch.empty(full, dtype=torch.uint8, device=dev)
+                share["keep"] = cfg["prep_owners"]  # the keyed objects stay alive, so their ids stay theirs
             p.flags = flags
             residuals = share["buffer"] if as_residuals else None
             scratch = None if as_residuals else share["buffer"]
@@ -213,6 +216,7 @@ class _LinearAttention(torch.autograd.Function):
         return o, final
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, d_o, d_final):
         lib = _lib.load()
         q, k, v, g, beta, h0, residuals = ctx.saved_tensors
@@ -266,8 +270,19 @@ def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_stat
     def i32(x):
         return None if x is None else torch.as_tensor(x).to(device=dev, dtype=torch.int32).contiguous()
 
+    if cu_seqlens is not None and not (isinstance(cu_seqlens, torch.Tensor) and cu_seqlens.is_cuda):
+        # a table that is still on the host is checked here (reference.py:170-203 takes it on trust); one that
+        # already lives on the device is clamped by the kernels instead (a bad row then counts as empty)
+        cu_host = torch.as_tensor(cu_seqlens).to(torch.int64).flatten()
+        if cu_host.numel() < 1 or int(cu_host[0]) != 0 or int(cu_host[-1]) != q.shape[1] or \
+                bool((cu_host[1:] < cu_host[:-1]).any()):
+            raise ValueError(f"cu_seqlens must start at 0, end at T = {q.shape[1]} and never decrease; got "
+                             f"{cu_host.tolist()[:8]}{'...' if cu_host.numel() > 8 else ''}")
     cfg = dict(kind=kind, scale=float(scale), l2norm=bool(use_qk_l2norm), precision=precision,
-               output_final_state=bool(output_final_state), cu_seqlens=i32(cu_seqlens), segment_ids=i32(segment_ids))
+               output_final_state=bool(output_final_state), cu_seqlens=i32(cu_seqlens), segment_ids=i32(segment_ids),
+               prep_owners=(k, g, beta, segment_ids, cu_seqlens, q if use_qk_l2norm else None),
+               prep_identity=tuple((id(x), getattr(x, "_version", 0)) for x in (k, g, beta, segment_ids, cu_seqlens,
+                                                                                q if use_qk_l2norm else None)))
     o, final = _LinearAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), f32(g), f32(beta),
                                       f32(initial_state), cfg)
     return o, (final if output_final_state else None)
@@ -304,6 +319,15 @@ def kda(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=
     return _run("kda", q, k, v, g, beta, scale=scale, initial_state=initial_state,
                 output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
                 use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision, sub_chunk=sub_chunk)
+
+
+def device_status(device=None) -> int:
+    """Synchronises ``device``'s current stream and returns (and clears) its failure status word: non-zero when a
+    bounded wait inside one of the tensor-core kernels ran out since the last query, in which case the outputs of
+    that call must be discarded. The reference's kernels have no such word (their waits are unbounded)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        return _lib.device_status(torch.cuda.current_stream(dev).cuda_stream)
 
 
 FUNCTIONS = {

@@ -2,8 +2,12 @@
 
 Follows ``src/jla/layers/linear_attention.py:84-86`` (``_mamba_gate``: ``-exp(A_log) * softplus(a + dt_bias)`` in
 float32, ``A_log`` broadcast per head) and ``:159-162`` (``_write_strength``: ``sigmoid``, doubled with
-``allow_neg_eigval``), in torch float64 so that autograd supplies the gradients. Parity: pinned by closed-form values
-(``tests/test_oracle.py``), the formulas having no free choices.
+``allow_neg_eigval``), in torch float64 so that autograd supplies the gradients. Parity of these two: pinned to the
+reference's float64 oracle, whose ``gate="softplus"`` branch applies the same activations in front of the KDA
+recurrence (``benchmarks/diff_vector_gate.py:215-225``; fixture ``tests/golden/kda_softplus.npz``, checked by
+``tests/test_oracle_golden.py``), and by closed-form values (``tests/test_oracle.py``). The norm and the short
+convolution below are restated from the layers' source and checked by closed forms only (parity unpinned: the
+reference's layers need JAX to run).
 """
 
 from __future__ import annotations

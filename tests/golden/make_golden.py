@@ -70,6 +70,9 @@ KDA_SPECS = {
     # the head size of the chunked tensor-core kernels (K = V = 128): packed rows with partial chunks, and extreme gates
     "kda_d128_packed_h0": dict(B=1, T=200, H=2, K=128, V=128, gate="plain", cu=(0, 64, 65, 192, 200), h0=True),
     "kda_d128_extreme": dict(B=1, T=160, H=2, K=128, V=128, gate="extreme", h0=True),
+    # the layers' softplus gate inside the oracle (g = -exp(A_log) softplus(raw + dt_bias), beta = sigmoid(raw)):
+    # pins the CPU restatement of the gate activations together with the recurrence (strong decays: A in (1, 16))
+    "kda_softplus": dict(B=1, T=120, H=2, K=32, V=32, gate="softplus", h0=True, l2norm=True),
 }
 
 
@@ -96,6 +99,14 @@ def draw_kda(c: dict, seed: int) -> dict:
         g[:, 64:96] = -30.0
         g[:, 100:103] = -1000.0
         g[:, 120:150] = 0.0
+    if c["gate"] == "softplus":  # raw gate activations and the gate's parameters; beta is drawn before its sigmoid
+        x["g"] = bf16(rng.standard_normal((B, T, H, K)))
+        x["A_log"] = np.log(rng.uniform(1.0, 16.0, (H,))).astype(np.float32)
+        x["dt_bias"] = (0.1 * rng.standard_normal((H * K,))).astype(np.float32)
+        x["beta"] = bf16(rng.standard_normal((B, T, H)))
+        if c.get("h0"):
+            x["h0"] = (0.5 * rng.standard_normal((B, H, K, V))).astype(np.float32)
+        return x
     x["g"] = g.astype(np.float32)
     sharp = 6.0 if c["gate"] == "extreme" else 1.0
     x["beta"] = (1.0 / (1.0 + np.exp(-sharp * rng.standard_normal((B, T, H))))).astype(np.float32)
@@ -108,6 +119,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of jla-org/jax-linear-attention")
     ap.add_argument("--out", default=HERE)
+    ap.add_argument("--only", nargs="*", default=None, help="fixture names to (re)write; the manifest keeps the others")
     args = ap.parse_args()
     bench_dir = os.path.join(args.reference, "benchmarks")
     sys.path.insert(0, bench_dir)
@@ -118,7 +130,13 @@ def main() -> None:
     tor.DEV = "cpu"  # shim 2 (module line 39)
 
     manifest = {}
+    manifest_path = os.path.join(args.out, "MANIFEST.json")
+    if args.only is not None and os.path.exists(manifest_path):
+        with open(manifest_path) as f:
+            manifest = json.load(f)
     for name, spec in SCALAR_SPECS.items():
+        if args.only is not None and name not in args.only:
+            continue
         case = gen.gen_case(name, spec)
         meta = json.loads(str(case["meta"]))
         res = tor.run_oracle(case, meta)
@@ -139,6 +157,8 @@ def main() -> None:
     sys.modules["jla.ops"].reference = sys.modules["jla.ops.reference"]
     dvg = importlib.import_module("diff_vector_gate")
     for i, (name, c) in enumerate(KDA_SPECS.items()):
+        if args.only is not None and name not in args.only:
+            continue
         x = draw_kda(c, seed=1000 + i)
         res = dvg.oracle64("kda", c, x)
         arrays = {f"in_{k}": v for k, v in x.items()}
@@ -149,7 +169,7 @@ def main() -> None:
         np.savez_compressed(path, **arrays)
         manifest[name] = dict(spec=c, source="diff_vector_gate.oracle64", bytes=os.path.getsize(path))
         print(name, manifest[name]["bytes"])
-    with open(os.path.join(args.out, "MANIFEST.json"), "w") as f:
+    with open(manifest_path, "w") as f:
         json.dump(manifest, f, indent=1, sort_keys=True, default=list)
 
 

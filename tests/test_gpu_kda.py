@@ -139,3 +139,31 @@ def test_chunked_forward_against_the_reference_float64_oracle(name):
     got = run_cuda("kda", ins, scale=meta["scale"], dtype="bfloat16", grads=False)
     assert np.isfinite(got["o"]).all() and np.isfinite(got["ht"]).all()
     compare(got, {"o": want["o"], "ht": want["final"]}, 1e-2, name)
+
+
+def test_config3_full_size_gradient_slices_against_the_oracle():
+    """The KDA benchmark shape (B4 T4096 H16 d128 bf16, documents U[128, 4096]) forward + backward at full size:
+    everything finite, and two (batch row, head) slices of the output and of ALL gradients (q, k, v, the
+    per-channel gate, beta) against the float64 chunked oracle run on that slice alone (heads and batch rows are
+    independent). Tolerance of the path: relative L2 <= 1e-2."""
+    from jax_linear_attention_b200 import ops
+
+    case = baseline_config(3)
+    dev = "cuda"
+    names = ("q", "k", "v", "g", "beta")
+    t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16 if n in ("q", "k", "v", "do") else torch.float32,
+                         requires_grad=n in names) for n in (*names, "do")}
+    seg = torch.tensor(case["seg"], device=dev)
+    o, s = ops.linear_attention("kda", t["q"], t["k"], t["v"], g=t["g"], beta=t["beta"], segment_ids=seg,
+                                output_final_state=True)
+    grads = torch.autograd.grad(o, [t[n] for n in names], t["do"])
+    assert all(bool(torch.isfinite(x.float()).all()) for x in (o, s, *grads))
+    for b, h in ((0, 3), (3, 12)):
+        sl = {n: case[n][b:b + 1, :, h:h + 1] for n in (*names, "do")}
+        sl["seg"] = case["seg"][b:b + 1]
+        sl["dht"] = np.zeros((1, 1, 128, 128), np.float32)
+        want = run_oracle("kda", sl, scale=128 ** -0.5, chunked=True)
+        got = dict(o=o.detach()[b:b + 1, :, h:h + 1].float().cpu().numpy(), ht=s.detach()[b:b + 1, h:h + 1].cpu().numpy())
+        for n, gr in zip(names, grads):
+            got["d" + n] = gr[b:b + 1, :, h:h + 1].float().cpu().numpy()
+        compare(got, want, 1e-2, f"config3 slice {b},{h}")

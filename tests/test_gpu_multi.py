@@ -1,5 +1,6 @@
 """Two-GPU tests (skipped on a single-GPU box): sequence parallelism over NCCL against the single-GPU result, and
-batch x heads sharding against the unsharded run. Ranks are child processes, one per GPU."""
+batch x heads sharding (``shard_kernel_call``, no collective) against the unsharded run. Ranks are child processes,
+one per GPU."""
 
 import os
 import socket
@@ -99,3 +100,66 @@ def test_pieces_two_gpus_match_one_gpu(tmp_path, kind):
         assert rel_l2(got, want[key]) < 1e-2, key
     assert rel_l2(parts[-1]["f"], want["ht"]) < 1e-2
     assert rel_l2(parts[0]["dh0"], want["dh0"]) < 1e-2
+
+
+def _shard_worker(rank, world, out, spec):
+    """One rank of the batch x heads sharded call: slices its shard out of the global case, runs forward and
+    backward through ``shard_kernel_call`` on its own GPU (no process group: the path has no collective)."""
+    torch.cuda.set_device(rank)
+    from jax_linear_attention_b200 import ops
+    from jax_linear_attention_b200.distributed import plan_shards, shard_kernel_call, shard_slices
+
+    case = make_case("gated_deltanet", seed=61, **spec)
+    dev = torch.device("cuda", rank)
+    t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16 if n in "qkv" else torch.float32,
+                         requires_grad=True) for n in ("q", "k", "v", "g", "beta", "h0")}
+    seg = torch.tensor(case["seg"], device=dev)
+
+    def fn(q, k, v, g, beta, **opts):
+        return ops.linear_attention("gated_deltanet", q, k, v, g=g, beta=beta, **opts)
+
+    o, f = shard_kernel_call(fn, t["q"], t["k"], t["v"], [t["g"], t["beta"]],
+                             dict(initial_state=t["h0"], segment_ids=seg, output_final_state=True,
+                                  scale=case["meta"]["scale"]),
+                             rank=rank, world=world, supports=ops.cuda.SUPPORTS["gated_deltanet"])
+    B, H, Hk = spec["B"], spec["H"], spec.get("Hk", spec["H"])
+    bs, hs, ks = shard_slices(plan_shards(B, H, Hk, world), rank, B, H, Hk)
+    do = torch.tensor(case["do"], device=dev, dtype=torch.bfloat16)[bs][:, :, hs]
+    dht = torch.tensor(case["dht"], device=dev)[bs][:, hs]
+    names = list(t)
+    grads = torch.autograd.grad([o, f], [t[n] for n in names], [do, dht])
+    res = {"o": o.detach().float().cpu().numpy(), "ht": f.detach().cpu().numpy()}
+    # the gradient of a global leaf is zero outside this rank's shard: save only the shard
+    cut = {"q": lambda x: x[bs][:, :, ks], "k": lambda x: x[bs][:, :, ks], "v": lambda x: x[bs][:, :, hs],
+           "g": lambda x: x[bs][:, :, hs], "beta": lambda x: x[bs][:, :, hs], "h0": lambda x: x[bs][:, hs]}
+    for n, gr in zip(names, grads):
+        res["d" + n] = cut[n](gr).detach().float().cpu().numpy()
+    np.savez(os.path.join(out, f"rank{rank}.npz"), **res)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("spec,axis", [
+    (dict(B=2, T=700, H=4, K=128, V=128, docs="mixed", h0=True), "batch"),           # the batch splits first
+    (dict(B=1, T=700, H=4, Hk=2, K=128, V=128, docs="mixed", h0=True), "heads"),     # heads, in whole key groups
+    (dict(B=1, T=500, H=8, Hk=2, K=64, V=64, docs="mixed", h0=True), "heads"),       # the mma.sync head size
+])
+def test_batch_x_heads_sharding_two_gpus_matches_one_gpu(tmp_path, spec, axis):
+    """The reference's check for its kernel sharding (tests/test_kernel_sharding.py:310-354: 2 GPUs = 1 GPU,
+    bf16-close): every (batch row, head) recurrence is independent, so the shards of a two-rank call put side by
+    side are the unsharded call -- same kernels on the same rows, hence equal bits for everything except the key
+    gradients of heads whose group sums run in a different launch geometry."""
+    import torch.multiprocessing as mp
+
+    from tests._util import run_cuda
+
+    world = 2
+    mp.spawn(_shard_worker, args=(world, str(tmp_path), spec), nprocs=world, join=True)
+    case = make_case("gated_deltanet", seed=61, **spec)
+    want = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="bfloat16")
+    parts = [dict(np.load(tmp_path / f"rank{r}.npz")) for r in range(world)]
+    cat_axis = {"batch": dict.fromkeys(("o", "ht", "dq", "dk", "dv", "dg", "dbeta", "dh0"), 0),
+                "heads": dict(o=2, ht=1, dq=2, dk=2, dv=2, dg=2, dbeta=2, dh0=1)}[axis]
+    for key, ax in cat_axis.items():
+        got = np.concatenate([p[key] for p in parts], axis=ax)
+        assert got.shape == want[key].shape, key
+        assert rel_l2(got, want[key]) < 1e-6, (key, rel_l2(got, want[key]))

@@ -80,7 +80,25 @@ def test_mamba2_matches_reference_oracle(name):
     assert max_rel(st2.detach().numpy(), state.detach().numpy()) < 1e-12
 
 
-@pytest.mark.parametrize("name", [n for n in NAMES if n.startswith("kda")])
+def test_softplus_gate_and_write_strength_match_reference_oracle64():
+    """The gate activations of the layers (oracle/gates.py) in front of the KDA recurrence, against the reference's
+    float64 oracle run with its ``gate="softplus"`` branch (benchmarks/diff_vector_gate.py:215-225): raw gate
+    activations, ``A_log`` in (log 1, log 16), a ``dt_bias`` per channel, beta before its sigmoid."""
+    from oracle import gates
+
+    meta, ins, want = load("kda_softplus")
+    f64 = torch.float64
+    t = {n: torch.tensor(v, dtype=f64) for n, v in ins.items()}
+    g = gates.mamba_gate(t["g"], t["A_log"], t["dt_bias"])
+    beta = gates.write_strength(t["beta"])
+    assert float(g.min()) < -20.0  # strong decays: the activations matter
+    o, final = recurrence.kda(t["q"], t["k"], t["v"], g, beta, scale=meta["scale"], initial_state=t["h0"],
+                              output_final_state=True, use_qk_l2norm=True)
+    assert max_rel(o.numpy(), want["o"]) < 1e-10
+    assert max_rel(final.numpy(), want["final"]) < 1e-10
+
+
+@pytest.mark.parametrize("name", [n for n in NAMES if n.startswith("kda") and n != "kda_softplus"])
 def test_kda_matches_reference_oracle64(name):
     meta, ins, want = load(name)
     f64 = torch.float64

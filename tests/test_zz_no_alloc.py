@@ -91,3 +91,7 @@ def test_noalloc_rejects_what_does_not_fit_or_needs_residuals():
     p.B, p.T, p.flags = 1, 256, _lib.FLAG_SAVE_RESIDUALS
     rc = lib.jla_linear_attention_fwd_noalloc(C.byref(p), C.c_void_p(dummy.data_ptr()), None, None)
     assert rc == _lib.ERR_BAD_ARGUMENT and b"forward only" in lib.jla_last_error()
+    # the array is shared by every call on the device: nobody can promise that an earlier call's tables are still there
+    p.flags = _lib.FLAG_PREP_DONE
+    rc = lib.jla_linear_attention_fwd_noalloc(C.byref(p), C.c_void_p(dummy.data_ptr()), None, None)
+    assert rc == _lib.ERR_BAD_ARGUMENT and b"PREP_DONE" in lib.jla_last_error()
