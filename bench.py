@@ -15,17 +15,28 @@ times recorded by the library inside the timed region), SM clocks sampled during
 baseline (the oracle port of the reference's chunked algorithm, timed on this host's cores on a bounded sample).
 ``--impl reference`` times that CPU port alone (the reference's own JAX CPU path cannot run here: JAX is not
 installed on the image).
+
+Timing: a block is exactly ``--steps`` steps between two CUDA events, bracketed by a barrier and a device
+synchronisation, maximum over the ranks. Blocks are repeated until a second of GPU time has been spent;
+``ms_per_step`` and ``value`` are the median block, ``blocks`` lists the spread.
+
+With N > 1 two more curves are measured after the headline and reported under extra keys of the same line:
+``strong`` (the same B8 T2048 H16 problem cut over the N ranks by batch x heads through ``shard_kernel_call``)
+and ``longctx`` (one 1,064,960-token sequence cut over the N ranks along T, NCCL send/recv of the fp32 state),
+each with a correctness check of one shard against an unsharded run.
 """
 
 from __future__ import annotations
 
 import argparse
 import ctypes as C
+import hashlib
 import json
 import os
 import statistics
 import subprocess
 import sys
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -149,25 +160,38 @@ def host_case(workload: str, seed: int) -> dict:
     return baseline_config(WORKLOADS[workload]["index"], seed=seed)
 
 
+LONG_BLOCKS = 32  # the long sequence is drawn in 32 blocks of 33,280 tokens, each from its own seed, so that any
+                  # rank of 1, 2, 4 or 8 draws exactly its tokens and every world size sees the same sequence
+
+
 def longctx_device_inputs(device, rank: int, world: int, seed: int = 0) -> dict:
-    """Config 4 shard of this rank, drawn on the device (17 GB of fp32 NumPy per tensor would not fit a host
-    round trip): q, k ~ N(0,1) L2-normalised, v, dO ~ N(0,1), beta = sigmoid(N(0,1)), g = logsigmoid(N(0,1)+3);
-    document lengths U[4096, 131072] drawn once on the host for the whole sequence."""
+    """The 1,064,960-token workload's shard of this rank, drawn on the device (17 GB of fp32 NumPy per tensor would
+    not fit a host round trip): q, k ~ N(0,1) L2-normalised, v, dO ~ N(0,1), beta = sigmoid(N(0,1)),
+    g = logsigmoid(N(0,1)+3); document lengths U[4096, 131072] drawn once on the host for the whole sequence."""
     from oracle.cases import uniform_docs
 
     tl = LONG_T // world
-    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
-
-    def randn(*shape):
-        return torch.randn(*shape, generator=gen, device=device, dtype=torch.float32)
+    tb = LONG_T // LONG_BLOCKS
+    per = LONG_BLOCKS // world
 
     def unit(x):
         return (x * torch.rsqrt((x * x).sum(-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
 
+    parts = {n: [] for n in ("q", "k", "v", "do", "beta", "g")}
+    for blk in range(rank * per, (rank + 1) * per):
+        gen = torch.Generator(device=device).manual_seed(seed * 1000 + blk)
+
+        def randn(*shape):
+            return torch.randn(*shape, generator=gen, device=device, dtype=torch.float32)
+
+        parts["q"].append(unit(randn(1, tb, 16, 128)))
+        parts["k"].append(unit(randn(1, tb, 16, 128)))
+        parts["v"].append(randn(1, tb, 16, 128).to(torch.bfloat16))
+        parts["do"].append(randn(1, tb, 16, 128).to(torch.bfloat16))
+        parts["beta"].append(torch.sigmoid(randn(1, tb, 16)))
+        parts["g"].append(torch.nn.functional.logsigmoid(randn(1, tb, 16) + 3.0))
+    out = {n: torch.cat(v, dim=1) if len(v) > 1 else v[0] for n, v in parts.items()}
     seg = torch.from_numpy(uniform_docs(np.random.default_rng(seed), 1, LONG_T, 4096, 131072))
-    out = dict(q=unit(randn(1, tl, 16, 128)), k=unit(randn(1, tl, 16, 128)), v=randn(1, tl, 16, 128).to(torch.bfloat16),
-               do=randn(1, tl, 16, 128).to(torch.bfloat16), beta=torch.sigmoid(randn(1, tl, 16)),
-               g=torch.nn.functional.logsigmoid(randn(1, tl, 16) + 3.0))
     out["seg"] = seg[:, rank * tl:(rank + 1) * tl].to(device=device, dtype=torch.int32)
     if world == 1:
         ids = out["seg"][0]
@@ -266,7 +290,10 @@ def cpu_port_step(case: dict, rows: int) -> float:
     return time.perf_counter() - t0
 
 
-def cpu_baseline(case: dict, rows: int = 1, budget_s: float = 12.0) -> dict:
+CPU_ROWS = 4  # batch rows of the workload that one CPU pass computes (both CPU legs use the same sample)
+
+
+def cpu_baseline(case: dict, rows: int = CPU_ROWS, budget_s: float = 12.0) -> dict:
     """The oracle port timed on a bounded sample: ``rows`` batch rows per pass, passes repeated until about
     ``budget_s`` seconds of CPU work are spent (one untimed pass first)."""
     cpu_port_step(case, rows)
@@ -281,15 +308,18 @@ def cpu_baseline(case: dict, rows: int = 1, budget_s: float = 12.0) -> dict:
 
 
 def run_reference(args) -> None:
-    """The reference arm: the CPU port of the reference's chunked algorithm on this host's cores."""
+    """The reference arm: the CPU port of the reference's chunked algorithm on this host's cores. One step is one
+    fwd+bwd over the same bounded sample the ``cpu_baseline`` leg uses; ``--steps`` and ``--warmup`` are honoured up
+    to 50 steps (a step takes about a second)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     case = host_case(args.workload, seed=0)
-    rows = 1
-    for _ in range(max(args.warmup, 0) and 1):
+    rows = min(CPU_ROWS, case["q"].shape[0])
+    warmup = max(0, min(args.warmup, 5))
+    for _ in range(warmup):
         cpu_port_step(case, rows)
-    steps = max(1, min(args.steps, 3))
+    steps = max(1, min(args.steps, 50))
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_port_step(case, rows)
@@ -299,13 +329,74 @@ def run_reference(args) -> None:
     sample = (f"each step = fwd+bwd of {rows} of {case['q'].shape[0]} batch rows (T={T}, all heads) with the chunk-64 "
               f"oracle port in float32 on {torch.get_num_threads()} threads; {steps} timed steps")
     line = dict(impl="reference", metric=METRIC, value=value, unit="tokens/s", n_gpus=args.gpus, steps=steps,
-                warmup=1 if args.warmup else 0, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak",
+                warmup=warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak",
                 vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(workload=WORKLOADS[args.workload]["name"], note="CPU port of src/jla/ops/chunked.py; the "
                             "reference's JAX CPU path is unavailable on this box (JAX not installed)"),
                 cpu_baseline=dict(value=value, unit="tokens/s", cores=torch.get_num_threads(), kind="port", sample=sample),
                 e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
+
+
+def bind_to_gpu_numa_node(local: int) -> str:
+    """Pins this process to the CPUs next to its GPU (read from sysfs) before any pinned buffer is allocated, so that
+    the host side of every PCIe copy is local memory. Host-side scheduling only; returns what was done."""
+    try:
+        props = torch.cuda.get_device_properties(local)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return f"{bdf}: no usable CPU in {text}"
+        os.sched_setaffinity(0, cpus)
+        return f"{bdf}: {len(cpus)} CPUs ({text})"
+    except (OSError, AttributeError, ValueError) as err:
+        return f"not bound ({type(err).__name__}: {err})"
+
+
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "dram_traffic.json")
+
+
+def profiled_traffic(kernel: str, workload: str):
+    """DRAM bytes per (chunk, head) unit of ``kernel`` from a committed ncu capture, or None when there is none or the
+    kernel's source changed after the capture (the file keeps a hash of the source next to each figure)."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            table = json.load(f)
+    except (OSError, ValueError):
+        return None
+    entry = table.get(workload, {}).get(kernel)
+    if not entry:
+        return None
+    try:
+        with open(os.path.join(ROOT, entry["source"]), "rb") as f:
+            digest = hashlib.sha256(f.read()).hexdigest()[:16]
+    except OSError:
+        return None
+    if digest != entry.get("source_sha256_16"):
+        return None
+    return dict(bytes_per_unit=entry["dram_bytes"] / entry["units"], commit=entry.get("commit"))
+
+
+class Deadline:
+    """Extras measured after the headline must never cost the headline: if they have not finished ``seconds`` after
+    they began, rank 0 prints the line as it stands and every rank leaves."""
+
+    def __init__(self, seconds: float, on_expire):
+        self.timer = threading.Timer(seconds, on_expire)
+        self.timer.daemon = True
+
+    def __enter__(self):
+        self.timer.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.timer.cancel()
 
 
 def main() -> None:
@@ -317,6 +408,8 @@ def main() -> None:
     ap.add_argument("--workload", default="gdn", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (for profiler captures)")
+    ap.add_argument("--no-extras", action="store_true", help="N > 1: skip the strong-scaling and long-context curves")
+    ap.add_argument("--single-block", action="store_true", help="time one block of --steps steps only (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -330,6 +423,7 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device: the CUDA kernels have no CPU fallback")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -361,27 +455,41 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        tms = torch.tensor([ms], device=device)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        return float(tms.item())
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed_block(step_fn, steps: int) -> float:
+        """Exactly ``steps`` steps between two events, barrier + synchronise on both sides; ms, max over ranks."""
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            step_fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
     # ---- device-resident timing
     for _ in range(args.warmup):
         run_step(args.workload, dev)
     lib.jla_profile_enable(1)
     lib.jla_profile_reset()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    blocks_ms = []
     with ClockSampler(local) as clocks:
-        e0.record()
-        for _ in range(args.steps):
-            run_step(args.workload, dev)
-        e1.record()
-        barrier()
-    ms = e0.elapsed_time(e1)
+        while True:
+            blocks_ms.append(timed_block(lambda: run_step(args.workload, dev), args.steps))
+            if args.single_block or sum(blocks_ms) >= 1000.0 or len(blocks_ms) >= 400:
+                break
     prof = profile_table(lib)
     lib.jla_profile_enable(0)
-    if dist is not None:
-        tms = torch.tensor([ms], device=device)
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        ms = float(tms.item())
+    ms = statistics.median(blocks_ms)
     ms_per_step = ms / args.steps
+    status_after_timing = _lib.device_status()
 
     # ---- end to end: pinned host inputs -> device -> fwd+bwd -> results back to pinned host memory
     out_host = None
@@ -426,21 +534,27 @@ def main() -> None:
     torch.cuda.current_stream(device).wait_stream(s_out)
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if dist is not None:
-        tms = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        e2e_ms = float(tms.item())
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
     d2h = sum(t.numel() * t.element_size() for t in out_host) if out_host else 0
 
+    line = None
     if rank == 0:
         pk = peaks()
-        launches = sum(v["launches"] for v in prof.values())
+        launches = sum(v["launches"] for v in prof.values()) // max(len(blocks_ms), 1)  # per timed block
         K, V = (case["q"].shape[3], case["v"].shape[3]) if "q" in case else (case["B"].shape[3], case["x"].shape[3])
         H = case["v"].shape[2] if "v" in case else case["x"].shape[2]
         units = (tokens // CHUNK) * H  # (chunk, head) pairs per launch
         model = kernel_model(K, V, delta=args.workload != "ssd", save=True)
         roof = None
+        step_traffic = 0.0
+        step_traffic_known = bool(prof)
+        for name in prof:  # DRAM bytes of the whole step from the committed captures, if every kernel has a current one
+            t = profiled_traffic(name, args.workload)
+            small = prof[name]["total_ms"] / prof[name]["launches"] < 0.03  # table and gate prologues: a few MB
+            if t is None and not small:
+                step_traffic_known = False
+            elif t is not None:
+                step_traffic += t["bytes_per_unit"] * units
         if prof:
             top = max(prof, key=lambda n: prof[n]["total_ms"])
             per_launch_ms = prof[top]["total_ms"] / prof[top]["launches"]
@@ -456,14 +570,10 @@ def main() -> None:
                     ach = fl / (per_launch_ms * 1e-3) / 1e12
                     roof = dict(bound="tensor", achieved=ach, peak=pk["bf16_tflops"], unit="TFLOP/s",
                                 frac=ach / pk["bf16_tflops"])
-                # DRAM bytes per unit from ncu captures of this workload (profiles/*.md); scaled by the units of a launch
-                ncu_bytes_per_unit = {"sg_grads_k": 805.7e6 / 4096, "sg_grads_q": 491.2e6 / 4096,
-                                      "sg_bwd_state": 454.0e6 / 4096, "kkt_inv": 92.9e6 / 4096}
-                ncu_kda = {"kda_intra": 1023.5e6 / 4208, "kda_prep": 524.4e6 / 4208, "kda_chunk_grads": 1038.4e6 / 4208}
-                traffic = (ncu_bytes_per_unit.get(top) if args.workload == "gdn"
-                           else ncu_kda.get(top) if args.workload == "kda" else None)
+                t = profiled_traffic(top, args.workload)
                 roof.update(kernel=top, ms_per_launch=per_launch_ms,
-                            traffic=None if traffic is None else traffic * units, peak_source=pk["source"],
+                            traffic=None if t is None else t["bytes_per_unit"] * units,
+                            traffic_measured_at=None if t is None else t["commit"], peak_source=pk["source"],
                             algorithmic_bytes_per_launch=by, algorithmic_flops_per_launch=fl)
         # whole-step view against both rooflines (dense 64x64 tiles, no recompute, inverse excluded: 491,520 FLOP and
         # 2,816 B per token and head for the delta-rule kinds)
@@ -477,26 +587,168 @@ def main() -> None:
             dtype="bf16", data="synthetic",
             config=dict(workload=WORKLOADS[args.workload]["name"], per_gpu_batch=list(shape[:2]),
                         l2="inputs larger than L2 (hundreds of MB of q,k,v,dO + residuals per step)",
+                        timing=f"median of {len(blocks_ms)} blocks of {args.steps} steps (CUDA events, barrier + "
+                               "synchronise around each block, max over ranks)",
+                        host_binding=numa,
                         parallelism=(f"sequence-parallel over {world} GPUs: documents cut into pieces joined by affine "
                                      "maps, NCCL send/recv of the fp32 state" if longctx and world > 1
                                      else "one GPU, documents as cu_seqlens rows" if longctx
                                      else f"batch x heads, {world} GPU(s), no communication")),
+            blocks=dict(count=len(blocks_ms), ms_per_step_median=ms_per_step, ms_per_step_min=min(blocks_ms) / args.steps,
+                        ms_per_step_max=max(blocks_ms) / args.steps, ms_per_step_first=blocks_ms[0] / args.steps,
+                        total_timed_ms=sum(blocks_ms)),
             e2e=None if not e2e_steps else dict(
                 value=world * tokens / (e2e_ms / e2e_steps * 1e-3), unit="tokens/s", h2d_bytes_per_step=h2d,
                 d2h_bytes_per_step=d2h, steps=e2e_steps, ms_per_step=e2e_ms / e2e_steps),
             gpu_launches=launches,
+            device_status=status_after_timing,
             clocks=clocks.summary(),
             roofline=roof,
             step=dict(tflops_algorithmic=step_flops / sec / 1e12, frac_of_bf16_peak=step_flops / sec / 1e12 / pk["bf16_tflops"],
-                      gbs_algorithmic=step_bytes / sec / 1e9, frac_of_hbm_peak=step_bytes / sec / 1e9 / pk["hbm_gbs"]),
+                      gbs_algorithmic=step_bytes / sec / 1e9, frac_of_hbm_peak=step_bytes / sec / 1e9 / pk["hbm_gbs"],
+                      min_traffic_bytes=step_bytes,
+                      step_traffic_bytes=step_traffic if step_traffic_known else None,
+                      traffic_over_minimum=step_traffic / step_bytes if step_traffic_known else None),
             kernels={n: dict(launches=v["launches"], ms_per_launch=v["total_ms"] / v["launches"]) for n, v in prof.items()},
         )
         if not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(case, rows=4) if args.workload in ("gdn", "kda") else None
-        print(json.dumps(line))
+            line["cpu_baseline"] = cpu_baseline(case) if args.workload in ("gdn", "kda") else None
+
+    # ---- N > 1: the curves that the weak-scaling headline cannot show
+    if world > 1 and args.workload == "gdn" and not args.no_extras:
+        printed = threading.Event()
+
+        def emit():
+            if rank == 0 and not printed.is_set():
+                printed.set()
+                print(json.dumps(line), flush=True)
+
+        def expire():
+            if rank == 0:
+                for key in ("strong", "longctx"):
+                    line.setdefault(key, dict(error="not finished within the time limit of the extra measurements"))
+            emit()
+            os._exit(0)
+
+        with Deadline(240.0, expire):
+            for key, fn in (("strong", strong_scaling), ("longctx", longctx_curve)):
+                try:
+                    res = fn(device, rank, world, dist, timed_block, ms_per_step, dev)
+                except Exception as err:  # an extra must not cost the headline
+                    res = dict(error=f"{type(err).__name__}: {err}"[:300])
+                if rank == 0:
+                    line[key] = res
+        emit()
+    elif rank == 0:
+        print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def strong_scaling(device, rank, world, dist, timed_block, one_gpu_ms_per_step, rank0_dev) -> dict:
+    """The B8 T2048 H16 d128 problem of seed 0 cut over the ranks by batch x heads (``shard_kernel_call``: batch
+    first, then heads; no collective). Rank 0's weak-scaling problem is that very problem, so its unsharded output
+    and time are the references: the shard must equal the matching slice bit for bit."""
+    from jax_linear_attention_b200 import ops
+    from jax_linear_attention_b200.distributed import plan_shards, shard_kernel_call, shard_slices
+
+    case = host_case("gdn", seed=0)
+    t = {n: torch.from_numpy(np.ascontiguousarray(case[n])) for n in ("q", "k", "v", "g", "beta", "do", "seg")}
+    B, T, H = case["v"].shape[:3]
+    bs, hs, ks = shard_slices(plan_shards(B, H, H, world), rank, B, H, H)
+    half = ("q", "k", "v", "do")
+    full = {n: (x.to(torch.bfloat16) if n in half else x.to(torch.int32) if n == "seg" else x.float()) for n, x in t.items()}
+    # every rank keeps only its shard on the device; shard_kernel_call slices the (here already local) tensors
+    loc = dict(q=full["q"][bs][:, :, ks], k=full["k"][bs][:, :, ks], v=full["v"][bs][:, :, hs], g=full["g"][bs][:, :, hs],
+               beta=full["beta"][bs][:, :, hs], do=full["do"][bs][:, :, hs], seg=full["seg"][bs])
+    loc = {n: x.contiguous().to(device) for n, x in loc.items()}
+
+    def fn(q, k, v, g, beta, **opts):
+        return ops.linear_attention("gated_deltanet", q, k, v, g=g, beta=beta, **opts)
+
+    def step():
+        leaves = [loc[n].requires_grad_(True) for n in ("q", "k", "v", "g", "beta")]
+        o, _ = shard_kernel_call(fn, leaves[0], leaves[1], leaves[2], leaves[3:], dict(segment_ids=loc["seg"]),
+                                 rank=0, world=1, supports=ops.cuda.SUPPORTS["gated_deltanet"])
+        return o, torch.autograd.grad(o, leaves, loc["do"])
+
+    for _ in range(3):
+        o, _ = step()
+    ok = None
+    if rank == 0:  # its weak-scaling inputs are the global problem
+        leaves = [rank0_dev[n].requires_grad_(True) for n in ("q", "k", "v", "g", "beta")]
+        o_full, _ = ops.linear_attention("gated_deltanet", *leaves[:3], g=leaves[3], beta=leaves[4],
+                                         segment_ids=rank0_dev.get("seg"))
+        ok = bool(torch.equal(o_full[bs][:, :, hs], o))
+    steps = 20
+    blocks = [timed_block(lambda: step(), steps) for _ in range(5)]
+    ms = statistics.median(blocks) / steps
+    tokens = B * T
+    return dict(what=f"B{B} T{T} H{H} d128 problem cut over {world} ranks by batch x heads (per rank: batch "
+                     f"{loc['q'].shape[0]}, heads {loc['v'].shape[2]}), no communication",
+                ms_per_step=ms, tokens_per_s=tokens / (ms * 1e-3), one_gpu_ms_per_step=one_gpu_ms_per_step,
+                speedup=one_gpu_ms_per_step / ms, efficiency=one_gpu_ms_per_step / ms / world,
+                shard_equals_unsharded_slice=ok)
+
+
+def longctx_curve(device, rank, world, dist, timed_block, *_unused) -> dict:
+    """One 1,064,960-token sequence (H16 d128, documents U[4096, 131072]) cut over the ranks along T. The one-GPU
+    reference (rank 0 alone, documents as independent rows) gives the speed-up's denominator and the check: rank 0's
+    shard of the sequence-parallel output against the same tokens of the one-GPU output."""
+    from jax_linear_attention_b200 import ops
+    from jax_linear_attention_b200.distributed import context_parallel_linear_attention, plan_pieces
+
+    torch.cuda.empty_cache()
+    dev = longctx_device_inputs(device, rank, world)
+    names = ("q", "k", "v", "g", "beta")
+    plan = plan_pieces(dev["seg"], 8192)
+
+    def step():
+        leaves = [dev[n].requires_grad_(True) for n in names]
+        o, _ = context_parallel_linear_attention("gated_deltanet", *leaves[:3], g=leaves[3], beta=leaves[4],
+                                                 segment_ids=dev["seg"], piece_len=plan)
+        return o, torch.autograd.grad(o, leaves, dev["do"])
+
+    o_cp, _ = step()
+    step()
+    steps = 3
+    blocks = [timed_block(lambda: step(), steps) for _ in range(3)]
+    ms = statistics.median(blocks) / steps
+    o_cp = o_cp.detach()
+    # one GPU, rank 0 only; the others wait at the next barrier
+    one_ms, err = None, None
+    if rank == 0:
+        one = longctx_device_inputs(device, 0, 1)
+
+        def one_step():
+            leaves = [one[n].requires_grad_(True) for n in names]
+            o, _ = ops.linear_attention("gated_deltanet", *leaves[:3], g=leaves[3], beta=leaves[4], cu_seqlens=one["cu"])
+            return o, torch.autograd.grad(o, leaves, one["do"])
+
+        o_one, _ = one_step()
+        tl = LONG_T // world
+        a, b = o_cp[:, :tl].float(), o_one.detach()[:, :tl].float()
+        err = float((a - b).norm() / b.norm())
+        del a, b
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        times = []
+        for _ in range(3):
+            torch.cuda.synchronize()
+            e0.record()
+            one_step()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        one_ms = statistics.median(times)
+        del one, o_one
+    torch.cuda.empty_cache()
+    dist.barrier()
+    return dict(what=f"one sequence of {LONG_T} tokens, H16 d128, cut over {world} ranks along T; documents in pieces of "
+                     "8192 tokens joined by affine maps; NCCL send/recv of the fp32 state",
+                ms_per_step=ms, tokens_per_s=LONG_T / (ms * 1e-3), one_gpu_ms_per_step=one_ms,
+                speedup=None if one_ms is None else one_ms / ms,
+                rank0_shard_vs_one_gpu_rel_l2=err, tolerance=1e-2, within_tolerance=None if err is None else err <= 1e-2)
 
 
 if __name__ == "__main__":

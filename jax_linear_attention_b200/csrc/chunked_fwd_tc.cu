@@ -28,6 +28,25 @@ using umma::swz_tile;
 constexpr int K = 128, V = 128;
 constexpr int kBarBase = 6;  // full / empty barriers of the ring (at most 3 stages) come first
 
+// Build with -DJLA_TRACE to record, for the first CTA, the global timer at the hand-offs of the serial chain
+// (16 slots per chunk: 0-8 by the first state warp, 9-14 by the MMA issuer); jla_debug_fwd_trace() copies them out.
+#ifdef JLA_TRACE
+__device__ unsigned long long g_fwd_trace[64 * 16];
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define JLA_MARK(it, slot)                                                                     \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && (it) < 64) g_fwd_trace[(it) * 16 + (slot)] = global_timer();         \
+  } while (0)
+#else
+#define JLA_MARK(it, slot) \
+  do {                     \
+  } while (0)
+#endif
+
 // VG (per-channel gates, KDA): the tiles come gate-folded from kda_prep_kernel, one set per chunk slot:
 // q -> cin q exp(G), k -> cin k exp(G) (recall), k2 -> tail k exp(G_63 - G) (write), p -> the masked score tile,
 // ag -> T beta_j, and the G/beta vector of the stage carries the decay exp(G_63) of the K state columns instead.
@@ -213,10 +232,12 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         const uint32_t aq = umma::smem_addr(st_q(s)), ak = umma::smem_addr(st_k(s));
         if (!wait(bars + B_ST, ph, abort_flag)) break;
         umma::fence_after_sync();
+        JLA_MARK(it, 9);
         if (DELTA) {
           umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, ak, 64, false);  // S^T K^T
           umma::commit(bars + B_M1);
         }
+        JLA_MARK(it, 10);
         const uint32_t co = cO + (it & 1) * 64;
         if (!p.state_only) {
           if (!VG) {
@@ -231,14 +252,18 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         if (DELTA) {
           if (!wait(bars + B_W, ph, abort_flag)) break;
           umma::fence_after_sync();
+          JLA_MARK(it, 11);
           umma::gemm_ts<128, 64, 4, false, FMT>(tmem + cA1, tmem + cWb, umma::smem_addr(st_t0(s)), 64, false);  // W^T Ag^T
           umma::commit(bars + B_M2);
+          JLA_MARK(it, 12);
         }
         if (!wait(bars + B_VN, ph, abort_flag)) break;
         umma::fence_after_sync();
+        JLA_MARK(it, 13);
         umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cVg, VG ? umma::smem_addr(st_k2(s)) : ak, 64,
                                               true);  // S^T += (Gamma_r Vn)^T K
         umma::commit(bars + B_M3);
+        JLA_MARK(it, 14);
         if (!p.state_only) {
           const uint32_t ap = VG ? umma::smem_addr(st_p(s)) : umma::smem_addr(Pb + (it & 1) * 8192);
           umma::gemm_ts<128, 64, 4, false, FMT>(tmem + co, tmem + cWb, ap, 64, true);  // += Vn^T P^T
@@ -282,6 +307,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         if (!ok) break;
         umma::fence_after_sync();
       }
+      if (tid == 128) JLA_MARK(it, 0);
       uint32_t hpk[32];  // the 16-bit copy of this half row, stored as a residual once the chain is released
 #pragma unroll
       for (int b2 = 0; b2 < 2; ++b2) {
@@ -309,6 +335,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
       umma::fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + B_ST);
+      if (tid == 128) JLA_MARK(it, 1);
       if (p.hT_out) {
         T* hT = static_cast<T*>(p.hT_out) + (((long)c * p.H + h) * V + v) * K + 64 * half;
 #pragma unroll
@@ -317,6 +344,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         }
       }
 
+      if (tid == 128) JLA_MARK(it, 2);
       const T* vs = reinterpret_cast<const T*>(st_v(s));
       const int j0 = 32 * half;  // this warp's 32 tokens (columns of the [V x 64] accumulators)
       if (DELTA) {
@@ -324,6 +352,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
         ok = wait(bars + B_M1, ph, abort_flag);
         if (!ok) break;
         umma::fence_after_sync();
+        if (tid == 128) JLA_MARK(it, 3);
         {
           float x[32];
           ld_row32<T>(x, tl + cA1 + j0);
@@ -340,6 +369,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
           umma::fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bars + B_W);
+          if (tid == 128) JLA_MARK(it, 4);
           if (p.wT_out) {  // residual for the key-side gradient kernel (dAg = dVn W^T)
             T* wT = static_cast<T*>(p.wT_out) + (((long)c * p.H + h) * V + v) * 64 + j0;
 #pragma unroll
@@ -349,9 +379,11 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
           }
         }
         // ---- Vn^T = W^T Ag^T
+        if (tid == 128) JLA_MARK(it, 5);
         ok = wait(bars + B_M2, ph, abort_flag);
         if (!ok) break;
         umma::fence_after_sync();
+        if (tid == 128) JLA_MARK(it, 6);
         {
           float x[32];
           ld_row32<T>(x, tl + cA1 + j0);
@@ -371,6 +403,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
             mbar_arrive(bars + B_VN);
             mbar_arrive(bars + NS + s);  // done with this stage's v and gate vectors
           }
+          if (tid == 128) JLA_MARK(it, 7);
           if (p.vnT_out) {
             T* vnT = static_cast<T*>(p.vnT_out) + (((long)c * p.H + h) * V + v) * 64 + j0;
 #pragma unroll
@@ -378,6 +411,7 @@ __global__ void __launch_bounds__(640, 1) sg_fwd_tc_kernel(const __grid_constant
               *reinterpret_cast<uint4*>(vnT + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
             }
           }
+          if (tid == 128) JLA_MARK(it, 8);
         }
       } else {
         // ---- Vn = V: the value rows themselves, and their Gamma_r-scaled copy
@@ -600,3 +634,9 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
 }
 
 }  // namespace jla
+
+#ifdef JLA_TRACE
+extern "C" int jla_debug_fwd_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, jla::g_fwd_trace, sizeof(unsigned long long) * 64 * 16) == cudaSuccess ? 0 : -4;
+}
+#endif

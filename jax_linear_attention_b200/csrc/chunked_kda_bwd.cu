@@ -8,11 +8,19 @@
 //   dQs = scale dO S^T    dKs = -dW S^T    dKu = Vn dS+^T    dP = scale dO Vn^T    dAg = dVn W^T    dd = rowsum(dS+ * S)
 // The second kernel takes these back through the triangular solve and the decayed scores and unfolds the gates:
 //   dT = dAg beta_j,  dbeta_j += sum_i dAg_ij T_ij,  dA = -strict(T^T dT T^T),  dbeta_i += sum_j dA_ij Akk_ij,
-//   dAkk = beta_i dA,   dq^ = dP k~,  dk^ = dAkk k~,  dk~ = dP^T q^ + dAkk^T k^      (q^, k^, k~: mid-point factors)
+//   dq^ = dP k~,  dk^ = beta_i dA k~,  dk~ = dP^T q^ + dA^T (beta k^)               (q^, k^, k~: mid-point factors)
 //   dq = dq^ e^(G-R) + dQs cin e^G          dk = [dk^ e^(G-R) + dKs cin e^G] + [dk~ e^(R-G) + dKu tail e^(G63-G)]
 //   dG_i = q dq + k (read-side dk - write-side dk);   dG_63 += sum_i k dKu tail e^(G63-G) + d dd
 //   dg_t = sum_(i >= t) dG_i + dG_63        (G is a running sum over the chunk's tokens)
 // Chunks whose decay is too strong for the factored scores take exact fp32 loops, as in the forward.
+//
+// Rounding of dG on the factored path. A pair (i, j) of tokens enters dG twice, +X_ij at row i and -X_ij at row j,
+// and a gate parameter's gradient multiplies dG_i by the cumulative decay G_i (dA_log = sum_i dG_i G_i), so the two
+// copies must agree far below bf16 precision or their difference is amplified by |G| (the reference met the same
+// effect: tests/test_vector_gate_gate_grads.py:1-14). Both copies are therefore formed from the SAME 16-bit operands
+// the tensor cores multiply: +X = q^ (dP k~) + (beta k^) (dA k~) and -X = k~ (dP^T q^ + dA^T (beta k^)), with q^, k~
+// and beta k^ read back from the rounded tiles, never recomputed from q, k in fp32. Then X+ and X- differ only by the
+// order of the fp32 accumulation.
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
@@ -151,10 +159,10 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
   T* tq = reinterpret_cast<T*>(smem_raw);  // raw q
   T* tk = tq + 64 * LDK;                   // raw k
   T* tqh = tk + 64 * LDK;                  // q exp(G - R)
-  T* tkh = tqh + 64 * LDK;                 // k exp(G - R)
+  T* tkh = tqh + 64 * LDK;                 // beta_i k exp(G - R)
   T* tb = tkh + 64 * LDK;                  // k exp(R - G)
   T* Tt = tb + 64 * LDK;                   // [64][LDC] T
-  T* Xd = Tt + 64 * LDC;                   // dT, later dAkk = beta_i dA
+  T* Xd = Tt + 64 * LDC;                   // dT
   T* Xm = Xd + 64 * LDC;                   // dAg, then M1 = dT T^T, then dA
   T* Xp = Xm + 64 * LDC;                   // dP
   float* Gm = reinterpret_cast<float*>(Xp + 64 * LDC);  // [64][KD]
@@ -240,7 +248,6 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     }
     __syncthreads();  // M1 (Xm) has been read by every warp
     store_acc<T, 2>(Xm, LDC, r0, 16 * cq, accA, lane);                                      // dA
-    store_acc<T, 2>(Xd, LDC, r0, 16 * cq, accA, lane, betas[r0 + g], betas[r0 + g + 8]);    // dAkk = beta_i dA
   }
   const long tokbase = ((long)m.tok0 * p.H + h) * KD;
   const long tstride = (long)p.H * KD;
@@ -254,6 +261,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     // ---- the factored operands
     for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
       const int i = idx >> 4, c8 = (idx & 15) * 8;
+      const float bi = betas[i];
       const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
       uint4 oq, ok, ob;
@@ -269,14 +277,14 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
         const float d1 = Gm[i * KD + c8 + 2 * e + 1] - 0.5f * Glast[c8 + 2 * e + 1];
         const float u0 = __expf(d0), u1 = __expf(d1), n0 = __expf(-d0), n1 = __expf(-d1);
         oqw[e] = pack2<T>(qf.x * u0, qf.y * u1);
-        okw[e] = pack2<T>(kf.x * u0, kf.y * u1);
+        okw[e] = pack2<T>(bi * kf.x * u0, bi * kf.y * u1);
         obw[e] = pack2<T>(kf.x * n0, kf.y * n1);
       }
       *reinterpret_cast<uint4*>(tqh + i * LDK + c8) = oq;
       *reinterpret_cast<uint4*>(tkh + i * LDK + c8) = ok;
       *reinterpret_cast<uint4*>(tb + i * LDK + c8) = ob;
     }
-    __syncthreads();  // factored tiles, dA (Xm) and dAkk (Xd) complete
+    __syncthreads();  // factored tiles and dA (Xm) complete
     float db0 = 0.f, db1 = 0.f;
     const int i0 = r0 + g, i1 = r0 + g + 8;
     const bool cin0 = entering && run[i0] == 0, cin1 = entering && run[i1] == 0;
@@ -290,7 +298,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     warp_gemm<T, 4, 4, A_ROW, B_KN>(accU, Xm + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dA k~
     warp_gemm<T, 4, 4, A_ROW, B_KN>(accQ, Xp + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dP k~
     warp_gemm<T, 4, 4, A_COL, B_KN>(accW, Xp + r0, LDC, tqh + kc0, LDK, lane);        // dP^T q^
-    warp_gemm<T, 4, 4, A_COL, B_KN>(accW, Xd + r0, LDC, tkh + kc0, LDK, lane);        // + dAkk^T k^
+    warp_gemm<T, 4, 4, A_COL, B_KN>(accW, Xm + r0, LDC, tkh + kc0, LDK, lane);        // + dA^T (beta k^)
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       float colsum[2] = {0.f, 0.f};
@@ -304,7 +312,9 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
         const float2 ku2 = *reinterpret_cast<const float2*>(dku + i * KD + col);
         const float2 qr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tq + i * LDK + col));
         const float2 kr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tk + i * LDK + col));
-        const float2 kh2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tkh + i * LDK + col));
+        const float2 kh2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tkh + i * LDK + col));  // beta k^
+        const float2 qh2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tqh + i * LDK + col));  // q^
+        const float2 kt2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tb + i * LDK + col));   // k~
         float dqv[2], dkv[2];
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
@@ -314,14 +324,17 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
           const float eu = __expf(d), en = __expf(-d);
           // exp(G_i) = exp(d) exp(R) and exp(G_63 - G_i) = exp(-d) exp(R) with R = G_63 / 2 (|R| <= 30 on this path)
           const float eg = cin ? eu * eR[x] : 0.f, ew = tail ? en * eR[x] : 0.f;
-          const float kh = x ? kh2.y : kh2.x;
-          if (hi) db1 += kh * accU[nt][e]; else db0 += kh * accU[nt][e];
-          const float dq = accQ[nt][e] * eu + (x ? qs2.y : qs2.x) * eg;
-          const float dkr = (hi ? b1 : b0) * accU[nt][e] * eu + (x ? ks2.y : ks2.x) * eg;
+          const float khb = x ? kh2.y : kh2.x, qh = x ? qh2.y : qh2.x, kt = x ? kt2.y : kt2.x;
+          const float qr = x ? qr2.y : qr2.x, kr = x ? kr2.y : kr2.x;
+          if (hi) db1 += kr * eu * accU[nt][e]; else db0 += kr * eu * accU[nt][e];  // dbeta_i += k^_i . (dA k~)_i
+          const float dqs_e = (x ? qs2.y : qs2.x) * eg, dks_e = (x ? ks2.y : ks2.x) * eg;
+          const float dq = accQ[nt][e] * eu + dqs_e;
+          const float dkr = (hi ? b1 : b0) * accU[nt][e] * eu + dks_e;
           const float kuw = (x ? ku2.y : ku2.x) * ew;
           const float dkw = accW[nt][e] * en + kuw;
-          const float qr = x ? qr2.y : qr2.x, kr = x ? kr2.y : kr2.x;
-          dGt[i * KD + col + x] = qr * dq + kr * (dkr - dkw);
+          // the pair terms from the rounded operands themselves (see the file header), the state terms in fp32
+          dGt[i * KD + col + x] = (qh * accQ[nt][e] + khb * accU[nt][e] - kt * accW[nt][e]) +
+                                  (qr * dqs_e + kr * (dks_e - kuw));
           colsum[x] += kr * kuw;
           dqv[x] = dq;
           dkv[x] = dkr + dkw;
@@ -354,7 +367,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     // ---- exact path: thread = key channel (threads 0..127), fp32 with the true exponent of every pair of one
     // document. The write-side dk accumulates in dGt[j][ch]; q dq + k dk_read and dk_read are parked in the factored
     // tiles, which this path does not build.
-    __syncthreads();  // dA (Xm) and dAkk (Xd) complete
+    __syncthreads();  // dA (Xm) complete
     const int ch = tid & (KD - 1);
     const bool active = tid < KD;
     float* keep = reinterpret_cast<float*>(tqh);  // [64][KD] fp32 over tqh | tkh
@@ -368,9 +381,11 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
           if (run[j] != run[i]) continue;
           const float e = __expf(Gi - Gm[j * KD + ch]);
           const float kj = to_f32(tk[j * LDK + ch]) * e;
-          const float dp = to_f32(Xp[i * LDC + j]), dakk = to_f32(Xd[i * LDC + j]);
+          // beta_i dA_ij from the same rounded dA that the row direction sums (u below): the two copies of a pair's
+          // term in dG must agree to fp32 rounding (see the file header)
+          const float dp = to_f32(Xp[i * LDC + j]), da = to_f32(Xm[i * LDC + j]), dakk = betas[i] * da;
           dq += dp * kj;
-          u += to_f32(Xm[i * LDC + j]) * kj;
+          u += da * kj;
           dGt[j * KD + ch] += (dp * qi + dakk * ki) * e;
         }
         float x = ki * u;  // dbeta_i += sum over channels of k_i u_i

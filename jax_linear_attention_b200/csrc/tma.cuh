@@ -49,6 +49,29 @@ __device__ __forceinline__ void load_bulk(void* smem_dst, const void* gsrc, uint
                : "memory");
 }
 
+// ---- stores (shared -> global) ------------------------------------------------------------------------------
+// One box from a 128-byte-swizzled shared-memory tile to global memory through a tensor map made by encode_3d.
+// Issued by ONE thread after the writers of the tile have fenced their generic-proxy writes
+// (umma::fence_async_smem) and synchronised with it. Completion is tracked per thread in bulk groups:
+// store_commit() closes a group, store_wait_read<N>() returns once all but the N newest groups have finished
+// READING shared memory (the tile may be overwritten), store_wait<N>() once they are complete in global memory.
+// The inner coordinate must be a multiple of 8 elements and no coordinate may be negative.
+__device__ __forceinline__ void store_3d(const CUtensorMap* map, const void* smem_src, int c_inner, int c_mid, int c_outer) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];\n" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(umma::smem_addr(smem_src)), "r"(c_inner), "r"(c_mid), "r"(c_outer)
+               : "memory");
+}
+__device__ __forceinline__ void store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void store_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

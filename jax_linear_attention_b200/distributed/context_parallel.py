@@ -46,6 +46,62 @@ from ..ops.cuda import final_state_only, shared_prep, state_grads_only
 
 _GATES = {"simple_gla": ("g",), "deltanet": ("beta",), "gated_deltanet": ("g", "beta"), "kda": ("g", "beta")}
 
+_DTYPE_CODES = {torch.float32: 1, torch.float64: 2, torch.int32: 3, torch.int64: 4, torch.bfloat16: 5, torch.float16: 6}
+_MAGIC = 0x4A4C41  # "JLA"
+
+
+class StateMessageError(RuntimeError):
+    """A hand-off between neighbouring ranks failed: the peer never sent (the group's timeout ran out), or what it
+    announced is not the tensor this rank expects. Raised on the host before any kernel consumes the message."""
+
+
+def _checked(group) -> bool:
+    """Announce every message with a small header (shape, dtype) and compare it on arrival? Always on gloo groups
+    (the CPU tests); on NCCL only with ``JLA_B200_CP_CHECK=1``, because reading the header costs a device
+    synchronisation per hand-off."""
+    import os
+
+    return dist.get_backend(group) == "gloo" or os.environ.get("JLA_B200_CP_CHECK", "0") == "1"
+
+
+def _header(t: torch.Tensor) -> torch.Tensor:
+    fields = [_MAGIC, _DTYPE_CODES.get(t.dtype, 0), t.dim(), *t.shape]
+    return torch.tensor(fields + [0] * (8 - len(fields)), dtype=torch.int64, device=t.device)
+
+
+def send_state(t: torch.Tensor, dst: int, group, what: str = "state"):
+    """``isend`` of a hand-off tensor (preceded by its header when checks are on); returns the request to wait on."""
+    t = t.contiguous()
+    try:
+        if _checked(group):
+            dist.send(_header(t), dst, group=group)
+        return dist.isend(t, dst, group=group)
+    except RuntimeError as err:
+        raise StateMessageError(f"context parallel: sending the {what} to rank {dst} failed: {err}") from err
+
+
+def recv_state(t: torch.Tensor, src: int, group, what: str = "state") -> torch.Tensor:
+    """Blocking receive of a hand-off tensor into ``t``. With checks on, the peer's header is compared with ``t``
+    first, so a message of another shape or dtype is refused instead of being reinterpreted; a peer that never
+    sends surfaces as ``StateMessageError`` when the process group's timeout runs out (never a hang: every group
+    this module is used with is created with a finite timeout)."""
+    try:
+        if _checked(group):
+            got = torch.zeros(8, dtype=torch.int64, device=t.device)
+            dist.recv(got, src, group=group)
+            want = _header(t)
+            if not torch.equal(got.cpu(), want.cpu()):
+                g = got.cpu().tolist()
+                raise StateMessageError(
+                    f"context parallel: rank {src} announced a {what} message with header {g} (magic, dtype code, ndim, "
+                    f"shape); expected {want.cpu().tolist()} = {tuple(t.shape)} {t.dtype}")
+        dist.recv(t, src, group=group)
+    except StateMessageError:
+        raise
+    except RuntimeError as err:
+        raise StateMessageError(f"context parallel: no {what} arrived from rank {src}: {err}") from err
+    return t
+
 
 def _first_starts(seg_local, prev_last, t_local: int) -> list[int]:
     """Per row, the index of the first token that starts a new document (``t_local`` if none)."""
@@ -113,11 +169,11 @@ class _ContextParallel(torch.autograd.Function):
             f = torch.empty(batch, xs[2].shape[2], q.shape[3], xs[2].shape[3], dtype=sdt, device=dev)
         send_req = None
         if next_rank is not None and early:
-            send_req = dist.isend(f.contiguous(), next_rank, group=group)
+            send_req = send_state(f, next_rank, group)
         s_in_leaf, prefix = None, []
         if rank > 0:
             s_in = torch.empty_like(f)
-            dist.recv(s_in, prev_rank, group=group)
+            recv_state(s_in, prev_rank, group)
             s_in_leaf = s_in.requires_grad_(True)
             with torch.enable_grad():
                 for b, length in enumerate(starts):
@@ -132,7 +188,7 @@ class _ContextParallel(torch.autograd.Function):
         if send_req is not None:
             send_req.wait()
         if next_rank is not None and not early:
-            dist.send(f.contiguous(), next_rank, group=group)
+            send_state(f, next_rank, group).wait()
 
         ctx.state = dict(leaves=leaves, h0_leaf=h0_leaf, o_a=o_a, f_a=f_a, s_in_leaf=s_in_leaf, prefix=prefix,
                          starts=starts, t_local=t_local, group=group, prev_rank=prev_rank, next_rank=next_rank,
@@ -152,7 +208,7 @@ class _ContextParallel(torch.autograd.Function):
             nonlocal g_f
             if st["next_rank"] is not None:
                 g_f = torch.empty(st["f_shape"], dtype=st["sdt"], device=st["dev"])
-                dist.recv(g_f, st["next_rank"], group=group)
+                recv_state(g_f, st["next_rank"], group, "state gradient")
             else:
                 g_f = (d_f.contiguous() if d_f is not None
                        else torch.zeros(st["f_shape"], dtype=st["sdt"], device=st["dev"]))
@@ -175,7 +231,7 @@ class _ContextParallel(torch.autograd.Function):
                         acc += x
                 if got[-1] is not None:
                     d_s_in += got[-1]
-            dist.send(d_s_in.contiguous(), st["prev_rank"], group=group)
+            send_state(d_s_in, st["prev_rank"], group, "state gradient").wait()
         if g_f is None:
             recv_gf()
         if st["o_a"] is None:  # the whole shard was handled by the correction pass
@@ -317,13 +373,13 @@ class _PiecewiseContextParallel(torch.autograd.Function):
                 if not cont[tail]:
                     scan(tail, pieces)
                     if next_rank is not None:
-                        send_req = dist.isend(s_out[-1:].contiguous(), next_rank, group=group)
+                        send_req = send_state(s_out[-1:], next_rank, group)
                 if prev_rank is not None:
-                    dist.recv(s_recv, prev_rank, group=group)
+                    recv_state(s_recv, prev_rank, group)
                 if cont[tail]:  # one document fills the whole shard
                     scan(0, pieces)
                     if next_rank is not None:
-                        send_req = dist.isend(s_out[-1:].contiguous(), next_rank, group=group)
+                        send_req = send_state(s_out[-1:], next_rank, group)
                 else:
                     scan(0, tail)
                 if send_req is not None:
@@ -380,10 +436,10 @@ class _PiecewiseContextParallel(torch.autograd.Function):
         if head < pieces:
             scan(head, 0)
             if st["prev_rank"] is not None:
-                send_req = dist.isend(ds_in[:1].contiguous() if cont[0] else torch.zeros_like(ds_in[:1]),
-                                      st["prev_rank"], group=group)
+                send_req = send_state(ds_in[:1] if cont[0] else torch.zeros_like(ds_in[:1]), st["prev_rank"], group,
+                                      "state gradient")
         if st["next_rank"] is not None:
-            dist.recv(g_next, st["next_rank"], group=group)
+            recv_state(g_next, st["next_rank"], group, "state gradient")
         elif d_f is not None:
             g_next = d_f.to(sdt).contiguous()
         if head < pieces:
@@ -391,8 +447,8 @@ class _PiecewiseContextParallel(torch.autograd.Function):
         else:
             scan(pieces, 0)
             if st["prev_rank"] is not None:
-                send_req = dist.isend(ds_in[:1].contiguous() if cont[0] else torch.zeros_like(ds_in[:1]),
-                                      st["prev_rank"], group=group)
+                send_req = send_state(ds_in[:1] if cont[0] else torch.zeros_like(ds_in[:1]), st["prev_rank"], group,
+                                      "state gradient")
         got = torch.autograd.grad([o, f], [*leaves, s_in_leaf], [d_o, ds_out.to(f.dtype)], allow_unused=True)
         if send_req is not None:
             send_req.wait()

@@ -246,3 +246,62 @@ def test_piece_table_cuts_documents_and_marks_continuations():
     assert cu == [0, 10, 13, 22] and cont == [False, False, False]
     cu, cont = _piece_table(torch.zeros(7, dtype=torch.int64), cont0=True, piece_len=7)
     assert cu == [0, 7] and cont == [True]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Failure detection on the host: a neighbour that never sends, and a message that is not the tensor expected.
+# The failures are made on the CPU ranks themselves (no kernel runs, nothing hangs): every hand-off is announced
+# by a small header and every receive ends with the process group's timeout at the latest.
+def _fault_worker(rank, world, port, out, fault):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from jax_linear_attention_b200.distributed import context_parallel as cp
+
+    result = "no error"
+    try:
+        if fault == "never_sends":
+            if rank == 0:
+                pass  # rank 0 leaves the step out: its neighbour waits for a state that is never sent
+            else:
+                case = make_case("simple_gla", B=1, T=32, H=1, K=8, V=8, seed=3)
+                t = {n: torch.tensor(case[n][:, 16:], dtype=F64) for n in ("q", "k", "v", "g")}
+                cp.context_parallel_linear_attention("simple_gla", t["q"], t["k"], t["v"], g=t["g"], call=_oracle_call)
+        elif fault == "wrong_shape":
+            if rank == 0:
+                cp.send_state(torch.zeros(1, 1, 8, 4, dtype=F64), 1, dist.group.WORLD).wait()  # V = 4 instead of 8
+            else:
+                cp.recv_state(torch.empty(1, 1, 8, 8, dtype=F64), 0, dist.group.WORLD)
+        elif fault == "wrong_dtype":
+            if rank == 0:
+                cp.send_state(torch.zeros(1, 1, 8, 8, dtype=torch.float32), 1, dist.group.WORLD).wait()
+            else:
+                cp.recv_state(torch.empty(1, 1, 8, 8, dtype=F64), 0, dist.group.WORLD)
+    except cp.StateMessageError as err:
+        result = f"StateMessageError: {err}"
+    except Exception as err:  # anything else is a test failure, reported by the parent
+        result = f"{type(err).__name__}: {err}"
+    with open(os.path.join(out, f"rank{rank}.txt"), "w") as f:
+        f.write(result)
+    # no barrier here: after a failed hand-off the group is not in a state to run one; the ranks just leave
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+@pytest.mark.parametrize("fault,needle", [("never_sends", "arrived from rank 0"), ("wrong_shape", "expected"),
+                                          ("wrong_dtype", "expected")])
+def test_a_failed_state_hand_off_is_an_error_on_the_host_not_a_hang(tmp_path, fault, needle):
+    import time
+
+    t0 = time.time()
+    mp.spawn(_fault_worker, args=(2, _free_port(), str(tmp_path), fault), nprocs=2, join=True)
+    assert time.time() - t0 < 60, "the receiver must give up at the group's timeout"
+    got = (tmp_path / "rank1.txt").read_text()
+    assert got.startswith("StateMessageError") and needle in got, got
+    if fault == "never_sends":
+        assert (tmp_path / "rank0.txt").read_text() == "no error"
+    # (after a refused message the sender may see its payload's connection closed by the receiver: also an error on
+    # the host, also no hang)
