@@ -7,9 +7,15 @@
 //   dS^T  = keep gamma dS+^T + (scale cin Gamma dO)^T-rows Q - (cin Gamma dW)^T-rows K
 //                                                               A operands from TMEM, Q and K read MN-major
 //
-// Roles: one TMA thread (q, k, dO, Ag tiles + gate vectors, 3-stage ring), one MMA thread, eight "state" warps
-// (thread = value row v; warp pairs split the 64 token columns) and eight "score" warps that build scale (Q K^T) D
-// one chunk ahead. Residuals for the chunk-gradient kernel are written transposed: dh^T [V][K], dVn^T [V][64].
+// Roles: one TMA thread (ring A: q, k and gate vectors, three slots because the scores are built a chunk ahead; ring
+// B: dO and the Ag tile, two slots), one MMA thread, eight "state" warps (thread = value row v; warp pairs split the
+// 64 token columns) and eight "score" warps that work one chunk ahead, off the serial chain: scale (Q K^T) D, the
+// scaled 16-bit copy (scale cin Gamma dO)^T as a TMEM operand, and the per-token scalars. The MMA thread issues the
+// chain's products the moment their operands are ready and the others (next chunk's scores, the dO^T Q part of the
+// state update) in the gap in which the chain waits for an epilogue.
+// As in the forward, nothing leaves the chunk loop through ordinary global stores (they slow down the issue of every
+// tcgen05.mma of the CTA): the residuals dh^T [V][K], dVn^T [V][64] and the output dv are written into swizzled
+// shared-memory tiles and stored by TMA from two otherwise idle threads.
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
@@ -22,13 +28,14 @@ namespace {
 using umma::swz_tile;
 
 constexpr int K = 128, V = 128;
-constexpr int kBarBase = 6;  // full / empty barriers of the ring (at most 3 stages) come first
+constexpr int kThreads = 640;
 
 // VG (per-channel gates, KDA): gate-folded tiles per chunk slot as in the forward (chunked_kda_prep.cu):
 // q -> cin q exp(G), k -> cin k exp(G), k2 -> tail k exp(G_63 - G), p -> the masked score tile, ag -> T beta_j; the
 // gate vector of the stage carries exp(G_63) per key channel.
 struct BwdTcMaps {
-  CUtensorMap q, k, d_o, ag, k2, p;
+  CUtensorMap q, k, d_o, ag, k2, p;   // loads
+  CUtensorMap dv, dh_res, dvn_res;    // stores
 };
 
 struct BwdTcParams {
@@ -39,7 +46,6 @@ struct BwdTcParams {
   const float* d_final;
   void* dv;
   float* dh0;
-  void *dhT_out, *dvnT_out;
   int H, Hk;
   float scale;
   int* status;
@@ -47,18 +53,29 @@ struct BwdTcParams {
 
 template <bool VG>
 struct SmemT {
-  static constexpr int NS = VG ? 2 : 3;
-  static constexpr int kStage = 64 * K * 2 * 2 + 64 * V * 2 + 8192 + (VG ? 64 * K * 2 + 8192 : 0);  // q, k, dO, Ag (+ k2, P)
-  static constexpr int kPb = NS * kStage;                // scale P tiles [2][64x64]
-  static constexpr int kGates = kPb + (VG ? 0 : 2 * 8192);
+  static constexpr int NA = VG ? 2 : 3;
+  static constexpr int NB = 2;
+  static constexpr int kSlotA = 2 * 64 * K * 2;                                           // q, k
+  static constexpr int kSlotB = 64 * V * 2 + 8192 + (VG ? 64 * K * 2 + 8192 : 0);         // dO, Ag (+ k2, P)
+  static constexpr int kRingB = NA * kSlotA;
+  static constexpr int kPb = kRingB + NB * kSlotB;           // scale P tiles [2][64 x 64] (not VG)
+  static constexpr int kStgH = kPb + (VG ? 0 : 2 * 8192);    // dh^T staging, two [V x 64] column blocks
+  static constexpr int kStgDvn = kStgH + V * K * 2;          // dVn^T staging [V x 64]
+  static constexpr int kGates = kStgDvn + V * 64 * 2;
   static constexpr int kGateStride = 640;
-  static constexpr int kScal = kGates + NS * kGateStride;  // per stage and state warp: gam[64], gamr[64]
-  static constexpr int kBars = kScal + NS * 4096;
-  static constexpr int kNumBars = kBarBase + 12;
+  static constexpr int kScal = kGates + NA * kGateStride;    // per A slot: gam[64], gamr[64], keep gamma
+  static constexpr int kScalStride = 1024;
+  static constexpr int kBars = kScal + NA * kScalStride;
+  static constexpr int kNumBars = 40;
   static constexpr int kBytes = kBars + kNumBars * 8 + 64 + 1024;
+  static_assert(kBytes <= 232448, "shared memory of one CTA");
 };
 
-enum { B_PDONE = kBarBase, B_PFREE, B_PA0, B_PA1, B_ST, B_MA, B_DV, B_MB, B_DW, B_MC };
+enum {
+  B_FULLA = 0, B_EMPTYA = 3, B_FULLB = 6, B_EMPTYB = 8,
+  B_PDONE = 10, B_PFREE, B_PA0, B_PA1, B_ST, B_MA, B_DV, B_MB, B_DW, B_MC,
+  B_HS_FULL, B_HS_FREE, B_DVN_FULL, B_DVN_FREE, B_DVO_FULL0, B_DVO_FULL1, B_DOB0, B_DOB1, B_DOBFREE0, B_DOBFREE1, B_GAM /* 3 */
+};
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(bar)) : "memory");
@@ -94,11 +111,16 @@ __device__ __forceinline__ void ld_row32(float (&v)[32], uint32_t taddr) {
   umma::wait_ld();
 }
 
+// 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 64] swizzled column block
+__device__ __forceinline__ uint4* swz_chunk(unsigned char* block, int row, int chunk) {
+  return reinterpret_cast<uint4*>(block + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
 template <typename T, bool DELTA, bool VG>
-__global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_constant__ BwdTcMaps maps, BwdTcParams p) {
+__global__ void __launch_bounds__(kThreads, 1) sg_bwd_state_tc_kernel(const __grid_constant__ BwdTcMaps maps, BwdTcParams p) {
   static_assert(DELTA || !VG, "per-channel gates come with the delta rule");
   using Smem = SmemT<VG>;
-  constexpr int NS = Smem::NS;
+  constexpr int NA = Smem::NA, NB = Smem::NB;
   constexpr int FMT = umma::Fmt<T>::value;
   const int row = blockIdx.x / p.H, h = blockIdx.x - row * p.H;
   const int hk = h / (p.H / p.Hk);
@@ -108,25 +130,32 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
 
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  auto st_q = [&](int s) { return base + s * Smem::kStage; };
-  auto st_k = [&](int s) { return st_q(s) + 64 * K * 2; };
-  auto st_do = [&](int s) { return st_k(s) + 64 * K * 2; };
-  auto st_ag = [&](int s) { return st_do(s) + 64 * V * 2; };
-  auto st_k2 = [&](int s) { return st_ag(s) + 8192; };       // VG only
-  auto st_p = [&](int s) { return st_k2(s) + 64 * K * 2; };  // VG only
-  auto st_G = [&](int s) { return reinterpret_cast<float*>(base + Smem::kGates + s * Smem::kGateStride); };
-  auto st_runs = [&](int s) { return reinterpret_cast<unsigned char*>(st_G(s) + 128); };
-  auto st_meta = [&](int s) { return reinterpret_cast<volatile int*>(st_runs(s) + 64); };
-  auto st_gam = [&](int s) { return reinterpret_cast<float*>(base + Smem::kScal + s * 4096); };
+  auto st_q = [&](int sa) { return base + sa * Smem::kSlotA; };
+  auto st_k = [&](int sa) { return st_q(sa) + 64 * K * 2; };
+  auto st_do = [&](int sb) { return base + Smem::kRingB + sb * Smem::kSlotB; };
+  auto st_ag = [&](int sb) { return st_do(sb) + 64 * V * 2; };
+  auto st_k2 = [&](int sb) { return st_ag(sb) + 8192; };       // VG only
+  auto st_p = [&](int sb) { return st_k2(sb) + 64 * K * 2; };  // VG only
+  auto st_G = [&](int sa) { return reinterpret_cast<float*>(base + Smem::kGates + sa * Smem::kGateStride); };
+  auto st_runs = [&](int sa) { return reinterpret_cast<unsigned char*>(st_G(sa) + 128); };
+  auto st_meta = [&](int sa) { return reinterpret_cast<volatile int*>(st_runs(sa) + 64); };
+  auto st_gam = [&](int sa) { return reinterpret_cast<float*>(base + Smem::kScal + sa * Smem::kScalStride); };
   unsigned char* Pb = base + Smem::kPb;
+  unsigned char* stgH = base + Smem::kStgH;
+  unsigned char* stgDvn = base + Smem::kStgDvn;
   uint64_t* bars = reinterpret_cast<uint64_t*>(base + Smem::kBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) {
-      umma::mbar_init(bars + s, 1);
-      umma::mbar_init(bars + NS + s, 1 + 8 + 8);
+    for (int s = 0; s < 3; ++s) {
+      umma::mbar_init(bars + B_FULLA + s, 1);
+      umma::mbar_init(bars + B_EMPTYA + s, 1 + 8);  // MMA commit + the state warps
+      umma::mbar_init(bars + B_GAM + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      umma::mbar_init(bars + B_FULLB + s, 1);
+      umma::mbar_init(bars + B_EMPTYB + s, 1 + 1);  // MMA commit + the dv store thread
     }
     umma::mbar_init(bars + B_PDONE, 1);
     umma::mbar_init(bars + B_PFREE, 8);
@@ -138,6 +167,16 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
     umma::mbar_init(bars + B_MB, 1);
     umma::mbar_init(bars + B_DW, 8);
     umma::mbar_init(bars + B_MC, 1);
+    umma::mbar_init(bars + B_HS_FULL, 8);
+    umma::mbar_init(bars + B_HS_FREE, 1);
+    umma::mbar_init(bars + B_DVN_FULL, 8);
+    umma::mbar_init(bars + B_DVN_FREE, 1);
+    umma::mbar_init(bars + B_DVO_FULL0, 8);
+    umma::mbar_init(bars + B_DVO_FULL1, 8);
+    umma::mbar_init(bars + B_DOB0, 8);
+    umma::mbar_init(bars + B_DOB1, 8);
+    umma::mbar_init(bars + B_DOBFREE0, 1);
+    umma::mbar_init(bars + B_DOBFREE1, 1);
     umma::mbar_init_fence();
     *abort_flag = 0;
   }
@@ -147,106 +186,151 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
   umma::fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   // dS^T fp32 | dS^T 16-bit | acc1 = dS+^T K^T, later dW^T | acc2 = dO^T (scale P) | dVn^T 16-bit |
-  // -(cin Gamma) dW^T 16-bit | scale (cin Gamma) dO^T 16-bit | Q K^T
-  constexpr uint32_t cS = 0, cSb = 128, cA1 = 192, cA2 = 256, cDVb = 320, cDWb = 352, cDOb = 384, cP = 416;
+  // -(cin Gamma) dW^T 16-bit | scale (cin Gamma) dO^T 16-bit, two buffers (written a chunk ahead) | Q K^T
+  constexpr uint32_t cS = 0, cSb = 128, cA1 = 192, cA2 = 256, cDVb = 320, cDWb = 352, cDOb0 = 384, cP = 448;
 
   if (warp == 0) {
+    // ------------------------------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int it = 0; it < n; ++it) {
-        const int s = it % NS, c = rc.x + (n - 1 - it);
-        if (!wait(bars + NS + s, ((it / NS) & 1) ^ 1, abort_flag)) break;
+        const int sa = it % NA, sb = it % NB, c = rc.x + (n - 1 - it);
+        if (!wait(bars + B_EMPTYA + sa, ((it / NA) & 1) ^ 1, abort_flag)) break;
         const ChunkMeta m = p.meta[c];
-        volatile int* ms = st_meta(s);
+        volatile int* ms = st_meta(sa);
         ms[0] = m.tok0;
         ms[1] = m.len;
         ms[2] = m.flags;
-        const uint32_t bytes = 64 * K * 2 * 2 + 64 * V * 2 + (DELTA ? 8192 : 0) + (VG ? 64 * K * 2 + 8192 : 0) + 512 + 64;
-        tma::expect_tx(bars + s, bytes);
         const int slot_row = (c * p.H + h) * 64;
+        tma::expect_tx(bars + B_FULLA + sa, 2 * 64 * K * 2 + 512 + 64);
         if (VG) {
-          tma::load_tile<64, K>(st_k(s), &maps.k, 0, 0, slot_row, bars + s);
-          tma::load_tile<64, K>(st_q(s), &maps.q, 0, 0, slot_row, bars + s);
-          tma::load_tile<64, K>(st_k2(s), &maps.k2, 0, 0, slot_row, bars + s);
-          tma::load_tile<64, 64>(st_p(s), &maps.p, 0, 0, slot_row, bars + s);
+          tma::load_tile<64, K>(st_k(sa), &maps.k, 0, 0, slot_row, bars + B_FULLA + sa);
+          tma::load_tile<64, K>(st_q(sa), &maps.q, 0, 0, slot_row, bars + B_FULLA + sa);
         } else {
-          tma::load_tile<64, K>(st_k(s), &maps.k, 0, hk, m.tok0, bars + s);
-          tma::load_tile<64, K>(st_q(s), &maps.q, 0, hk, m.tok0, bars + s);
+          tma::load_tile<64, K>(st_k(sa), &maps.k, 0, hk, m.tok0, bars + B_FULLA + sa);
+          tma::load_tile<64, K>(st_q(sa), &maps.q, 0, hk, m.tok0, bars + B_FULLA + sa);
         }
-        tma::load_tile<64, V>(st_do(s), &maps.d_o, 0, h, m.tok0, bars + s);
-        if (DELTA) tma::load_tile<64, 64>(st_ag(s), &maps.ag, 0, 0, slot_row, bars + s);
-        bulk_copy(st_G(s), p.gates + ((long)c * p.H + h) * 128, 512, bars + s);
-        bulk_copy(st_runs(s), p.runs + (long)c * 64, 64, bars + s);
+        bulk_copy(st_G(sa), p.gates + ((long)c * p.H + h) * 128, 512, bars + B_FULLA + sa);
+        bulk_copy(st_runs(sa), p.runs + (long)c * 64, 64, bars + B_FULLA + sa);
+        if (!wait(bars + B_EMPTYB + sb, ((it / NB) & 1) ^ 1, abort_flag)) break;
+        tma::expect_tx(bars + B_FULLB + sb, 64 * V * 2 + (DELTA ? 8192 : 0) + (VG ? 64 * K * 2 + 8192 : 0));
+        tma::load_tile<64, V>(st_do(sb), &maps.d_o, 0, h, m.tok0, bars + B_FULLB + sb);
+        if (DELTA) tma::load_tile<64, 64>(st_ag(sb), &maps.ag, 0, 0, slot_row, bars + B_FULLB + sb);
+        if (VG) {
+          tma::load_tile<64, K>(st_k2(sb), &maps.k2, 0, 0, slot_row, bars + B_FULLB + sb);
+          tma::load_tile<64, 64>(st_p(sb), &maps.p, 0, 0, slot_row, bars + B_FULLB + sb);
+        }
       }
     }
   } else if (warp == 1) {
+    // -------------------------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       auto issue_p = [&](int it) {
-        const int s = it % NS;
-        if (!wait(bars + s, (it / NS) & 1, abort_flag)) return false;
+        const int sa = it % NA;
+        if (!wait(bars + B_FULLA + sa, (it / NA) & 1, abort_flag)) return false;
         if (!wait(bars + B_PFREE, (it & 1) ^ 1, abort_flag)) return false;
         umma::fence_after_sync();
-        umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP, umma::smem_addr(st_q(s)), 64, umma::smem_addr(st_k(s)), 64,
+        umma::gemm<64, 64, K / 16, false, false, FMT>(tmem + cP, umma::smem_addr(st_q(sa)), 64, umma::smem_addr(st_k(sa)), 64,
                                                       false);
         umma::commit(bars + B_PDONE);
         return true;
       };
       bool okm = n > 0 && !VG ? issue_p(0) : true;
       for (int it = 0; it < n && okm; ++it) {
-        const int s = it % NS;
+        const int sa = it % NA, sb = it % NB;
         const uint32_t ph = it & 1;
-        const uint32_t aq = umma::smem_addr(st_q(s)), ak = umma::smem_addr(st_k(s)), ado = umma::smem_addr(st_do(s));
+        const uint32_t aq = umma::smem_addr(st_q(sa)), ak = umma::smem_addr(st_k(sa)), ado = umma::smem_addr(st_do(sb));
         if (!wait(bars + B_ST, ph, abort_flag)) break;
+        if (!wait(bars + B_FULLA + sa, (it / NA) & 1, abort_flag)) break;
+        if (!wait(bars + B_FULLB + sb, (it / NB) & 1, abort_flag)) break;
         umma::fence_after_sync();
-        umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, VG ? umma::smem_addr(st_k2(s)) : ak, 64,
+        umma::gemm_ts<128, 64, K / 16, false, FMT>(tmem + cA1, tmem + cSb, VG ? umma::smem_addr(st_k2(sb)) : ak, 64,
                                                    false);  // dS+^T K^T
         if (!VG && !wait(bars + B_PA0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
         // dO^T (scale P): A = dO tile read MN-major (M = value index), B = P tile read MN-major (rows i)
         umma::gemm<128, 64, 4, true, true, FMT>(tmem + cA2, ado, 64,
-                                                VG ? umma::smem_addr(st_p(s)) : umma::smem_addr(Pb + (it & 1) * 8192), 64, false);
+                                                VG ? umma::smem_addr(st_p(sb)) : umma::smem_addr(Pb + (it & 1) * 8192), 64, false);
         umma::commit(bars + B_MA);
+        // Off the chain, while the state group combines the two accumulators: the dO part of the state update (its
+        // 16-bit operand was written a chunk ahead by the score group) and the next chunk's scores.
+        if (!wait(bars + B_DOB0 + (it & 1), (it >> 1) & 1, abort_flag)) break;
+        umma::fence_after_sync();
+        umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cDOb0 + 32 * ph, aq, 64, true);  // += (s cg dO)^T Q
+        umma::commit(bars + B_DOBFREE0 + (it & 1));  // the operand buffer may be rewritten once this product is done
         if (!VG && it + 1 < n && !issue_p(it + 1)) break;
         if (DELTA) {
           if (!wait(bars + B_DV, ph, abort_flag)) break;
           umma::fence_after_sync();
-          umma::gemm_ts<128, 64, 4, true, FMT>(tmem + cA1, tmem + cDVb, umma::smem_addr(st_ag(s)), 64, false);  // dVn^T Ag
+          umma::gemm_ts<128, 64, 4, true, FMT>(tmem + cA1, tmem + cDVb, umma::smem_addr(st_ag(sb)), 64, false);  // dVn^T Ag
           umma::commit(bars + B_MB);
+          umma::commit(bars + B_EMPTYB + sb);  // dO, Ag (and with VG k2, P) are consumed when these products are done
+        } else {
+          umma::commit(bars + B_EMPTYB + sb);
         }
         if (!wait(bars + B_DW, ph, abort_flag)) break;
         umma::fence_after_sync();
-        umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cDOb, aq, 64, true);                // += (s cg dO)^T Q
         if (DELTA) umma::gemm_ts<128, 128, 4, true, FMT>(tmem + cS, tmem + cDWb, ak, 64, true);     // += (-cg dW)^T K
         umma::commit(bars + B_MC);
-        umma::commit(bars + NS + s);
+        umma::commit(bars + B_EMPTYA + sa);
       }
+    }
+  } else if (warp == 2) {
+    // --------------------------------------------------------- residual stores: dh^T, dVn^T as TMA tensor stores
+    if (lane == 0) {
+      bool ok = true;
+      for (int it = 0; it < n && ok; ++it) {
+        const int row0 = ((rc.x + (n - 1 - it)) * p.H + h) * V;
+        ok = wait(bars + B_HS_FULL, it & 1, abort_flag);
+        if (!ok) break;
+        tma::store_3d(&maps.dh_res, stgH, 0, 0, row0);
+        tma::store_3d(&maps.dh_res, stgH + V * 128, 64, 0, row0);
+        tma::store_commit();
+        tma::store_wait_read<0>();
+        mbar_arrive(bars + B_HS_FREE);
+        if (DELTA) {
+          ok = wait(bars + B_DVN_FULL, it & 1, abort_flag);
+          if (!ok) break;
+          tma::store_3d(&maps.dvn_res, stgDvn, 0, 0, row0);
+          tma::store_commit();
+          tma::store_wait_read<0>();
+          mbar_arrive(bars + B_DVN_FREE);
+        }
+      }
+      tma::store_wait<0>();
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------ dv: the staged tile of a full chunk as TMA tensor stores
+    if (lane == 0) {
+      bool ok = true;
+      for (int it = 0; it < n && ok; ++it) {
+        const int sb = it % NB;
+        ok = wait(bars + B_DVO_FULL0 + (it & 1), (it >> 1) & 1, abort_flag);
+        if (!ok) break;
+        const ChunkMeta m = p.meta[rc.x + (n - 1 - it)];
+        if (m.len == 64) {  // a partial chunk was written by the state warps themselves (rows past its end belong to others)
+          tma::store_3d(&maps.dv, st_do(sb), 0, h, m.tok0);
+          tma::store_3d(&maps.dv, st_do(sb) + 64 * 128, 64, h, m.tok0);
+          tma::store_commit();
+          tma::store_wait_read<0>();
+        }
+        mbar_arrive(bars + B_EMPTYB + sb);
+      }
+      tma::store_wait<0>();
     }
   } else if (warp >= 4 && warp < 12) {
     const int q4 = warp & 3, half = (warp - 4) >> 2, v = 32 * q4 + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     bool ok = true;
     for (int it = 0; it < n && ok; ++it) {
-      const int s = it % NS, c = rc.x + (n - 1 - it);
+      const int sa = it % NA, sb = it % NB;
       const uint32_t ph = it & 1;
-      ok = wait(bars + s, (it / NS) & 1, abort_flag);
+      // the chunk's tiles have landed (and, without VG, its per-token scalars are written)
+      ok = wait(bars + (VG ? B_FULLA : B_GAM) + sa, (it / NA) & 1, abort_flag);
       if (!ok) break;
-      const float* Gs = st_G(s);
-      const unsigned char* runs = st_runs(s);
-      const int tok0 = st_meta(s)[0], len = st_meta(s)[1], flags = st_meta(s)[2];
-      float* gam = st_gam(s) + (warp - 4) * 128;
-      float* gamr = gam + 64;
-#pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const int j = lane + 32 * jj;
-        if (VG) {  // masks and decays are folded into the operands
-          gam[j] = 1.f;
-          gamr[j] = 1.f;
-        } else {
-          const RowScalars rs = row_scalars(Gs, runs, flags, j);
-          gam[j] = rs.gam;
-          gamr[j] = rs.gamr;
-        }
-      }
-      __syncwarp();
-      const float kg = VG ? 0.f : keep_gamma(Gs, runs, flags);
+      const float* Gs = st_G(sa);
+      const int tok0 = st_meta(sa)[0], len = st_meta(sa)[1];
+      const float* gam = st_gam(sa);
+      const float* gamr = gam + 64;
+      const float kg = VG ? 0.f : gam[128];
       const float pscale = VG ? p.scale : 1.f;  // VG: the score tile comes unscaled
       const int j0 = 32 * half;
       // ---- dS+ of this chunk: 16-bit copy, residual, decayed fp32 copy
@@ -278,29 +362,21 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
         for (int i = 0; i < 32; ++i) x[i] *= VG ? Gs[blk * 32 + i] : kg;  // VG: exp(G_63) of key channel blk * 32 + i
         umma::st_32x32b_x32(tl + cS + blk * 32, x);
       }
-      // ---- scale (cin Gamma)_i dO^T as a 16-bit A operand (tokens i of this warp's half)
-      const T* dos = reinterpret_cast<const T*>(st_do(s));
-      {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int j = j0 + 2 * i;
-          const float a = (j < len) ? to_f32(dos[swz_tile(64, j, v)]) * p.scale * gam[j] : 0.f;
-          const float b = (j + 1 < len) ? to_f32(dos[swz_tile(64, j + 1, v)]) * p.scale * gam[j + 1] : 0.f;
-          pk[i] = pack2<T>(a, b);
-        }
-        umma::st_32x32b_x16(tl + cDOb + 16 * half, pk);
-      }
       umma::wait_st();
       umma::fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + B_ST);
-      {
-        T* dhT = static_cast<T*>(p.dhT_out) + (((long)c * p.H + h) * V + v) * K + 64 * half;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          *reinterpret_cast<uint4*>(dhT + i * 8) = make_uint4(hpk[4 * i], hpk[4 * i + 1], hpk[4 * i + 2], hpk[4 * i + 3]);
+      {  // this half row of dS+^T into the staging tile (column block `half`, row v)
+        if (it > 0) {
+          ok = wait(bars + B_HS_FREE, ph ^ 1, abort_flag);
+          if (!ok) break;
         }
+        unsigned char* blk = stgH + half * (V * 128);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) *swz_chunk(blk, v, i) = make_uint4(hpk[4 * i], hpk[4 * i + 1], hpk[4 * i + 2], hpk[4 * i + 3]);
+        umma::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + B_HS_FULL);
       }
       // ---- dVn^T = dO^T (scale P) + (tail Gamma_r)_j (dS+^T K^T)
       ok = wait(bars + B_MA, ph, abort_flag);
@@ -313,27 +389,37 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
         umma::ld_32x32b_x32(y, tl + cA2 + j0);
         umma::wait_ld();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int j = j0 + 2 * i;
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 gr = VG ? make_float4(1.f, 1.f, 1.f, 1.f) : *reinterpret_cast<const float4*>(gamr + j0 + 4 * i4);
+          const int j = j0 + 4 * i4;
           // columns of tokens past a partial chunk are forced to zero (their inputs are other rows' data)
-          dvn[i] = pack2<T>(j < len ? pscale * y[2 * i] + gamr[j] * x[2 * i] : 0.f,
-                            j + 1 < len ? pscale * y[2 * i + 1] + gamr[j + 1] * x[2 * i + 1] : 0.f);
+          const float a0 = j < len ? pscale * y[4 * i4] + gr.x * x[4 * i4] : 0.f;
+          const float a1 = j + 1 < len ? pscale * y[4 * i4 + 1] + gr.y * x[4 * i4 + 1] : 0.f;
+          const float a2 = j + 2 < len ? pscale * y[4 * i4 + 2] + gr.z * x[4 * i4 + 2] : 0.f;
+          const float a3 = j + 3 < len ? pscale * y[4 * i4 + 3] + gr.w * x[4 * i4 + 3] : 0.f;
+          dvn[2 * i4] = pack2<T>(a0, a1);
+          dvn[2 * i4 + 1] = pack2<T>(a2, a3);
         }
       }
-      T* stg = reinterpret_cast<T*>(st_do(s)) + (warp - 4) * 32 * 32;  // [32 tokens][32 values]: dv staging (dO is dead)
+      // the dead dO tile of this chunk takes dv as a [64 tokens x V] swizzled tile (thread = value column v)
+      T* stg = reinterpret_cast<T*>(st_do(sb));
       if (DELTA) {
         umma::st_32x32b_x16(tl + cDVb + 16 * half, dvn);
+        {  // (the shared-memory stores run while the TMEM store completes)
+          if (it > 0) {
+            ok = wait(bars + B_DVN_FREE, ph ^ 1, abort_flag);
+            if (!ok) break;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) *swz_chunk(stgDvn, v, 4 * half + i) = make_uint4(dvn[4 * i], dvn[4 * i + 1], dvn[4 * i + 2], dvn[4 * i + 3]);
+        }
         umma::wait_st();
         umma::fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + B_DV);
-        {
-          T* dvnT = static_cast<T*>(p.dvnT_out) + (((long)c * p.H + h) * V + v) * 64 + j0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            *reinterpret_cast<uint4*>(dvnT + i * 8) = make_uint4(dvn[4 * i], dvn[4 * i + 1], dvn[4 * i + 2], dvn[4 * i + 3]);
-          }
-        }
+        umma::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + B_DVN_FULL);
         // ---- dW^T = dVn^T Ag ; -(cin Gamma)_j dW^T as the next A operand; dv
         ok = wait(bars + B_MB, ph, abort_flag);
         if (!ok) break;
@@ -342,39 +428,50 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
         ld_row32(x, tl + cA1 + j0);
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int j = j0 + 2 * i;
-          pk[i] = pack2<T>(-gam[j] * x[2 * i], -gam[j + 1] * x[2 * i + 1]);
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 gm = VG ? make_float4(1.f, 1.f, 1.f, 1.f) : *reinterpret_cast<const float4*>(gam + j0 + 4 * i4);
+          pk[2 * i4] = pack2<T>(-gm.x * x[4 * i4], -gm.y * x[4 * i4 + 1]);
+          pk[2 * i4 + 1] = pack2<T>(-gm.z * x[4 * i4 + 2], -gm.w * x[4 * i4 + 3]);
         }
         umma::st_32x32b_x16(tl + cDWb + 16 * half, pk);
         umma::wait_st();
         umma::fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + B_DW);
+        if (lane == 0) {
+          mbar_arrive(bars + B_DW);
+          mbar_arrive(bars + B_EMPTYA + sa);  // done with this chunk's gate vectors
+        }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) stg[i * 32 + lane] = from_f32<T>(x[i]);
+        for (int i = 0; i < 32; ++i) stg[swz_tile(64, j0 + i, v)] = from_f32<T>(x[i]);
       } else {
         umma::fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + B_DW);  // dW = dVn: nothing more for the state update
+        if (lane == 0) {
+          mbar_arrive(bars + B_DW);  // dW = dVn: nothing more for the state update
+          mbar_arrive(bars + B_EMPTYA + sa);
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 f = unpack2<T>(dvn[i]);
-          stg[(2 * i) * 32 + lane] = from_f32<T>(f.x);
-          stg[(2 * i + 1) * 32 + lane] = from_f32<T>(f.y);
+          stg[swz_tile(64, j0 + 2 * i, v)] = from_f32<T>(f.x);
+          stg[swz_tile(64, j0 + 2 * i + 1, v)] = from_f32<T>(f.y);
         }
       }
-      __syncwarp();
-      T* dv = static_cast<T*>(p.dv) + ((long)(tok0 + j0) * p.H + h) * V + 32 * q4;
+      if (len < 64) {  // partial chunk: this warp writes its own 32 tokens x 32 value columns, up to the chunk's end
+        __syncwarp();
+        T* dv = static_cast<T*>(p.dv) + ((long)(tok0 + j0) * p.H + h) * V + 32 * q4;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int idx = lane + 32 * i, tok = idx >> 2, part = idx & 3;
-        if (j0 + tok < len) {
-          *reinterpret_cast<uint4*>(dv + (long)tok * p.H * V + part * 8) = *reinterpret_cast<const uint4*>(stg + tok * 32 + part * 8);
+        for (int i = 0; i < 4; ++i) {
+          const int idx = lane + 32 * i, tok = idx >> 2, part = idx & 3;
+          if (j0 + tok < len) {
+            *reinterpret_cast<uint4*>(dv + (long)tok * p.H * V + part * 8) =
+                *reinterpret_cast<const uint4*>(stg + swz_tile(64, j0 + tok, 32 * q4 + part * 8));
+          }
         }
       }
+      umma::fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + NS + s);
+      if (lane == 0) mbar_arrive(bars + B_DVO_FULL0 + (it & 1));
     }
     // ---- gradient of the initial state
     if (ok && n > 0) ok = wait(bars + B_MC, (n - 1) & 1, abort_flag);
@@ -397,24 +494,60 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
       }
     }
   } else if (warp >= 12) {
-    // ---- score group: scale (Q K^T) D one chunk ahead, stored [i][j] (read MN-major by the dO^T P product)
+    // ---- score group, one chunk ahead of the chain: the per-token scalars (first warp), the scaled 16-bit copy
+    // (scale cin Gamma dO)^T as a TMEM operand (thread = value row v, 32 tokens per warp), and scale (Q K^T) D stored
+    // [i][j] (read MN-major by the dO^T P product)
     const int q4 = warp & 3, half = (warp - 12) >> 2, g = lane >> 2, t = lane & 3;
-    const int r0 = 16 * q4;
+    const int r0 = 16 * q4, v = 32 * q4 + lane;
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     bool ok = true;
-    for (int it = 0; it < n && ok; ++it) {
-      const int s = it % NS, buf = it & 1;
-      ok = wait(bars + s, (it / NS) & 1, abort_flag);
-      if (!ok) break;
-      if (VG) {  // the score tile arrives with the stage: nothing to build
+    auto prepare = [&](int it) {
+      const int sa = it % NA, sb = it % NB, buf = it & 1;
+      if (!wait(bars + B_FULLA + sa, (it / NA) & 1, abort_flag)) return false;
+      const float* Gs = st_G(sa);
+      const unsigned char* runs = st_runs(sa);
+      const int len = st_meta(sa)[1], flags = st_meta(sa)[2];
+      float* gam = st_gam(sa);
+      if (!VG && warp == 12) {  // per-token scalars, once for the CTA
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = lane + 32 * jj;
+          const RowScalars rs = row_scalars(Gs, runs, flags, j);
+          gam[j] = rs.gam;
+          gam[64 + j] = rs.gamr;
+        }
+        if (lane == 0) gam[128] = keep_gamma(Gs, runs, flags);
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + NS + s);
-        continue;
+        if (lane == 0) mbar_arrive(bars + B_GAM + sa);
       }
-      const float* Gs = st_G(s);
-      const unsigned char* runs = st_runs(s);
-      ok = wait(bars + B_PDONE, it & 1, abort_flag);
-      if (!ok) break;
+      // ---- scale (cin Gamma)_i dO^T, tokens 32 half .. + 31 of value row v
+      if (!wait(bars + B_FULLB + sb, (it / NB) & 1, abort_flag)) return false;
+      if (it >= 2) {  // the product that read this buffer two chunks ago is done (one barrier per buffer: a wait on a
+        // barrier that completes every chunk could be two phases late and would then mistake the parity)
+        if (!wait(bars + B_DOBFREE0 + buf, ((it >> 1) & 1) ^ 1, abort_flag)) return false;
+        umma::fence_after_sync();
+      }
+      {
+        if (!VG && !wait(bars + B_GAM + sa, (it / NA) & 1, abort_flag)) return false;  // the first warp's scalars
+        const T* dos = reinterpret_cast<const T*>(st_do(sb));
+        const int j0 = 32 * half;
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int j = j0 + 2 * i;
+          const float2 cg = VG ? make_float2(1.f, 1.f) : *reinterpret_cast<const float2*>(gam + j);
+          const float a = (j < len) ? to_f32(dos[swz_tile(64, j, v)]) * p.scale * cg.x : 0.f;
+          const float b = (j + 1 < len) ? to_f32(dos[swz_tile(64, j + 1, v)]) * p.scale * cg.y : 0.f;
+          pk[i] = pack2<T>(a, b);
+        }
+        umma::st_32x32b_x16(tl + cDOb0 + 32 * buf + 16 * half, pk);
+        umma::wait_st();
+        umma::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + B_DOB0 + buf);
+      }
+      if (VG) return true;  // the score tile arrives with the stage: nothing to build
+      if (!wait(bars + B_PDONE, it & 1, abort_flag)) return false;
       umma::fence_after_sync();
       float acc[4][4];
       umma::ld_16x256b<4>(acc, tl + cP + 32 * half);
@@ -425,7 +558,6 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
       const int i0 = r0 + g, i1 = r0 + g + 8;
       const float G0 = Gs[i0], G1 = Gs[i1];
       const int run0 = runs[i0], run1 = runs[i1];
-      const int len = st_meta(s)[1];
       // rows of tokens past a partial chunk hold other rows' q and dO: their scores must not reach dVn
       const float s0 = i0 < len ? p.scale : 0.f, s1 = i1 < len ? p.scale : 0.f;
       T* pt = reinterpret_cast<T*>(Pb + buf * 8192);
@@ -439,11 +571,10 @@ __global__ void __launch_bounds__(640, 1) sg_bwd_state_tc_kernel(const __grid_co
       }
       umma::fence_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bars + B_PA0 + buf);
-        mbar_arrive(bars + NS + s);
-      }
-    }
+      if (lane == 0) mbar_arrive(bars + B_PA0 + buf);
+      return true;
+    };
+    for (int it = 0; it < n && ok; ++it) ok = prepare(it);
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -457,7 +588,7 @@ int launch_one(const BwdTcMaps& maps, const BwdTcParams& bp, int blocks, cudaStr
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemT<VG>::kBytes));
   {
     ProfScope ps(VG ? kProfKdaBwdState : kProfSgBwdState, s);
-    kern<<<blocks, 640, SmemT<VG>::kBytes, s>>>(maps, bp);
+    kern<<<blocks, kThreads, SmemT<VG>::kBytes, s>>>(maps, bp);
   }
   JLA_LAUNCH_OK();
   return JLA_OK;
@@ -473,7 +604,10 @@ int launch_sg_bwd_state_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scra
   const uint64_t tokens = (uint64_t)p.B * p.T, slots = (uint64_t)pl.nc * p.H;
   const bool vg = p.kind == JLA_KIND_KDA;
   BwdTcMaps maps;
-  bool ok = tma::encode_3d(&maps.d_o, io.d_o, p.V, p.H, tokens, 64);
+  bool ok = tma::encode_3d(&maps.d_o, io.d_o, p.V, p.H, tokens, 64) && tma::encode_3d(&maps.dv, io.dv, p.V, p.H, tokens, 64) &&
+            tma::encode_3d(&maps.dh_res, scratch + pl.dh, p.K, 1, slots * p.V, p.V);
+  if (ok && pl.delta) ok = tma::encode_3d(&maps.dvn_res, scratch + pl.dvn, 64, 1, slots * p.V, p.V);
+  if (ok && !pl.delta) maps.dvn_res = maps.d_o;
   if (vg) {
     ok = ok && tma::encode_3d(&maps.q, c.res + pl.kda_q, p.K, 1, slots * 64, 64) &&
          tma::encode_3d(&maps.k, c.res + pl.kda_kr, p.K, 1, slots * 64, 64) &&
@@ -494,8 +628,6 @@ int launch_sg_bwd_state_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scra
   bp.d_final = io.d_final;
   bp.dv = io.dv;
   bp.dh0 = io.dh0;
-  bp.dhT_out = scratch + pl.dh;
-  bp.dvnT_out = scratch + pl.dvn;
   bp.H = p.H;
   bp.Hk = p.Hk;
   bp.scale = p.scale;

@@ -520,12 +520,6 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
           }
           umma::st_32x32b_x16(tl + cWb + 16 * half, pk);
           umma::st_32x32b_x16(tl + cVg + 16 * half, pg);
-          if (save) {  // (the shared-memory stores run while the TMEM stores complete)
-            ok = wait(bars + B_WV_FREE, 0, abort_flag);  // this chunk's W^T has left the tile
-            if (!ok) break;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) *swz_chunk(stgWV, v, 4 * half + i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-          }
           umma::wait_st();
           umma::fence_before_sync();
           __syncwarp();
@@ -534,7 +528,11 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
             mbar_arrive(bars + B_EMPTYA + sa);  // done with this chunk's gate vectors
           }
           if (tid == 128) JLA_MARK(it, 7);
-          if (save) {
+          if (save) {  // only after the chain has been handed on: the tile may still be on its way out with W^T
+            ok = wait(bars + B_WV_FREE, 0, abort_flag);
+            if (!ok) break;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) *swz_chunk(stgWV, v, 4 * half + i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
             umma::fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + B_WV_FULL);
