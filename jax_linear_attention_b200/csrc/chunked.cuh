@@ -140,6 +140,7 @@ struct ChunkedCtx {
 };
 
 int launch_prep(const ChunkedCtx& c, cudaStream_t s);                           // tables, G/beta/runs, T0, l2norm
+int launch_kkt_tc(const ChunkedCtx& c, cudaStream_t s);                         // T0, Ag for K = 128 (tcgen05)
 int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s);                       // KDA: gate-folded operands, P, Ag
 int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cudaStream_t s);  // after the reverse pass
 int launch_sg_fwd(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s);

@@ -234,6 +234,7 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
   }
   if (!pl.delta) return JLA_OK;
   if (p.kind == JLA_KIND_KDA) return launch_kda_prep(c, s);
+  if (use_tc_kernels(p)) return launch_kkt_tc(c, s);  // K = V = 128: the inverse on the Blackwell tensor cores
   KktParams kp{meta, c.k_eff, gates, runs, c.res + pl.t0, c.res + pl.ag, p.H, p.Hk};
   const int blocks = pl.nc * p.H;
   if (p.dtype == JLA_DTYPE_BF16) {
