@@ -63,32 +63,64 @@ __global__ void build_tables_kernel(Rows rows, int nc, ChunkMeta* meta, int2* ro
   for (int c = total + tid; c < nc; c += nt) meta[c] = ChunkMeta{0, 0, 0, 0};
 }
 
-// One block per chunk slot: G = chunk-local cumsum of g and beta, head-major; run ids of the tokens; flag bit 0.
-__global__ void prep_gates_kernel(Rows rows, int H, const float* __restrict__ g, const float* __restrict__ beta,
-                                  ChunkMeta* meta, float* __restrict__ gates, unsigned char* __restrict__ runs) {
-  const int c = blockIdx.x;
-  const ChunkMeta m = meta[c];
-  if (m.len == 0) return;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    float* out = gates + ((long)c * H + h) * 128;
-    float acc = 0.f;
-    for (int i = 0; i < kChunk; ++i) {
-      const bool ok = i < m.len;
-      if (ok && g) acc += g[(long)(m.tok0 + i) * H + h];
-      out[i] = acc;
-      out[64 + i] = (ok && beta) ? beta[(long)(m.tok0 + i) * H + h] : 0.f;
+// Gate vectors of every (chunk, head): G = chunk-local cumulative sum of g, beta head-major; plus, once per chunk,
+// the run ids of its tokens and flag bit 0. One warp per (chunk, head): a lane owns two tokens, the cumulative sum is
+// a warp scan. Blocks of eight warps cover eight heads of one chunk; the block of the first head group also writes
+// the chunk's run ids and, for dense rows (`dense_tables`), the chunk table itself, so that the one-block table kernel
+// only runs for packed sequences.
+__global__ void __launch_bounds__(256) prep_gates_kernel(Rows rows, int H, int nc, int dense_tables, const float* __restrict__ g,
+                                                         const float* __restrict__ beta, ChunkMeta* meta, int2* row_chunks,
+                                                         float* __restrict__ gates, unsigned char* __restrict__ runs) {
+  const int c = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  ChunkMeta m;
+  if (dense_tables) {
+    const int per = (rows.T + kChunk - 1) / kChunk;
+    const int r = c / max(per, 1), i = c - r * per;
+    m.tok0 = r * rows.T + i * kChunk;
+    m.len = min(kChunk, rows.T - i * kChunk);
+    m.row = r;
+    m.flags = 0;
+    if (blockIdx.y == 0 && threadIdx.x == 0 && c == 0) {
+      for (int rr = 0; rr <= rows.B; ++rr) row_chunks[rr] = make_int2(rr * per, rr < rows.B ? per : 0);
+    }
+  } else {
+    m = meta[c];
+  }
+  if (blockIdx.y == 0 && warp == 7) {  // run ids and the "starts a document" flag, once per chunk (also for len == 0)
+    int row_tok0 = 0, row_len = 0;
+    if (m.len > 0) rows.range(m.row, row_tok0, row_len);
+    const int t0 = 2 * lane, t1 = 2 * lane + 1;
+    const int s0 = (m.len > 0 && t0 > 0 && t0 < m.len && rows.resets(m.tok0 + t0, row_tok0)) ? 1 : 0;
+    const int s1 = (m.len > 0 && t1 < m.len && rows.resets(m.tok0 + t1, row_tok0)) ? 1 : 0;
+    int incl = s0 + s1;  // inclusive scan of the number of document starts up to this lane's second token
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += x;
+    }
+    runs[(long)c * 64 + t0] = (unsigned char)(incl - s1);
+    runs[(long)c * 64 + t1] = (unsigned char)incl;
+    if (lane == 0) {
+      m.flags = (m.len > 0 && rows.resets(m.tok0, row_tok0)) ? 1 : 0;
+      if (dense_tables || m.flags) meta[c] = m;
     }
   }
-  if (threadIdx.x == 0) {
-    int row_tok0, row_len;
-    rows.range(m.row, row_tok0, row_len);
-    int run = 0;
-    for (int i = 0; i < kChunk; ++i) {
-      if (i > 0 && i < m.len && rows.resets(m.tok0 + i, row_tok0)) ++run;
-      runs[(long)c * 64 + i] = (unsigned char)run;
-    }
-    if (rows.resets(m.tok0, row_tok0)) meta[c].flags = 1;
+  const int h = blockIdx.y * 8 + warp;
+  if (h >= H || m.len == 0) return;
+  const int t0 = 2 * lane, t1 = 2 * lane + 1;
+  const float g0 = (g && t0 < m.len) ? g[(long)(m.tok0 + t0) * H + h] : 0.f;
+  const float g1 = (g && t1 < m.len) ? g[(long)(m.tok0 + t1) * H + h] : 0.f;
+  const float b0 = (beta && t0 < m.len) ? beta[(long)(m.tok0 + t0) * H + h] : 0.f;
+  const float b1 = (beta && t1 < m.len) ? beta[(long)(m.tok0 + t1) * H + h] : 0.f;
+  float incl = g0 + g1;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float x = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += x;
   }
+  float* out = gates + ((long)c * H + h) * 128;
+  *reinterpret_cast<float2*>(out + t0) = make_float2(incl - g1, incl);
+  *reinterpret_cast<float2*>(out + 64 + t0) = make_float2(b0, b1);
 }
 
 struct KktParams {
@@ -214,7 +246,8 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
   int2* row_chunks = reinterpret_cast<int2*>(c.res + pl.row_chunks);
   float* gates = reinterpret_cast<float*>(c.res + pl.gates);
   unsigned char* runs = reinterpret_cast<unsigned char*>(c.res + pl.runs);
-  {
+  const bool dense = p.cu_seqlens == nullptr;
+  if (!dense) {
     ProfScope ps(kProfTables, s);
     build_tables_kernel<<<1, 256, 0, s>>>(rows, pl.nc, meta, row_chunks);
   }
@@ -222,7 +255,9 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
   {
     ProfScope ps(kProfGates, s);
     // KDA gates are per channel: its own prologue folds them into the operands; here G stays zero
-    prep_gates_kernel<<<pl.nc, 64, 0, s>>>(rows, p.H, p.kind == JLA_KIND_KDA ? nullptr : p.g, p.beta, meta, gates, runs);
+    prep_gates_kernel<<<dim3(pl.nc, (p.H + 7) / 8), 256, 0, s>>>(rows, p.H, pl.nc, dense ? 1 : 0,
+                                                                 p.kind == JLA_KIND_KDA ? nullptr : p.g, p.beta, meta, row_chunks,
+                                                                 gates, runs);
   }
   JLA_LAUNCH_OK();
   if (pl.l2norm) {
