@@ -251,6 +251,22 @@ int jla_profile_read(int kernel_id, double* total_ms, int* launches);
 int jla_selftest_umma(int m, int n, int kd, int a_mn_major, int b_mn_major, const void* a, const void* b, float* c,
                       int* status, jla_stream_t stream);
 
+/* Scan over the pieces of a sequence cut into independently processed pieces that are joined by affine maps
+ * S_out[p] = M[p] S_in[p] + E[p]; replaces gdr_piece_scan / gdr_piece_scan_bwd
+ * (src/jla/ops/mosaic_gpu/scalar_gate_scan.py:49-140), the fp32 scan between the passes of the reference's intra-GPU
+ * sequence split (src/jla/ops/mosaic_gpu/scalar_gate.py:199-271). All tensors fp32, device memory:
+ *   maps [P, H, K, K]; cont [P] int32 (piece p continues the document of piece p - 1: its entering state is the
+ *   state leaving p - 1, otherwise zero and its map is never read); boundary [H, K, V] or NULL (= zero);
+ *   forward  (backward = 0): states [P, H, K, V] holds E on entry and S_out on return for pieces p_lo .. p_hi - 1
+ *            (piece 0 continues `boundary`); ds_out is ignored;
+ *   backward (backward = 1): states holds dS_in (the entering-state gradients for a zero final-state cotangent) and
+ *            gets M^T dS_out added; ds_out [P, H, K, V] (zero-filled by the caller) receives every piece's
+ *            final-state cotangent; pieces p_hi - 1 down to p_lo; piece P - 1 takes `boundary` as its cotangent.
+ * K in {64, 128}, V a multiple of 32. The range arguments let a caller scan the pieces that do not depend on a
+ * neighbouring rank's state before that state has arrived. */
+int jla_piece_scan(int backward, int P, int H, int K, int V, const float* maps, const int32_t* cont, const float* boundary,
+                   float* states, float* ds_out, int p_lo, int p_hi, jla_stream_t stream);
+
 /* Failure status of the tensor-core kernels. Every wait inside them (on a TMA copy, an MMA completion or another
  * warp role) is bounded: a wait that runs out makes the kernel return normally with a non-zero code in a status
  * word that lives on the GPU (one word per GPU that loads the library), and the results of that launch are

@@ -76,6 +76,9 @@ def load() -> C.CDLL:
     lib.jla_linear_attention_fwd.argtypes = [C.POINTER(Problem), C.POINTER(FwdIO), C.c_void_p]
     lib.jla_linear_attention_bwd.restype = C.c_int
     lib.jla_linear_attention_bwd.argtypes = [C.POINTER(Problem), C.POINTER(BwdIO), C.c_void_p]
+    lib.jla_piece_scan.restype = C.c_int
+    lib.jla_piece_scan.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     lib.jla_device_status.restype = C.c_int
     lib.jla_device_status.argtypes = [C.POINTER(C.c_int), C.c_void_p]
     lib.jla_selftest_bounded_wait.restype = C.c_int

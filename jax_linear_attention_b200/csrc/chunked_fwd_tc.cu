@@ -43,7 +43,8 @@ constexpr int kThreads = 640;  // 20 warps: loads, products, two store threads, 
 // (32 slots per chunk: 0, 1, 3, 4, 6, 7 by the first state warp, 20 and up by the first score warp, the others by the MMA issuer); jla_debug_fwd_trace() copies them out.
 #ifdef JLA_TRACE
 __device__ unsigned long long g_fwd_trace[64 * 32];
-__device__ unsigned long long g_fwd_cta[4096 * 4];  // per CTA: kernel entry, first chunk start, last chunk end, exit
+__device__ unsigned long long g_fwd_cta[4096 * 4];
+__device__ unsigned long long g_fwd_warps[64 * 16 * 6];  // first CTA: per chunk and compute warp, six event times  // per CTA: kernel entry, first chunk start, last chunk end, exit
 __device__ __forceinline__ unsigned long long global_timer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -53,9 +54,16 @@ __device__ __forceinline__ unsigned long long global_timer() {
   do {                                                                                         \
     if (blockIdx.x == 0 && (it) < 64) g_fwd_trace[(it) * 32 + (slot)] = global_timer();         \
   } while (0)
+#define JLA_WMARK(it, w, ev)                                                                                   \
+  do {                                                                                                         \
+    if (blockIdx.x == 0 && (it) < 64 && lane == 0) g_fwd_warps[((it) * 16 + (w)) * 6 + (ev)] = global_timer(); \
+  } while (0)
 #else
 #define JLA_MARK(it, slot) \
   do {                     \
+  } while (0)
+#define JLA_WMARK(it, w, ev) \
+  do {                       \
   } while (0)
 #endif
 
@@ -122,7 +130,11 @@ __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, volatile in
     uint32_t done;
     asm volatile(
         "{\n.reg .pred p;\n"
+#ifdef JLA_TEST_WAIT
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+#endif
         "selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(done)
         : "r"(addr), "r"(parity)
@@ -409,6 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
         umma::fence_after_sync();
       }
       if (tid == 128) JLA_MARK(it, 0);
+      JLA_WMARK(it, warp - 4, 0);
 #ifdef JLA_TRACE
       if (tid == 128 && it == 0 && blockIdx.x < 4096) g_fwd_cta[blockIdx.x * 4 + 1] = global_timer();
 #endif
@@ -440,6 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + B_ST);
       if (tid == 128) JLA_MARK(it, 1);
+      JLA_WMARK(it, warp - 4, 1);
       if (save) {  // this half row of h^T into the staging tile (column block `half`, row v)
         if (it > 0) {
           ok = wait(bars + B_HS_FREE, ph ^ 1, abort_flag);
@@ -463,6 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
         if (!ok) break;
         umma::fence_after_sync();
         if (tid == 128) JLA_MARK(it, 3);
+        JLA_WMARK(it, warp - 4, 2);
         {
           float x[32];
           ld_row32<T>(x, tl + cA1 + j0);
@@ -495,6 +510,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
             mbar_arrive(bars + B_EMPTYB + sb);  // done with this chunk's v
           }
           if (tid == 128) JLA_MARK(it, 4);
+          JLA_WMARK(it, warp - 4, 3);
           if (save) {
             umma::fence_async_smem();
             __syncwarp();
@@ -506,6 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
         if (!ok) break;
         umma::fence_after_sync();
         if (tid == 128) JLA_MARK(it, 6);
+        JLA_WMARK(it, warp - 4, 4);
         {
           float x[32];
           ld_row32<T>(x, tl + cA1 + j0);
@@ -528,6 +545,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
             mbar_arrive(bars + B_EMPTYA + sa);  // done with this chunk's gate vectors
           }
           if (tid == 128) JLA_MARK(it, 7);
+          JLA_WMARK(it, warp - 4, 5);
           if (save) {  // only after the chain has been handed on: the tile may still be on its way out with W^T
             ok = wait(bars + B_WV_FREE, 0, abort_flag);
             if (!ok) break;
@@ -622,9 +640,11 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
       const float* Gs = st_G(sa);
       const unsigned char* runs = st_runs(sa);
       if (tid == 384) JLA_MARK(it, 20);
+      JLA_WMARK(it, warp - 4, 0);
       if (!wait(bars + B_PDONE, it & 1, abort_flag)) return false;
       umma::fence_after_sync();
       if (tid == 384) JLA_MARK(it, 21);
+      JLA_WMARK(it, warp - 4, 1);
       float acc[4][4];
       umma::ld_16x256b<4>(acc, tl + cP + 32 * half);
       umma::wait_ld();
@@ -665,6 +685,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + B_PA0 + buf);
       if (tid == 384) JLA_MARK(it, 22);
+      JLA_WMARK(it, warp - 4, 2);
       return true;
     };
     const int n_out = p.state_only ? 0 : n;
@@ -691,6 +712,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
       if (!ok) break;
       umma::fence_after_sync();
       if (tid == 384) JLA_MARK(it, 24);
+      JLA_WMARK(it, warp - 4, 3);
       const int tok0 = st_meta(sa)[0], len = st_meta(sa)[1];
       // Free the accumulator, then transpose through the chunk's dead q tile ([64 tokens x V], swizzled): a full chunk
       // leaves from there as two TMA tensor stores issued by the output store thread.
@@ -721,6 +743,7 @@ __global__ void __launch_bounds__(kThreads, 1) sg_fwd_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + B_O_FULL0 + (it & 1));
       if (tid == 384) JLA_MARK(it, 25);
+      JLA_WMARK(it, warp - 4, 4);
     }
   }
   umma::fence_before_sync();
@@ -808,6 +831,9 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
 }  // namespace jla
 
 #ifdef JLA_TRACE
+extern "C" int jla_debug_fwd_warps(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, jla::g_fwd_warps, sizeof(unsigned long long) * 64 * 16 * 6) == cudaSuccess ? 0 : -4;
+}
 extern "C" int jla_debug_fwd_cta(unsigned long long* out, int n) {
   return cudaMemcpyFromSymbol(out, jla::g_fwd_cta, sizeof(unsigned long long) * 4 * n) == cudaSuccess ? 0 : -4;
 }

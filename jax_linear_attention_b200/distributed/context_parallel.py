@@ -124,10 +124,7 @@ class _ContextParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, call, kind, group, seg, want_final, *tensors):
         # tensors = (q, k, v, *gates, h0 or None)
-        rank, world = dist.get_rank(group), dist.get_world_size(group)
-        ranks = dist.get_process_group_ranks(group)
-        prev_rank = ranks[rank - 1] if rank > 0 else None
-        next_rank = ranks[rank + 1] if rank < world - 1 else None
+        rank, world, prev_rank, next_rank = _group_info(group)
         *xs, h0 = tensors
         q = xs[0]
         batch, t_local = q.shape[:2]
@@ -254,6 +251,64 @@ class _ContextParallel(torch.autograd.Function):
         return (None, None, None, None, None, *grads, d_h0)
 
 
+def _group_info(group):
+    """``(rank, world, prev_rank, next_rank)`` of this process in ``group``; ``group=False`` means a single process
+    with no process group at all (the intra-GPU split: nothing is sent anywhere)."""
+    if group is False:
+        return 0, 1, None, None
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ranks = dist.get_process_group_ranks(group)
+    return rank, world, (ranks[rank - 1] if rank > 0 else None), (ranks[rank + 1] if rank < world - 1 else None)
+
+
+def piece_scan(maps, cont, cont_device, boundary, states, p_lo: int, p_hi: int, *, ds_out=None):
+    """The scan over pieces ``p_lo .. p_hi - 1`` (forward: ``states`` holds E and becomes S_out) or, with ``ds_out``,
+    ``p_hi - 1`` down to ``p_lo`` of the transposed recursion (``states`` holds dS_in). CUDA float32 tensors run the
+    library's scan kernel (``jla_piece_scan``); anything else (the CPU ranks of the tests, float64) takes the same
+    recursion written with torch products."""
+    if p_lo >= p_hi:
+        return
+    pieces, heads, kd, vd = states.shape
+    backward = ds_out is not None
+    if states.is_cuda:
+        if maps is None:  # no piece continues another: only the last piece's cotangent has to be placed
+            if backward and p_hi == pieces:
+                ds_out[-1] = 0 if boundary is None else boundary
+            return
+        if states.dtype != torch.float32 or maps.dtype != torch.float32:
+            raise ValueError("the piece scan kernel takes float32 states and maps")
+        import ctypes as C
+
+        from .. import _lib
+
+        lib = _lib.load()
+        for t in (maps, states, boundary, ds_out):
+            if t is not None and not t.is_contiguous():
+                raise ValueError("the piece scan kernel takes contiguous tensors")
+        with torch.cuda.device(states.device):
+            stream = torch.cuda.current_stream(states.device).cuda_stream
+            _lib.check(lib.jla_piece_scan(1 if backward else 0, pieces, heads, kd, vd, maps.data_ptr(),
+                                          cont_device.data_ptr(), None if boundary is None else boundary.data_ptr(),
+                                          states.data_ptr(), None if ds_out is None else ds_out.data_ptr(),
+                                          p_lo, p_hi, C.c_void_p(stream)), "piece scan")
+        return
+    if not backward:
+        for p in range(p_lo, p_hi):
+            if cont[p]:
+                prev = states[p - 1] if p > 0 else (boundary if boundary is not None else torch.zeros_like(states[0]))
+                states[p] += maps[p] @ prev
+        return
+    for p in range(p_hi - 1, p_lo - 1, -1):
+        if p == pieces - 1:
+            ds_out[p] = 0 if boundary is None else boundary
+        elif cont[p + 1]:
+            ds_out[p] = states[p + 1]
+        else:
+            continue
+        if cont[p] and maps is not None:
+            states[p] += maps[p].transpose(-1, -2) @ ds_out[p]
+
+
 def _piece_table(ids, cont0: bool, piece_len: int):
     """Cut points of the local row: document starts plus every ``piece_len`` tokens inside a document.
     Returns (cu, cont): ``cu`` has P + 1 entries; ``cont[p]`` says piece p continues the document of piece p - 1
@@ -283,17 +338,17 @@ class PiecePlan:
         # cost a synchronous host-to-device copy in the middle of the step
         self.cont_index = torch.tensor([p for p in range(1, len(cont)) if cont[p]], dtype=torch.long,
                                        device=cu_device.device)
+        self.cont_device = torch.tensor([1 if c else 0 for c in cont], dtype=torch.int32, device=cu_device.device)
 
 
 def plan_pieces(segment_ids, piece_len: int, *, group=None, t_local: int | None = None, device=None) -> PiecePlan:
     """Builds the piece table of this rank's shard (collective: neighbouring ranks exchange one document id, and the
     ids are read on the host). A caller whose document layout stays the same over many calls builds the plan once and
-    passes it as ``piece_len=plan``; that also keeps the device-to-host copy out of the step."""
-    group = group if group is not None else dist.group.WORLD
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    ranks = dist.get_process_group_ranks(group)
-    prev_rank = ranks[rank - 1] if rank > 0 else None
-    next_rank = ranks[rank + 1] if rank < world - 1 else None
+    passes it as ``piece_len=plan``; that also keeps the device-to-host copy out of the step. ``group=False``: a single
+    process without a process group (the split inside one GPU)."""
+    if group is not False:
+        group = group if group is not None else dist.group.WORLD
+    rank, world, prev_rank, next_rank = _group_info(group)
     if segment_ids is None:
         ids = torch.zeros(t_local, dtype=torch.int64)
         cont0 = rank > 0
@@ -323,10 +378,7 @@ class _PiecewiseContextParallel(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, pcall, kind, group, seg, piece_len, *tensors):
-        rank, world = dist.get_rank(group), dist.get_world_size(group)
-        ranks = dist.get_process_group_ranks(group)
-        prev_rank = ranks[rank - 1] if rank > 0 else None
-        next_rank = ranks[rank + 1] if rank < world - 1 else None
+        rank, world, prev_rank, next_rank = _group_info(group)
         *xs, h0 = tensors
         q, k, v, *gates = xs
         t_local, heads, kd, vd = q.shape[1], v.shape[2], q.shape[3], v.shape[3]
@@ -358,14 +410,12 @@ class _PiecewiseContextParallel(torch.autograd.Function):
                             vz=torch.zeros(1, t_local, heads, kd, dtype=v.dtype, device=dev))
                     eye, vz = plan.buffers["eye"], plan.buffers["vz"]
                     _, m_map = pcall(kind, [plain[0], plain[1], vz, *plain[3:]], cu_t, eye)
-                    m_map = m_map.to(sdt)
-                s_out = e_state.to(sdt).clone()
+                    m_map = m_map.to(sdt).contiguous()
+                s_out = e_state.to(sdt).clone().contiguous()
                 s_recv = torch.zeros(1, heads, kd, vd, dtype=sdt, device=dev)
 
                 def scan(p0, p1):  # S_out[p] = E[p] + M[p] S_out[p - 1] along a document's pieces
-                    for p in range(p0, p1):
-                        if cont[p]:
-                            torch.baddbmm(s_out[p], m_map[p], s_out[p - 1] if p > 0 else s_recv[0], out=s_out[p])
+                    piece_scan(m_map, cont, plan.cont_device, s_recv[0], s_out, p0, p1)
 
                 # the shard's last document starts at piece `tail`: its states do not depend on the received state
                 tail = max((p for p in range(pieces) if not cont[p]), default=0)
@@ -400,7 +450,7 @@ class _PiecewiseContextParallel(torch.autograd.Function):
                 o, f = pcall(kind, leaves, cu_t, s_in_leaf)
         finally:
             share.__exit__(None, None, None)
-        ctx.state = dict(leaves=leaves, s_in_leaf=s_in_leaf, o=o, f=f, m_map=m_map, cont=cont, group=group,
+        ctx.state = dict(leaves=leaves, s_in_leaf=s_in_leaf, o=o, f=f, m_map=m_map, cont=cont, group=group, plan=plan,
                          prev_rank=prev_rank, next_rank=next_rank, has_h0=has_h0, h0_given=h0 is not None, sdt=sdt)
         return o.detach(), f.detach()[-1:].to(sdt)
 
@@ -414,21 +464,13 @@ class _PiecewiseContextParallel(torch.autograd.Function):
         # entering-state gradients for a zero final-state cotangent
         with state_grads_only():
             (e_grad,) = torch.autograd.grad([o], [s_in_leaf], [d_o], retain_graph=True)
-        ds_in = e_grad.to(sdt).clone()
+        ds_in = e_grad.to(sdt).clone().contiguous()
         ds_out = torch.zeros_like(ds_in)
         g_next = torch.zeros_like(ds_in[:1])
-        m_t = None if m_map is None else m_map.transpose(-1, -2)
+        plan = st["plan"]
 
         def scan(p_hi, p_lo):  # pieces p_hi - 1 down to p_lo: dS_in[p] = e[p] + M[p]^T dS_out[p]
-            for p in range(p_hi - 1, p_lo - 1, -1):
-                if p == pieces - 1:
-                    ds_out[p] = g_next[0]
-                elif cont[p + 1]:
-                    ds_out[p] = ds_in[p + 1]
-                else:
-                    continue
-                if cont[p] and m_t is not None:
-                    torch.baddbmm(ds_in[p], m_t[p], ds_out[p], out=ds_in[p])
+            piece_scan(m_map, cont, plan.cont_device, g_next[0], ds_in, p_lo, p_hi, ds_out=ds_out)
 
         # the shard's first document ends before piece `head`: its gradients do not depend on the received one
         head = min((p for p in range(1, pieces) if not cont[p]), default=pieces)
@@ -441,7 +483,7 @@ class _PiecewiseContextParallel(torch.autograd.Function):
         if st["next_rank"] is not None:
             recv_state(g_next, st["next_rank"], group, "state gradient")
         elif d_f is not None:
-            g_next = d_f.to(sdt).contiguous()
+            g_next = d_f.to(sdt).contiguous().clone()
         if head < pieces:
             scan(pieces, head)
         else:
@@ -507,7 +549,8 @@ def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: s
 
     ``piece_len`` (tokens, or a ``PiecePlan`` from ``plan_pieces``; batch 1 only) cuts documents into independent
     pieces joined by affine maps, which is what lets a long document use more than one SM per head and more than
-    one rank.
+    one rank. With ``group=False`` and a ``piece_len`` the call involves no process group at all: it is the split of
+    one sequence inside one GPU (``ops.cuda`` applies it by itself when a call would leave most SMs idle).
 
     ``call(kind, leaves, state, seg, tslice, row)`` or, with pieces, ``piece_call(kind, leaves, cu, init)`` may
     replace the op (tests inject the CPU oracle).
@@ -535,5 +578,5 @@ def context_parallel_linear_attention(kind: str, q, k, v, *, group=None, impl: s
     else:
         call = call or _default_call(impl, inputs)
         o, f = _ContextParallel.apply(call, kind, group, seg, want_final, q, k, v, *gates, h0)
-    last = dist.get_rank(group) == dist.get_world_size(group) - 1
+    last = group is False or dist.get_rank(group) == dist.get_world_size(group) - 1
     return o, (f if (want_final and last) else None)

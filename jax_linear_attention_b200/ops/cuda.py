@@ -247,6 +247,57 @@ class _LinearAttention(torch.autograd.Function):
         return dq, dk, dv, dg, dbeta, dh0, None
 
 
+# Sequence split policy for the serial state passes, after ``pieces()`` of the reference
+# (``src/jla/ops/mosaic_gpu/scalar_gate.py:98-148``): a state pass runs one CTA per (row, head), so a call with few
+# rows and heads leaves most SMs idle while each CTA walks a long chain of chunks. Such a call is cut along T into
+# pieces that run as independent rows, joined by affine maps (``distributed.context_parallel``, ``group=False``).
+MAX_SPLIT_CTAS = 32          # split only when rows * heads is at most this
+MIN_PIECE_CHUNKS = 8         # every piece keeps at least this many chunks
+MAX_DELTA_PIECES = 8         # the delta rule pays an extra state pass for the maps and their scan
+DELTA_PIECE_CHUNKS_ABOVE_4 = 32
+
+
+def pieces(batch: int, heads: int, seq_len: int, *, delta: bool, sm_count: int = 148) -> int:
+    """Pieces per sequence for the serial state passes (a power of two; 1 = no split)."""
+    ctas = max(batch * heads, 1)
+    if ctas > MAX_SPLIT_CTAS:
+        return 1
+    chunks = -(-seq_len // CHUNK)
+    limit = min(MAX_DELTA_PIECES, sm_count // ctas) if delta else sm_count // ctas
+    cp = 1
+    while 2 * cp <= limit and chunks // (2 * cp) >= MIN_PIECE_CHUNKS:
+        if delta and 2 * cp > 4 and chunks // (2 * cp) < DELTA_PIECE_CHUNKS_ABOVE_4:
+            break
+        cp *= 2
+    return cp
+
+
+class no_pieces:
+    """``with no_pieces():`` calls run unsplit whatever the policy says (the split's own passes, A/B timing)."""
+    active = False
+
+    def __enter__(self):
+        self._outer = no_pieces.active
+        no_pieces.active = True
+        return self
+
+    def __exit__(self, *exc):
+        no_pieces.active = self._outer
+
+
+def _split_applies(kind, q, v, cu_seqlens, initial_state, precision) -> int:
+    """Pieces per sequence for this call, 1 if it runs unsplit. The split needs the chunked tensor-core path (16-bit
+    tensors with K = V = 128), one packed row, and no cu_seqlens (the pieces themselves are passed that way)."""
+    if no_pieces.active or _PassOptions.share is not None or cu_seqlens is not None or q.shape[0] != 1:
+        return 1
+    if q.dtype == torch.float32 or q.shape[-1] != 128 or v.shape[-1] != 128 or _path(precision) == "recurrent":
+        return 1
+    if kind == "kda" and q.dtype != torch.bfloat16:
+        return 1
+    sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+    return pieces(1, v.shape[2], q.shape[1], delta=kind != "simple_gla", sm_count=sms)
+
+
 def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_state, cu_seqlens, segment_ids,
          use_qk_l2norm=False, chunk_size=CHUNK, precision=None, sub_chunk=None):
     del sub_chunk  # the kernels choose their own sub-blocking
@@ -263,6 +314,18 @@ def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_stat
     dev = q.device
     if scale is None:
         scale = q.shape[-1] ** -0.5
+    cp = _split_applies(kind, q, v, cu_seqlens, initial_state, precision)
+    if cp > 1:
+        from ..distributed.context_parallel import context_parallel_linear_attention
+
+        piece_len = -(-(-(-q.shape[1] // CHUNK)) // cp) * CHUNK  # whole chunks per piece
+        gates = {n: x for n, x in (("g", g), ("beta", beta)) if x is not None}
+        extra = dict(use_qk_l2norm=use_qk_l2norm) if kind != "simple_gla" else {}
+        with no_pieces():
+            o, final = context_parallel_linear_attention(
+                kind, q, k, v, group=False, impl="cuda", piece_len=piece_len, scale=scale, initial_state=initial_state,
+                output_final_state=output_final_state, segment_ids=segment_ids, precision=precision, **gates, **extra)
+        return o, (final if output_final_state else None)
 
     def f32(x):
         return None if x is None else x.to(device=dev, dtype=torch.float32).contiguous()

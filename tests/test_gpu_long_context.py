@@ -4,12 +4,15 @@ beyond 32 bits. The acceptance checks are those of the reference's long-context 
 (tests/test_long_context.py:238-267 and :302-319 of the reference):
 
 * the one call equals two chained calls over the halves (the second starts from the first's final state) -- bit for
-  bit here, because the split (532,480 = 8,320 chunks) is chunk aligned and both runs walk the same chunks;
+  bit here, because the split (532,480 = 8,320 chunks) is chunk aligned and both runs walk the same chunks (with
+  the library's own sequence split switched off: a call with one row of 16 heads is otherwise cut into pieces joined
+  by affine maps, and then the one call and the halves cut at different places; the split call is held to the
+  unsplit one at 1e-2, the tolerance of the path);
 * 256-token windows of the one call's output agree with the float64 token loop of the oracle started from the state
   carried into the window (tolerance of the path: relative L2 <= 1e-2);
-* gradients: one call against the two chained halves (<= 4e-3 relative L2; equal bits are not required because the
-  state gradient crosses the split through a float32 tensor instead of staying in the accumulator), and the last
-  window against the oracle's autograd (<= 1e-2).
+* gradients: one call (split into pieces by the library) against the two chained halves (each split on its own),
+  <= 1e-2 relative L2 (the two runs cut the sequence at different places), and the last window against the
+  oracle's autograd (<= 1e-2).
 
 Inputs are drawn on the device (a host round trip of 4 x 8.7 GB of float32 would dominate the test).
 """
@@ -72,12 +75,12 @@ def _call(x, lo, hi, state=None, grad=False):
 
 def _state_before(x, start):
     """The state carried into token ``start`` (a CUDA pass over the prefix that skips scores and outputs)."""
-    from jax_linear_attention_b200.ops.cuda import final_state_only
+    from jax_linear_attention_b200.ops.cuda import final_state_only, no_pieces
 
     if start == 0:
         return None
     assert x["seg_host"][0, start] == x["seg_host"][0, start - 1], "window must not begin at a document start"
-    with torch.no_grad(), final_state_only():
+    with torch.no_grad(), final_state_only(), no_pieces():
         return _call(x, 0, start)[1]
 
 
@@ -105,9 +108,17 @@ def _windows(seg_row):
 
 @needs_big_gpu
 def test_one_call_equals_chained_halves_and_float64_windows(inputs):
+    from jax_linear_attention_b200.ops.cuda import no_pieces
+
     x = inputs
     with torch.no_grad():
+        o_split, final_split, _ = _call(x, 0, T_BIG)  # the default: one row of 16 heads is split into pieces
+    with torch.no_grad(), no_pieces():
         o, final, _ = _call(x, 0, T_BIG)
+        num = float((o_split[:, ::7].float() - o[:, ::7].float()).norm())
+        assert 0 < num <= 1e-2 * float(o[:, ::7].float().norm())
+        assert float((final_split - final).norm()) <= 1e-2 * float(final.norm())
+        del o_split, final_split
         o1, s1, _ = _call(x, 0, SPLIT)
         assert torch.equal(o[:, :SPLIT], o1)
         del o1
@@ -124,9 +135,11 @@ def test_one_call_equals_chained_halves_and_float64_windows(inputs):
 
 @needs_big_gpu
 def test_gradients_of_one_call_equal_chained_halves_and_a_float64_window(inputs):
+    from jax_linear_attention_b200.ops.cuda import no_pieces
+
     x = inputs
     names = ("q", "k", "v", "g", "beta")
-    o, _, leaves = _call(x, 0, T_BIG, grad=True)
+    o, _, leaves = _call(x, 0, T_BIG, grad=True)  # the default call: split into pieces
     one = torch.autograd.grad(o, [leaves[n] for n in names], x["do"])
     del o, leaves
     assert all(bool(torch.isfinite(t[:, ::4097].float()).all()) for t in one)
@@ -140,7 +153,7 @@ def test_gradients_of_one_call_equal_chained_halves_and_a_float64_window(inputs)
         for label, got, want in (("half 1", one[i][:, :SPLIT], chained[i]), ("half 2", one[i][:, SPLIT:], chained[5 + i])):
             num = float((got.float() - want.float()).norm())
             den = float(want.float().norm())
-            assert num <= 4e-3 * den, (n, label, num / den)
+            assert num <= 1e-2 * den, (n, label, num / den)
     del chained
     # the last window's gradients depend on nothing after it: float64 autograd of the token loop, started from the
     # state the kernels carried into the window

@@ -1,0 +1,77 @@
+"""The sequence split inside one GPU: a call with few rows and heads is cut along T into pieces that run as
+independent kernel rows, joined by affine maps and a device-side scan (the reference's intra-GPU split,
+src/jla/ops/mosaic_gpu/scalar_gate.py:129-271, scalar_gate_scan.py:49-140). Checked here: the scan kernel against the
+same recursion written with torch products, and the split call against the unsplit call (tolerance of the path,
+relative L2 <= 1e-2: the pieces re-enter with an fp32 state and the maps come from passes with 16-bit operands) and
+against the float64 oracle."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.cases import make_case, rel_l2
+from tests._util import compare, run_cuda, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("K,V", [(128, 128), (64, 64), (128, 64)])
+def test_scan_kernel_matches_the_recursion(K, V):
+    from jax_linear_attention_b200.distributed.context_parallel import piece_scan
+
+    torch.manual_seed(K + V)
+    dev = torch.device("cuda")
+    P, H = 9, 3
+    cont = [False, True, True, False, True, False, False, True, True]
+    cont_dev = torch.tensor([int(c) for c in cont], dtype=torch.int32, device=dev)
+    maps = (torch.randn(P, H, K, K, device=dev) * K ** -0.5).contiguous()
+    e = torch.randn(P, H, K, V, device=dev)
+    boundary = torch.randn(H, K, V, device=dev)
+    # forward, in two ranges as a rank does (tail first, then the head that depends on the received state)
+    got = e.clone()
+    piece_scan(maps, cont, cont_dev, boundary, got, 5, P)
+    piece_scan(maps, cont, cont_dev, boundary, got, 0, 5)
+    want = e.double().cpu()
+    piece_scan(maps.double().cpu(), cont, None, boundary.double().cpu(), want, 0, P)
+    assert rel_l2(got.cpu().numpy(), want.numpy()) < 1e-5
+    # a piece that starts a document keeps its E
+    assert torch.equal(got[3], e[3]) and torch.equal(got[0], e[0])
+    # backward
+    ds_in, ds_out = e.clone(), torch.zeros_like(e)
+    piece_scan(maps, cont, cont_dev, boundary, ds_in, 3, P, ds_out=ds_out)
+    piece_scan(maps, cont, cont_dev, boundary, ds_in, 0, 3, ds_out=ds_out)
+    w_in, w_out = e.double().cpu(), torch.zeros(P, H, K, V, dtype=torch.float64)
+    piece_scan(maps.double().cpu(), cont, None, boundary.double().cpu(), w_in, 0, P, ds_out=w_out)
+    assert rel_l2(ds_in.cpu().numpy(), w_in.numpy()) < 1e-5
+    assert rel_l2(ds_out.cpu().numpy(), w_out.numpy()) < 1e-5
+
+
+def test_policy_follows_the_reference():
+    from jax_linear_attention_b200.ops.cuda import pieces
+
+    assert pieces(8, 16, 2048, delta=True) == 1          # 128 rows x heads fill the GPU
+    assert pieces(1, 16, 2048, delta=True) == 4          # one row of a batch x heads shard over 8 GPUs
+    assert pieces(1, 16, 1_064_960, delta=True) == 8     # at most 8 pieces with the delta rule
+    assert pieces(1, 4, 4096, delta=False) == 8          # every piece keeps at least 8 chunks
+    assert pieces(1, 2, 900, delta=True) == 1
+
+
+@pytest.mark.parametrize("kind", ["gated_deltanet", "simple_gla", "kda"])
+def test_split_call_matches_the_unsplit_call_and_the_oracle(kind):
+    from jax_linear_attention_b200.ops.cuda import no_pieces, pieces
+
+    T, H = 4096, 4
+    assert pieces(1, H, T, delta=kind != "simple_gla") > 1
+    case = make_case(kind, B=1, T=T, H=H, K=128, V=128, seed=71, h0=True, docs="uniform", doc_range=(300, 3000),
+                     gates="kda_baseline" if kind == "kda" else "baseline")
+    split = run_cuda(kind, case, scale=case["meta"]["scale"], dtype="bfloat16")
+    with no_pieces():
+        plain = run_cuda(kind, case, scale=case["meta"]["scale"], dtype="bfloat16")
+    for name in plain:
+        assert np.isfinite(split[name]).all(), name
+        assert rel_l2(split[name], plain[name]) < 1e-2, (name, rel_l2(split[name], plain[name]))
+    assert any(not np.array_equal(split[n], plain[n]) for n in plain), "the split did not run"
+    want = run_oracle(kind, case, scale=case["meta"]["scale"], chunked=True)
+    compare(split, want, 1e-2, f"{kind} split")
