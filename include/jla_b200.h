@@ -47,11 +47,15 @@ enum jla_kind {              /* src/jla/ops/__init__.py:47-60 (KINDS) */
   JLA_KIND_GATED_DELTANET = 2, /* S' = exp(g) S; S = S' + beta k^T (v - k S')                         */
   JLA_KIND_KDA = 3           /* S' = diag(exp(g)) S; S = S' + beta k^T (v - k S')   (g per key channel) */
 };
+/* Gated DeltaNet-2 (src/jla/ops/reference.py:313-343, S = S' + k^T (w v - (b k) S') with an erase gate b per key
+ * channel and a write gate w per value channel) is KDA with beta = 1, the values w * v and a separate read key
+ * b * k: see jla_problem.k_read. */
 
 enum jla_dtype { JLA_DTYPE_BF16 = 0, JLA_DTYPE_F16 = 1, JLA_DTYPE_F32 = 2 };
 
 enum jla_path {
-  JLA_PATH_AUTO = 0,      /* f32 tensors: RECURRENT; bf16/f16: CHUNKED where it applies (KDA: bf16, K = V = 128) */
+  JLA_PATH_AUTO = 0,      /* f32 tensors: RECURRENT; bf16/f16: CHUNKED where it applies (KDA: bf16, K = V = 128).
+                           * A call with k_read always runs RECURRENT, whatever is asked for here. */
   JLA_PATH_RECURRENT = 1, /* fp32 token scan in the order of reference.py:140-157 (any K, V <= 256)            */
   JLA_PATH_CHUNKED = 2    /* chunk-64 tensor-core kernels (bf16/f16, K and V in {64, 128})                      */
 };
@@ -94,6 +98,9 @@ typedef struct jla_problem {
   const float* h0;           /* optional initial state */
   const int32_t* segment_ids; /* optional */
   const int32_t* cu_seqlens;  /* optional; excludes segment_ids */
+  const void* k_read;         /* optional, delta-rule kinds: [B, T, H, K] dtype, one row per VALUE head. When given, the
+                               * recall reads the state with it (S = S' + beta k^T (v - k_read S')), k still writes.
+                               * It is used as passed (JLA_FLAG_QK_L2NORM normalises q and k only). */
 } jla_problem;
 
 typedef struct jla_fwd_io {
@@ -118,6 +125,7 @@ typedef struct jla_bwd_io {
   size_t residual_bytes;
   void* scratch;            /* jla_bwd_scratch_bytes() bytes */
   size_t scratch_bytes;
+  void* dk_read;            /* [B, T, H, K] dtype: gradient of k_read (required when the problem has one) */
 } jla_bwd_io;
 
 /* Library/ABI version: major * 1000 + minor. */
@@ -126,12 +134,14 @@ int jla_abi_version(void);
 /* Text of the last rejected call on this host thread ("" if none). */
 const char* jla_last_error(void);
 
-/* NULL if the library has a kernel for `p` (pointers in `p` are ignored), else the reason as text.
+/* NULL if the library has a kernel for `p`, else the reason as text. Of the pointers in `p` only k_read is looked
+ * at, and only whether it is NULL (a call with a read key takes another path).
  * Mirrors unsupported_reason() of src/jla/ops/mosaic_gpu/scalar_gate.py:476-515 and
  * src/jla/ops/mosaic_gpu/vector_gate_ops.py:262-304. */
 const char* jla_unsupported_reason(const jla_problem* p);
 
-/* Buffer sizes in bytes for problem `p` (0 is a valid answer; pointers in `p` are ignored). */
+/* Buffer sizes in bytes for problem `p` (0 is a valid answer; of the pointers in `p` only k_read is looked at, and
+ * only whether it is NULL). */
 size_t jla_residual_bytes(const jla_problem* p);
 size_t jla_fwd_scratch_bytes(const jla_problem* p);
 size_t jla_bwd_scratch_bytes(const jla_problem* p);

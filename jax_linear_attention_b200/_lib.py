@@ -32,7 +32,7 @@ class Problem(C.Structure):
         ("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("Hk", C.c_int32), ("K", C.c_int32), ("V", C.c_int32),
         ("num_seqs", C.c_int32), ("scale", C.c_float),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p), ("beta", C.c_void_p),
-        ("h0", C.c_void_p), ("segment_ids", C.c_void_p), ("cu_seqlens", C.c_void_p),
+        ("h0", C.c_void_p), ("segment_ids", C.c_void_p), ("cu_seqlens", C.c_void_p), ("k_read", C.c_void_p),
     ]
 
 
@@ -47,7 +47,7 @@ class BwdIO(C.Structure):
     _fields_ = [
         ("d_o", C.c_void_p), ("d_final", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("dg", C.c_void_p), ("dbeta", C.c_void_p), ("dh0", C.c_void_p), ("residuals", C.c_void_p),
-        ("residual_bytes", C.c_size_t), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t),
+        ("residual_bytes", C.c_size_t), ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("dk_read", C.c_void_p),
     ]
 
 

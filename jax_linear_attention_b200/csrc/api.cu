@@ -32,6 +32,7 @@ namespace {
 // chunked KDA forward then keeps no residuals).
 int resolve_path(const jla_problem& p, bool bwd = false) {
   if (bwd && p.kind == JLA_KIND_KDA && kda_scan_backward()) return JLA_PATH_RECURRENT;
+  if (p.k_read) return JLA_PATH_RECURRENT;  // the chunk kernels read and write the state with the same key
   if (p.path == JLA_PATH_AUTO) {
     // f32 tensors run the exact token scan; so does whatever the chunked kernels do not cover (chunked_unsupported()).
     if (p.dtype == JLA_DTYPE_F32 || chunked_unsupported(p) != nullptr) {
@@ -91,6 +92,10 @@ int check_common(const jla_problem* p) {
     set_error("this kind takes beta");
     return JLA_ERR_BAD_ARGUMENT;
   }
+  if (p->k_read && p->kind == JLA_KIND_SIMPLE_GLA) {
+    set_error("k_read is an option of the delta-rule kinds");
+    return JLA_ERR_BAD_ARGUMENT;
+  }
   if (p->cu_seqlens && p->segment_ids) {
     set_error("pass cu_seqlens or segment_ids, not both");
     return JLA_ERR_BAD_ARGUMENT;
@@ -109,7 +114,7 @@ using namespace jla;
 
 extern "C" {
 
-int jla_abi_version(void) { return 1000; }
+int jla_abi_version(void) { return 1001; }
 
 const char* jla_last_error(void) { return g_error; }
 
@@ -147,6 +152,10 @@ int jla_linear_attention_bwd(const jla_problem* p, const jla_bwd_io* io, jla_str
   const bool has_tokens = (long)p->B * p->T > 0;
   if (!io || (has_tokens && (!io->d_o || !io->dq || !io->dk || !io->dv))) {
     set_error("null gradient buffer");
+    return JLA_ERR_BAD_ARGUMENT;
+  }
+  if (has_tokens && p->k_read && !io->dk_read) {
+    set_error("null gradient buffer for k_read");
     return JLA_ERR_BAD_ARGUMENT;
   }
   if (has_tokens && ((p->kind != JLA_KIND_DELTANET && !io->dg) || (p->kind != JLA_KIND_SIMPLE_GLA && !io->dbeta))) {

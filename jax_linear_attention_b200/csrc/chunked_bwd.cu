@@ -289,7 +289,9 @@ struct GradSmem {
 };
 
 template <typename T, int K, int V, bool DELTA>
-__global__ void __launch_bounds__(256, 1) sg_chunk_grads_kernel(BwdParams p) {
+// (Without the delta rule and with V = 64 -- the Mamba-2 shape -- two CTAs fit the shared memory of an SM; capping the
+// registers at 128 lets them, and a second resident CTA hides the first one's load and barrier latencies.)
+__global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_grads_kernel(BwdParams p) {
   using L = GradSmem<T, K, V, DELTA>;
   constexpr int LDK = L::LDK, LDV = L::LDV, LDC = L::LDC;
   constexpr int ONT = V / 16, KNT = K / 16;

@@ -27,12 +27,14 @@ struct RecParams {
   int delta, l2norm;
   float scale;
   const void *q, *k, *v;
+  const void* k_read;  // optional [B*T, H, K]: the recall reads the state with it (k still writes); nullptr = k
   const float *g, *beta, *h0;
   void* o;
   float* final_state;
   const void* d_o;
   const float* d_final;
   float *dq_acc, *dk_acc;  // [B*T, H, K] f32
+  float* dkr_acc;          // [B*T, H, K] f32: gradient of k_read (with k_read only)
   void* dv;
   float *dg, *dbeta, *dh0;
   float* ckpt;  // [H][total_blocks][K*V]
@@ -41,13 +43,13 @@ struct RecParams {
 };
 
 struct Smem {
-  float *qs, *ks, *vs, *eg, *bs, *inv, *part, *dos, *us, *es, *red;
+  float *qs, *ks, *kr, *vs, *eg, *bs, *inv, *part, *dos, *us, *es, *red;  // kr: the read key (= ks without k_read)
   int* rs;
 };
 
 __host__ __device__ inline size_t smem_floats(int K, int V, int KS, bool bwd) {
-  size_t n = 2 * TB * K + TB * V + TB * K + TB + 2 * TB + TB /*rs*/ + 3 * (size_t)KS * V;
-  if (bwd) n += 3 * TB * V + 2 * (size_t)(3 * 8 * K + 64);
+  size_t n = 3 * TB * K + TB * V + TB * K + TB + 2 * TB + TB /*rs*/ + 3 * (size_t)KS * V;
+  if (bwd) n += 3 * TB * V + 2 * (size_t)(4 * 8 * K + 64);
   return n;
 }
 
@@ -55,7 +57,8 @@ __device__ inline Smem carve(float* base, int K, int V, int KS, bool bwd) {
   Smem s;
   s.qs = base;
   s.ks = s.qs + TB * K;
-  s.vs = s.ks + TB * K;
+  s.kr = s.ks + TB * K;
+  s.vs = s.kr + TB * K;
   s.eg = s.vs + TB * V;
   s.bs = s.eg + TB * K;
   s.inv = s.bs + TB;
@@ -82,6 +85,7 @@ __device__ void load_block(const RecParams& p, const Smem& s, int tok, int nb, i
     const long src = ((long)(tok + j) * p.Hk + hk) * K + c;
     s.qs[idx] = to_f32(q[src]);
     s.ks[idx] = to_f32(k[src]);
+    if (p.k_read) s.kr[idx] = to_f32(static_cast<const T*>(p.k_read)[((long)(tok + j) * p.H + h) * K + c]);
     if (p.gate == 2) s.eg[idx] = expf(p.g[((long)(tok + j) * p.H + h) * K + c]);
   }
   for (int idx = tid; idx < nb * V; idx += NT) {
@@ -114,6 +118,10 @@ __device__ void load_block(const RecParams& p, const Smem& s, int tok, int nb, i
     }
     __syncthreads();
   }
+  if (!p.k_read) {  // the write key is also the read key (after its normalisation)
+    for (int idx = tid; idx < nb * K; idx += NT) s.kr[idx] = s.ks[idx];
+    __syncthreads();
+  }
 }
 
 // One forward token: reset, decay, (delta) recall and write. Returns the written value u_v; *resid gets
@@ -142,7 +150,7 @@ __device__ __forceinline__ float forward_token(const RecParams& p, const Smem& s
   if (p.delta) {
     float partial = 0.f;
 #pragma unroll
-    for (int i = 0; i < KPT; ++i) partial += s.ks[j * K + ks * KPT + i] * S[i];
+    for (int i = 0; i < KPT; ++i) partial += s.kr[j * K + ks * KPT + i] * S[i];
     float* part_r = s.part + 2 * KS * V;
     part_r[ks * V + v] = partial;
     __syncthreads();
@@ -281,11 +289,12 @@ __global__ void __launch_bounds__(512) rec_bwd_kernel(RecParams p) {
 
     for (int j = nb - 1; j >= 0; --j) {
       const long tok = tok0 + t0 + j;
-      float* red = s.red + (j & 1) * (3 * 8 * K + 64);
+      float* red = s.red + (j & 1) * (4 * 8 * K + 64);
       float* red_q = red;
       float* red_k = red + 8 * K;
       float* red_g = red + 16 * K;
       float* red_s = red + 24 * K;  // [0..31] dbeta partials, [32..63] scalar dg partials (per warp, <= 16 warps)
+      float* red_kr = red + 24 * K + 64;
       float Sp[KPT], tmp[KPT];
       const float u = s.us[j * V + v];
       const float dov = s.dos[j * V + v];
@@ -307,9 +316,14 @@ __global__ void __launch_bounds__(512) rec_bwd_kernel(RecParams p) {
       for (int t = 0; t < KS; ++t) du += part_r[t * V + v];
       const float beta = s.bs[j];
       const float dr = p.delta ? -beta * du : 0.f;
+      float tmpr[KPT];  // the read key's gradient S'_t dr_t; added to dk when the write key is also the read key
 #pragma unroll
-      for (int i = 0; i < KPT; ++i) tmp[i] = dS[i] * u + Sp[i] * dr;
+      for (int i = 0; i < KPT; ++i) {
+        tmpr[i] = Sp[i] * dr;
+        tmp[i] = dS[i] * u + (p.k_read ? 0.f : tmpr[i]);
+      }
       reduce_over_v<KPT>(tmp, red_k, K, V, ks, v);
+      if (p.k_read) reduce_over_v<KPT>(tmpr, red_kr, K, V, ks, v);
       if (ks == 0) dv[(tok * p.H + h) * V + v] = from_f32<T>(p.delta ? beta * du : du);
       if (p.delta) {  // dbeta_t = sum_v du_v (v_v - r_v): reduce over the ks == 0 threads (warps 0 .. VW-1)
         float x = ks == 0 ? du * s.es[j * V + v] : 0.f;
@@ -319,7 +333,7 @@ __global__ void __launch_bounds__(512) rec_bwd_kernel(RecParams p) {
       float gsum = 0.f;
 #pragma unroll
       for (int i = 0; i < KPT; ++i) {
-        const float dSp = dS[i] + s.ks[j * K + ks * KPT + i] * dr;  // gradient of S'_t
+        const float dSp = dS[i] + s.kr[j * K + ks * KPT + i] * dr;  // gradient of S'_t
         tmp[i] = dSp * Sp[i];
         gsum += tmp[i];
         const float decay = p.gate == 1 ? s.eg[j] : (p.gate == 2 ? s.eg[j * K + ks * KPT + i] : 1.f);
@@ -332,14 +346,16 @@ __global__ void __launch_bounds__(512) rec_bwd_kernel(RecParams p) {
       }
       __syncthreads();  // #2
       if (tid < K) {
-        float aq = 0.f, ak = 0.f, ag = 0.f;
+        float aq = 0.f, ak = 0.f, ag = 0.f, akr = 0.f;
         for (int w = 0; w < VW; ++w) {
           aq += red_q[w * K + tid];
           ak += red_k[w * K + tid];
           if (p.gate == 2) ag += red_g[w * K + tid];
+          if (p.k_read) akr += red_kr[w * K + tid];
         }
         p.dq_acc[(tok * p.H + h) * K + tid] = p.scale * aq;
         p.dk_acc[(tok * p.H + h) * K + tid] = ak;
+        if (p.k_read) p.dkr_acc[(tok * p.H + h) * K + tid] = akr;
         if (p.gate == 2) p.dg[(tok * p.H + h) * K + tid] = ag;
       }
       if (tid == 0) {
@@ -381,6 +397,7 @@ RecParams base_params(const jla_problem& p) {
   r.l2norm = (p.flags & JLA_FLAG_QK_L2NORM) != 0;
   r.scale = p.scale;
   r.q = p.q; r.k = p.k; r.v = p.v; r.g = p.g; r.beta = p.beta; r.h0 = p.h0;
+  r.k_read = p.k_read;
   return r;
 }
 
@@ -426,7 +443,7 @@ int launch_dtype(const RecParams& rp, int dtype, int kpt, bool bwd, int rows, cu
 }
 
 struct BwdScratch {
-  float *dq_acc, *dk_acc, *ckpt, *spre;
+  float *dq_acc, *dk_acc, *dkr_acc, *ckpt, *spre;
   long total_blocks;
   size_t bytes;
 };
@@ -439,6 +456,7 @@ BwdScratch carve_bwd(const jla_problem& p, void* base) {
   s.total_blocks = tokens / TB + rows + 1;
   s.dq_acc = c.take<float>((size_t)tokens * p.H * p.K);
   s.dk_acc = c.take<float>((size_t)tokens * p.H * p.K);
+  s.dkr_acc = c.take<float>(p.k_read ? (size_t)tokens * p.H * p.K : 0);
   s.ckpt = c.take<float>((size_t)p.H * s.total_blocks * p.K * p.V);
   s.spre = c.take<float>((size_t)rows * p.H * TB * p.K * p.V);
   s.bytes = c.bytes();
@@ -473,7 +491,7 @@ int recurrent_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t strea
     return JLA_ERR_WORKSPACE;
   }
   rp.d_o = io.d_o; rp.d_final = io.d_final;
-  rp.dq_acc = s.dq_acc; rp.dk_acc = s.dk_acc;
+  rp.dq_acc = s.dq_acc; rp.dk_acc = s.dk_acc; rp.dkr_acc = s.dkr_acc;
   rp.dv = io.dv; rp.dg = io.dg; rp.dbeta = io.dbeta; rp.dh0 = io.dh0;
   rp.ckpt = s.ckpt; rp.spre = s.spre; rp.total_blocks = s.total_blocks;
   const int rows = p.cu_seqlens ? p.num_seqs : p.B;
@@ -485,6 +503,10 @@ int recurrent_bwd(const jla_problem& p, const jla_bwd_io& io, cudaStream_t strea
   const bool l2 = (p.flags & JLA_FLAG_QK_L2NORM) != 0;
   int rc = finalize_key_grad(s.dq_acc, p.q, io.dq, p.dtype, tokens, p.H, p.Hk, p.K, l2, stream);
   if (rc != JLA_OK) return rc;
+  if (p.k_read) {  // one row per value head, used as passed: no group sum, no norm to differentiate through
+    rc = finalize_key_grad(s.dkr_acc, nullptr, io.dk_read, p.dtype, tokens, p.H, p.H, p.K, false, stream);
+    if (rc != JLA_OK) return rc;
+  }
   return finalize_key_grad(s.dk_acc, p.k, io.dk, p.dtype, tokens, p.H, p.Hk, p.K, l2, stream);
 }
 

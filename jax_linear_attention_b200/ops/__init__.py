@@ -28,6 +28,7 @@ KINDS: dict[str, tuple[str, tuple[str, ...]]] = {
     "deltanet": ("delta_rule", ("beta",)),
     "gated_deltanet": ("gated_delta_rule", ("g", "beta")),
     "kda": ("kda", ("g", "beta")),
+    "gdn2": ("gdn2", ("g", "b", "w")),
 }
 _GATE_NAMES = frozenset(name for _, gates in KINDS.values() for name in gates)
 
@@ -61,7 +62,7 @@ for _kind in KINDS:
 def linear_attention(kind: str, q, k, v, *, impl: str = "auto", **inputs: Any):
     """Run a linear-attention op; returns ``(o, final_state)``.
 
-    ``inputs`` holds the kind's gates by name (``g``, ``beta``) plus the options passed through: ``scale``,
+    ``inputs`` holds the kind's gates by name (``g``, ``beta``; ``g``, ``b``, ``w`` for ``gdn2``) plus the options passed through: ``scale``,
     ``initial_state``, ``output_final_state``, ``segment_ids``, ``cu_seqlens``, ``use_qk_l2norm`` (delta-rule
     kinds), ``chunk_size`` (must be 64), ``sub_chunk`` (KDA; accepted, unused) and ``precision``
     (``"highest"`` = the fp32 token-scan kernels).

@@ -54,12 +54,19 @@ def _problem(kind: str, dtype, B, T, H, Hk, K, V, num_seqs, scale, flags, precis
     return p
 
 
-def unsupported_reason(kind: str, q, k, v, gates: tuple, options: dict) -> str | None:
-    """Why the CUDA kernels cannot run this call (``None`` if they can).
+def unsupported_reason(kind: str, q, k, v, gates: tuple, options: dict, *, read_key: bool = False) -> str | None:
+    """Why the CUDA kernels cannot run this call (``None`` if they can); ``read_key``: the call passes a separate
+    read key (Gated DeltaNet-2), which selects the token scan.
 
     Works on anything with ``.shape`` and ``.dtype`` (tensors or shape structs), so it can be evaluated
     on per-shard shapes; mirrors ``unsupported_reason`` of ``mosaic_gpu/scalar_gate.py:476-515``.
     """
+    if kind == "gdn2":  # KDA kernels with a read key; the erase and write gates are shaped like k and v
+        if len(gates) != 3 or _shape(gates[1]) != _shape(q) or _shape(gates[2]) != _shape(v) or \
+                _shape(q)[2:3] != _shape(v)[2:3]:
+            return (f"b must be [B, T, H, K] = {_shape(q)} and w must be [B, T, H, V] = {_shape(v)} with as many key "
+                    f"heads as value heads; got {[_shape(x) for x in gates[1:]]}")
+        kind, gates, read_key = "kda", gates[:1], True
     delta = kind != "simple_gla"
     allowed = _COMMON_OPTIONS | ({"use_qk_l2norm"} if delta else set()) | ({"sub_chunk"} if kind == "kda" else set())
     extra = sorted(set(options) - allowed)
@@ -101,6 +108,8 @@ def unsupported_reason(kind: str, q, k, v, gates: tuple, options: dict) -> str |
         return str(err)
     p = _problem(kind, q.dtype, batch, seq_len, heads, kv_heads, key_dim, value_dim,
                  0 if cu is None else max(rows, 0), 1.0, 0, precision)
+    if read_key:
+        p.k_read = 1  # only looked at for being non-NULL
     return _lib.unsupported_reason(p)
 
 
@@ -160,14 +169,14 @@ class state_grads_only:
 
 
 class _LinearAttention(torch.autograd.Function):
-    """``(o, final) = op(q, k, v, g, beta, h0)``; the config rides in ``cfg``."""
+    """``(o, final) = op(q, k, v, g, beta, h0, k_read)``; the config rides in ``cfg``."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, h0, cfg: dict):
+    def forward(ctx, q, k, v, g, beta, h0, k_read, cfg: dict):
         lib = _lib.load()
         B, T, Hk, K = q.shape
         H, V = v.shape[2:]
-        needs_grad = any(x is not None and x.requires_grad for x in (q, k, v, g, beta, h0))
+        needs_grad = any(x is not None and x.requires_grad for x in (q, k, v, g, beta, h0, k_read))
         flags = (_lib.FLAG_QK_L2NORM if cfg["l2norm"] else 0) | (_lib.FLAG_SAVE_RESIDUALS if needs_grad else 0)
         if _PassOptions.final_state_only and not needs_grad:
             flags |= _lib.FLAG_STATE_ONLY
@@ -176,7 +185,7 @@ class _LinearAttention(torch.autograd.Function):
         p = _problem(cfg["kind"], q.dtype, B, T, H, Hk, K, V, 0 if cu is None else rows, cfg["scale"], flags,
                      cfg["precision"])
         p.q, p.k, p.v, p.g, p.beta, p.h0 = (_ptr(x) for x in (q, k, v, g, beta, h0))
-        p.segment_ids, p.cu_seqlens = _ptr(seg), _ptr(cu)
+        p.segment_ids, p.cu_seqlens, p.k_read = _ptr(seg), _ptr(cu), _ptr(k_read)
         dev = q.device
         o = torch.empty_like(v)
         final = torch.empty(rows, H, K, V, dtype=torch.float32, device=dev) if cfg["output_final_state"] else None
@@ -212,14 +221,14 @@ class _LinearAttention(torch.autograd.Function):
             _lib.check(lib.jla_linear_attention_fwd(C.byref(p), C.byref(io), C.c_void_p(stream)),
                        f"{cfg['kind']} forward")
         ctx.cfg, ctx.flags, ctx.rows = cfg, flags, rows
-        ctx.save_for_backward(q, k, v, g, beta, h0, residuals)
+        ctx.save_for_backward(q, k, v, g, beta, h0, k_read, residuals)
         return o, final
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, d_o, d_final):
         lib = _lib.load()
-        q, k, v, g, beta, h0, residuals = ctx.saved_tensors
+        q, k, v, g, beta, h0, k_read, residuals = ctx.saved_tensors
         cfg = ctx.cfg
         B, T, Hk, K = q.shape
         H, V = v.shape[2:]
@@ -228,7 +237,7 @@ class _LinearAttention(torch.autograd.Function):
         p = _problem(cfg["kind"], q.dtype, B, T, H, Hk, K, V, 0 if cu is None else ctx.rows, cfg["scale"], flags,
                      cfg["precision"])
         p.q, p.k, p.v, p.g, p.beta, p.h0 = (_ptr(x) for x in (q, k, v, g, beta, h0))
-        p.segment_ids, p.cu_seqlens = _ptr(seg), _ptr(cu)
+        p.segment_ids, p.cu_seqlens, p.k_read = _ptr(seg), _ptr(cu), _ptr(k_read)
         dev = q.device
         d_o = d_o.contiguous() if d_o is not None else torch.zeros_like(v)
         d_final = None if d_final is None else d_final.contiguous().float()
@@ -236,15 +245,17 @@ class _LinearAttention(torch.autograd.Function):
         dg = None if g is None else torch.empty_like(g)
         dbeta = None if beta is None else torch.empty_like(beta)
         dh0 = None if h0 is None else torch.empty_like(h0)
+        dk_read = None if k_read is None else torch.empty_like(k_read)
         scr_bytes = lib.jla_bwd_scratch_bytes(C.byref(p))
         scratch = torch.empty(scr_bytes, dtype=torch.uint8, device=dev) if scr_bytes else None
         io = _lib.BwdIO(_ptr(d_o), _ptr(d_final), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dg), _ptr(dbeta), _ptr(dh0),
-                        _ptr(residuals), 0 if residuals is None else residuals.numel(), _ptr(scratch), scr_bytes)
+                        _ptr(residuals), 0 if residuals is None else residuals.numel(), _ptr(scratch), scr_bytes,
+                        _ptr(dk_read))
         stream = torch.cuda.current_stream(dev).cuda_stream
         with torch.cuda.device(dev):
             _lib.check(lib.jla_linear_attention_bwd(C.byref(p), C.byref(io), C.c_void_p(stream)),
                        f"{cfg['kind']} backward")
-        return dq, dk, dv, dg, dbeta, dh0, None
+        return dq, dk, dv, dg, dbeta, dh0, dk_read, None
 
 
 # Sequence split policy for the serial state passes, after ``pieces()`` of the reference
@@ -299,7 +310,7 @@ def _split_applies(kind, q, v, cu_seqlens, initial_state, precision) -> int:
 
 
 def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_state, cu_seqlens, segment_ids,
-         use_qk_l2norm=False, chunk_size=CHUNK, precision=None, sub_chunk=None):
+         use_qk_l2norm=False, chunk_size=CHUNK, precision=None, sub_chunk=None, k_read=None):
     del sub_chunk  # the kernels choose their own sub-blocking
     for name, x in (("q", q), ("k", k), ("v", v)):
         if not isinstance(x, torch.Tensor) or not x.is_cuda:
@@ -308,13 +319,13 @@ def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_stat
                                    cu_seqlens=cu_seqlens, segment_ids=segment_ids, chunk_size=chunk_size,
                                    precision=precision)
     gates = tuple(x for x in (g, beta) if x is not None)
-    why = unsupported_reason(kind, q, k, v, gates, options)
+    why = unsupported_reason(kind, q, k, v, gates, options, read_key=k_read is not None)
     if why is not None:
         raise ValueError(f"the CUDA kernels cannot run this {kind} call: {why}")
     dev = q.device
     if scale is None:
         scale = q.shape[-1] ** -0.5
-    cp = _split_applies(kind, q, v, cu_seqlens, initial_state, precision)
+    cp = 1 if k_read is not None else _split_applies(kind, q, v, cu_seqlens, initial_state, precision)
     if cp > 1:
         from ..distributed.context_parallel import context_parallel_linear_attention
 
@@ -347,7 +358,7 @@ def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_stat
                prep_identity=tuple((id(x), getattr(x, "_version", 0)) for x in (k, g, beta, segment_ids, cu_seqlens,
                                                                                 q if use_qk_l2norm else None)))
     o, final = _LinearAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), f32(g), f32(beta),
-                                      f32(initial_state), cfg)
+                                      f32(initial_state), None if k_read is None else k_read.contiguous(), cfg)
     return o, (final if output_final_state else None)
 
 
@@ -384,6 +395,37 @@ def kda(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=
                 use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision, sub_chunk=sub_chunk)
 
 
+def gdn2(q, k, v, g, b, w, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+         segment_ids=None, use_qk_l2norm=False, chunk_size=CHUNK, sub_chunk=16, precision=None):
+    """Gated DeltaNet-2 (``gdn2`` of ``src/jla/ops/reference.py:313-343`` in the reference): ``S_t = (I - k_t (b_t *
+    k_t)^T) diag(exp g_t) S_{t-1} + k_t (w_t * v_t)^T`` with an erase gate ``b [B, T, H, K]`` and a write gate
+    ``w [B, T, H, V]``; ``b = w = beta`` is KDA.
+
+    The kernels see it as KDA with ``beta = 1``, the values ``w * v`` and a separate read key ``b * k`` (the key the
+    recall reads the state with; ``k`` still writes). The two products are formed here in the tensors' dtype -- for
+    16-bit tensors that rounds them once to 16 bits, as the reference's kernels round the gates
+    (``mosaic_gpu/gdn2.py:11-12``) -- and their gradients flow back to ``k``, ``b``, ``v`` and ``w`` through autograd.
+    The unit norm of ``use_qk_l2norm`` is applied first (the gate multiplies the normalised key, reference.py:118-119).
+    Calls with a read key run the fp32 token scan whatever the dtype.
+    """
+    if _shape(b) != _shape(q) or _shape(w) != _shape(v) or _shape(k) != _shape(q):
+        raise ValueError(f"b must be [B, T, H, K] = {_shape(q)} and w must be [B, T, H, V] = {_shape(v)} (q and k "
+                         f"with as many heads as v); got {_shape(b)} and {_shape(w)} with k {_shape(k)}")
+    if _shape(q)[2] != _shape(v)[2]:
+        raise ValueError(f"gdn2 needs as many key heads as value heads; got {_shape(q)[2]} and {_shape(v)[2]}")
+    if use_qk_l2norm:
+        def unit(x):
+            x32 = x.float()
+            return (x32 * torch.rsqrt((x32 * x32).sum(-1, keepdim=True) + 1e-6)).to(x.dtype)
+        q, k = unit(q), unit(k)
+    k_read = (b.to(torch.float32) * k.to(torch.float32)).to(k.dtype)
+    values = (w.to(torch.float32) * v.to(torch.float32)).to(v.dtype)
+    ones = torch.ones(_shape(v)[:3], dtype=torch.float32, device=v.device)
+    return _run("kda", q, k, values, g, ones, scale=scale, initial_state=initial_state,
+                output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
+                chunk_size=chunk_size, precision=precision, sub_chunk=sub_chunk, k_read=k_read)
+
+
 def device_status(device=None) -> int:
     """Synchronises ``device``'s current stream and returns (and clears) its failure status word: non-zero when a
     bounded wait inside one of the tensor-core kernels ran out since the last query, in which case the outputs of
@@ -398,5 +440,6 @@ FUNCTIONS = {
     "deltanet": delta_rule,
     "gated_deltanet": gated_delta_rule,
     "kda": kda,
+    "gdn2": gdn2,
 }
 SUPPORTS = {kind: _supports(kind) for kind in FUNCTIONS}

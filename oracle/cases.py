@@ -102,7 +102,7 @@ def make_case(kind: str, *, B: int, T: int, H: int, K: int, V: int, Hk: int | No
     out["q"], out["k"] = round_to(q, dtype), round_to(k, dtype)
     out["v"] = round_to(rng.standard_normal((B, T, H, V)), dtype)
     if kind != "deltanet":
-        gshape = (B, T, H, K) if kind == "kda" else (B, T, H)
+        gshape = (B, T, H, K) if kind in ("kda", "gdn2") else (B, T, H)
         if gates == "baseline":
             g = logsigmoid(rng.standard_normal(gshape) + 3.0)
         elif gates == "kda_baseline":
@@ -113,7 +113,14 @@ def make_case(kind: str, *, B: int, T: int, H: int, K: int, V: int, Hk: int | No
             mask = rng.random(gshape)
             g = np.where(mask < 0.1, -80.0, np.where(mask < 0.3, -1e-7, g))
         out["g"] = g.astype(np.float32)
-    if kind != "simple_gla":
+    if kind == "gdn2":  # erase gate per key channel, write gate per value channel (both in (0, 1), as sigmoids)
+        for name, shape in (("b", (B, T, H, K)), ("w", (B, T, H, V))):
+            gate = 1.0 / (1.0 + np.exp(-rng.standard_normal(shape)))
+            if gates == "extreme":
+                mask = rng.random(shape)
+                gate = np.where(mask < 0.1, 0.0, np.where(mask < 0.2, 1.0, gate))
+            out[name] = round_to(gate * beta_scale, dtype)  # the kernels take them in the tensors' dtype
+    elif kind != "simple_gla":
         beta = 1.0 / (1.0 + np.exp(-rng.standard_normal((B, T, H))))
         if gates == "extreme":
             mask = rng.random((B, T, H))

@@ -35,6 +35,7 @@ __all__ = [
     "gated_delta_rule",
     "gla",
     "kda",
+    "gdn2",
     "l2norm",
     "recurrence",
     "repeat_heads",
@@ -63,23 +64,29 @@ def repeat_heads(x: torch.Tensor, heads: int) -> torch.Tensor:
     return x.repeat_interleave(heads // x.shape[2], dim=2)
 
 
-def _step(state, q_t, k_t, v_t, g_t, beta_t, gate: str, delta: bool):
-    """One token for all rows and heads (``reference.py:140-157``). ``state [R, H, K, V]``."""
+def _step(state, q_t, k_t, v_t, g_t, beta_t, gate: str, delta: bool, erase_t=None, write_t=None):
+    """One token for all rows and heads (``reference.py:140-157``). ``state [R, H, K, V]``. With an erase gate
+    (Gated DeltaNet-2, ``reference.py:152-154``) the recall reads with ``erase_t * k_t`` and the write gate scales
+    the value; ``beta_t`` is unused then."""
     if gate == "scalar":
         state = state * torch.exp(g_t)[..., None, None]
     elif gate == "vector":
         state = state * torch.exp(g_t)[..., None]
-    if delta:
+    if delta and erase_t is None:
         recalled = torch.einsum("rhk,rhkv->rhv", k_t, state)
         v_t = beta_t[..., None] * (v_t - recalled)
+    elif delta:
+        recalled = torch.einsum("rhk,rhkv->rhv", erase_t * k_t, state)
+        v_t = write_t * v_t - recalled
     state = state + k_t[..., :, None] * v_t[..., None, :]
     return state, torch.einsum("rhk,rhkv->rhv", q_t, state)
 
 
 def recurrence(q, k, v, g=None, beta=None, *, gate: str, delta: bool, scale=None, initial_state=None,
                output_final_state: bool = False, cu_seqlens=None, segment_ids=None,
-               use_qk_l2norm: bool = False, dtype=torch.float64):
-    """Token loop of ``reference.py:105-205``; returns ``(o, final_state | None)`` in ``dtype``.
+               use_qk_l2norm: bool = False, dtype=torch.float64, erase=None, write=None):
+    """Token loop of ``reference.py:105-205``; returns ``(o, final_state | None)`` in ``dtype``. ``erase [B, T, H, K]``
+    and ``write [B, T, H, V]`` are the channel gates of Gated DeltaNet-2 (``beta`` is None then).
 
     Inputs are torch tensors (leaves that require grad keep their graph, so
     ``torch.autograd.grad`` of the outputs gives the oracle gradients).
@@ -103,6 +110,12 @@ def recurrence(q, k, v, g=None, beta=None, *, gate: str, delta: bool, scale=None
     k = repeat_heads(k, heads)
     g = None if g is None else g.to(dtype)
     beta = None if beta is None else beta.to(dtype)
+    if erase is not None:
+        if tuple(erase.shape) != tuple(q.shape) or write is None or tuple(write.shape) != tuple(v.shape):
+            raise ValueError(f"b must be [B, T, H, K] = {tuple(q.shape)} and w must be [B, T, H, V] = "
+                             f"{tuple(v.shape)}; got {tuple(erase.shape)} and "
+                             f"{None if write is None else tuple(write.shape)}")
+        erase, write = erase.to(dtype), write.to(dtype)
 
     def tok(x, t):
         return None if x is None else x[:, t]
@@ -115,7 +128,8 @@ def recurrence(q, k, v, g=None, beta=None, *, gate: str, delta: bool, scale=None
         for t in range(seq_len):
             if resets is not None:
                 state = state * (~resets[:, t]).to(dtype)[:, None, None, None]
-            state, o_t = _step(state, q[:, t], k[:, t], v[:, t], tok(g, t), tok(beta, t), gate, delta)
+            state, o_t = _step(state, q[:, t], k[:, t], v[:, t], tok(g, t), tok(beta, t), gate, delta, tok(erase, t),
+                                 tok(write, t))
             outs.append(o_t)
         final = state
     else:
@@ -129,7 +143,8 @@ def recurrence(q, k, v, g=None, beta=None, *, gate: str, delta: bool, scale=None
         for n in range(num_seqs):
             state = state0[n][None]
             for t in range(cu[n], cu[n + 1]):
-                state, o_t = _step(state, q[:, t], k[:, t], v[:, t], tok(g, t), tok(beta, t), gate, delta)
+                state, o_t = _step(state, q[:, t], k[:, t], v[:, t], tok(g, t), tok(beta, t), gate, delta, tok(erase, t),
+                                 tok(write, t))
                 outs.append(o_t)
             if cu[n + 1] > cu[n]:
                 finals[n] = state[0]
@@ -178,10 +193,20 @@ def kda(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=
                       use_qk_l2norm=use_qk_l2norm, dtype=dtype)
 
 
+def gdn2(q, k, v, g, b, w, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+         segment_ids=None, use_qk_l2norm=False, dtype=torch.float64):
+    """Gated DeltaNet-2 (``reference.py:313-343``): ``S_t = (I - k_t (b_t * k_t)^T) diag(exp g_t) S_{t-1} + k_t (w_t *
+    v_t)^T`` with an erase gate ``b [B, T, H, K]`` and a write gate ``w [B, T, H, V]``; ``b = w = beta`` is KDA."""
+    return recurrence(q, k, v, g, None, gate="vector", delta=True, scale=scale, initial_state=initial_state,
+                      output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
+                      use_qk_l2norm=use_qk_l2norm, dtype=dtype, erase=b, write=w)
+
+
 KIND_FUNCTIONS = {
     "simple_gla": (simple_gla, ("g",)),
     "gla": (gla, ("g",)),
     "deltanet": (delta_rule, ("beta",)),
     "gated_deltanet": (gated_delta_rule, ("g", "beta")),
     "kda": (kda, ("g", "beta")),
+    "gdn2": (gdn2, ("g", "b", "w")),
 }

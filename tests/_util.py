@@ -14,7 +14,8 @@ from oracle.cases import max_rel, rel_l2
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
-GATES = {"simple_gla": ("g",), "deltanet": ("beta",), "gated_deltanet": ("g", "beta"), "kda": ("g", "beta")}
+GATES = {"simple_gla": ("g",), "deltanet": ("beta",), "gated_deltanet": ("g", "beta"), "kda": ("g", "beta"),
+         "gdn2": ("g", "b", "w")}
 
 
 def load_golden(name):
@@ -32,8 +33,9 @@ def run_cuda(kind, ins, *, scale, dtype, l2norm=False, precision=None, grads=Tru
 
     td = TORCH_DTYPE[dtype]
     leaves = {}
-    for n in ("q", "k", "v"):
-        leaves[n] = torch.tensor(ins[n], dtype=td, device=device, requires_grad=grads)
+    for n in ("q", "k", "v", "b", "w"):  # (b, w: the channel gates of Gated DeltaNet-2, in the tensors' dtype)
+        if n in ins:
+            leaves[n] = torch.tensor(ins[n], dtype=td, device=device, requires_grad=grads)
     for n in ("g", "beta", "h0"):
         if n in ins:
             leaves[n] = torch.tensor(ins[n], dtype=torch.float32, device=device, requires_grad=grads)
@@ -60,8 +62,8 @@ def run_cuda(kind, ins, *, scale, dtype, l2norm=False, precision=None, grads=Tru
 
 def run_oracle(kind, ins, *, scale, l2norm=False, grads=True, cu_seqlens=None, chunked=False, dtype=torch.float64):
     """The CPU oracle on the same inputs (float64 token loop, or the chunked form when ``chunked``)."""
-    leaves = {n: torch.tensor(ins[n], dtype=dtype, requires_grad=grads) for n in ("q", "k", "v", "g", "beta", "h0")
-              if n in ins}
+    leaves = {n: torch.tensor(ins[n], dtype=dtype, requires_grad=grads) for n in ("q", "k", "v", "b", "w", "g", "beta",
+                                                                                       "h0") if n in ins}
     mod = oracle_chunked if chunked else oracle_rec
     fn, gate_names = mod.KIND_FUNCTIONS[kind]
     opts = dict(scale=scale, initial_state=leaves.get("h0"), output_final_state=True, dtype=dtype)

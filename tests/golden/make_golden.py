@@ -9,7 +9,8 @@ What it imports from the reference (read-only, nothing is copied):
 * ``benchmarks/xcheck_scalar_gate.py``: ``gen_case`` (NumPy inputs, seed = crc32 of the case name),
 * ``benchmarks/xcheck_scalar_gate_torch.py``: ``run_oracle`` (float64 token loop + autograd VJP) for
   Gated DeltaNet, DeltaNet, simple GLA and Mamba-2 SSD,
-* ``benchmarks/diff_vector_gate.py``: ``oracle64`` (NumPy float64 token loop, forward only) for KDA.
+* ``benchmarks/diff_vector_gate.py``: ``oracle64`` (NumPy float64 token loop, forward only) for KDA and Gated
+  DeltaNet-2.
 
 Shims, because those modules were written for a CUDA torch / JAX environment: a no-op
 ``torch.cuda.set_per_process_memory_fraction`` and ``DEV = "cpu"`` for the torch module; empty stand-in
@@ -75,6 +76,16 @@ KDA_SPECS = {
     "kda_softplus": dict(B=1, T=120, H=2, K=32, V=32, gate="softplus", h0=True, l2norm=True),
 }
 
+# Gated DeltaNet-2 (erase gate b [B, T, H, K], write gate w [B, T, H, V]) through the same float64 loop
+# (diff_vector_gate.oracle64("gdn2", ...)).
+GDN2_SPECS = {
+    "gdn2_dense_h0": dict(B=2, T=100, H=2, K=32, V=32, gate="plain", h0=True),
+    "gdn2_packed_l2norm": dict(B=1, T=200, H=2, K=32, V=16, gate="plain", cu=(0, 37, 100, 101, 128, 170, 200),
+                               l2norm=True),
+    "gdn2_extreme": dict(B=1, T=160, H=2, K=32, V=32, gate="extreme", h0=True),
+    "gdn2_d128": dict(B=1, T=200, H=2, K=128, V=128, gate="plain", cu=(0, 64, 65, 192, 200), h0=True),
+}
+
 
 def bf16(x):
     return torch.from_numpy(np.asarray(x, np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
@@ -109,6 +120,9 @@ def draw_kda(c: dict, seed: int) -> dict:
         return x
     x["g"] = g.astype(np.float32)
     sharp = 6.0 if c["gate"] == "extreme" else 1.0
+    if c.get("gdn2"):  # channel gates in (0, 1), bf16-representable (the kernels take them in the tensors' dtype)
+        x["b"] = bf16(1.0 / (1.0 + np.exp(-sharp * rng.standard_normal((B, T, H, K)))))
+        x["w"] = bf16(1.0 / (1.0 + np.exp(-sharp * rng.standard_normal((B, T, H, V)))))
     x["beta"] = (1.0 / (1.0 + np.exp(-sharp * rng.standard_normal((B, T, H))))).astype(np.float32)
     if c.get("h0"):
         x["h0"] = (0.5 * rng.standard_normal((B, H, K, V))).astype(np.float32)
@@ -165,6 +179,20 @@ def main() -> None:
         arrays["out_o"] = np.asarray(res["o"], np.float64)
         arrays["out_final"] = np.asarray(res["final"], np.float64)
         arrays["meta"] = np.array(json.dumps(dict(c, kind="kda", name=name, scale=c["K"] ** -0.5)))
+        path = os.path.join(args.out, f"{name}.npz")
+        np.savez_compressed(path, **arrays)
+        manifest[name] = dict(spec=c, source="diff_vector_gate.oracle64", bytes=os.path.getsize(path))
+        print(name, manifest[name]["bytes"])
+    for i, (name, c) in enumerate(GDN2_SPECS.items()):
+        if args.only is not None and name not in args.only:
+            continue
+        x = draw_kda(dict(c, gdn2=True), seed=2000 + i)
+        del x["beta"]
+        res = dvg.oracle64("gdn2", c, x)
+        arrays = {f"in_{k}": v for k, v in x.items()}
+        arrays["out_o"] = np.asarray(res["o"], np.float64)
+        arrays["out_final"] = np.asarray(res["final"], np.float64)
+        arrays["meta"] = np.array(json.dumps(dict(c, kind="gdn2", name=name, scale=c["K"] ** -0.5)))
         path = os.path.join(args.out, f"{name}.npz")
         np.savez_compressed(path, **arrays)
         manifest[name] = dict(spec=c, source="diff_vector_gate.oracle64", bytes=os.path.getsize(path))

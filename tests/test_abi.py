@@ -73,7 +73,7 @@ def test_unsupported_reason_and_sizes_without_a_gpu():
 def test_dispatcher_mirrors_reference_errors():
     from jax_linear_attention_b200 import ops
 
-    assert set(ops.KINDS) == {"simple_gla", "deltanet", "gated_deltanet", "kda"}
+    assert set(ops.KINDS) == {"simple_gla", "deltanet", "gated_deltanet", "kda", "gdn2"}
     assert ops.available("kda") == ("cuda",)
     q = torch.zeros(1, 8, 2, 64)
     g = torch.zeros(1, 8, 2)
@@ -96,6 +96,11 @@ def test_dispatcher_mirrors_reference_errors():
     assert ops.cuda.SUPPORTS["simple_gla"](qs, qs, vs, gs)
     assert not ops.cuda.SUPPORTS["simple_gla"](qs, qs, vs, gs, chunk_size=32)
     assert "g must be" in ops.cuda.unsupported_reason("kda", qs, qs, vs, (gs, gs), {})
+    # Gated DeltaNet-2: gates shaped like k and v, as many key heads as value heads
+    q4 = Spec((2, 100, 4, 64), torch.float32)
+    assert ops.cuda.SUPPORTS["gdn2"](q4, q4, vs, q4, q4, vs)
+    assert "b must be" in ops.cuda.unsupported_reason("gdn2", q4, q4, vs, (q4, gs, vs), {})
+    assert "b must be" in ops.cuda.unsupported_reason("gdn2", qs, qs, vs, (qs, qs, vs), {})
 
 
 def test_register_adds_an_implementation():

@@ -36,7 +36,7 @@ def test_fixture_set_is_complete():
     assert sorted(manifest) == NAMES and len(NAMES) >= 17
 
 
-@pytest.mark.parametrize("name", [n for n in NAMES if not n.startswith("kda") and not n.startswith("mamba2")])
+@pytest.mark.parametrize("name", [n for n in NAMES if not n.startswith(("kda", "mamba2", "gdn2"))])
 def test_scalar_gate_kinds_match_reference_oracle(name):
     meta, ins, want = load(name)
     f64 = torch.float64
@@ -112,3 +112,32 @@ def test_kda_matches_reference_oracle64(name):
                               use_qk_l2norm=bool(meta.get("l2norm")))
     assert max_rel(o.numpy(), want["o"]) < 1e-10
     assert max_rel(final.numpy(), want["final"]) < 1e-10
+
+
+@pytest.mark.parametrize("name", [n for n in NAMES if n.startswith("gdn2")])
+def test_gdn2_matches_reference_oracle64(name):
+    """Gated DeltaNet-2 (erase gate b, write gate w) against ``diff_vector_gate.oracle64("gdn2", ...)``."""
+    meta, ins, want = load(name)
+    f64 = torch.float64
+    t = {n: torch.tensor(v, dtype=f64) for n, v in ins.items()}
+    seg = None
+    if "cu" in meta:
+        cu = np.asarray(meta["cu"])
+        seg = torch.tensor(np.searchsorted(cu[1:], np.arange(meta["T"]), side="right")[None])
+    o, final = recurrence.gdn2(t["q"], t["k"], t["v"], t["g"], t["b"], t["w"], scale=meta["scale"],
+                               initial_state=t.get("h0"), output_final_state=True, segment_ids=seg,
+                               use_qk_l2norm=bool(meta.get("l2norm")))
+    assert max_rel(o.numpy(), want["o"]) < 1e-10
+    assert max_rel(final.numpy(), want["final"]) < 1e-10
+
+
+def test_gdn2_with_equal_gates_is_kda():
+    """``b = w = beta`` recovers KDA (reference.py:330-331)."""
+    meta, ins, _ = load("kda_dense_h0")
+    f64 = torch.float64
+    t = {n: torch.tensor(v, dtype=f64) for n, v in ins.items()}
+    beta = t["beta"][..., None]
+    kw = dict(scale=meta["scale"], initial_state=t.get("h0"), output_final_state=True)
+    o1, f1 = recurrence.kda(t["q"], t["k"], t["v"], t["g"], t["beta"], **kw)
+    o2, f2 = recurrence.gdn2(t["q"], t["k"], t["v"], t["g"], beta.expand_as(t["k"]), beta.expand_as(t["v"]), **kw)
+    assert torch.allclose(o1, o2, rtol=0, atol=1e-12) and torch.allclose(f1, f2, rtol=0, atol=1e-12)
