@@ -41,11 +41,14 @@ struct BwdStateSmem {
   static constexpr int LDK = K + 8, LDV = V + 8, LDC = 72;
   static constexpr int kStageElems = 2 * 64 * LDK + 64 * LDV + (DELTA ? 64 * LDC : 0);
   static constexpr int kStageBytes = kStageElems * 2 + 512 + 64;
-  static constexpr int kBytes = 2 * kStageBytes + (K * LDV + (DELTA ? 3 : 2) * 64 * LDV + (DELTA ? 64 * LDC : 0)) * 2;
+  // Without the delta rule only the 16-bit dS+ copy lives outside the stages: dv goes to global memory from the
+  // accumulators and the scale (cin Gamma) factor of the dS update is applied to the query fragments in registers.
+  static constexpr int kBytes = 2 * kStageBytes + (K * LDV + (DELTA ? 3 * 64 * LDV + 64 * LDC : 0)) * 2;
 };
 
+// (Two CTAs per SM for the Mamba-2 shape, as in the forward pass: 108 KB of shared memory and <= 128 registers each.)
 template <typename T, int K, int V, bool DELTA>
-__global__ void __launch_bounds__(256, 1) sg_bwd_state_kernel(BwdParams p) {
+__global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_bwd_state_kernel(BwdParams p) {
   using L = BwdStateSmem<T, K, V, DELTA>;
   constexpr int LDK = L::LDK, LDV = L::LDV, LDC = L::LDC;
   constexpr int WR = K / 16, WC = 8 / WR, SNT = V / 8 / WC, ONT = V / 16;
@@ -122,7 +125,11 @@ __global__ void __launch_bounds__(256, 1) sg_bwd_state_kernel(BwdParams p) {
     const RowScalars rs1 = row_scalars(Gs, runs, m.flags, r0 + g + 8);
 
     store_tile<T, V>(static_cast<T*>(p.dh) + ((long)c * p.H + h) * K * V, V, dSb, LDV, K, tid, 256);
-    {  // dOs = scale (cin Gamma) dO; AgT[j][i] = Ag_ij
+    if (!DELTA) {
+      // scale (cin Gamma) per token for the dS update, kept in the (unused) beta half of the gate vectors and
+      // applied to the query fragments (ordered before its readers by Sa)
+      if (tid < 64) stage_g(s)[64 + tid] = p.scale * row_scalars(Gs, runs, m.flags, tid).gam;
+    } else {  // dOs = scale (cin Gamma) dO; AgT[j][i] = Ag_ij
       const int i = tid >> 2, j0 = (tid & 3) * (V / 4);
       const float sg = p.scale * row_scalars(Gs, runs, m.flags, i).gam;
 #pragma unroll
@@ -130,7 +137,7 @@ __global__ void __launch_bounds__(256, 1) sg_bwd_state_kernel(BwdParams p) {
         const float2 x = unpack2<T>(*reinterpret_cast<const uint32_t*>(doS + i * LDV + j0 + jj));
         *reinterpret_cast<uint32_t*>(dOs + i * LDV + j0 + jj) = pack2<T>(x.x * sg, x.y * sg);
       }
-      if (DELTA) {
+      {
         const T* t0S = stage_t0(s);
         const int c16 = (tid & 3) * 16;
         const float Gi = Gs[i];
@@ -171,9 +178,20 @@ __global__ void __launch_bounds__(256, 1) sg_bwd_state_kernel(BwdParams p) {
       acc[nt][3] *= rs1.gamr;
     }
     warp_gemm_ra<T, ONT, 4, B_KN>(acc, pfrag, doS + c0, LDV, lane);
-    store_acc<T, ONT>(dVnb, LDV, r0, c0, acc, lane);
-    __syncthreads();  // Sa: dVnb, dOs, AgT complete; every warp is done reading dSb
     T* dv = static_cast<T*>(p.dv) + ((long)m.tok0 * p.H + h) * V;
+    if (DELTA) {
+      store_acc<T, ONT>(dVnb, LDV, r0, c0, acc, lane);
+    } else {  // dV = dVn, straight from the accumulators
+#pragma unroll
+      for (int nt = 0; nt < ONT; ++nt) {
+        const int col = c0 + nt * 8 + 2 * t;
+        if (r0 + g < m.len)
+          *reinterpret_cast<uint32_t*>(dv + (long)(r0 + g) * p.H * V + col) = pack2<T>(acc[nt][0], acc[nt][1]);
+        if (r0 + g + 8 < m.len)
+          *reinterpret_cast<uint32_t*>(dv + (long)(r0 + g + 8) * p.H * V + col) = pack2<T>(acc[nt][2], acc[nt][3]);
+      }
+    }
+    __syncthreads();  // Sa: dVnb, dOs, AgT complete; every warp is done reading dSb
     if (DELTA) {
       store_tile<T, V>(static_cast<T*>(p.dvn) + ((long)c * p.H + h) * 64 * V, V, dVnb, LDV, 64, tid, 256);
       zero_acc(acc);
@@ -188,8 +206,6 @@ __global__ void __launch_bounds__(256, 1) sg_bwd_state_kernel(BwdParams p) {
       }
       store_acc<T, ONT>(dWs, LDV, r0, c0, acc, lane, -rs0.gam, -rs1.gam);
       __syncthreads();  // Sb: dWs complete
-    } else {
-      store_tile<T, V>(dv, (long)p.H * V, dVnb, LDV, m.len, tid, 256);  // dV = dVn
     }
     // dS = keep gamma dS+ + Q^T (scale cin Gamma dO) - K^T (cin Gamma dW)
     const float kg = keep_gamma(Gs, runs, m.flags);
@@ -200,8 +216,12 @@ __global__ void __launch_bounds__(256, 1) sg_bwd_state_kernel(BwdParams p) {
       accD[nt][2] *= kg;
       accD[nt][3] *= kg;
     }
-    warp_gemm<T, SNT, 4, A_COL, B_KN>(accD, qS + sr0, LDK, dOs + sc0, LDV, lane);
-    if (DELTA) warp_gemm<T, SNT, 4, A_COL, B_KN>(accD, kS + sr0, LDK, dWs + sc0, LDV, lane);
+    if (DELTA) {
+      warp_gemm<T, SNT, 4, A_COL, B_KN>(accD, qS + sr0, LDK, dOs + sc0, LDV, lane);
+      warp_gemm<T, SNT, 4, A_COL, B_KN>(accD, kS + sr0, LDK, dWs + sc0, LDV, lane);
+    } else {
+      warp_gemm_scaled_a<T, SNT, 4, B_KN>(accD, qS + sr0, LDK, betas, doS + sc0, LDV, lane);
+    }
     store_acc<T, SNT>(dSb, LDV, sr0, sc0, accD, lane);
   }
 

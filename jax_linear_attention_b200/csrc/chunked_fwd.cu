@@ -33,11 +33,16 @@ struct FwdSmem {
   static constexpr int LDK = K + 8, LDV = V + 8, LDC = 72;
   static constexpr int kStageElems = 2 * 64 * LDK + 64 * LDV + (DELTA ? 64 * LDC : 0);
   static constexpr int kStageBytes = kStageElems * 2 + 512 + 64;  // + gates (128 f32) + runs (64 u8)
-  static constexpr int kBytes = 2 * kStageBytes + (K * LDV + 3 * 64 * LDV + (DELTA ? 64 * LDC : 0)) * 2;
+  // Without the delta rule only the 16-bit state copy lives outside the stages: the output is staged in the chunk's
+  // dead q tile and the Gamma_r factor of the state update is applied to the key fragments in registers.
+  static constexpr int kBytes = 2 * kStageBytes + (K * LDV + (DELTA ? 3 * 64 * LDV + 64 * LDC : 0)) * 2;
 };
 
+// (Without the delta rule and with V = 64 -- the Mamba-2 shape, 4 x 128 chains at B = 8, H = 64 -- two CTAs share an SM:
+// 108 KB of shared memory and at most 128 registers each. The pass is bound by the latency of its dependent products
+// and barriers, so the second chain runs in the first one's gaps.)
 template <typename T, int K, int V, bool DELTA>
-__global__ void __launch_bounds__(256, 1) sg_fwd_kernel(FwdParams p) {
+__global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_fwd_kernel(FwdParams p) {
   using L = FwdSmem<T, K, V, DELTA>;
   constexpr int LDK = L::LDK, LDV = L::LDV, LDC = L::LDC;
   constexpr int WR = K / 16, WC = 8 / WR;   // warps over state rows / columns
@@ -152,15 +157,10 @@ __global__ void __launch_bounds__(256, 1) sg_fwd_kernel(FwdParams p) {
       warp_gemm<T, ONT, 4, A_ROW, B_KN>(acc, Agb + r0 * LDC, LDC, Wb + c0, LDV, lane);
       store_acc<T, ONT>(Vnb, LDV, r0, c0, acc, lane);
       store_acc<T, ONT>(VnS, LDV, r0, c0, acc, lane, rs0.gamr, rs1.gamr);
-    } else {
-      // Vn = V: only the Gamma_r-scaled copy for the state update is needed
-      const int i = tid >> 2, j0 = (tid & 3) * (V / 4);
-      const float gr = row_scalars(Gs, runs, m.flags, i).gamr;
-#pragma unroll
-      for (int jj = 0; jj < V / 4; jj += 2) {
-        const float2 x = unpack2<T>(*reinterpret_cast<const uint32_t*>(vS + i * LDV + j0 + jj));
-        *reinterpret_cast<uint32_t*>(VnS + i * LDV + j0 + jj) = pack2<T>(x.x * gr, x.y * gr);
-      }
+    } else if (tid < 64) {
+      // Vn = V. The state update needs tail Gamma_r per token: kept in the (unused) beta half of the gate vectors
+      // and applied to the key fragments (ordered before its readers by S3 / S4)
+      stage_g(s)[64 + tid] = row_scalars(Gs, runs, m.flags, tid).gamr;
     }
 
     // P = (Q K^T) D for this warp's 16 rows and all 64 columns, kept as A fragments
@@ -192,9 +192,12 @@ __global__ void __launch_bounds__(256, 1) sg_fwd_kernel(FwdParams p) {
     __syncthreads();  // S3: Vnb / VnS complete
     const T* vn = DELTA ? Vnb : vS;
     warp_gemm_ra<T, ONT, 4, B_KN>(accO, pfrag, vn + c0, LDV, lane);
-    store_acc<T, ONT>(Wb, LDV, r0, c0, accO, lane, p.scale, p.scale);  // O staged in Wb
-    __syncthreads();  // S4: every warp is done with Sb and Wb holds O
-    store_tile<T, V>(static_cast<T*>(p.o) + ((long)m.tok0 * p.H + h) * V, (long)p.H * V, Wb, LDV, m.len, tid, 256);
+    // O staged in Wb; without the delta rule in the q tile, which every warp finished reading before S3
+    T* oS = DELTA ? Wb : stage_q(s);
+    constexpr int LDO = DELTA ? LDV : LDK;
+    store_acc<T, ONT>(oS, LDO, r0, c0, accO, lane, p.scale, p.scale);
+    __syncthreads();  // S4: every warp is done with Sb and the staging tile holds O
+    store_tile<T, V>(static_cast<T*>(p.o) + ((long)m.tok0 * p.H + h) * V, (long)p.H * V, oS, LDO, m.len, tid, 256);
     if (DELTA && p.vn_out) {
       store_tile<T, V>(static_cast<T*>(p.vn_out) + ((long)c * p.H + h) * 64 * V, V, Vnb, LDV, 64, tid, 256);
     }
@@ -207,7 +210,11 @@ __global__ void __launch_bounds__(256, 1) sg_fwd_kernel(FwdParams p) {
       accS[nt][2] *= kg;
       accS[nt][3] *= kg;
     }
-    warp_gemm<T, SNT, 4, A_COL, B_KN>(accS, kS + sr0, LDK, VnS + sc0, LDV, lane);
+    if (DELTA) {
+      warp_gemm<T, SNT, 4, A_COL, B_KN>(accS, kS + sr0, LDK, VnS + sc0, LDV, lane);
+    } else {
+      warp_gemm_scaled_a<T, SNT, 4, B_KN>(accS, kS + sr0, LDK, betas, vS + sc0, LDV, lane);
+    }
     store_acc<T, SNT>(Sb, LDV, sr0, sc0, accS, lane);
   }
 

@@ -104,6 +104,36 @@ __device__ __forceinline__ void warp_gemm(float (&acc)[NT][4], const T* a_base, 
   }
 }
 
+// acc += (A diag(w))(16 x 16*KSTEPS) * B with A stored A_COL (X[k][m]) and one fp32 weight per k index: the weights
+// are applied to the 16-bit A fragments in registers (one rounding, as if X's rows had been scaled in memory).
+template <typename T, int NT, int KSTEPS, int BMODE>
+__device__ __forceinline__ void warp_gemm_scaled_a(float (&acc)[NT][4], const T* a_base, int lda, const float* w,
+                                                   const T* b_base, int ldb, int lane) {
+  static_assert(NT % 2 == 0, "n-tiles come in pairs");
+  const int t2 = (lane & 3) * 2;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    uint32_t a[4];
+    load_a<T, A_COL>(a, a_base, lda, ks * 16, lane);
+    // a[0], a[1]: k = 16 ks + 2t, +1 (rows g, g + 8); a[2], a[3]: k = 16 ks + 8 + 2t, +1
+    const float2 w0 = *reinterpret_cast<const float2*>(w + ks * 16 + t2);
+    const float2 w1 = *reinterpret_cast<const float2*>(w + ks * 16 + 8 + t2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack2<T>(a[i]);
+      const float2 ww = i < 2 ? w0 : w1;
+      a[i] = pack2<T>(x.x * ww.x, x.y * ww.y);
+    }
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      load_b2<T, BMODE>(b, b_base, ldb, np * 16, ks * 16, lane);
+      mma16816<T>(acc[2 * np], a, b[0], b[1]);
+      mma16816<T>(acc[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
 // Same with the A fragments already in registers: afrag[ks] is the 16x16 A block of k-step ks.
 template <typename T, int NT, int KSTEPS, int BMODE>
 __device__ __forceinline__ void warp_gemm_ra(float (&acc)[NT][4], const uint32_t (&afrag)[KSTEPS][4], const T* b_base,
