@@ -553,8 +553,8 @@ def main() -> None:
             small = prof[name]["total_ms"] / prof[name]["launches"] < 0.03  # table and gate prologues: a few MB
             if t is None and not small:
                 step_traffic_known = False
-            elif t is not None:
-                step_traffic += t["bytes_per_unit"] * units
+            elif t is not None:  # (a kernel may launch more than once per step: the two key-gradient finalisers)
+                step_traffic += t["bytes_per_unit"] * units * prof[name]["launches"] / (len(blocks_ms) * args.steps)
         if prof:
             top = max(prof, key=lambda n: prof[n]["total_ms"])
             per_launch_ms = prof[top]["total_ms"] / prof[top]["launches"]

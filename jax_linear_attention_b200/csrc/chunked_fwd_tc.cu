@@ -130,11 +130,7 @@ __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, volatile in
     uint32_t done;
     asm volatile(
         "{\n.reg .pred p;\n"
-#ifdef JLA_TEST_WAIT
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-#endif
         "selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(done)
         : "r"(addr), "r"(parity)
