@@ -69,13 +69,42 @@ def _header(t: torch.Tensor) -> torch.Tensor:
     return torch.tensor(fields + [0] * (8 - len(fields)), dtype=torch.int64, device=t.device)
 
 
+class _Requests:
+    """The requests of one batched point-to-point call, waited on together."""
+
+    def __init__(self, works):
+        self.works = works
+
+    def wait(self):
+        for w in self.works:
+            w.wait()
+
+
+def _p2p(op, t: torch.Tensor, peer: int, group) -> _Requests:
+    """One point-to-point transfer as a batched op: NCCL then runs it as a grouped send/recv of its own instead of
+    serialising it with every other operation of the process group (what an unbatched ``send``/``recv`` does on a
+    group that was initialised eagerly)."""
+    return _Requests(dist.batch_isend_irecv([dist.P2POp(op, t, peer, group=group)]))
+
+
+def _exchange_with_neighbours(send: torch.Tensor, recv: torch.Tensor, prev_rank, next_rank, group) -> None:
+    """``send`` goes to the next rank and ``recv`` is filled by the previous one (either may be absent), as one batch."""
+    ops = []
+    if next_rank is not None:
+        ops.append(dist.P2POp(dist.isend, send, next_rank, group=group))
+    if prev_rank is not None:
+        ops.append(dist.P2POp(dist.irecv, recv, prev_rank, group=group))
+    if ops:
+        _Requests(dist.batch_isend_irecv(ops)).wait()
+
+
 def send_state(t: torch.Tensor, dst: int, group, what: str = "state"):
     """``isend`` of a hand-off tensor (preceded by its header when checks are on); returns the request to wait on."""
     t = t.contiguous()
     try:
         if _checked(group):
-            dist.send(_header(t), dst, group=group)
-        return dist.isend(t, dst, group=group)
+            _p2p(dist.isend, _header(t), dst, group).wait()
+        return _p2p(dist.isend, t, dst, group)
     except RuntimeError as err:
         raise StateMessageError(f"context parallel: sending the {what} to rank {dst} failed: {err}") from err
 
@@ -88,14 +117,14 @@ def recv_state(t: torch.Tensor, src: int, group, what: str = "state") -> torch.T
     try:
         if _checked(group):
             got = torch.zeros(8, dtype=torch.int64, device=t.device)
-            dist.recv(got, src, group=group)
+            _p2p(dist.irecv, got, src, group).wait()
             want = _header(t)
             if not torch.equal(got.cpu(), want.cpu()):
                 g = got.cpu().tolist()
                 raise StateMessageError(
                     f"context parallel: rank {src} announced a {what} message with header {g} (magic, dtype code, ndim, "
                     f"shape); expected {want.cpu().tolist()} = {tuple(t.shape)} {t.dtype}")
-        dist.recv(t, src, group=group)
+        _p2p(dist.irecv, t, src, group).wait()
     except StateMessageError:
         raise
     except RuntimeError as err:
@@ -135,13 +164,7 @@ class _ContextParallel(torch.autograd.Function):
         if seg is not None and world > 1:  # the previous rank's last segment id decides whether token 0 is a start
             last = seg[:, -1].contiguous()
             recv = torch.empty_like(last)
-            reqs = []
-            if next_rank is not None:
-                reqs.append(dist.isend(last, next_rank, group=group))
-            if prev_rank is not None:
-                reqs.append(dist.irecv(recv, prev_rank, group=group))
-            for r in reqs:
-                r.wait()
+            _exchange_with_neighbours(last, recv, prev_rank, next_rank, group)
             prev_last = recv.cpu() if prev_rank is not None else None
 
         leaves = [x.detach().requires_grad_(True) for x in xs]
@@ -361,13 +384,7 @@ def plan_pieces(segment_ids, piece_len: int, *, group=None, t_local: int | None 
         if world > 1:  # does this shard's first token continue the previous rank's document?
             last = segment_ids[:, -1].contiguous()
             recv = torch.empty_like(last)
-            reqs = []
-            if next_rank is not None:
-                reqs.append(dist.isend(last, next_rank, group=group))
-            if prev_rank is not None:
-                reqs.append(dist.irecv(recv, prev_rank, group=group))
-            for r in reqs:
-                r.wait()
+            _exchange_with_neighbours(last, recv, prev_rank, next_rank, group)
             cont0 = prev_rank is not None and int(recv.cpu()[0]) == int(ids[0])
     cu, cont = _piece_table(ids, cont0, int(piece_len))
     return PiecePlan(cu, cont, torch.tensor(cu, dtype=torch.int32, device=device))

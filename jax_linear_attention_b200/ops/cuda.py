@@ -266,6 +266,11 @@ MAX_SPLIT_CTAS = 32          # split only when rows * heads is at most this
 MIN_PIECE_CHUNKS = 8         # every piece keeps at least this many chunks
 MAX_DELTA_PIECES = 8         # the delta rule pays an extra state pass for the maps and their scan
 DELTA_PIECE_CHUNKS_ABOVE_4 = 32
+# Not in the reference (whose split runs inside one jitted graph): here the split is a sequence of calls driven from
+# the host -- two state-only passes, the scan, the real pass, and their mirror images backward -- and costs about
+# 1.2 ms of launches whatever the length. Measured on a B200 (one row, 4 and 16 heads, d = 128, forward + backward):
+# 8 Ki tokens 1.29 ms unsplit = 1.30 ms split; 16 Ki 2.50 against 1.67 ms; 128 Ki 19.4 against 9.3 ms.
+MIN_SPLIT_CHUNKS = 192       # shorter sequences run unsplit
 
 
 def pieces(batch: int, heads: int, seq_len: int, *, delta: bool, sm_count: int = 148) -> int:
@@ -274,6 +279,8 @@ def pieces(batch: int, heads: int, seq_len: int, *, delta: bool, sm_count: int =
     if ctas > MAX_SPLIT_CTAS:
         return 1
     chunks = -(-seq_len // CHUNK)
+    if chunks < MIN_SPLIT_CHUNKS:
+        return 1
     limit = min(MAX_DELTA_PIECES, sm_count // ctas) if delta else sm_count // ctas
     cp = 1
     while 2 * cp <= limit and chunks // (2 * cp) >= MIN_PIECE_CHUNKS:

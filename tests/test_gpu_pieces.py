@@ -52,17 +52,22 @@ def test_policy_follows_the_reference():
     from jax_linear_attention_b200.ops.cuda import pieces
 
     assert pieces(8, 16, 2048, delta=True) == 1          # 128 rows x heads fill the GPU
-    assert pieces(1, 16, 2048, delta=True) == 4          # one row of a batch x heads shard over 8 GPUs
+    assert pieces(1, 16, 2048, delta=True) == 1          # too short to pay for the split's own launches (measured)
+    assert pieces(1, 16, 8192, delta=True) == 1
+    assert pieces(1, 16, 16384, delta=True) == 8         # 32 chunks per piece: the most the delta rule takes
+    assert pieces(1, 16, 12288, delta=True) == 4         # more than 4 pieces only with 32 chunks each
     assert pieces(1, 16, 1_064_960, delta=True) == 8     # at most 8 pieces with the delta rule
-    assert pieces(1, 4, 4096, delta=False) == 8          # every piece keeps at least 8 chunks
+    assert pieces(1, 4, 16384, delta=False) == 32        # every piece keeps at least 8 chunks
     assert pieces(1, 2, 900, delta=True) == 1
 
 
 @pytest.mark.parametrize("kind", ["gated_deltanet", "simple_gla", "kda"])
-def test_split_call_matches_the_unsplit_call_and_the_oracle(kind):
+def test_split_call_matches_the_unsplit_call_and_the_oracle(kind, monkeypatch):
+    from jax_linear_attention_b200.ops import cuda
     from jax_linear_attention_b200.ops.cuda import no_pieces, pieces
 
-    T, H = 4096, 4
+    monkeypatch.setattr(cuda, "MIN_SPLIT_CHUNKS", 8)  # the policy's length floor is a speed matter; 4096 tokens keep
+    T, H = 4096, 4                                    # the float64 oracle of this test short
     assert pieces(1, H, T, delta=kind != "simple_gla") > 1
     case = make_case(kind, B=1, T=T, H=H, K=128, V=128, seed=71, h0=True, docs="uniform", doc_range=(300, 3000),
                      gates="kda_baseline" if kind == "kda" else "baseline")
