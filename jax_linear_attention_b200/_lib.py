@@ -9,9 +9,10 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libjla_b200.so")
+# The in-tree build's output; JLA_B200_LIB names another build of the same library (e.g. the CMake build's).
+LIB_PATH = os.environ.get("JLA_B200_LIB") or os.path.join(HERE, "libjla_b200.so")
 
-KIND = {"simple_gla": 0, "deltanet": 1, "gated_deltanet": 2, "kda": 3}
+KIND = {"simple_gla": 0, "deltanet": 1, "gated_deltanet": 2, "kda": 3}  # (gdn2: KDA with a read key, ops.cuda.gdn2)
 PATH = {"auto": 0, "recurrent": 1, "chunked": 2}
 FLAG_QK_L2NORM = 1
 FLAG_SAVE_RESIDUALS = 2
