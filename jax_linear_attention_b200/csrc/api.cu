@@ -32,7 +32,7 @@ namespace {
 // chunked KDA forward then keeps no residuals).
 int resolve_path(const jla_problem& p, bool bwd = false) {
   if (bwd && p.kind == JLA_KIND_KDA && kda_scan_backward()) return JLA_PATH_RECURRENT;
-  if (p.k_read) return JLA_PATH_RECURRENT;  // the chunk kernels read and write the state with the same key
+  if (p.k_read && p.kind != JLA_KIND_KDA) return JLA_PATH_RECURRENT;  // only the KDA chunk kernels take a read key
   if (p.path == JLA_PATH_AUTO) {
     // f32 tensors run the exact token scan; so does whatever the chunked kernels do not cover (chunked_unsupported()).
     if (p.dtype == JLA_DTYPE_F32 || chunked_unsupported(p) != nullptr) {

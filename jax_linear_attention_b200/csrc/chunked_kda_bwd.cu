@@ -21,6 +21,10 @@
 // the tensor cores multiply: +X = q^ (dP k~) + (beta k^) (dA k~) and -X = k~ (dP^T q^ + dA^T (beta k^)), with q^, k~
 // and beta k^ read back from the rounded tiles, never recomputed from q, k in fp32. Then X+ and X- differ only by the
 // order of the fp32 accumulation.
+//
+// With a separate read key (jla_problem.k_read, Gated DeltaNet-2) the read side of every formula above (k^, the rows
+// of Akk, dKs, "read-side dk") belongs to the read key and is returned as dk_read per value head; the write side
+// (k~, dKu, "write-side dk") is dk. The RK variant of the second kernel keeps the raw read key in a tile of its own.
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
@@ -34,6 +38,8 @@ constexpr float kBoundedLog = 60.f;  // the same bound as chunked_kda_prep.cu
 struct KdaGradParams {
   const ChunkMeta* meta;
   const void *q, *k;   // [tokens, Hk, K]
+  const void* k_read;  // [tokens, H, K] or nullptr
+  void* dk_read;       // [tokens, H, K] tensor dtype (with k_read)
   const float* g;      // [tokens, H, K]
   const float* gates;  // per (chunk, head): G (zero), beta[64]
   const unsigned char* runs;
@@ -143,7 +149,7 @@ __device__ __forceinline__ float col_reduce(float x) {
   return x;
 }
 
-template <typename T>
+template <typename T, bool RK>
 __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p) {
   constexpr int LDK = KD + 8, LDC = 72, NT = 512;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
@@ -173,10 +179,15 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
   float* dbrow = Glast + KD;               // [4][64] per column quarter
   float* dbcol = dbrow + 256;              // [64]
   int* run = reinterpret_cast<int*>(dbcol + 64);  // [64]
+  T* tr = RK ? reinterpret_cast<T*>(run + 64) : tk;  // raw read key (RK: a tile of its own)
 
   const long kstride = (long)p.Hk * KD;
   load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
   load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
+  if (RK) {
+    load_tile_async<T, 64, KD>(tr, LDK, static_cast<const T*>(p.k_read) + ((long)m.tok0 * p.H + h) * KD, (long)p.H * KD,
+                               m.len, tid, NT);
+  }
   load_tile_async<T, 64, 64>(Tt, LDC, static_cast<const T*>(p.t0) + slot * 4096, 64, 64, tid, NT);
   load_tile_async<T, 64, 64>(Xm, LDC, static_cast<const T*>(p.dag) + slot * 4096, 64, 64, tid, NT);
   load_tile_async<T, 64, 64>(Xp, LDC, static_cast<const T*>(p.dp) + slot * 4096, 64, 64, tid, NT);
@@ -253,6 +264,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
   const long tstride = (long)p.H * KD;
   T* dq16 = p.dq ? static_cast<T*>(p.dq) + ((long)m.tok0 * p.Hk + hk) * KD : nullptr;  // direct stores (H == Hk)
   T* dk16 = p.dk ? static_cast<T*>(p.dk) + ((long)m.tok0 * p.Hk + hk) * KD : nullptr;
+  T* dkr16 = RK ? static_cast<T*>(p.dk_read) + tokbase : nullptr;  // read-side dk, one row per value head
   const float* dqs = p.dqs + slot * 64 * KD;
   const float* dks = p.dks + slot * 64 * KD;
   const float* dku = p.dku + slot * 64 * KD;
@@ -264,20 +276,22 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
       const float bi = betas[i];
       const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      const uint4 rv = *reinterpret_cast<const uint4*>(tr + i * LDK + c8);
       uint4 oq, ok, ob;
       const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
       const uint32_t* kw = reinterpret_cast<const uint32_t*>(&kv);
+      const uint32_t* rw2 = reinterpret_cast<const uint32_t*>(&rv);
       uint32_t* oqw = reinterpret_cast<uint32_t*>(&oq);
       uint32_t* okw = reinterpret_cast<uint32_t*>(&ok);
       uint32_t* obw = reinterpret_cast<uint32_t*>(&ob);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kw[e]);
+        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kw[e]), rf = unpack2<T>(rw2[e]);
         const float d0 = Gm[i * KD + c8 + 2 * e] - 0.5f * Glast[c8 + 2 * e];
         const float d1 = Gm[i * KD + c8 + 2 * e + 1] - 0.5f * Glast[c8 + 2 * e + 1];
         const float u0 = __expf(d0), u1 = __expf(d1), n0 = __expf(-d0), n1 = __expf(-d1);
         oqw[e] = pack2<T>(qf.x * u0, qf.y * u1);
-        okw[e] = pack2<T>(bi * kf.x * u0, bi * kf.y * u1);
+        okw[e] = pack2<T>(bi * rf.x * u0, bi * rf.y * u1);
         obw[e] = pack2<T>(kf.x * n0, kf.y * n1);
       }
       *reinterpret_cast<uint4*>(tqh + i * LDK + c8) = oq;
@@ -311,11 +325,12 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
         const float2 ks2 = *reinterpret_cast<const float2*>(dks + i * KD + col);
         const float2 ku2 = *reinterpret_cast<const float2*>(dku + i * KD + col);
         const float2 qr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tq + i * LDK + col));
-        const float2 kr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tk + i * LDK + col));
+        const float2 kr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tr + i * LDK + col));  // read key
+        const float2 kw2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tk + i * LDK + col));  // write key
         const float2 kh2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tkh + i * LDK + col));  // beta k^
         const float2 qh2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tqh + i * LDK + col));  // q^
         const float2 kt2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tb + i * LDK + col));   // k~
-        float dqv[2], dkv[2];
+        float dqv[2], dkv[2], dkrv[2];
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           const int e = 2 * hi + x;
@@ -325,7 +340,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
           // exp(G_i) = exp(d) exp(R) and exp(G_63 - G_i) = exp(-d) exp(R) with R = G_63 / 2 (|R| <= 30 on this path)
           const float eg = cin ? eu * eR[x] : 0.f, ew = tail ? en * eR[x] : 0.f;
           const float khb = x ? kh2.y : kh2.x, qh = x ? qh2.y : qh2.x, kt = x ? kt2.y : kt2.x;
-          const float qr = x ? qr2.y : qr2.x, kr = x ? kr2.y : kr2.x;
+          const float qr = x ? qr2.y : qr2.x, kr = x ? kr2.y : kr2.x, kwr = x ? kw2.y : kw2.x;
           if (hi) db1 += kr * eu * accU[nt][e]; else db0 += kr * eu * accU[nt][e];  // dbeta_i += k^_i . (dA k~)_i
           const float dqs_e = (x ? qs2.y : qs2.x) * eg, dks_e = (x ? ks2.y : ks2.x) * eg;
           const float dq = accQ[nt][e] * eu + dqs_e;
@@ -334,10 +349,11 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
           const float dkw = accW[nt][e] * en + kuw;
           // the pair terms from the rounded operands themselves (see the file header), the state terms in fp32
           dGt[i * KD + col + x] = (qh * accQ[nt][e] + khb * accU[nt][e] - kt * accW[nt][e]) +
-                                  (qr * dqs_e + kr * (dks_e - kuw));
-          colsum[x] += kr * kuw;
+                                  (qr * dqs_e + kr * dks_e - kwr * kuw);
+          colsum[x] += kwr * kuw;
           dqv[x] = dq;
-          dkv[x] = dkr + dkw;
+          dkv[x] = RK ? dkw : dkr + dkw;
+          dkrv[x] = dkr;
         }
         if (i < m.len) {
           if (dq16) {
@@ -347,6 +363,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
             *reinterpret_cast<float2*>(p.dq_acc + tokbase + i * tstride + col) = make_float2(dqv[0], dqv[1]);
             *reinterpret_cast<float2*>(p.dk_acc + tokbase + i * tstride + col) = make_float2(dkv[0], dkv[1]);
           }
+          if (RK) *reinterpret_cast<uint32_t*>(dkr16 + (long)i * tstride + col) = pack2<T>(dkrv[0], dkrv[1]);
         }
       }
       const float a = col_reduce(colsum[0]), b = col_reduce(colsum[1]);
@@ -375,7 +392,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
       for (int i = 0; i < 64; ++i) dGt[i * KD + ch] = 0.f;
       for (int i = 0; i < 64; ++i) {
         const float Gi = Gm[i * KD + ch];
-        const float qi = to_f32(tq[i * LDK + ch]), ki = to_f32(tk[i * LDK + ch]);
+        const float qi = to_f32(tq[i * LDK + ch]), ki = to_f32(tr[i * LDK + ch]);  // ki: the read key of token i
         float dq = 0.f, u = 0.f;
         for (int j = 0; j <= i; ++j) {
           if (run[j] != run[i]) continue;
@@ -419,9 +436,10 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
         dGt[i * KD + ch] = keep[i * KD + ch] - ki * dkw;
         colsum += ki * kuw;
         if (i < m.len) {
-          const float dk = to_f32(tb[i * LDK + ch]) + dkw;
+          const float dk = RK ? dkw : to_f32(tb[i * LDK + ch]) + dkw;
           if (dk16) dk16[(long)i * kstride + ch] = from_f32<T>(dk);
           else p.dk_acc[tokbase + i * tstride + ch] = dk;
+          if (RK) dkr16[(long)i * tstride + ch] = tb[i * LDK + ch];
         }
       }
     }
@@ -451,10 +469,10 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
 template <typename T>
 int launch_grads(const KdaGradParams& gp, int blocks, cudaStream_t s) {
   const size_t smem_a = (2 * 64 * (VD + 8) + 2 * VD * (KD + 8) + 3 * VD * 72) * sizeof(T) + 2 * KD * sizeof(float);
-  const size_t smem_b = (5 * 64 * (KD + 8) + 4 * 64 * 72) * sizeof(T) +
+  const size_t smem_b = ((gp.k_read ? 6 : 5) * 64 * (KD + 8) + 4 * 64 * 72) * sizeof(T) +
                         (2 * 64 * KD + 4 * KD + 64 + KD + 256 + 64) * sizeof(float) + 64 * sizeof(int);
   auto* ka = kda_state_grads_kernel<T>;
-  auto* kb = kda_intra_grads_kernel<T>;
+  auto* kb = gp.k_read ? kda_intra_grads_kernel<T, true> : kda_intra_grads_kernel<T, false>;
   JLA_CUDA_OK(cudaFuncSetAttribute(ka, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
   JLA_CUDA_OK(cudaFuncSetAttribute(kb, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b));
   {
@@ -484,6 +502,8 @@ int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, c
   gp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
   gp.q = c.q_eff;
   gp.k = c.k_eff;
+  gp.k_read = p.k_read;
+  gp.dk_read = io.dk_read;
   gp.g = p.g;
   gp.gates = reinterpret_cast<const float*>(c.res + pl.gates);
   gp.runs = reinterpret_cast<const unsigned char*>(c.res + pl.runs);

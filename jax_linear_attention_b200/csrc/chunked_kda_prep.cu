@@ -18,6 +18,11 @@
 //   (q exp(G - R)) (k exp(R - G))^T,   |G - R| <= |G_63| / 2,
 // and run on the tensor cores when no channel decays by more than exp(-kBoundedLog) over the chunk. Chunks with a
 // stronger decay take the exact fp32 loop over (i, j, c) instead, so the result never depends on the bound.
+//
+// With a separate read key (jla_problem.k_read, Gated DeltaNet-2: S = S' + k^T (v - k_read S')) the key has two roles:
+// wherever a token READS the state or the earlier tokens of its chunk -- the rows of Akk and the operand kr -- the
+// read key stands for k; wherever it WRITES -- the columns of Akk and Aqk, the operand kw -- k itself does. The RK
+// variant of the kernel keeps the read key in a tile of its own (one CTA per SM instead of two).
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
@@ -32,6 +37,7 @@ constexpr float kBoundedLog = 60.f;  // exp(+-30) factors: far inside the bf16 /
 struct KdaPrepParams {
   const ChunkMeta* meta;
   const void *q, *k;   // [tokens, Hk, K] (after the optional L2 norm)
+  const void* k_read;  // [tokens, H, K] or nullptr
   const float* g;      // [tokens, H, K]
   const float* gates;  // per (chunk, head): G[64] (zero here), beta[64]
   const unsigned char* runs;
@@ -42,8 +48,8 @@ struct KdaPrepParams {
   int H, Hk;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
+template <typename T, bool RK>
+__global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams p) {
   constexpr int LDK = KD + 8, LDA = kTriLda, LDM = kTriLdm, LDP = 72, NT = 256;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
@@ -62,6 +68,7 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
   float* betas = M + 32 * LDM;                   // [64]
   float* Glast = betas + 64;                     // [KD]
   int* run = reinterpret_cast<int*>(Glast + KD); // [64]
+  T* tr = RK ? reinterpret_cast<T*>(run + 64) : tk;  // the read key, then read key exp(G - R) (RK: a tile of its own)
   float* X = reinterpret_cast<float*>(smem_raw);
   static_assert(64 * LDK * sizeof(T) >= 64 * LDA * sizeof(float), "X overlays the q tile");
   T* pst = tb;
@@ -69,6 +76,10 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
   const long kstride = (long)p.Hk * KD;
   load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
   load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
+  if (RK) {
+    load_tile_async<T, 64, KD>(tr, LDK, static_cast<const T*>(p.k_read) + ((long)m.tok0 * p.H + h) * KD, (long)p.H * KD,
+                               m.len, tid, NT);
+  }
   cp_async_commit();
   if (tid < 64) {
     betas[tid] = p.gates[slot * 128 + 64 + tid];
@@ -120,16 +131,18 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
       const bool tail = i < m.len && run[i] == run_last;
       uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      uint4 rv = RK ? *reinterpret_cast<const uint4*>(tr + i * LDK + c8) : kv;  // the read key
       uint4 bv, oq, or_, ow;
       uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
       uint32_t* kwd = reinterpret_cast<uint32_t*>(&kv);
+      uint32_t* rwd = reinterpret_cast<uint32_t*>(&rv);
       uint32_t* bw = reinterpret_cast<uint32_t*>(&bv);
       uint32_t* oqw = reinterpret_cast<uint32_t*>(&oq);
       uint32_t* orw = reinterpret_cast<uint32_t*>(&or_);
       uint32_t* oww = reinterpret_cast<uint32_t*>(&ow);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]);
+        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]), rf = unpack2<T>(rwd[e]);
         const float d0 = Gm[i * KD + c8 + 2 * e] - 0.5f * Glast[c8 + 2 * e];
         const float d1 = Gm[i * KD + c8 + 2 * e + 1] - 0.5f * Glast[c8 + 2 * e + 1];
         const float u0 = __expf(d0), u1 = __expf(d1), n0 = __expf(-d0), n1 = __expf(-d1);
@@ -137,26 +150,26 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
         const float e0 = cin ? u0 * r0 : 0.f, e1 = cin ? u1 * r1 : 0.f;
         const float w0 = tail ? n0 * r0 : 0.f, w1 = tail ? n1 * r1 : 0.f;
         oqw[e] = pack2<T>(qf.x * e0, qf.y * e1);
-        orw[e] = pack2<T>(kf.x * e0, kf.y * e1);
+        orw[e] = pack2<T>(rf.x * e0, rf.y * e1);
         oww[e] = pack2<T>(kf.x * w0, kf.y * w1);
         qw[e] = pack2<T>(qf.x * u0, qf.y * u1);
-        kwd[e] = pack2<T>(kf.x * u0, kf.y * u1);
+        rwd[e] = pack2<T>(rf.x * u0, rf.y * u1);
         bw[e] = pack2<T>(kf.x * n0, kf.y * n1);
       }
       *reinterpret_cast<uint4*>(qs + i * KD + c8) = oq;
       *reinterpret_cast<uint4*>(kr + i * KD + c8) = or_;
       *reinterpret_cast<uint4*>(kw + i * KD + c8) = ow;
       *reinterpret_cast<uint4*>(tq + i * LDK + c8) = qv;
-      *reinterpret_cast<uint4*>(tk + i * LDK + c8) = kv;
+      *reinterpret_cast<uint4*>(tr + i * LDK + c8) = rv;  // (tr is tk without a read key)
       *reinterpret_cast<uint4*>(tb + i * LDK + c8) = bv;
     }
     __syncthreads();
-    // warps 0-3: q^ k~^T (the score tile), warps 4-7: k^ k~^T (the solve matrix); 16 rows each
+    // warps 0-3: q^ k~^T (the score tile), warps 4-7: k^ k~^T (the solve matrix; k^ from the read key); 16 rows each
     const int rw = warp & 3;
     const bool score = warp < 4;
     float acc[8][4];
     zero_acc(acc);
-    warp_gemm<T, 8, KD / 16, A_ROW, B_NK>(acc, (score ? tq : tk) + rw * 16 * LDK, LDK, tb, LDK, lane);
+    warp_gemm<T, 8, KD / 16, A_ROW, B_NK>(acc, (score ? tq : tr) + rw * 16 * LDK, LDK, tb, LDK, lane);
     __syncthreads();  // every warp has read the tiles: X and the staged P may take their place
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -187,20 +200,22 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
       const bool tail = i < m.len && run[i] == run_last;
       const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
+      const uint4 rv = *reinterpret_cast<const uint4*>(tr + i * LDK + c8);
       const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
       const uint32_t* kwd = reinterpret_cast<const uint32_t*>(&kv);
+      const uint32_t* rwd = reinterpret_cast<const uint32_t*>(&rv);
       uint4 oq, or_, ow;
       uint32_t* oqw = reinterpret_cast<uint32_t*>(&oq);
       uint32_t* orw = reinterpret_cast<uint32_t*>(&or_);
       uint32_t* oww = reinterpret_cast<uint32_t*>(&ow);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]);
+        const float2 qf = unpack2<T>(qw[e]), kf = unpack2<T>(kwd[e]), rf = unpack2<T>(rwd[e]);
         const float g0 = Gm[i * KD + c8 + 2 * e], g1 = Gm[i * KD + c8 + 2 * e + 1];
         const float e0 = cin ? __expf(g0) : 0.f, e1 = cin ? __expf(g1) : 0.f;
         const float w0 = tail ? __expf(Glast[c8 + 2 * e] - g0) : 0.f, w1 = tail ? __expf(Glast[c8 + 2 * e + 1] - g1) : 0.f;
         oqw[e] = pack2<T>(qf.x * e0, qf.y * e1);
-        orw[e] = pack2<T>(kf.x * e0, kf.y * e1);
+        orw[e] = pack2<T>(rf.x * e0, rf.y * e1);
         oww[e] = pack2<T>(kf.x * w0, kf.y * w1);
       }
       *reinterpret_cast<uint4*>(qs + i * KD + c8) = oq;
@@ -218,7 +233,7 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
           const float e = __expf(Gm[i * KD + ch] - Gm[j * KD + ch]);
           const float kj = to_f32(tk[j * LDK + ch]) * e;
           sq += to_f32(tq[i * LDK + ch]) * kj;
-          sk += to_f32(tk[i * LDK + ch]) * kj;
+          sk += to_f32(tr[i * LDK + ch]) * kj;
         }
       }
       A[i * LDA + j] = j < i ? betas[i] * sk : 0.f;
@@ -269,6 +284,7 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
   kp.meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
   kp.q = c.q_eff;
   kp.k = c.k_eff;
+  kp.k_read = p.k_read;
   kp.g = p.g;
   kp.gates = reinterpret_cast<const float*>(c.res + pl.gates);
   kp.runs = reinterpret_cast<const unsigned char*>(c.res + pl.runs);
@@ -286,9 +302,9 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
     return JLA_ERR_UNSUPPORTED;
   }
   using T = __nv_bfloat16;
-  const size_t smem = 3 * 64 * (KD + 8) * sizeof(T) + (64 * KD + 64 * kTriLda + 32 * kTriLdm + 64 + KD) * sizeof(float) +
-                      64 * sizeof(int);
-  auto* kern = kda_prep_kernel<T>;
+  const size_t smem = (p.k_read ? 4 : 3) * 64 * (KD + 8) * sizeof(T) +
+                      (64 * KD + 64 * kTriLda + 32 * kTriLdm + 64 + KD) * sizeof(float) + 64 * sizeof(int);
+  auto* kern = p.k_read ? kda_prep_kernel<T, true> : kda_prep_kernel<T, false>;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
     ProfScope ps(kProfKdaPrep, s);

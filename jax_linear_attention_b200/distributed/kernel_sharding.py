@@ -68,14 +68,21 @@ def shard_kernel_call(fn, q, k, v, gates, options, *, rank: int, world: int, sup
     heads = v.shape[2]
     plan = plan_shards(batch, heads, key_heads, world)
     bs, hs, ks = shard_slices(plan, rank, batch, heads, key_heads)
-    lq, lk, lv = q[bs][:, :, ks], k[bs][:, :, ks], v[bs][:, :, hs]
-    lgates = [g[bs][:, :, hs] for g in gates]
+    def cut(x, dim: int, sl: slice):
+        """``x`` restricted to ``sl`` along ``dim``; the tensor itself when the slice is the whole axis (a view would
+        cost an autograd node forward and a zero-filled copy of the gradient backward)."""
+        if (sl.start or 0) == 0 and (sl.stop is None or sl.stop >= x.shape[dim]):
+            return x
+        return x.narrow(dim, sl.start or 0, sl.stop - (sl.start or 0))
+
+    lq, lk, lv = cut(cut(q, 0, bs), 2, ks), cut(cut(k, 0, bs), 2, ks), cut(cut(v, 0, bs), 2, hs)
+    lgates = [cut(cut(g, 0, bs), 2, hs) for g in gates]
     lopts = dict(options)
     if lopts.get("initial_state") is not None:
         st = lopts["initial_state"]
-        lopts["initial_state"] = st[:, hs] if lopts.get("cu_seqlens") is not None else st[bs][:, hs]
+        lopts["initial_state"] = cut(st, 1, hs) if lopts.get("cu_seqlens") is not None else cut(cut(st, 0, bs), 1, hs)
     if lopts.get("segment_ids") is not None:
-        lopts["segment_ids"] = lopts["segment_ids"][bs]
+        lopts["segment_ids"] = cut(lopts["segment_ids"], 0, bs)
     if supports is not None and not supports(lq, lk, lv, *lgates, **lopts):
         raise ValueError(f"the kernels do not accept the per-shard call of plan {plan} (local q {tuple(lq.shape)}, "
                          f"v {tuple(lv.shape)})")

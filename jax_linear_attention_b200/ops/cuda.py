@@ -56,7 +56,7 @@ def _problem(kind: str, dtype, B, T, H, Hk, K, V, num_seqs, scale, flags, precis
 
 def unsupported_reason(kind: str, q, k, v, gates: tuple, options: dict, *, read_key: bool = False) -> str | None:
     """Why the CUDA kernels cannot run this call (``None`` if they can); ``read_key``: the call passes a separate
-    read key (Gated DeltaNet-2), which selects the token scan.
+    read key (Gated DeltaNet-2), which only the KDA chunk kernels and the token scan take.
 
     Works on anything with ``.shape`` and ``.dtype`` (tensors or shape structs), so it can be evaluated
     on per-shard shapes; mirrors ``unsupported_reason`` of ``mosaic_gpu/scalar_gate.py:476-515``.
@@ -413,7 +413,8 @@ def gdn2(q, k, v, g, b, w, *, scale=None, initial_state=None, output_final_state
     16-bit tensors that rounds them once to 16 bits, as the reference's kernels round the gates
     (``mosaic_gpu/gdn2.py:11-12``) -- and their gradients flow back to ``k``, ``b``, ``v`` and ``w`` through autograd.
     The unit norm of ``use_qk_l2norm`` is applied first (the gate multiplies the normalised key, reference.py:118-119).
-    Calls with a read key run the fp32 token scan whatever the dtype.
+    bf16 tensors with ``K = V = 128`` run the KDA chunk kernels (the read key in tiles of its own); every other call
+    with a read key runs the fp32 token scan.
     """
     if _shape(b) != _shape(q) or _shape(w) != _shape(v) or _shape(k) != _shape(q):
         raise ValueError(f"b must be [B, T, H, K] = {_shape(q)} and w must be [B, T, H, V] = {_shape(v)} (q and k "

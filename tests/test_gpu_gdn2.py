@@ -40,11 +40,52 @@ def test_float32_gradients_match_the_oracle_autograd(spec):
     compare(got, want, 1e-4, f"gdn2 f32 {spec}")
 
 
-def test_bf16_head_128_matches_the_oracle():
-    case = make_case("gdn2", B=2, T=300, H=4, K=128, V=128, seed=72, gates="kda_baseline", docs="mixed", h0=True)
+@pytest.mark.parametrize("gates,docs,T", [("kda_baseline", "mixed", 300), ("plain", "uniform", 700),
+                                          ("kda_baseline", None, 64)])
+def test_bf16_head_128_runs_the_chunked_kernels_and_matches_the_oracle(gates, docs, T):
+    """bf16 tensors with K = V = 128 take the KDA chunk kernels with the read key in tiles of its own: forward and
+    every gradient (q, k, v, g, b, w, initial state) against the float64 oracle's autograd."""
+    case = make_case("gdn2", B=2, T=T, H=4, K=128, V=128, seed=72 + T, gates=gates, docs=docs, h0=True,
+                     doc_range=(40, 300))
     want = run_oracle("gdn2", case, scale=case["meta"]["scale"])
     got = run_cuda("gdn2", case, scale=case["meta"]["scale"], dtype="bfloat16")
-    compare(got, want, 1e-2, "gdn2 bf16 d128")
+    compare(got, want, 1e-2, f"gdn2 bf16 d128 {gates} {docs}")
+    scan = run_cuda("gdn2", case, scale=case["meta"]["scale"], dtype="bfloat16", precision="highest")
+    assert any(not np.array_equal(got[n], scan[n]) for n in got), "the chunked kernels did not run"
+    compare(got, scan, 1e-2, "gdn2 chunked against the token scan")
+
+
+def test_bf16_strong_decay_takes_the_exact_score_path():
+    """Channels that decay by e^-80 at one token in ten (the factored scores would overflow) and gates at 0 and 1:
+    the chunks run the exact fp32 loops, forward and backward, with the read key in its own role."""
+    case = make_case("gdn2", B=1, T=320, H=2, K=128, V=128, seed=75, gates="extreme", docs="mixed", h0=True)
+    assert float(np.abs(case["g"]).max()) >= 80.0
+    want = run_oracle("gdn2", case, scale=case["meta"]["scale"])
+    got = run_cuda("gdn2", case, scale=case["meta"]["scale"], dtype="bfloat16")
+    assert all(np.isfinite(x).all() for x in got.values())
+    compare(got, want, 1.5e-2, "gdn2 extreme gates")
+
+
+def test_bf16_l2norm_and_packed_rows():
+    """In-op unit norm (applied before the erase gate multiplies the key) and cu_seqlens rows with partial chunks."""
+    from jax_linear_attention_b200 import ops
+
+    case = make_case("gdn2", B=1, T=200, H=2, K=128, V=128, seed=76, gates="kda_baseline", l2norm=True)
+    cu = [0, 64, 65, 192, 200]
+    dev = "cuda"
+    t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16) for n in ("q", "k", "v", "b", "w")}
+    g = torch.tensor(case["g"], device=dev)
+    h0 = torch.tensor(np.random.default_rng(1).standard_normal((4, 2, 128, 128)).astype(np.float32) * 0.5, device=dev)
+    outs = []
+    for precision in (None, "highest"):
+        with torch.no_grad():
+            outs.append(ops.linear_attention("gdn2", t["q"], t["k"], t["v"], g=g, b=t["b"], w=t["w"],
+                                             cu_seqlens=torch.tensor(cu, device=dev, dtype=torch.int32),
+                                             initial_state=h0, output_final_state=True, use_qk_l2norm=True,
+                                             scale=case["meta"]["scale"], precision=precision))
+    (o, f), (o_ref, f_ref) = outs
+    assert rel_l2(o.float().cpu().numpy(), o_ref.float().cpu().numpy()) < 1e-2
+    assert rel_l2(f.cpu().numpy(), f_ref.cpu().numpy()) < 1e-2
 
 
 def test_equal_gates_are_kda():
