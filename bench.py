@@ -1,4 +1,4 @@
-"""Benchmark of the hot path: Gated DeltaNet chunk forward + backward at BASELINE config 1.
+"""Benchmark of the hot path: Gated DeltaNet chunk forward + backward at B8 T2048 H16 K = V = 128, bf16, packed documents.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gdn|ssd|kda]
 

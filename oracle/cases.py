@@ -81,7 +81,7 @@ def make_case(kind: str, *, B: int, T: int, H: int, K: int, V: int, Hk: int | No
 
     ``kind``: simple_gla | deltanet | gated_deltanet | kda. ``docs``: None | "uniform" | "mixed".
     ``gates``: "plain" (g = logsigmoid(N(3, 1.5))), "baseline" (g = logsigmoid(N(0,1)+3), the
-    BASELINE configs), "extreme" (10 % of tokens forget everything, 20 % keep everything; beta hits 0 and 1),
+    benchmark workloads), "extreme" (10 % of tokens forget everything, 20 % keep everything; beta hits 0 and 1),
     "kda_baseline" (per channel logsigmoid(N(0,1)+4)/8).
     """
     rng = np.random.default_rng(seed)
@@ -142,7 +142,7 @@ def make_case(kind: str, *, B: int, T: int, H: int, K: int, V: int, Hk: int | No
 def make_mamba2_case(*, B: int, T: int, H: int, P: int, N: int, G: int = 1, seed: int = 0,
                      dtype: str = "bfloat16", docs: str | None = None, h0: bool = False,
                      baseline: bool = False) -> dict:
-    """Mamba-2 SSD inputs. ``baseline=True`` draws BASELINE config 2's distributions (B, C ~ N(0,1)/sqrt(N),
+    """Mamba-2 SSD inputs. ``baseline=True`` draws the distributions of the Mamba-2 benchmark workload (B, C ~ N(0,1)/sqrt(N),
     dt = softplus(N(0,1) + log(expm1(U[0.001, 0.1]))), A = -exp(log U[1, 16]), D ~ N(0,1)); otherwise the
     differential-harness style (B, C ~ 0.5 N(0,1), dt = softplus(N(0,1) - 3), A = -U[0.5, 4])."""
     rng = np.random.default_rng(seed)
@@ -173,7 +173,8 @@ def make_mamba2_case(*, B: int, T: int, H: int, P: int, N: int, G: int = 1, seed
     return out
 
 
-# The five BASELINE configurations; ``shrink`` overrides sizes for tests that must finish on a CPU.
+# The five benchmark workloads (0: GDN fp32 B1 T512 H4 d64; 1: GDN bf16 B8 T2048 H16 d128; 2: Mamba-2 SSD B8 T2048 H64
+# P64 N128; 3: KDA bf16 B4 T4096 H16 d128; 4: GDN on one 1,064,960-token sequence); ``shrink`` overrides sizes for tests that must finish on a CPU.
 def baseline_config(index: int, seed: int = 0, **shrink) -> dict:
     if index == 0:
         spec = dict(B=1, T=512, H=4, K=64, V=64, dtype="float32", gates="baseline")
@@ -198,7 +199,7 @@ def baseline_config(index: int, seed: int = 0, **shrink) -> dict:
                     doc_range=(4096, 131072))
         spec.update(shrink)
         return make_case("gated_deltanet", seed=seed, **spec)
-    raise ValueError(f"no BASELINE config {index}")
+    raise ValueError(f"no benchmark workload {index}")
 
 
 def rel_l2(x, want) -> float:

@@ -125,7 +125,7 @@ def test_final_state_chains_across_two_calls():
 
 
 def test_baseline_config1_full_size_slices_and_properties():
-    """BASELINE config 1 at full size (B8 T2048 H16 d128, bf16, packed documents): two (b, h) slices against the
+    """The headline benchmark workload at full size (B8 T2048 H16 d128, bf16, packed documents): two (b, h) slices against the
     oracle, plus the size-independent property that every head of every batch row is independent (running a
     slice alone gives the same bits)."""
     from jax_linear_attention_b200 import ops

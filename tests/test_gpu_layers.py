@@ -1,4 +1,4 @@
-"""GPU parity of the callers around the op: the Mamba-2 SSD mapping (BASELINE config 2's op) and KDA through the
+"""GPU parity of the callers around the op: the Mamba-2 SSD mapping (the op of the B8 T2048 H64 P64 N128 benchmark workload) and KDA through the
 default dispatch. Tolerance: relative L2 <= 1e-2 against the float64 oracle (bf16 tensors, fp32 state)."""
 
 import numpy as np
@@ -59,7 +59,7 @@ def test_mamba2_ssd_shared_bc(docs):
 
 
 def test_mamba2_ssd_config2_full_size_runs_and_matches_a_slice():
-    """BASELINE config 2 at full size (B8 T2048 H64 P64 N128 G1): finite everywhere; batch row 0 against the oracle
+    """The Mamba-2 benchmark workload at full size (B8 T2048 H64 P64 N128 G1): finite everywhere; batch row 0 against the oracle
     on a 4-head slice (heads are independent given B, C)."""
     from jax_linear_attention_b200.layers import mamba2_ssd
 
@@ -79,7 +79,7 @@ def test_mamba2_ssd_config2_full_size_runs_and_matches_a_slice():
 
 @pytest.mark.parametrize("docs", [None, "uniform"])
 def test_kda_default_dispatch_bf16(docs):
-    """KDA (config 3's op at a reduced size) through impl='auto': bf16 tensors, per-channel gates, documents."""
+    """KDA (the op of the B4 T4096 H16 d128 benchmark workload at a reduced size) through impl='auto': bf16 tensors, per-channel gates, documents."""
     case = make_case("kda", B=2, T=600, H=4, K=128, V=128, seed=9, gates="kda_baseline", docs=docs, h0=True,
                      doc_range=(128, 600))
     want = run_oracle("kda", case, scale=case["meta"]["scale"], chunked=True)
@@ -185,7 +185,7 @@ def test_short_conv_matches_the_cpu_restatement(K, head_dim, act, docs, with_sta
 
 
 def test_mamba2_ssd_config2_gradient_slice_against_the_oracle():
-    """BASELINE config 2's shape (T2048 H64 P64 N128 G1 bf16), forward + backward: the full-size call is finite
+    """The Mamba-2 benchmark workload's shape (T2048 H64 P64 N128 G1 bf16), forward + backward: the full-size call is finite
     everywhere; batch row 0 restricted to 4 heads is run on its own through the kernels and held to the float64
     oracle for y and ALL gradients (dx, ddt, dA, dB, dC, dD) -- dB and dC sum over the heads that share them, so they
     are only comparable on a call that has exactly those heads; and the full-size call's dx and ddt of those heads

@@ -1,7 +1,7 @@
 """GPU parity of the fp32 token-scan kernels (JLA_PATH_RECURRENT) through the public API and the C ABI.
 
 Tolerance: relative L2 error <= 1e-5 against the float64 oracle (the fp32 configuration's bar), on the
-golden fixtures made by the reference's own oracles and on BASELINE config 0.
+golden fixtures made by the reference's own oracles and on the fp32 benchmark workload (GDN forward, B1 T512 H4 d64).
 """
 
 import numpy as np
@@ -40,7 +40,7 @@ def test_golden_kda_fixtures(name):
 
 
 def test_baseline_config0_forward_fp32():
-    """BASELINE config 0: GDN forward, fp32, B=1 T=512 H=4 d=64, zero initial state, one document."""
+    """The fp32 benchmark workload: GDN forward, fp32, B=1 T=512 H=4 d=64, zero initial state, one document."""
     case = baseline_config(0)
     want = run_oracle("gated_deltanet", case, scale=case["meta"]["scale"], grads=False, chunked=True)
     got = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="float32", grads=False)
@@ -90,3 +90,13 @@ def test_rejected_calls_raise():
         ops.linear_attention("nope", q, q, q)
     with pytest.raises(ValueError, match="no CPU fallback"):
         ops.linear_attention("simple_gla", q.cpu(), q.cpu(), q.cpu(), g=g.cpu())
+
+
+def test_head_size_256_runs_the_token_scan():
+    """K = V = 256 (the head size of the reference's K-blocked kernels, ``mosaic_gpu/scalar_gate_kb.py``): no chunk
+    kernel here, so 16-bit calls of that size take the fp32 token scan; forward and all gradients against the
+    float64 oracle at the tolerance of bf16 tensors."""
+    case = make_case("gated_deltanet", B=1, T=150, H=2, K=256, V=256, seed=31, docs="mixed", h0=True)
+    want = run_oracle("gated_deltanet", case, scale=case["meta"]["scale"])
+    got = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="bfloat16")
+    compare(got, want, 1e-2, "gdn K = V = 256")
