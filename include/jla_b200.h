@@ -169,6 +169,20 @@ int jla_linear_attention_bwd(const jla_problem* p, const jla_bwd_io* io, jla_str
 size_t jla_noalloc_scratch_limit(void);
 int jla_linear_attention_fwd_noalloc(const jla_problem* p, void* o, float* final_state, jla_stream_t stream);
 
+/* Element-wise glue of Gated DeltaNet-2 around the KDA kernels (src/jla/ops/reference.py:152-154: the erase gate b
+ * multiplies the key where it reads the state, the write gate w the value; the XLA fusions next to the kernel call in
+ * src/jla/ops/mosaic_gpu/vector_gate_ops.py). All tensors share `dtype` and are flat: n_k elements for k, b, k_read
+ * and their gradients, n_v for v, w, v_gated and theirs (multiples of 8).
+ *   inputs_fwd:  k_read = k * b, v_gated = v * w              (the call then passes k_read as jla_problem.k_read,
+ *                                                              v_gated as v and beta = 1 with JLA_KIND_KDA)
+ *   inputs_bwd:  dk = dk_read * b, db = dk_read * k, dv = dv_gated * w, dw = dv_gated * v
+ *                (dk is the read side's share; the caller adds the dk the backward call returned) */
+int jla_gdn2_inputs_fwd(int dtype, int64_t n_k, int64_t n_v, const void* k, const void* b, const void* v, const void* w,
+                        void* k_read, void* v_gated, jla_stream_t stream);
+int jla_gdn2_inputs_bwd(int dtype, int64_t n_k, int64_t n_v, const void* k, const void* b, const void* v, const void* w,
+                        const void* dk_read, const void* dv_gated, void* dk, void* db, void* dv, void* dw,
+                        jla_stream_t stream);
+
 /* Element-wise glue of the Mamba-2 SSD layer around the simple_gla kernels, fused so every [tokens, H, P] tensor is
  * read and written once; replaces the XLA fusions around the kernel call in mamba2_ssd (src/jla/layers/ssm.py:207-229)
  * and their transposes (ssm.py:76-84). 16-bit x, v, o, y and gradients; dt, A, D, g and their gradients f32;

@@ -80,6 +80,10 @@ def load() -> C.CDLL:
     lib.jla_piece_scan.restype = C.c_int
     lib.jla_piece_scan.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    lib.jla_gdn2_inputs_fwd.restype = C.c_int
+    lib.jla_gdn2_inputs_fwd.argtypes = [C.c_int, C.c_int64, C.c_int64] + [C.c_void_p] * 7
+    lib.jla_gdn2_inputs_bwd.restype = C.c_int
+    lib.jla_gdn2_inputs_bwd.argtypes = [C.c_int, C.c_int64, C.c_int64] + [C.c_void_p] * 11
     lib.jla_device_status.restype = C.c_int
     lib.jla_device_status.argtypes = [C.POINTER(C.c_int), C.c_void_p]
     lib.jla_selftest_bounded_wait.restype = C.c_int

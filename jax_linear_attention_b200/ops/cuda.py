@@ -402,32 +402,69 @@ def kda(q, k, v, g, beta, *, scale=None, initial_state=None, output_final_state=
                 use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision, sub_chunk=sub_chunk)
 
 
+class _Gdn2Inputs(torch.autograd.Function):
+    """``(k_read, v_gated) = (k * b, v * w)`` and its gradient, one fused kernel each way (``jla_gdn2_inputs_*``):
+    fp32 products rounded once to the tensors' dtype."""
+
+    @staticmethod
+    def forward(ctx, k, b, v, w):
+        lib = _lib.load()
+        k, b, v, w = (x.contiguous() for x in (k, b, v, w))
+        k_read, v_gated = torch.empty_like(k), torch.empty_like(v)
+        stream = torch.cuda.current_stream(k.device).cuda_stream
+        with torch.cuda.device(k.device):
+            _lib.check(lib.jla_gdn2_inputs_fwd(_DTYPES[k.dtype], k.numel(), v.numel(), *(_ptr(x) for x in (k, b, v, w)),
+                                               _ptr(k_read), _ptr(v_gated), C.c_void_p(stream)), "gdn2 inputs")
+        ctx.save_for_backward(k, b, v, w)
+        return k_read, v_gated
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dk_read, dv_gated):
+        lib = _lib.load()
+        k, b, v, w = ctx.saved_tensors
+        dk_read = torch.zeros_like(k) if dk_read is None else dk_read.contiguous()
+        dv_gated = torch.zeros_like(v) if dv_gated is None else dv_gated.contiguous()
+        dk, db, dv, dw = torch.empty_like(k), torch.empty_like(k), torch.empty_like(v), torch.empty_like(v)
+        stream = torch.cuda.current_stream(k.device).cuda_stream
+        with torch.cuda.device(k.device):
+            _lib.check(lib.jla_gdn2_inputs_bwd(_DTYPES[k.dtype], k.numel(), v.numel(), *(_ptr(x) for x in (k, b, v, w)),
+                                               _ptr(dk_read), _ptr(dv_gated), *(_ptr(x) for x in (dk, db, dv, dw)),
+                                               C.c_void_p(stream)), "gdn2 inputs backward")
+        return dk, db, dv, dw
+
+
 def gdn2(q, k, v, g, b, w, *, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
          segment_ids=None, use_qk_l2norm=False, chunk_size=CHUNK, sub_chunk=16, precision=None):
     """Gated DeltaNet-2 (``gdn2`` of ``src/jla/ops/reference.py:313-343`` in the reference): ``S_t = (I - k_t (b_t *
     k_t)^T) diag(exp g_t) S_{t-1} + k_t (w_t * v_t)^T`` with an erase gate ``b [B, T, H, K]`` and a write gate
-    ``w [B, T, H, V]``; ``b = w = beta`` is KDA.
+    ``w [B, T, H, V]`` in the tensors' dtype; ``b = w = beta`` is KDA.
 
     The kernels see it as KDA with ``beta = 1``, the values ``w * v`` and a separate read key ``b * k`` (the key the
-    recall reads the state with; ``k`` still writes). The two products are formed here in the tensors' dtype -- for
-    16-bit tensors that rounds them once to 16 bits, as the reference's kernels round the gates
-    (``mosaic_gpu/gdn2.py:11-12``) -- and their gradients flow back to ``k``, ``b``, ``v`` and ``w`` through autograd.
-    The unit norm of ``use_qk_l2norm`` is applied first (the gate multiplies the normalised key, reference.py:118-119).
-    bf16 tensors with ``K = V = 128`` run the KDA chunk kernels (the read key in tiles of its own); every other call
-    with a read key runs the fp32 token scan.
+    recall reads the state with; ``k`` still writes). The two products and their gradients are one fused kernel each
+    way (``jla_gdn2_inputs_*``): fp32 products rounded once to the tensors' dtype, as the reference's kernels round
+    the gates (``mosaic_gpu/gdn2.py:11-12``); the read side's and the write side's key gradients are added by
+    autograd. The unit norm of ``use_qk_l2norm`` is applied first (the gate multiplies the normalised key,
+    reference.py:118-119). bf16 tensors with ``K = V = 128`` run the KDA chunk kernels (the read key in tiles of its
+    own); every other call with a read key runs the fp32 token scan.
     """
+    for name, x in (("q", q), ("k", k), ("v", v), ("b", b), ("w", w)):
+        if not isinstance(x, torch.Tensor) or not x.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor: the 'cuda' implementation has no CPU fallback")
     if _shape(b) != _shape(q) or _shape(w) != _shape(v) or _shape(k) != _shape(q):
         raise ValueError(f"b must be [B, T, H, K] = {_shape(q)} and w must be [B, T, H, V] = {_shape(v)} (q and k "
                          f"with as many heads as v); got {_shape(b)} and {_shape(w)} with k {_shape(k)}")
     if _shape(q)[2] != _shape(v)[2]:
         raise ValueError(f"gdn2 needs as many key heads as value heads; got {_shape(q)[2]} and {_shape(v)[2]}")
+    if k.dtype not in _DTYPES or len({k.dtype, v.dtype}) != 1 or k.shape[-1] % 8 or v.shape[-1] % 8:
+        raise ValueError(f"k and v must share a dtype in {tuple(_DTYPES)} and have head sizes that are multiples of 8; "
+                         f"got {k.dtype} {_shape(k)}, {v.dtype} {_shape(v)}")
     if use_qk_l2norm:
         def unit(x):
             x32 = x.float()
             return (x32 * torch.rsqrt((x32 * x32).sum(-1, keepdim=True) + 1e-6)).to(x.dtype)
         q, k = unit(q), unit(k)
-    k_read = (b.to(torch.float32) * k.to(torch.float32)).to(k.dtype)
-    values = (w.to(torch.float32) * v.to(torch.float32)).to(v.dtype)
+    k_read, values = _Gdn2Inputs.apply(k, b.to(k.dtype), v, w.to(v.dtype))
     ones = torch.ones(_shape(v)[:3], dtype=torch.float32, device=v.device)
     return _run("kda", q, k, values, g, ones, scale=scale, initial_state=initial_state,
                 output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
