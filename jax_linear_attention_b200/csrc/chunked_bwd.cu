@@ -308,17 +308,23 @@ struct GradSmem {
   static_assert(K * LDV <= 64 * LDK + 64 * LDV, "dS+ must fit in the q | do region");
 };
 
-template <typename T, int K, int V, bool DELTA>
 // (Without the delta rule and with V = 64 -- the Mamba-2 shape -- two CTAs fit the shared memory of an SM; capping the
 // registers at 128 lets them, and a second resident CTA hides the first one's load and barrier latencies.)
+//
+// NH > 1 (grouped key heads only): one CTA walks NH adjacent value heads of one key group for the same chunk and keeps
+// their dq and dk sums in its accumulators, so the fp32 partials that finalize_key_grad sums over the group are
+// [tokens, H / NH, K] instead of [tokens, H, K] (the reference sums the group inside its kernel as well,
+// src/jla/ops/mosaic_gpu/scalar_gate_grouped.py:65-237). Everything else (dv, dg, the gate sums) stays per head.
+template <typename T, int K, int V, bool DELTA, int NH>
 __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_grads_kernel(BwdParams p) {
   using L = GradSmem<T, K, V, DELTA>;
   constexpr int LDK = L::LDK, LDV = L::LDV, LDC = L::LDC;
   constexpr int ONT = V / 16, KNT = K / 16;
-  const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
+  const int hgs = p.H / NH;  // head groups of NH per chunk
+  const int c = blockIdx.x / hgs, hg = blockIdx.x - c * hgs;
   const ChunkMeta m = p.meta[c];
   if (m.len == 0) return;
-  const int hk = h / (p.H / p.Hk);
+  const int hk = (hg * NH) / (p.H / p.Hk);  // NH divides the group size: every head of the walk shares the key head
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int r0 = 16 * (warp & 3), ch = warp >> 2;
   const int c0 = (V / 2) * ch, kc0 = (K / 2) * ch, cc0 = 32 * ch;
@@ -344,10 +350,17 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
   float* tot = dGv + 64;       // [8] per warp
   float* sdot = tot + 8;       // [8] per warp
   unsigned char* runs = reinterpret_cast<unsigned char*>(sdot + 8);
-  float tot_part = 0.f;
   const int quad = warp & 3;
   T* dSS = qS;  // dS+ overlays q | do once both are dead
+  float accK[KNT][4];  // dk, 16 rows x K/2 columns per warp; summed over the NH heads of the walk
+  float accQ[KNT][4];  // dq likewise
+  zero_acc(accK);
+  zero_acc(accQ);
 
+#pragma unroll 1
+  for (int hi = 0; hi < NH; ++hi) {
+  const int h = hg * NH + hi;
+  float tot_part = 0.f;
   const long ch_off = (long)c * p.H + h;
   // group 0: k, S, v, T0, gates, runs
   load_tile_async<T, 64, K>(kS, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * K, (long)p.Hk * K, m.len,
@@ -390,8 +403,6 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
   cp_async_wait<0>();
   __syncthreads();  // S1
 
-  float accK[KNT][4];  // dk, 16 rows x K/2 columns per warp
-  zero_acc(accK);
   {  // 2. dP = scale (dO Vn^T) D ; E = dP (Q K^T)
     float accP[4][4], accE[4][4];
     zero_acc(accP);
@@ -412,20 +423,37 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
     col_sums_add<4>(accE, dGcol + quad * 64, cc0, lane, -1.f);
     store_acc<T, 4>(Xa, LDC, r0, cc0, accP, lane);
   }
-  float accQ[KNT][4];
   {  // 3. dq = scale (cin Gamma)(dO S^T) + dP K
-    zero_acc(accQ);
-    warp_gemm<T, KNT, V / 16, A_ROW, B_NK>(accQ, doS + r0 * LDV, LDV, SS + kc0 * LDV, LDV, lane);
     const float s0 = p.scale * rs0.gam, s1 = p.scale * rs1.gam;
-#pragma unroll
-    for (int nt = 0; nt < KNT; ++nt) {
-      accQ[nt][0] *= s0;
-      accQ[nt][1] *= s0;
-      accQ[nt][2] *= s1;
-      accQ[nt][3] *= s1;
-    }
     float d0, d1;
-    row_dots<T, KNT>(accQ, qS, LDK, r0, kc0, lane, d0, d1);
+    if (NH == 1) {  // straight into the accumulator
+      warp_gemm<T, KNT, V / 16, A_ROW, B_NK>(accQ, doS + r0 * LDV, LDV, SS + kc0 * LDV, LDV, lane);
+#pragma unroll
+      for (int nt = 0; nt < KNT; ++nt) {
+        accQ[nt][0] *= s0;
+        accQ[nt][1] *= s0;
+        accQ[nt][2] *= s1;
+        accQ[nt][3] *= s1;
+      }
+      row_dots<T, KNT>(accQ, qS, LDK, r0, kc0, lane, d0, d1);
+    } else {  // this head's term alone is needed for its gate gradient: through a temporary
+      float accS[KNT][4];
+      zero_acc(accS);
+      warp_gemm<T, KNT, V / 16, A_ROW, B_NK>(accS, doS + r0 * LDV, LDV, SS + kc0 * LDV, LDV, lane);
+#pragma unroll
+      for (int nt = 0; nt < KNT; ++nt) {
+        accS[nt][0] *= s0;
+        accS[nt][1] *= s0;
+        accS[nt][2] *= s1;
+        accS[nt][3] *= s1;
+      }
+      row_dots<T, KNT>(accS, qS, LDK, r0, kc0, lane, d0, d1);
+#pragma unroll
+      for (int nt = 0; nt < KNT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) accQ[nt][e] += accS[nt][e];
+      }
+    }
     if (t == 0) {
       dGrow[ch * 64 + r0 + g] += d0;
       dGrow[ch * 64 + r0 + g + 8] += d1;
@@ -433,7 +461,7 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
   }
   __syncthreads();  // S2: Xa = dP complete
   warp_gemm<T, KNT, 4, A_ROW, B_KN>(accQ, Xa + r0 * LDC, LDC, kS + kc0, LDK, lane);
-  {
+  if (hi == NH - 1) {
     const long tok0 = (long)m.tok0 + r0 + g;
 #pragma unroll
     for (int nt = 0; nt < KNT; ++nt) {
@@ -443,7 +471,7 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
         if (r0 + g + 8 * hh >= m.len) continue;
         const long tok = tok0 + 8 * hh;
         if (p.dq_acc) {
-          *reinterpret_cast<float2*>(p.dq_acc + (tok * p.H + h) * K + col) = make_float2(accQ[nt][2 * hh], accQ[nt][2 * hh + 1]);
+          *reinterpret_cast<float2*>(p.dq_acc + (tok * hgs + hg) * K + col) = make_float2(accQ[nt][2 * hh], accQ[nt][2 * hh + 1]);
         } else {
           *reinterpret_cast<uint32_t*>(static_cast<T*>(p.dq) + (tok * p.Hk + hk) * K + col) =
               pack2<T>(accQ[nt][2 * hh], accQ[nt][2 * hh + 1]);
@@ -577,14 +605,14 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
     // dk out
     const long tok0 = (long)m.tok0 + r0 + g;
 #pragma unroll
-    for (int nt = 0; nt < KNT; ++nt) {
+    for (int nt = 0; nt < KNT && hi == NH - 1; ++nt) {
       const int col = kc0 + nt * 8 + 2 * t;
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         if (r0 + g + 8 * hh >= m.len) continue;
         const long tok = tok0 + 8 * hh;
         if (p.dk_acc) {
-          *reinterpret_cast<float2*>(p.dk_acc + (tok * p.H + h) * K + col) = make_float2(accK[nt][2 * hh], accK[nt][2 * hh + 1]);
+          *reinterpret_cast<float2*>(p.dk_acc + (tok * hgs + hg) * K + col) = make_float2(accK[nt][2 * hh], accK[nt][2 * hh + 1]);
         } else {
           *reinterpret_cast<uint32_t*>(static_cast<T*>(p.dk) + (tok * p.Hk + hk) * K + col) =
               pack2<T>(accK[nt][2 * hh], accK[nt][2 * hh + 1]);
@@ -621,10 +649,12 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
       }
     }
   }
+  if (NH > 1) __syncthreads();  // the next head's loads overwrite the tiles and vectors read above
+  }  // heads of the walk
 }
 
 template <typename T, int K, int V, bool DELTA>
-int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, bool legacy_grads, cudaStream_t s) {
+int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, bool legacy_grads, int head_walk, cudaStream_t s) {
   {
     auto* kern = sg_bwd_state_kernel<T, K, V, DELTA>;
     constexpr int smem = BwdStateSmem<T, K, V, DELTA>::kBytes;
@@ -636,12 +666,16 @@ int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, bool lega
     JLA_LAUNCH_OK();
   }
   if (legacy_grads) {
-    auto* kern = sg_chunk_grads_kernel<T, K, V, DELTA>;
     constexpr int smem = GradSmem<T, K, V, DELTA>::kBytes;
+    // the Mamba-2 shape with grouped heads: walks of 8, 4 or 2 heads per CTA (see the kernel)
+    auto* kern = sg_chunk_grads_kernel<T, K, V, DELTA, 1>;
+    if (!DELTA && V == 64 && K == 128 && head_walk == 8) kern = sg_chunk_grads_kernel<T, K, V, DELTA, (!DELTA && V == 64 && K == 128) ? 8 : 1>;
+    if (!DELTA && V == 64 && K == 128 && head_walk == 4) kern = sg_chunk_grads_kernel<T, K, V, DELTA, (!DELTA && V == 64 && K == 128) ? 4 : 1>;
+    if (!DELTA && V == 64 && K == 128 && head_walk == 2) kern = sg_chunk_grads_kernel<T, K, V, DELTA, (!DELTA && V == 64 && K == 128) ? 2 : 1>;
     JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     {
       ProfScope ps(kProfSgChunkGrads, s);
-      kern<<<chunk_blocks, 256, smem, s>>>(bp);
+      kern<<<chunk_blocks / head_walk, 256, smem, s>>>(bp);
     }
     JLA_LAUNCH_OK();
   }
@@ -649,11 +683,11 @@ int launch_one(const BwdParams& bp, int rows_blocks, int chunk_blocks, bool lega
 }
 
 template <typename T, bool DELTA>
-int launch_kv(const BwdParams& bp, int K, int V, int rb, int cb, bool legacy, cudaStream_t s) {
-  if (K == 128 && V == 128) return launch_one<T, 128, 128, DELTA>(bp, rb, cb, legacy, s);
-  if (K == 128 && V == 64) return launch_one<T, 128, 64, DELTA>(bp, rb, cb, legacy, s);
-  if (K == 64 && V == 128) return launch_one<T, 64, 128, DELTA>(bp, rb, cb, legacy, s);
-  return launch_one<T, 64, 64, DELTA>(bp, rb, cb, legacy, s);
+int launch_kv(const BwdParams& bp, int K, int V, int rb, int cb, bool legacy, int walk, cudaStream_t s) {
+  if (K == 128 && V == 128) return launch_one<T, 128, 128, DELTA>(bp, rb, cb, legacy, walk, s);
+  if (K == 128 && V == 64) return launch_one<T, 128, 64, DELTA>(bp, rb, cb, legacy, walk, s);
+  if (K == 64 && V == 128) return launch_one<T, 64, 128, DELTA>(bp, rb, cb, legacy, walk, s);
+  return launch_one<T, 64, 64, DELTA>(bp, rb, cb, legacy, walk, s);
 }
 
 }  // namespace
@@ -693,22 +727,26 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
   bp.scale = p.scale;
   const int rb = pl.rows * p.H, cb = pl.nc * p.H;
   const bool legacy = !use_tc_kernels(p);  // mma.sync chunk gradients (row-major residuals)
+  // heads per CTA walk of the legacy gradient kernel (sums dq, dk over them in registers): the Mamba-2 shape with
+  // grouped key heads only
+  const int group = p.H / p.Hk;
+  const int walk = (legacy && !direct && !pl.delta && p.K == 128 && p.V == 64) ? (group % 8 == 0 ? 8 : group % 4 == 0 ? 4 : group % 2 == 0 ? 2 : 1) : 1;
   int rc;
   if (!legacy) {
     rc = launch_sg_bwd_state_tc(c, io, scratch, s);
   } else if (p.dtype == JLA_DTYPE_BF16) {
-    rc = pl.delta ? launch_kv<__nv_bfloat16, true>(bp, p.K, p.V, rb, cb, legacy, s)
-                  : launch_kv<__nv_bfloat16, false>(bp, p.K, p.V, rb, cb, legacy, s);
+    rc = pl.delta ? launch_kv<__nv_bfloat16, true>(bp, p.K, p.V, rb, cb, legacy, walk, s)
+                  : launch_kv<__nv_bfloat16, false>(bp, p.K, p.V, rb, cb, legacy, walk, s);
   } else {
-    rc = pl.delta ? launch_kv<__half, true>(bp, p.K, p.V, rb, cb, legacy, s)
-                  : launch_kv<__half, false>(bp, p.K, p.V, rb, cb, legacy, s);
+    rc = pl.delta ? launch_kv<__half, true>(bp, p.K, p.V, rb, cb, legacy, walk, s)
+                  : launch_kv<__half, false>(bp, p.K, p.V, rb, cb, legacy, walk, s);
   }
   if (rc == JLA_OK && !legacy && (p.flags & JLA_FLAG_STATE_GRADS_ONLY)) return rc;
   if (rc == JLA_OK && !legacy) rc = kda ? launch_kda_grads(c, io, scratch, s) : launch_chunk_grads_tc(c, io, scratch, direct, s);
   if (rc != JLA_OK || direct) return rc;
-  rc = finalize_key_grad(bp.dq_acc, p.q, io.dq, p.dtype, tokens, p.H, p.Hk, p.K, pl.l2norm, s);
+  rc = finalize_key_grad(bp.dq_acc, p.q, io.dq, p.dtype, tokens, p.H / walk, p.Hk, p.K, pl.l2norm, s);
   if (rc != JLA_OK) return rc;
-  return finalize_key_grad(bp.dk_acc, p.k, io.dk, p.dtype, tokens, p.H, p.Hk, p.K, pl.l2norm, s);
+  return finalize_key_grad(bp.dk_acc, p.k, io.dk, p.dtype, tokens, p.H / walk, p.Hk, p.K, pl.l2norm, s);
 }
 
 }  // namespace jla
