@@ -1,6 +1,6 @@
 """Benchmark of the hot path: Gated DeltaNet chunk forward + backward at B8 T2048 H16 K = V = 128, bf16, packed documents.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gdn|ssd|kda]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gdn|ssd|kda|gdn2|longctx]
 
 One step = one forward + backward of ``ops.linear_attention("gated_deltanet", ...)`` over one batch
 (B=8, T=2048, H=16, K=V=128, bf16 q/k/v/dO, fp32 gates, packed documents of uniform length 64-2048 as
@@ -53,6 +53,8 @@ WORKLOADS = {
     "gdn": dict(name="config1: gated_deltanet B8 T2048 H16 K128 V128 chunk64 bf16, packed docs U[64,2048]", index=1),
     "ssd": dict(name="config2: mamba2 SSD B8 T2048 H64 P64 N128 G1 bf16", index=2),
     "kda": dict(name="config3: kda B4 T4096 H16 K128 V128 bf16, packed docs U[128,4096]", index=3),
+    "gdn2": dict(name="gdn2 (Gated DeltaNet-2, erase and write gates per channel) at config3's shape: B4 T4096 H16 K128 "
+                      "V128 bf16, packed docs U[128,4096]", index=None),
     "longctx": dict(name="config4: gated_deltanet B1 T1064960 H16 K128 V128 bf16, packed docs U[4096,131072], "
                          "sequence-parallel over the ranks", index=4),
 }
@@ -60,6 +62,7 @@ METRICS = {
     "gdn": None,  # the headline metric
     "ssd": "Mamba-2 SSD chunk fwd+bwd tokens/s (B8·T2048·H64·P64·N128 bf16)",
     "kda": "KDA fwd+bwd tokens/s (B4·T4096·H16·d128 bf16)",
+    "gdn2": "Gated DeltaNet-2 fwd+bwd tokens/s (B4·T4096·H16·d128 bf16)",
     "longctx": "GDN fwd+bwd tokens/s on one 1,064,960-token sequence (H16·d128 bf16), sequence-parallel",
 }
 LONG_T = 1_064_960
@@ -155,8 +158,11 @@ class ClockSampler:
 
 
 def host_case(workload: str, seed: int) -> dict:
-    from oracle.cases import baseline_config
+    from oracle.cases import baseline_config, make_case
 
+    if workload == "gdn2":  # no published configuration: the KDA workload's shape and gates, b and w as sigmoids
+        return make_case("gdn2", seed=seed, B=4, T=4096, H=16, K=128, V=128, dtype="bfloat16", gates="kda_baseline",
+                         docs="uniform", doc_range=(128, 4096))
     return baseline_config(WORKLOADS[workload]["index"], seed=seed)
 
 
@@ -203,7 +209,7 @@ def longctx_device_inputs(device, rank: int, world: int, seed: int = 0) -> dict:
 def to_torch_host(case: dict, workload: str) -> dict:
     """Pinned host tensors in the dtypes of the op call."""
     out = {}
-    half = ("q", "k", "v", "do") if workload != "ssd" else ("x", "B", "C", "do")
+    half = ("q", "k", "v", "do", "b", "w") if workload != "ssd" else ("x", "B", "C", "do")
     for name, arr in case.items():
         if name == "meta" or name in ("h0", "dht"):
             continue
@@ -219,6 +225,7 @@ def to_torch_host(case: dict, workload: str) -> dict:
 
 
 GRAD_NAMES = {"gdn": ("q", "k", "v", "g", "beta"), "kda": ("q", "k", "v", "g", "beta"),
+              "gdn2": ("q", "k", "v", "g", "b", "w"),
               "ssd": ("x", "dt", "A", "B", "C"), "longctx": ("q", "k", "v", "g", "beta")}
 
 
@@ -249,6 +256,9 @@ def run_step(workload: str, dev: dict):
                 dev["plan"] = plan_pieces(dev["seg"], 8192)
             o, _ = context_parallel_linear_attention("gated_deltanet", dev["q"], dev["k"], dev["v"], g=dev["g"],
                                                      beta=dev["beta"], segment_ids=dev["seg"], piece_len=dev["plan"])
+    elif workload == "gdn2":
+        o, _ = ops.linear_attention("gdn2", dev["q"], dev["k"], dev["v"], g=dev["g"], b=dev["b"], w=dev["w"],
+                                    segment_ids=dev.get("seg"))
     else:
         kind = "gated_deltanet" if workload == "gdn" else "kda"
         o, _ = ops.linear_attention(kind, dev["q"], dev["k"], dev["v"], g=dev["g"], beta=dev["beta"],
@@ -313,6 +323,10 @@ def run_reference(args) -> None:
     to 50 steps (a step takes about a second)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if args.workload not in ("gdn", "kda"):
+        print(json.dumps(dict(impl="reference", unavailable=f"the timed CPU port covers the gdn and kda workloads, not "
+                                                             f"{args.workload}")))
         return
     case = host_case(args.workload, seed=0)
     rows = min(CPU_ROWS, case["q"].shape[0])
