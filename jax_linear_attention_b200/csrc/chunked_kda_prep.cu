@@ -22,7 +22,9 @@
 // With a separate read key (jla_problem.k_read, Gated DeltaNet-2: S = S' + k^T (v - k_read S')) the key has two roles:
 // wherever a token READS the state or the earlier tokens of its chunk -- the rows of Akk and the operand kr -- the
 // read key stands for k; wherever it WRITES -- the columns of Akk and Aqk, the operand kw -- k itself does. The RK
-// variant of the kernel keeps the read key in a tile of its own (one CTA per SM instead of two).
+// variant reads the read key from global memory where it folds the operands (its factored form takes the place of
+// the raw k tile, which is dead by then); the exact path stages it in the tile of the factored write key, which that
+// path does not build, and holds its score results in registers until the tile is free.
 #include "chunked.cuh"
 #include "profile.cuh"
 #include "mma.cuh"
@@ -49,7 +51,7 @@ struct KdaPrepParams {
 };
 
 template <typename T, bool RK>
-__global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams p) {
+__global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
   constexpr int LDK = KD + 8, LDA = kTriLda, LDM = kTriLdm, LDP = 72, NT = 256;
   const int c = blockIdx.x / p.H, h = blockIdx.x - c * p.H;
   const ChunkMeta m = p.meta[c];
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams
   float* betas = M + 32 * LDM;                   // [64]
   float* Glast = betas + 64;                     // [KD]
   int* run = reinterpret_cast<int*>(Glast + KD); // [64]
-  T* tr = RK ? reinterpret_cast<T*>(run + 64) : tk;  // the read key, then read key exp(G - R) (RK: a tile of its own)
+  T* tr = tk;  // factored path: read key exp(G - R) takes the raw k tile's place
   float* X = reinterpret_cast<float*>(smem_raw);
   static_assert(64 * LDK * sizeof(T) >= 64 * LDA * sizeof(float), "X overlays the q tile");
   T* pst = tb;
@@ -76,10 +78,8 @@ __global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams
   const long kstride = (long)p.Hk * KD;
   load_tile_async<T, 64, KD>(tq, LDK, static_cast<const T*>(p.q) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
   load_tile_async<T, 64, KD>(tk, LDK, static_cast<const T*>(p.k) + ((long)m.tok0 * p.Hk + hk) * KD, kstride, m.len, tid, NT);
-  if (RK) {
-    load_tile_async<T, 64, KD>(tr, LDK, static_cast<const T*>(p.k_read) + ((long)m.tok0 * p.H + h) * KD, (long)p.H * KD,
-                               m.len, tid, NT);
-  }
+  const T* krg = RK ? static_cast<const T*>(p.k_read) + ((long)m.tok0 * p.H + h) * KD : nullptr;  // read key rows
+  const long krstride = (long)p.H * KD;
   cp_async_commit();
   if (tid < 64) {
     betas[tid] = p.gates[slot * 128 + 64 + tid];
@@ -131,7 +131,8 @@ __global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams
       const bool tail = i < m.len && run[i] == run_last;
       uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
-      uint4 rv = RK ? *reinterpret_cast<const uint4*>(tr + i * LDK + c8) : kv;  // the read key
+      uint4 rv = kv;  // the read key (tokens past a partial chunk's end read as zero, like the tiles)
+      if (RK) rv = i < m.len ? *reinterpret_cast<const uint4*>(krg + i * krstride + c8) : make_uint4(0u, 0u, 0u, 0u);
       uint4 bv, oq, or_, ow;
       uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
       uint32_t* kwd = reinterpret_cast<uint32_t*>(&kv);
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams
       *reinterpret_cast<uint4*>(kr + i * KD + c8) = or_;
       *reinterpret_cast<uint4*>(kw + i * KD + c8) = ow;
       *reinterpret_cast<uint4*>(tq + i * LDK + c8) = qv;
-      *reinterpret_cast<uint4*>(tr + i * LDK + c8) = rv;  // (tr is tk without a read key)
+      *reinterpret_cast<uint4*>(tr + i * LDK + c8) = rv;  // over the raw k tile, which this thread has just read
       *reinterpret_cast<uint4*>(tb + i * LDK + c8) = bv;
     }
     __syncthreads();
@@ -194,13 +195,20 @@ __global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams
     }
   } else {
     // ---- exact path. The state-side operands with their own (always non-positive) exponents:
+    T* te = RK ? tb : tk;  // the raw read key of this path (tb holds no factored tile here)
+    if (RK) {
+      load_tile_async<T, 64, KD>(te, LDK, krg, krstride, m.len, tid, NT);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncthreads();
+    }
     for (int idx = tid; idx < 64 * (KD / 8); idx += NT) {
       const int i = idx >> 4, c8 = (idx & 15) * 8;
       const bool cin = entering && run[i] == 0;
       const bool tail = i < m.len && run[i] == run_last;
       const uint4 qv = *reinterpret_cast<const uint4*>(tq + i * LDK + c8);
       const uint4 kv = *reinterpret_cast<const uint4*>(tk + i * LDK + c8);
-      const uint4 rv = *reinterpret_cast<const uint4*>(tr + i * LDK + c8);
+      const uint4 rv = *reinterpret_cast<const uint4*>(te + i * LDK + c8);
       const uint32_t* qw = reinterpret_cast<const uint32_t*>(&qv);
       const uint32_t* kwd = reinterpret_cast<const uint32_t*>(&kv);
       const uint32_t* rwd = reinterpret_cast<const uint32_t*>(&rv);
@@ -224,7 +232,10 @@ __global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams
     }
     // every pair (i, j <= i) of one document, fp32 with the true exponent per channel
     __syncthreads();
-    for (int idx = tid; idx < 64 * 64; idx += NT) {
+    T sqv[64 * 64 / NT];  // this thread's scores: staged in pst only once the read key has left that tile
+#pragma unroll
+    for (int n = 0; n < 64 * 64 / NT; ++n) {
+      const int idx = tid + n * NT;
       const int i = idx >> 6, j = idx & 63;
       float sq = 0.f, sk = 0.f;
       if (j <= i && run[i] == run[j]) {
@@ -233,13 +244,18 @@ __global__ void __launch_bounds__(256, RK ? 1 : 2) kda_prep_kernel(KdaPrepParams
           const float e = __expf(Gm[i * KD + ch] - Gm[j * KD + ch]);
           const float kj = to_f32(tk[j * LDK + ch]) * e;
           sq += to_f32(tq[i * LDK + ch]) * kj;
-          sk += to_f32(tr[i * LDK + ch]) * kj;
+          sk += to_f32(te[i * LDK + ch]) * kj;
         }
       }
       A[i * LDA + j] = j < i ? betas[i] * sk : 0.f;
-      pst[i * LDP + j] = from_f32<T>(sq);
+      sqv[n] = from_f32<T>(sq);
     }
-    __syncthreads();  // the raw tiles have been read: X may take their place
+    __syncthreads();  // the raw tiles have been read: the staged P and X may take their place
+#pragma unroll
+    for (int n = 0; n < 64 * 64 / NT; ++n) {
+      const int idx = tid + n * NT;
+      pst[(idx >> 6) * LDP + (idx & 63)] = sqv[n];
+    }
   }
   for (int idx = tid; idx < 64 * LDA / 4; idx += NT) reinterpret_cast<float4*>(X)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
   __syncthreads();
@@ -302,8 +318,8 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
     return JLA_ERR_UNSUPPORTED;
   }
   using T = __nv_bfloat16;
-  const size_t smem = (p.k_read ? 4 : 3) * 64 * (KD + 8) * sizeof(T) +
-                      (64 * KD + 64 * kTriLda + 32 * kTriLdm + 64 + KD) * sizeof(float) + 64 * sizeof(int);
+  const size_t smem = 3 * 64 * (KD + 8) * sizeof(T) + (64 * KD + 64 * kTriLda + 32 * kTriLdm + 64 + KD) * sizeof(float) +
+                      64 * sizeof(int);
   auto* kern = p.k_read ? kda_prep_kernel<T, true> : kda_prep_kernel<T, false>;
   JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
