@@ -232,12 +232,10 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
     }
     // every pair (i, j <= i) of one document, fp32 with the true exponent per channel
     __syncthreads();
-    T sqv[64 * 64 / NT];  // this thread's scores: staged in pst only once the read key has left that tile
-#pragma unroll
-    for (int n = 0; n < 64 * 64 / NT; ++n) {
-      const int idx = tid + n * NT;
-      const int i = idx >> 6, j = idx & 63;
-      float sq = 0.f, sk = 0.f;
+    // one pair's scores: the read row i of the solve matrix (from the read key) and of the score tile (from q)
+    auto pair_scores = [&](int i, int j, float& sq, float& sk) {
+      sq = 0.f;
+      sk = 0.f;
       if (j <= i && run[i] == run[j]) {
         for (int cc = 0; cc < KD; ++cc) {
           const int ch = (cc + lane) & (KD - 1);  // lanes of a warp share i: spread the channels over the banks
@@ -247,14 +245,34 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
           sk += to_f32(te[i * LDK + ch]) * kj;
         }
       }
-      A[i * LDA + j] = j < i ? betas[i] * sk : 0.f;
-      sqv[n] = from_f32<T>(sq);
-    }
-    __syncthreads();  // the raw tiles have been read: the staged P and X may take their place
+    };
+    if (!RK) {  // pst (the tile of the factored write key) is free on this path: results go straight into it
+      for (int idx = tid; idx < 64 * 64; idx += NT) {
+        const int i = idx >> 6, j = idx & 63;
+        float sq, sk;
+        pair_scores(i, j, sq, sk);
+        A[i * LDA + j] = j < i ? betas[i] * sk : 0.f;
+        pst[i * LDP + j] = from_f32<T>(sq);
+      }
+      __syncthreads();  // the raw tiles have been read: X may take their place
+    } else {  // the read key sits in that tile: this thread's scores wait in registers until every thread has read it
+      T sqv[64 * 64 / NT];
 #pragma unroll
-    for (int n = 0; n < 64 * 64 / NT; ++n) {
-      const int idx = tid + n * NT;
-      pst[(idx >> 6) * LDP + (idx & 63)] = sqv[n];
+      for (int n = 0; n < 64 * 64 / NT; ++n) {
+        const int idx = tid + n * NT;
+        const int i = idx >> 6, j = idx & 63;
+        float sq, sk;
+        pair_scores(i, j, sq, sk);
+        A[i * LDA + j] = j < i ? betas[i] * sk : 0.f;
+        sqv[n] = from_f32<T>(sq);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int n = 0; n < 64 * 64 / NT; ++n) {
+        const int idx = tid + n * NT;
+        pst[(idx >> 6) * LDP + (idx & 63)] = sqv[n];
+      }
+      // (the barrier after the clearing of X below orders these stores before the tile is read)
     }
   }
   for (int idx = tid; idx < 64 * LDA / 4; idx += NT) reinterpret_cast<float4*>(X)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
