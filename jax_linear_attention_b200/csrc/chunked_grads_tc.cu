@@ -426,8 +426,11 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
                  aT0 = umma::smem_addr(t0S), aXb = umma::smem_addr(Xb), aDp = umma::smem_addr(dpS),
                  aEx = umma::smem_addr(exS);
 
+  // Units are walked from the last one down: the query-side kernel, which runs just before and hands over dP, walks
+  // them upwards, so the tiles both kernels read (q, k, S^T, Vn^T and the dP hand-off) of the units it touched last
+  // are still in L2 when this kernel starts with them. A negative index ends the walk.
   auto next_live = [&](int it) {
-    while (it < p.nitems && p.meta[it / p.H].len == 0) it += gridDim.x;
+    while (it >= 0 && p.meta[it / p.H].len == 0) it -= gridDim.x;
     return it;
   };
   // tid 0: everything of a unit's first phase except k (whose tile the previous unit reads until its end)
@@ -460,17 +463,17 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     runs[tid] = p.runs[(long)(item / p.H) * 64 + tid];
   };
 
-  int item = next_live(blockIdx.x);
+  int item = next_live(p.nitems - 1 - (int)blockIdx.x);
   if (tid == 0) {
     for (int i = 0; i < 8; ++i) umma::mbar_init(bars + i, i == L1 ? 2 : 1);
     umma::mbar_init_fence();
-    if (item < p.nitems) {
+    if (item >= 0) {
       load_first(item);
       load_k(item);
     }
   }
   if (warp == 1) umma::tmem_alloc(tmem_slot, 256);
-  if (tid < 64 && item < p.nitems) load_vec(item, 0);
+  if (tid < 64 && item >= 0) load_vec(item, 0);
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
@@ -479,11 +482,11 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   constexpr uint32_t cK = 0, cP1 = 128, cP2 = 192;
   bool ok = true, first_inflight = false, k_inflight = false;
 
-  for (int it = 0; item < p.nitems; ++it) {
+  for (int it = 0; item >= 0; ++it) {
     const int c = item / p.H, h = item - c * p.H;
     const int hk = h / (p.H / p.Hk);
     const ChunkMeta m = p.meta[c];
-    const int nxt = next_live(item + gridDim.x);
+    const int nxt = next_live(item - (int)gridDim.x);
     const uint32_t ph = it & 1;
     float* Gs = reinterpret_cast<float*>(base + L::kVec + (it & 1) * L::kVecStride);
     float* betas = Gs + 64;
@@ -668,7 +671,7 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
           tma::load_3d(qS, &maps.h, 64, 0, item * VD, bars + L2);
           tma::load_3d(exS, &maps.dh, 64, 0, item * VD, bars + L2);
         }
-      } else if (nxt < p.nitems && ok) {  // every product of this unit is done: the next unit's tiles may land
+      } else if (nxt >= 0 && ok) {  // every product of this unit is done: the next unit's tiles may land
         if (tid == 0) load_first(nxt);
         first_inflight = true;
         if (tid < 64) load_vec(nxt, (it & 1) ^ 1);
@@ -746,7 +749,7 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
     ok = __syncthreads_and(ok);  // k and the accumulators are final for this unit
     umma::fence_after_sync();
     if (!ok) break;
-    if (nxt < p.nitems) {
+    if (nxt >= 0) {
       if (tid == 0) load_k(nxt);
       k_inflight = true;
     }
@@ -779,7 +782,7 @@ sg_grads_k_tc_kernel(const __grid_constant__ GradMaps maps, GradParams p) {
   }
   if (!ok) {  // let requested copies land before the shared memory goes away (bounded waits)
     if (first_inflight || k_inflight) {
-      if (!k_inflight && tid == 0) load_k(next_live(item + gridDim.x));  // complete the byte count of the phase
+      if (!k_inflight && tid == 0) load_k(next_live(item - (int)gridDim.x));  // complete the byte count of the phase
       umma::mbar_wait(bars + L0, 0), umma::mbar_wait(bars + L0, 1);
     }
     if (tid == 0) atomicExch(p.status, 1);
