@@ -334,14 +334,28 @@ def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_stat
         scale = q.shape[-1] ** -0.5
     cp = 1 if k_read is not None else _split_applies(kind, q, v, cu_seqlens, initial_state, precision)
     if cp > 1:
-        from ..distributed.context_parallel import context_parallel_linear_attention
+        from ..distributed.context_parallel import context_parallel_linear_attention, plan_pieces
 
         piece_len = -(-(-(-q.shape[1] // CHUNK)) // cp) * CHUNK  # whole chunks per piece
+        plan = plan_pieces(segment_ids, piece_len, group=False, t_local=q.shape[1], device=dev)
+        if not any(plan.cont):
+            # No document is longer than a piece: the pieces are the documents, nothing has to be joined, and the call
+            # is the plain one with the documents as rows (one state pass instead of three forward and two backward).
+            rows = len(plan.cu) - 1
+            state = None
+            if initial_state is not None:  # it enters the first document only
+                state = torch.cat([initial_state.to(device=dev, dtype=torch.float32),
+                                   torch.zeros(rows - 1, *initial_state.shape[1:], dtype=torch.float32, device=dev)])
+            with no_pieces():
+                o, final = _run(kind, q, k, v, g, beta, scale=scale, initial_state=state,
+                                output_final_state=output_final_state, cu_seqlens=plan.cu_device, segment_ids=None,
+                                use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision)
+            return o, (final[-1:] if output_final_state else None)
         gates = {n: x for n, x in (("g", g), ("beta", beta)) if x is not None}
         extra = dict(use_qk_l2norm=use_qk_l2norm) if kind != "simple_gla" else {}
         with no_pieces():
             o, final = context_parallel_linear_attention(
-                kind, q, k, v, group=False, impl="cuda", piece_len=piece_len, scale=scale, initial_state=initial_state,
+                kind, q, k, v, group=False, impl="cuda", piece_len=plan, scale=scale, initial_state=initial_state,
                 output_final_state=output_final_state, segment_ids=segment_ids, precision=precision, **gates, **extra)
         return o, (final if output_final_state else None)
 

@@ -80,3 +80,29 @@ def test_split_call_matches_the_unsplit_call_and_the_oracle(kind, monkeypatch):
     assert any(not np.array_equal(split[n], plain[n]) for n in plain), "the split did not run"
     want = run_oracle(kind, case, scale=case["meta"]["scale"], chunked=True)
     compare(split, want, 1e-2, f"{kind} split")
+
+
+def test_documents_shorter_than_a_piece_run_as_plain_rows(monkeypatch):
+    """When no document is longer than a piece nothing has to be joined: the split call is the plain call with the
+    documents as rows (initial state into the first document, final state of the last), held to the unsplit packed
+    row and to the oracle."""
+    from jax_linear_attention_b200.distributed import context_parallel as cp_mod
+    from jax_linear_attention_b200.ops import cuda
+    from jax_linear_attention_b200.ops.cuda import no_pieces, pieces
+
+    monkeypatch.setattr(cuda, "MIN_SPLIT_CHUNKS", 8)
+    T, H = 4096, 4
+    assert pieces(1, H, T, delta=True) == 4  # pieces of 1024 tokens
+    case = make_case("gated_deltanet", B=1, T=T, H=H, K=128, V=128, seed=77, h0=True, docs="uniform",
+                     doc_range=(100, 900), gates="baseline")
+    calls = []
+    real = cp_mod.context_parallel_linear_attention
+    monkeypatch.setattr(cp_mod, "context_parallel_linear_attention", lambda *a, **k: calls.append(1) or real(*a, **k))
+    split = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="bfloat16")
+    assert not calls, "the piece machinery ran although no document needs joining"
+    with no_pieces():
+        plain = run_cuda("gated_deltanet", case, scale=case["meta"]["scale"], dtype="bfloat16")
+    for name in plain:
+        assert rel_l2(split[name], plain[name]) < 1e-2, (name, rel_l2(split[name], plain[name]))
+    want = run_oracle("gated_deltanet", case, scale=case["meta"]["scale"], chunked=True)
+    compare(split, want, 1e-2, "documents as rows")
