@@ -230,13 +230,18 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     Xd[i * LDC + j] = from_f32<T>(ok ? to_f32(Xm[i * LDC + j]) * betas[j] : 0.f);
     if (!ok) Xp[i * LDC + j] = from_f32<T>(0.f);  // dP arrives unmasked: only pairs of one document with j <= i count
   }
-  if (tid < 64) {
-    const int j = tid;
+  {  // eight threads per column j, eight rows each
+    const int j = tid >> 3, i8 = (tid & 7) * 8;
     float s = 0.f;
-    for (int i = j; i < 64; ++i) {
-      if (run[i] == run[j]) s += to_f32(Xm[i * LDC + j]) * to_f32(Tt[i * LDC + j]);
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii) {
+      const int i = i8 + ii;
+      if (i >= j && run[i] == run[j]) s += to_f32(Xm[i * LDC + j]) * to_f32(Tt[i * LDC + j]);
     }
-    dbcol[j] = s;
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if ((tid & 7) == 0) dbcol[j] = s;
   }
   __syncthreads();
   // ---- dA = -strict(T^T (dT T^T)): this warp's 16 rows x 16 columns
@@ -309,6 +314,20 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     zero_acc(accU);
     zero_acc(accQ);
     zero_acc(accW);
+    // The three fp32 state-side gradient tiles come from global memory in fragment order: the values of the first two
+    // column tiles are requested before the products (which hide their latency), those of the other two while the
+    // first two are folded.
+    float2 sgq[2][2], sgk[2][2], sgu[2][2];  // [nt & 1][hi]
+    auto request = [&](int nt) {
+#pragma unroll
+      for (int hi = 0; hi < 2; ++hi) {
+        const int off = (hi ? i1 : i0) * KD + kc0 + nt * 8 + 2 * t;
+        sgq[nt & 1][hi] = *reinterpret_cast<const float2*>(dqs + off);
+        sgk[nt & 1][hi] = *reinterpret_cast<const float2*>(dks + off);
+        sgu[nt & 1][hi] = *reinterpret_cast<const float2*>(dku + off);
+      }
+    };
+    request(0);
     warp_gemm<T, 4, 4, A_ROW, B_KN>(accU, Xm + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dA k~
     warp_gemm<T, 4, 4, A_ROW, B_KN>(accQ, Xp + r0 * LDC, LDC, tb + kc0, LDK, lane);   // dP k~
     warp_gemm<T, 4, 4, A_COL, B_KN>(accW, Xp + r0, LDC, tqh + kc0, LDK, lane);        // dP^T q^
@@ -317,13 +336,12 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     for (int nt = 0; nt < 4; ++nt) {
       float colsum[2] = {0.f, 0.f};
       const float eR[2] = {__expf(0.5f * Glast[kc0 + nt * 8 + 2 * t]), __expf(0.5f * Glast[kc0 + nt * 8 + 2 * t + 1])};
+      if (nt + 1 < 4) request(nt + 1);  // into the other half of the buffers
 #pragma unroll
       for (int hi = 0; hi < 2; ++hi) {
         const int i = hi ? i1 : i0, col = kc0 + nt * 8 + 2 * t;
         const bool cin = hi ? cin1 : cin0, tail = hi ? tl1 : tl0;
-        const float2 qs2 = *reinterpret_cast<const float2*>(dqs + i * KD + col);
-        const float2 ks2 = *reinterpret_cast<const float2*>(dks + i * KD + col);
-        const float2 ku2 = *reinterpret_cast<const float2*>(dku + i * KD + col);
+        const float2 qs2 = sgq[nt & 1][hi], ks2 = sgk[nt & 1][hi], ku2 = sgu[nt & 1][hi];
         const float2 qr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tq + i * LDK + col));
         const float2 kr2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tr + i * LDK + col));  // read key
         const float2 kw2 = unpack2<T>(*reinterpret_cast<const uint32_t*>(tk + i * LDK + col));  // write key
@@ -451,18 +469,29 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
   }
   __syncthreads();
 
-  // ---- dg: suffix sums over the chunk's tokens plus the terms that act through G_63; dbeta
-  if (tid < KD) {
-    const int ch = tid;
+  // ---- dg: suffix sums over the chunk's tokens plus the terms that act through G_63; dbeta. Four threads per
+  // channel, 16 tokens each: the segment sums go through part[] (whose column sums are read first), then every
+  // thread walks its own 16 tokens from the sum of everything behind them.
+  {
+    const int ch = tid & (KD - 1), seg = tid >> 7;
     const float keep_d = (entering && run_last == 0) ? __expf(Glast[ch]) : 0.f;
     float acc = part[ch] + part[KD + ch] + part[2 * KD + ch] + part[3 * KD + ch] + keep_d * p.dd[slot * KD + ch];
-    for (int i = 63; i >= 0; --i) {
+    float own = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) own += dGt[(16 * seg + i) * KD + ch];
+    __syncthreads();  // part[] has been read by every thread
+    part[seg * KD + ch] = own;
+    __syncthreads();
+    for (int sg = seg + 1; sg < 4; ++sg) acc += part[sg * KD + ch];
+#pragma unroll 4
+    for (int i = 16 * seg + 15; i >= 16 * seg; --i) {
       acc += dGt[i * KD + ch];
       if (i < m.len) p.dg[tokbase + i * tstride + ch] = acc;
     }
-  } else if (tid - KD < m.len) {
-    const int i = tid - KD;
-    p.dbeta[(long)(m.tok0 + i) * p.H + h] = dbrow[i] + dbrow[64 + i] + dbrow[128 + i] + dbrow[192 + i] + dbcol[i];
+    if (tid < m.len) {
+      p.dbeta[(long)(m.tok0 + tid) * p.H + h] =
+          dbrow[tid] + dbrow[64 + tid] + dbrow[128 + tid] + dbrow[192 + tid] + dbcol[tid];
+    }
   }
 }
 
