@@ -202,11 +202,14 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     const int ch = tid & (KD - 1), hh = tid >> 7;
     const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + ch;
     const long gstride = (long)p.H * KD;
+    float gv[16];  // all sixteen loads in flight before the first add
+#pragma unroll
+    for (int ii = 0; ii < 16; ++ii) gv[ii] = (16 * hh + ii < m.len) ? gp[(16 * hh + ii) * gstride] : 0.f;
     float acc = 0.f;
-#pragma unroll 8
-    for (int i = 16 * hh; i < 16 * hh + 16; ++i) {
-      if (i < m.len) acc += gp[i * gstride];
-      Gm[i * KD + ch] = acc;
+#pragma unroll
+    for (int ii = 0; ii < 16; ++ii) {
+      acc += gv[ii];
+      Gm[(16 * hh + ii) * KD + ch] = acc;
     }
     part[hh * KD + ch] = acc;
     cp_async_wait<0>();

@@ -93,10 +93,16 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
     const float* gp = p.g + ((long)m.tok0 * p.H + h) * KD + ch;
     const long gstride = (long)p.H * KD;
     float acc = 0.f;
-#pragma unroll 8
-    for (int i = 32 * hh; i < 32 * hh + 32; ++i) {
-      if (i < m.len) acc += gp[i * gstride];
-      Gm[i * KD + ch] = acc;
+#pragma unroll
+    for (int i0 = 32 * hh; i0 < 32 * hh + 32; i0 += 16) {
+      float gv[16];  // sixteen loads in flight before the first add
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) gv[ii] = (i0 + ii < m.len) ? gp[(i0 + ii) * gstride] : 0.f;
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        acc += gv[ii];
+        Gm[(i0 + ii) * KD + ch] = acc;
+      }
     }
     if (hh == 0) M[ch] = acc;  // scratch of the inverse, free until then
     cp_async_wait<0>();
