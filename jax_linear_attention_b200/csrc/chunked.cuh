@@ -27,6 +27,7 @@ struct Plan {
   bool delta, l2norm, save;
   size_t meta, row_chunks, gates, runs, t0, ag, qn, kn, h, vn, w, residual_bytes;  // residual buffer
   size_t kda_q, kda_kr, kda_kw, kda_p, kda_d;  // KDA: gate-folded operands per chunk slot (see chunked_kda_prep.cu)
+  size_t qk_tab;  // grouped simple GLA on the mma.sync kernels: Q K^T and K Q^T per (chunk, key head), see qk_table_kernel
   size_t kda_dag, kda_dqs, kda_dks, kda_dku, kda_dd;  // KDA backward scratch (see chunked_kda_bwd.cu)
   size_t fwd_scratch_bytes;                                                 // same layout without h, vn
   size_t dh, dvn, dq_acc, dk_acc, dp, dga, bwd_scratch_bytes;               // backward scratch
@@ -39,6 +40,15 @@ bool use_tc_kernels(const jla_problem& p);  // chunked_api.cu
 bool kda_scan_backward();  // chunked_api.cu
 
 inline int elem_size(int dtype) { return dtype == JLA_DTYPE_F32 ? 4 : 2; }
+
+// Without the delta rule the in-chunk scores Q K^T do not depend on the value head: when several value heads share a
+// key head (Mamba-2: all of them) the mma.sync kernels take the two 64 x 64 products Q K^T and K Q^T from a table
+// that a small kernel fills once per (chunk, key head), in the accumulator-fragment order of the warps that use
+// them (fp32, so the decayed scores round exactly as when every head computes the product itself).
+constexpr int kQkTabFloats = 2 * 64 * 64;  // per (chunk, key head): Q K^T then K Q^T
+inline bool shares_scores(const jla_problem& p) {
+  return p.kind == JLA_KIND_SIMPLE_GLA && !use_tc_kernels(p) && p.Hk > 0 && p.H / p.Hk >= 2;
+}
 
 inline Plan make_plan(const jla_problem& p) {
   Plan pl{};
@@ -74,6 +84,7 @@ inline Plan make_plan(const jla_problem& p) {
   pl.kda_kw = off(slot_tile);
   pl.kda_p = off(kda ? (size_t)pl.nc * p.H * 64 * 64 * es : 0);
   pl.kda_d = off(kda ? (size_t)pl.nc * p.H * p.K * sizeof(float) : 0);
+  pl.qk_tab = off(shares_scores(p) ? (size_t)pl.nc * p.Hk * kQkTabFloats * sizeof(float) : 0);
   pl.fwd_scratch_bytes = align_up(c.off);
   pl.h = off((size_t)pl.nc * p.H * p.K * p.V * es);
   pl.vn = off(pl.delta ? (size_t)pl.nc * p.H * 64 * p.V * es : 0);

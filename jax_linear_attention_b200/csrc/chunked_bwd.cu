@@ -25,6 +25,7 @@ struct BwdParams {
   const unsigned char* runs;
   const void *q, *k, *v, *t0, *d_o, *h, *vn;
   const float* d_final;
+  const float* qk_tab;  // Q K^T and K Q^T per (chunk, key head) in fragment order (qk_table_kernel), or nullptr
   void *dh, *dvn, *dv;
   float* dh0;
   void *dq, *dk;          // tensor dtype, written directly when dq_acc == nullptr
@@ -154,8 +155,18 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_bwd_state
     uint32_t pfrag[4][4];
     {
       float accP[8][4];
-      zero_acc(accP);
-      warp_gemm<T, 8, K / 16, A_ROW, B_NK>(accP, kS + r0 * LDK, LDK, qS, LDK, lane);
+      if (p.qk_tab) {  // K Q^T is shared by the value heads of the key head: this warp's fragments from the table
+        const float4* src = reinterpret_cast<const float4*>(p.qk_tab + ((long)c * p.Hk + hk) * kQkTabFloats + 4096) +
+                            (warp & 3) * 8 * 32 + lane;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const float4 x = __ldg(src + nt * 32);
+          accP[nt][0] = x.x, accP[nt][1] = x.y, accP[nt][2] = x.z, accP[nt][3] = x.w;
+        }
+      } else {
+        zero_acc(accP);
+        warp_gemm<T, 8, K / 16, A_ROW, B_NK>(accP, kS + r0 * LDK, LDK, qS, LDK, lane);
+      }
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
@@ -712,6 +723,7 @@ int launch_sg_bwd(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, cuda
   bp.h = c.res + pl.h;
   bp.vn = c.res + pl.vn;
   bp.d_final = io.d_final;
+  bp.qk_tab = shares_scores(p) ? reinterpret_cast<const float*>(c.res + pl.qk_tab) : nullptr;
   bp.dh = scratch + pl.dh;
   bp.dvn = scratch + pl.dvn;
   bp.dv = io.dv;

@@ -21,6 +21,7 @@ struct FwdParams {
   const unsigned char* runs;
   const void *q, *k, *v, *t0;
   const float* h0;
+  const float* qk_tab;  // Q K^T per (chunk, key head) in fragment order (qk_table_kernel), or nullptr
   void* o;
   float* final_state;
   void *h_out, *vn_out;  // residuals (nullptr when not saving)
@@ -167,8 +168,18 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_fwd_kerne
     uint32_t pfrag[4][4];
     {
       float accP[8][4];
-      zero_acc(accP);
-      warp_gemm<T, 8, K / 16, A_ROW, B_NK>(accP, qS + r0 * LDK, LDK, kS, LDK, lane);
+      if (p.qk_tab) {  // the product is shared by the value heads of the key head: this warp's fragments from the table
+        const float4* src = reinterpret_cast<const float4*>(p.qk_tab + ((long)c * p.Hk + hk) * kQkTabFloats) +
+                            (warp & 3) * 8 * 32 + lane;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const float4 x = __ldg(src + nt * 32);
+          accP[nt][0] = x.x, accP[nt][1] = x.y, accP[nt][2] = x.z, accP[nt][3] = x.w;
+        }
+      } else {
+        zero_acc(accP);
+        warp_gemm<T, 8, K / 16, A_ROW, B_NK>(accP, qS + r0 * LDK, LDK, kS, LDK, lane);
+      }
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int j = nt * 8 + 2 * t;
@@ -266,6 +277,7 @@ int launch_sg_fwd(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) {
   fp.v = p.v;
   fp.t0 = c.res + pl.t0;
   fp.h0 = p.h0;
+  fp.qk_tab = shares_scores(p) ? reinterpret_cast<const float*>(c.res + pl.qk_tab) : nullptr;
   fp.o = io.o;
   fp.final_state = io.final_state;
   fp.h_out = pl.save ? c.res + pl.h : nullptr;

@@ -235,6 +235,56 @@ int launch_kkt(const KktParams& kp, int blocks, cudaStream_t s) {
   return JLA_OK;
 }
 
+// Q K^T and K Q^T of one (chunk, key head) in fp32, stored in the accumulator-fragment order of warp_gemm: for the row
+// block rb = warp (16 rows), fragment register i (0 .. 31 = n-tile * 4 + e) of lane l sits at ((rb * 8 + i / 4) * 32 + l)
+// * 4 + i % 4, so that a warp of the state-pass kernels reads its whole 16 x 64 block with eight coalesced 16-byte
+// loads per lane. The products are the same instruction sequence the kernels would otherwise run per value head.
+template <typename T, int K>
+__global__ void __launch_bounds__(128) qk_table_kernel(const ChunkMeta* meta, const void* q, const void* k, float* tab, int Hk) {
+  constexpr int LDK = K + 8;
+  const int c = blockIdx.x / Hk, hk = blockIdx.x - c * Hk;
+  const ChunkMeta m = meta[c];
+  if (m.len == 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* qS = reinterpret_cast<T*>(smem_raw);
+  T* kS = qS + 64 * LDK;
+  load_tile_async<T, 64, K>(qS, LDK, static_cast<const T*>(q) + ((long)m.tok0 * Hk + hk) * K, (long)Hk * K, m.len, tid, 128);
+  load_tile_async<T, 64, K>(kS, LDK, static_cast<const T*>(k) + ((long)m.tok0 * Hk + hk) * K, (long)Hk * K, m.len, tid, 128);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  float* out = tab + (long)blockIdx.x * kQkTabFloats;
+#pragma unroll
+  for (int variant = 0; variant < 2; ++variant) {
+    float acc[8][4];
+    zero_acc(acc);
+    warp_gemm<T, 8, K / 16, A_ROW, B_NK>(acc, (variant ? kS : qS) + 16 * warp * LDK, LDK, variant ? qS : kS, LDK, lane);
+    float4* dst = reinterpret_cast<float4*>(out + variant * 4096) + warp * 8 * 32 + lane;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) dst[nt * 32] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+  }
+}
+
+template <typename T>
+int launch_qk_table(const ChunkedCtx& c, cudaStream_t s) {
+  const jla_problem& p = c.p;
+  const Plan& pl = c.plan;
+  const ChunkMeta* meta = reinterpret_cast<const ChunkMeta*>(c.res + pl.meta);
+  float* tab = reinterpret_cast<float*>(c.res + pl.qk_tab);
+  const int blocks = pl.nc * p.Hk;
+  if (p.K == 128) {
+    const int smem = 2 * 64 * (128 + 8) * sizeof(T);
+    JLA_CUDA_OK(cudaFuncSetAttribute(qk_table_kernel<T, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    qk_table_kernel<T, 128><<<blocks, 128, smem, s>>>(meta, c.q_eff, c.k_eff, tab, p.Hk);
+  } else {
+    const int smem = 2 * 64 * (64 + 8) * sizeof(T);
+    qk_table_kernel<T, 64><<<blocks, 128, smem, s>>>(meta, c.q_eff, c.k_eff, tab, p.Hk);
+  }
+  JLA_LAUNCH_OK();
+  return JLA_OK;
+}
+
 }  // namespace
 
 int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
@@ -265,6 +315,10 @@ int launch_prep(const ChunkedCtx& c, cudaStream_t s) {
     int rc = l2norm_fwd(p.q, c.res + pl.qn, p.dtype, nrows, p.K, s);
     if (rc != JLA_OK) return rc;
     rc = l2norm_fwd(p.k, c.res + pl.kn, p.dtype, nrows, p.K, s);
+    if (rc != JLA_OK) return rc;
+  }
+  if (shares_scores(p)) {  // grouped simple GLA on the mma.sync kernels: the in-chunk scores once per key head
+    const int rc = p.dtype == JLA_DTYPE_BF16 ? launch_qk_table<__nv_bfloat16>(c, s) : launch_qk_table<__half>(c, s);
     if (rc != JLA_OK) return rc;
   }
   if (!pl.delta) return JLA_OK;
