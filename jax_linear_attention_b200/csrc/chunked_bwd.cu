@@ -419,7 +419,17 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_chunk_gra
     zero_acc(accP);
     zero_acc(accE);
     warp_gemm<T, 4, V / 16, A_ROW, B_NK>(accP, doS + r0 * LDV, LDV, vnS + cc0 * LDV, LDV, lane);
-    warp_gemm<T, 4, K / 16, A_ROW, B_NK>(accE, qS + r0 * LDK, LDK, kS + cc0 * LDK, LDK, lane);
+    if (p.qk_tab) {  // Q K^T of this warp's 16 rows x 32 columns from the table shared by the key head's value heads
+      const float4* src = reinterpret_cast<const float4*>(p.qk_tab + ((long)c * p.Hk + hk) * kQkTabFloats) +
+                          ((warp & 3) * 8 + 4 * ch) * 32 + lane;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const float4 x = __ldg(src + nt * 32);
+        accE[nt][0] = x.x, accE[nt][1] = x.y, accE[nt][2] = x.z, accE[nt][3] = x.w;
+      }
+    } else {
+      warp_gemm<T, 4, K / 16, A_ROW, B_NK>(accE, qS + r0 * LDK, LDK, kS + cc0 * LDK, LDK, lane);
+    }
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       const int j = cc0 + nt * 8 + 2 * t;
