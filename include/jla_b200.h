@@ -190,7 +190,9 @@ int jla_gdn2_inputs_bwd(int dtype, int64_t n_k, int64_t n_v, const void* k, cons
  *   inputs_fwd:  v = round(x * dt), g = dt * A
  *   inputs_bwd:  dx = round(dv * dt), ddt = sum_p dv * x + dg * A, dA = sum_tokens dg * dt
  *   output_fwd:  y = round(o + D * x)
- *   output_bwd:  dx = round(D * dy), dD = sum_{tokens, p} dy * x      (do = dy needs no kernel) */
+ *   output_bwd:  dx = round(D * dy), dD = sum_{tokens, p} dy * x      (do = dy needs no kernel)
+ *   layer_bwd:   inputs_bwd and output_bwd in one pass for a layer with a D term: dx = round(dv * dt + D * dy),
+ *                ddt, dA, dD as above; x, dv and dy are read once and no partial dx tensors are summed afterwards */
 int jla_ssd_inputs_fwd(int dtype, int64_t tokens, int H, int P, const void* x, const float* dt, const float* a, void* v,
                        float* g, jla_stream_t stream);
 int jla_ssd_inputs_bwd(int dtype, int64_t tokens, int H, int P, const void* x, const float* dt, const float* a,
@@ -199,6 +201,9 @@ int jla_ssd_output_fwd(int dtype, int64_t tokens, int H, int P, const void* o, c
                        jla_stream_t stream);
 int jla_ssd_output_bwd(int dtype, int64_t tokens, int H, int P, const void* dy, const void* x, const float* d, void* dx,
                        float* dd, jla_stream_t stream);
+int jla_ssd_layer_bwd(int dtype, int64_t tokens, int H, int P, const void* x, const float* dt, const float* a,
+                      const float* d, const void* dv, const float* dg, const void* dy, void* dx, float* ddt, float* da,
+                      float* dd, jla_stream_t stream);
 
 /* Gate activations in front of the kernels, forward and backward in one pass each; replaces the XLA fusions of
  * _mamba_gate and _write_strength in the Gated DeltaNet and KDA mixers (src/jla/layers/linear_attention.py:84-86,

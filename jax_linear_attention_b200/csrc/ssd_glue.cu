@@ -6,6 +6,8 @@
 //            dx = dv * dt,  ddt = sum_p dv * x + dg * A,  dA = sum_{tokens} dg * dt
 //   output   y = o + D * x   (fp32 sum, rounded once)
 //            do = dy (the same tensor),  dx = D * dy,  dD = sum_{tokens, p} dy * x
+//   layer    both transposes in one pass when the layer has a D term: dx = dv * dt + D * dy with ddt, dA, dD as
+//            above (x, dv, dy read once, dx written once, instead of two partial dx tensors and their sum)
 //
 // HBM-bound: a thread owns 8 adjacent channels (one 16-byte load per tensor) of one head and walks a tile of
 // tokens, so the per-head sums dA, dD stay in registers and leave the block as one atomic per head.
@@ -43,13 +45,16 @@ __device__ __forceinline__ float group_sum(float x, int lanes) {
 struct GlueParams {
   long tokens;
   int H, P;
-  const void *x, *other;  // other: dv (inputs_bwd), o (output_fwd), dy (output_bwd)
+  const void *x, *other;  // other: dv (inputs_bwd, layer_bwd), o (output_fwd), dy (output_bwd)
+  const void* dy;         // layer_bwd only
   const float *dt, *a, *dg;
+  const float* d;         // layer_bwd only: the skip weights D [H]
   void* out;              // v, dx, y
   float *g, *ddt, *hsum;  // hsum: dA or dD [H]
+  float* dd;              // layer_bwd only: dD [H] (hsum is dA)
 };
 
-enum Mode { kInputsFwd, kInputsBwd, kOutputFwd, kOutputBwd };
+enum Mode { kInputsFwd, kInputsBwd, kOutputFwd, kOutputBwd, kLayerBwd };
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(THREADS) ssd_glue_kernel(GlueParams p) {
@@ -63,8 +68,9 @@ __global__ void __launch_bounds__(THREADS) ssd_glue_kernel(GlueParams p) {
   const long t0 = (long)blockIdx.y * TOKENS_PER_BLOCK;
   const long t1 = t0 + TOKENS_PER_BLOCK < p.tokens ? t0 + TOKENS_PER_BLOCK : p.tokens;
   const float coef = live && (MODE == kOutputFwd || MODE == kOutputBwd) ? p.a[h] : 0.f;  // D for the output side
-  const float ah = live && (MODE == kInputsFwd || MODE == kInputsBwd) ? p.a[h] : 0.f;
-  float hacc = 0.f;
+  const float ah = live && (MODE == kInputsFwd || MODE == kInputsBwd || MODE == kLayerBwd) ? p.a[h] : 0.f;
+  const float dh = live && MODE == kLayerBwd ? p.d[h] : 0.f;
+  float hacc = 0.f, dacc = 0.f;
   for (long t = t0; t < t1; ++t) {
     const long row = t * p.H + h;
     const long off = t * HP + col;
@@ -73,18 +79,22 @@ __global__ void __launch_bounds__(THREADS) ssd_glue_kernel(GlueParams p) {
       load8<T>(static_cast<const T*>(p.x) + off, xv);
       if (MODE != kInputsFwd) load8<T>(static_cast<const T*>(p.other) + off, ov);
     }
+    float yv[8] = {};
+    if (MODE == kLayerBwd && live) load8<T>(static_cast<const T*>(p.dy) + off, yv);
     if (MODE == kInputsFwd) {
       const float dt = live ? p.dt[row] : 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) res[i] = xv[i] * dt;
       if (live && head_lead) p.g[row] = dt * ah;
-    } else if (MODE == kInputsBwd) {
+    } else if (MODE == kInputsBwd || MODE == kLayerBwd) {
       const float dt = live ? p.dt[row] : 0.f;
       float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        res[i] = ov[i] * dt;
+        // the two-kernel form rounds dv * dt and D * dy to the activation dtype before their sum; here one rounding
+        res[i] = MODE == kLayerBwd ? fmaf(dh, yv[i], ov[i] * dt) : ov[i] * dt;
         dot += ov[i] * xv[i];
+        if (MODE == kLayerBwd) dacc += yv[i] * xv[i];
       }
       const float dg = live ? p.dg[row] : 0.f;
       if (pow2) {
@@ -106,8 +116,16 @@ __global__ void __launch_bounds__(THREADS) ssd_glue_kernel(GlueParams p) {
     }
     if (live) store8<T>(static_cast<T*>(p.out) + off, res);
   }
-  if (MODE == kInputsBwd) {
+  if (MODE == kInputsBwd || MODE == kLayerBwd) {
     if (live && head_lead) atomicAdd(p.hsum + h, hacc);
+    if (MODE == kLayerBwd) {
+      if (pow2) {
+        dacc = group_sum(dacc, lanes);
+        if (live && head_lead) atomicAdd(p.dd + h, dacc);
+      } else if (live) {
+        atomicAdd(p.dd + h, dacc);
+      }
+    }
   } else if (MODE == kOutputBwd) {
     if (pow2) {
       hacc = group_sum(hacc, lanes);
@@ -131,9 +149,10 @@ int launch(int dtype, const GlueParams& gp, cudaStream_t s) {
   if (gp.tokens == 0) return JLA_OK;
   const int lanes = gp.P / 8;
   const bool pow2 = lanes <= 32 && (lanes & (lanes - 1)) == 0;
-  if (MODE == kInputsBwd || MODE == kOutputBwd) {
+  if (MODE == kInputsBwd || MODE == kOutputBwd || MODE == kLayerBwd) {
     JLA_CUDA_OK(cudaMemsetAsync(gp.hsum, 0, sizeof(float) * gp.H, s));
-    if (MODE == kInputsBwd && !pow2) JLA_CUDA_OK(cudaMemsetAsync(gp.ddt, 0, sizeof(float) * gp.tokens * gp.H, s));
+    if (MODE == kLayerBwd) JLA_CUDA_OK(cudaMemsetAsync(gp.dd, 0, sizeof(float) * gp.H, s));
+    if (MODE != kOutputBwd && !pow2) JLA_CUDA_OK(cudaMemsetAsync(gp.ddt, 0, sizeof(float) * gp.tokens * gp.H, s));
   }
   const long tiles = (gp.tokens + TOKENS_PER_BLOCK - 1) / TOKENS_PER_BLOCK;
   if (tiles > 65535) {
@@ -183,4 +202,14 @@ extern "C" int jla_ssd_output_bwd(int dtype, int64_t tokens, int H, int P, const
   GlueParams gp{};
   gp.tokens = tokens, gp.H = H, gp.P = P, gp.x = x, gp.other = dy, gp.a = d, gp.out = dx, gp.hsum = dd;
   return launch<kOutputBwd>(dtype, gp, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int jla_ssd_layer_bwd(int dtype, int64_t tokens, int H, int P, const void* x, const float* dt, const float* a,
+                                 const float* d, const void* dv, const float* dg, const void* dy, void* dx, float* ddt,
+                                 float* da, float* dd, jla_stream_t stream) {
+  if (!x || !dt || !a || !d || !dv || !dg || !dy || !dx || !ddt || !da || !dd) return JLA_ERR_BAD_ARGUMENT;
+  GlueParams gp{};
+  gp.tokens = tokens, gp.H = H, gp.P = P, gp.x = x, gp.other = dv, gp.dy = dy, gp.dt = dt, gp.a = a, gp.d = d, gp.dg = dg;
+  gp.out = dx, gp.ddt = ddt, gp.hsum = da, gp.dd = dd;
+  return launch<kLayerBwd>(dtype, gp, static_cast<cudaStream_t>(stream));
 }

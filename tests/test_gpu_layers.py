@@ -58,6 +58,40 @@ def test_mamba2_ssd_shared_bc(docs):
         assert compare({name: got[name]}, {name: want[name]}, tol[name], f"ssd {name}")
 
 
+def test_mamba2_ssd_backward_routes_of_the_skip_term():
+    """The layer's backward has three routes for dx: one fused pass when D is given and a gradient reaches y, the
+    input side alone without D, and the input side alone when only the final state carries a gradient (then dD = 0).
+    Each is held to the float64 oracle."""
+    from jax_linear_attention_b200.layers import mamba2_ssd
+
+    case = make_mamba2_case(B=1, T=300, H=4, P=64, N=128, G=1, seed=11, docs="mixed", h0=False, baseline=True)
+    dev, f64 = "cuda", torch.float64
+    half = ("x", "B", "C")
+    for with_d, through_y in ((True, True), (False, True), (True, False)):
+        names = ["x", "dt", "A", "B", "C"] + (["D"] if with_d else [])
+        t = {n: torch.tensor(case[n], device=dev, dtype=torch.bfloat16 if n in half else torch.float32,
+                             requires_grad=True) for n in names}
+        r = {n: torch.tensor(case[n], dtype=f64, requires_grad=True) for n in names}
+        seg = torch.tensor(case["seg"])
+        y, st = mamba2_ssd(t["x"], t["dt"], t["A"], t["B"], t["C"], d=t.get("D"), segment_ids=seg.to(dev),
+                           output_final_state=True)
+        yr, sr = oracle_ssd.mamba2_ssd(r["x"], r["dt"], r["A"], r["B"], r["C"], d=r.get("D"), segment_ids=seg,
+                                       output_final_state=True, round_v_to=torch.bfloat16)
+        do = torch.tensor(case["do"]) * (1.0 if through_y else 0.0)
+        dht = torch.tensor(case["dht"])
+        outs, outs_r = ([y, st], [yr, sr]) if through_y else ([st], [sr])
+        cot = [do.to(dev, torch.bfloat16), dht.to(dev)] if through_y else [dht.to(dev)]
+        cot_r = [do.to(f64), dht.to(f64)] if through_y else [dht.to(f64)]
+        got = torch.autograd.grad(outs, [t[n] for n in names], cot, allow_unused=True)
+        want = torch.autograd.grad(outs_r, [r[n] for n in names], cot_r, allow_unused=True)
+        for n, a, b in zip(names, got, want):
+            if b is None:  # D and C reach only y
+                assert not through_y and n in ("D", "C") and (a is None or float(a.abs().max()) == 0.0), n
+                continue
+            tol = 3e-2 if n == "A" else 1e-2
+            assert rel_l2(a.detach().float().cpu().numpy(), b.numpy()) < tol, (with_d, through_y, n)
+
+
 def test_mamba2_ssd_config2_full_size_runs_and_matches_a_slice():
     """The Mamba-2 benchmark workload at full size (B8 T2048 H64 P64 N128 G1): finite everywhere; batch row 0 against the oracle
     on a 4-head slice (heads are independent given B, C)."""
