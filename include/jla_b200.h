@@ -54,7 +54,7 @@ enum jla_kind {              /* src/jla/ops/__init__.py:47-60 (KINDS) */
 enum jla_dtype { JLA_DTYPE_BF16 = 0, JLA_DTYPE_F16 = 1, JLA_DTYPE_F32 = 2 };
 
 enum jla_path {
-  JLA_PATH_AUTO = 0,      /* f32 tensors: RECURRENT; bf16/f16: CHUNKED where it applies (KDA: bf16, K = V = 128).
+  JLA_PATH_AUTO = 0,      /* f32 tensors: RECURRENT; bf16/f16: CHUNKED where it applies (KDA: K = V = 128).
                            * A call with k_read has chunked kernels for KDA only: the other kinds run RECURRENT
                            * with it, whatever is asked for here. */
   JLA_PATH_RECURRENT = 1, /* fp32 token scan in the order of reference.py:140-157 (any K, V <= 256)            */

@@ -41,6 +41,15 @@ bool kda_scan_backward();  // chunked_api.cu
 
 inline int elem_size(int dtype) { return dtype == JLA_DTYPE_F32 ? 4 : 2; }
 
+// Per-channel gates (KDA): a chunk's in-chunk scores run on the tensor cores, factored through the mid point of each
+// channel's decay, while no channel decays by more than exp(-bound) over the chunk; the factors then reach
+// exp(+-bound / 2) times an element of q or k and must stay inside the 16-bit type's range (bf16 shares fp32's
+// exponent; f16 ends at 65504, so its factors stop at exp(6) = 403). Chunks beyond the bound take the exact fp32 loop.
+template <typename T>
+__host__ __device__ constexpr float kda_bounded_log() { return 60.f; }
+template <>
+__host__ __device__ constexpr float kda_bounded_log<__half>() { return 12.f; }
+
 // Without the delta rule the in-chunk scores Q K^T do not depend on the value head: when several value heads share a
 // key head (Mamba-2: all of them) the mma.sync kernels take the two 64 x 64 products Q K^T and K Q^T from a table
 // that a small kernel fills once per (chunk, key head), in the accumulator-fragment order of the warps that use

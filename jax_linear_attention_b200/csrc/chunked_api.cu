@@ -10,8 +10,8 @@ namespace jla {
 const char* chunked_unsupported(const jla_problem& p) {
   if (p.dtype == JLA_DTYPE_F32) return "the chunked tensor-core kernels take bf16 or f16 tensors (f32 runs the recurrent path)";
   if ((p.K != 64 && p.K != 128) || (p.V != 64 && p.V != 128)) return "head dims K, V must be in (64, 128)";
-  if (p.kind == JLA_KIND_KDA && !(p.dtype == JLA_DTYPE_BF16 && use_tc_kernels(p))) {
-    return "the chunked KDA forward takes bf16 tensors with K = V = 128 (other calls run the recurrent path)";
+  if (p.kind == JLA_KIND_KDA && !use_tc_kernels(p)) {
+    return "the chunked KDA forward takes bf16 or f16 tensors with K = V = 128 (other calls run the recurrent path)";
   }
   return nullptr;
 }

@@ -634,7 +634,10 @@ int launch_sg_bwd_state_tc(const ChunkedCtx& c, const jla_bwd_io& io, char* scra
   bp.status = tc_status_ptr();
   if (!bp.status) return JLA_ERR_CUDA;
   const int blocks = pl.rows * p.H;
-  if (vg) return launch_one<__nv_bfloat16, true, true>(maps, bp, blocks, s);
+  if (vg) {
+    return p.dtype == JLA_DTYPE_BF16 ? launch_one<__nv_bfloat16, true, true>(maps, bp, blocks, s)
+                                     : launch_one<__half, true, true>(maps, bp, blocks, s);
+  }
   if (p.dtype == JLA_DTYPE_BF16) {
     return pl.delta ? launch_one<__nv_bfloat16, true>(maps, bp, blocks, s) : launch_one<__nv_bfloat16, false>(maps, bp, blocks, s);
   }

@@ -812,11 +812,8 @@ int launch_sg_fwd_tc(const ChunkedCtx& c, const jla_fwd_io& io, cudaStream_t s) 
   if (!fp.status) return JLA_ERR_CUDA;
   const int blocks = pl.rows * p.H;
   if (vg) {
-    if (p.dtype != JLA_DTYPE_BF16) {
-      set_error("chunked KDA: bf16 tensors only");
-      return JLA_ERR_UNSUPPORTED;
-    }
-    return launch_one<__nv_bfloat16, true, true>(maps, fp, blocks, s);
+    return p.dtype == JLA_DTYPE_BF16 ? launch_one<__nv_bfloat16, true, true>(maps, fp, blocks, s)
+                                     : launch_one<__half, true, true>(maps, fp, blocks, s);
   }
   if (p.dtype == JLA_DTYPE_BF16) {
     return pl.delta ? launch_one<__nv_bfloat16, true>(maps, fp, blocks, s) : launch_one<__nv_bfloat16, false>(maps, fp, blocks, s);

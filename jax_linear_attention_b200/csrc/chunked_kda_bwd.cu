@@ -33,7 +33,6 @@ namespace jla {
 namespace {
 
 constexpr int KD = 128, VD = 128;
-constexpr float kBoundedLog = 60.f;  // the same bound as chunked_kda_prep.cu
 
 struct KdaGradParams {
   const ChunkMeta* meta;
@@ -221,7 +220,7 @@ __global__ void __launch_bounds__(512, 1) kda_intra_grads_kernel(KdaGradParams p
     }
     const float total = acc + off;
     if (hh == 3) Glast[ch] = total;
-    unbounded = __syncthreads_or(hh == 3 && !(fabsf(total) <= kBoundedLog));
+    unbounded = __syncthreads_or(hh == 3 && !(fabsf(total) <= kda_bounded_log<T>()));
   }
   const bool entering = !(m.flags & 1);
   const int run_last = run[63];
@@ -526,8 +525,8 @@ int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, c
   const jla_problem& p = c.p;
   const Plan& pl = c.plan;
   if (pl.nc == 0) return JLA_OK;  // no tokens: nothing to differentiate through
-  if (p.dtype != JLA_DTYPE_BF16 || p.K != KD || p.V != VD) {
-    set_error("chunked KDA backward: bf16 tensors with K = V = 128 only");
+  if ((p.dtype != JLA_DTYPE_BF16 && p.dtype != JLA_DTYPE_F16) || p.K != KD || p.V != VD) {
+    set_error("chunked KDA backward: bf16 or f16 tensors with K = V = 128 only");
     return JLA_ERR_UNSUPPORTED;
   }
   KdaGradParams gp{};
@@ -563,7 +562,8 @@ int launch_kda_grads(const ChunkedCtx& c, const jla_bwd_io& io, char* scratch, c
   gp.H = p.H;
   gp.Hk = p.Hk;
   gp.scale = p.scale;
-  return launch_grads<__nv_bfloat16>(gp, pl.nc * p.H, s);
+  return p.dtype == JLA_DTYPE_BF16 ? launch_grads<__nv_bfloat16>(gp, pl.nc * p.H, s)
+                                   : launch_grads<__half>(gp, pl.nc * p.H, s);
 }
 
 }  // namespace jla

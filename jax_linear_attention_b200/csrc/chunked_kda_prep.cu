@@ -16,7 +16,7 @@
 // All exponents above are <= 0, so these never overflow. The two score matrices need exp(G_i - G_j) per channel
 // inside a contraction; they are factored through the per-channel mid point R = G_63 / 2,
 //   (q exp(G - R)) (k exp(R - G))^T,   |G - R| <= |G_63| / 2,
-// and run on the tensor cores when no channel decays by more than exp(-kBoundedLog) over the chunk. Chunks with a
+// and run on the tensor cores when no channel decays by more than exp(-kda_bounded_log<T>()) over the chunk. Chunks with a
 // stronger decay take the exact fp32 loop over (i, j, c) instead, so the result never depends on the bound.
 //
 // With a separate read key (jla_problem.k_read, Gated DeltaNet-2: S = S' + k^T (v - k_read S')) the key has two roles:
@@ -34,7 +34,6 @@ namespace jla {
 namespace {
 
 constexpr int KD = 128;
-constexpr float kBoundedLog = 60.f;  // exp(+-30) factors: far inside the bf16 / fp32 exponent range
 
 struct KdaPrepParams {
   const ChunkMeta* meta;
@@ -114,7 +113,7 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
       total = acc + off;
       Glast[ch] = total;
     }
-    unbounded = __syncthreads_or(hh == 1 && !(fabsf(total) <= kBoundedLog));
+    unbounded = __syncthreads_or(hh == 1 && !(fabsf(total) <= kda_bounded_log<T>()));
   }
   const bool entering = !(m.flags & 1);
   const int run_last = run[63];
@@ -126,7 +125,7 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
 
   if (!unbounded) {
     // ---- one pass over the tiles: the state-side operands to global memory and the factored operands in place.
-    // With d = G - R, R = G_63 / 2 (|d|, |R| <= kBoundedLog / 2 here): exp(G) = exp(d) exp(R) and
+    // With d = G - R, R = G_63 / 2 (|d|, |R| <= kda_bounded_log<T>() / 2 here): exp(G) = exp(d) exp(R) and
     // exp(G_63 - G) = exp(-d) exp(R), so two exponentials per element serve all five operands.
     float* eRs = M + KD;  // exp(R) per channel (scratch of the inverse, free until then)
     if (tid < KD) eRs[tid] = __expf(0.5f * Glast[tid]);
@@ -315,6 +314,20 @@ __global__ void __launch_bounds__(256, 2) kda_prep_kernel(KdaPrepParams p) {
   }
 }
 
+template <typename T>
+int launch_prep_t(const KdaPrepParams& kp, bool read_key, int blocks, cudaStream_t s) {
+  const size_t smem = 3 * 64 * (KD + 8) * sizeof(T) + (64 * KD + 64 * kTriLda + 32 * kTriLdm + 64 + KD) * sizeof(float) +
+                      64 * sizeof(int);
+  auto* kern = read_key ? kda_prep_kernel<T, true> : kda_prep_kernel<T, false>;
+  JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  {
+    ProfScope ps(kProfKdaPrep, s);
+    kern<<<blocks, 256, smem, s>>>(kp);
+  }
+  JLA_LAUNCH_OK();
+  return JLA_OK;
+}
+
 }  // namespace
 
 int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
@@ -337,21 +350,12 @@ int launch_kda_prep(const ChunkedCtx& c, cudaStream_t s) {
   kp.dvec = reinterpret_cast<float*>(c.res + pl.kda_d);
   kp.H = p.H;
   kp.Hk = p.Hk;
-  if (p.dtype != JLA_DTYPE_BF16 || p.K != KD) {
-    set_error("chunked KDA: bf16 tensors with K = 128 only");
+  if ((p.dtype != JLA_DTYPE_BF16 && p.dtype != JLA_DTYPE_F16) || p.K != KD) {
+    set_error("chunked KDA: bf16 or f16 tensors with K = 128 only");
     return JLA_ERR_UNSUPPORTED;
   }
-  using T = __nv_bfloat16;
-  const size_t smem = 3 * 64 * (KD + 8) * sizeof(T) + (64 * KD + 64 * kTriLda + 32 * kTriLdm + 64 + KD) * sizeof(float) +
-                      64 * sizeof(int);
-  auto* kern = p.k_read ? kda_prep_kernel<T, true> : kda_prep_kernel<T, false>;
-  JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  {
-    ProfScope ps(kProfKdaPrep, s);
-    kern<<<pl.nc * p.H, 256, smem, s>>>(kp);
-  }
-  JLA_LAUNCH_OK();
-  return JLA_OK;
+  return p.dtype == JLA_DTYPE_BF16 ? launch_prep_t<__nv_bfloat16>(kp, p.k_read != nullptr, pl.nc * p.H, s)
+                                   : launch_prep_t<__half>(kp, p.k_read != nullptr, pl.nc * p.H, s);
 }
 
 }  // namespace jla

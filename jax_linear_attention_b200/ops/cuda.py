@@ -310,8 +310,6 @@ def _split_applies(kind, q, v, cu_seqlens, initial_state, precision) -> int:
         return 1
     if q.dtype == torch.float32 or q.shape[-1] != 128 or v.shape[-1] != 128 or _path(precision) == "recurrent":
         return 1
-    if kind == "kda" and q.dtype != torch.bfloat16:
-        return 1
     sms = torch.cuda.get_device_properties(q.device).multi_processor_count
     return pieces(1, v.shape[2], q.shape[1], delta=kind != "simple_gla", sm_count=sms)
 
@@ -459,7 +457,7 @@ def gdn2(q, k, v, g, b, w, *, scale=None, initial_state=None, output_final_state
     way (``jla_gdn2_inputs_*``): fp32 products rounded once to the tensors' dtype, as the reference's kernels round
     the gates (``mosaic_gpu/gdn2.py:11-12``); the read side's and the write side's key gradients are added by
     autograd. The unit norm of ``use_qk_l2norm`` is applied first (the gate multiplies the normalised key,
-    reference.py:118-119). bf16 tensors with ``K = V = 128`` run the KDA chunk kernels (the read key in tiles of its
+    reference.py:118-119). bf16 and f16 tensors with ``K = V = 128`` run the KDA chunk kernels (the read key in tiles of its
     own); every other call with a read key runs the fp32 token scan.
     """
     for name, x in (("q", q), ("k", k), ("v", v), ("b", b), ("w", w)):

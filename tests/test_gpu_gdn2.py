@@ -55,6 +55,17 @@ def test_bf16_head_128_runs_the_chunked_kernels_and_matches_the_oracle(gates, do
     compare(got, scan, 1e-2, "gdn2 chunked against the token scan")
 
 
+def test_float16_head_128_runs_the_chunked_kernels():
+    """f16 tensors take the same kernels (factored scores up to exp(+-6), the exact loop beyond)."""
+    case = make_case("gdn2", B=1, T=300, H=2, K=128, V=128, seed=77, gates="plain", docs="mixed", h0=True,
+                     dtype="float16")
+    want = run_oracle("gdn2", case, scale=case["meta"]["scale"])
+    got = run_cuda("gdn2", case, scale=case["meta"]["scale"], dtype="float16")
+    compare(got, want, 1e-2, "gdn2 f16 d128")
+    scan = run_cuda("gdn2", case, scale=case["meta"]["scale"], dtype="float16", precision="highest")
+    assert any(not np.array_equal(got[n], scan[n]) for n in got), "the chunked kernels did not run"
+
+
 def test_bf16_strong_decay_takes_the_exact_score_path():
     """Channels that decay by e^-80 at one token in ten (the factored scores would overflow) and gates at 0 and 1:
     the chunks run the exact fp32 loops, forward and backward, with the read key in its own role."""

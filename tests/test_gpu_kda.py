@@ -45,6 +45,8 @@ def test_bf16_calls_take_the_chunked_path():
     assert lib.jla_residual_bytes(C.byref(p)) > 0         # only the chunked path keeps residuals
     p.flags = 0
     assert lib.jla_fwd_scratch_bytes(C.byref(p)) > 0      # and needs a forward scratch when it keeps none
+    p16 = _problem("kda", torch.float16, 2, 256, 4, 4, 128, 128, 0, 1.0, _lib.FLAG_SAVE_RESIDUALS, None)
+    assert lib.jla_residual_bytes(C.byref(p16)) > 0       # f16 tensors as well
     p64 = _problem("kda", torch.bfloat16, 2, 256, 4, 4, 64, 64, 0, 1.0, 0, None)
     assert lib.jla_fwd_scratch_bytes(C.byref(p64)) == 0   # other head sizes stay on the token scan
 
@@ -116,6 +118,19 @@ def test_gradients_under_strong_decay():
     for name, x in got.items():
         assert np.isfinite(x).all(), name
     compare(got, want, 1.5e-2, "kda fwd+bwd extreme gates")
+
+
+@pytest.mark.parametrize("gates,tol", [("kda_baseline", 5e-3), ("plain", 1e-2), ("extreme", 1.5e-2)])
+def test_float16_forward_and_gradients(gates, tol):
+    """f16 tensors on the same kernels: the factored scores stop at exp(+-6) there (f16 ends at 65504), so "plain"
+    gates (a chunk decays by up to e^-30 in places) mix factored and exact chunks and "extreme" ones are all exact."""
+    case = make_case("kda", B=1, T=260, H=2, K=128, V=128, seed=41, gates=gates, docs="mixed", h0=True,
+                     dtype="float16")
+    want = run_oracle("kda", case, scale=case["meta"]["scale"])
+    got = run_cuda("kda", case, scale=case["meta"]["scale"], dtype="float16")
+    for name, x in got.items():
+        assert np.isfinite(x).all(), name
+    compare(got, want, tol, f"kda f16 {gates}")
 
 
 def test_config3_full_size_matches_the_token_scan():
