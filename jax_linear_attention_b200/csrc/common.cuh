@@ -25,6 +25,53 @@ template <> __device__ __forceinline__ float from_f32<float>(float x) { return x
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
 
+// One-instruction approximations for the element-wise kernels (relative error about 2^-22: far below the rounding of
+// 16-bit outputs and inside the 1e-5 their float32 paths are held to); the IEEE-rounded reciprocal, the division and
+// the library exp / log cost ten to thirty instructions each.
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_exp(float x) {  // one multiply and one ex2, no range fix-up
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+__device__ __forceinline__ float fast_log(float x) {  // x > 0; absolute error about 1e-7 near x = 1
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y * 0.6931471805599453f;
+}
+__device__ __forceinline__ float fast_rsqrt(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Asynchronous copy of one thread's row (BYTES = 8, 16 or 32) from global to shared memory; `valid` false writes
+// zeros without reading. One commit per group of rows, cp_async_wait_groups<N> leaves the N newest groups in flight.
+template <int BYTES>
+__device__ __forceinline__ void cp_async_row(void* smem, const void* gmem, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int n = valid ? (BYTES < 16 ? BYTES : 16) : 0;
+  if constexpr (BYTES == 8) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(d), "l"(gmem), "r"(n));
+  } else {
+#pragma unroll
+    for (int i = 0; i < BYTES / 16; ++i) {
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(d + 16 * i),
+                   "l"(static_cast<const char*>(gmem) + 16 * i), "r"(n));
+    }
+  }
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_groups() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Groups in a thread's ring of asynchronous copies: one being worked on, the others in flight (two where a row is 32
+// bytes, so that the widest blocks still fit their shared memory).
+__host__ __device__ constexpr int ring_stages(int row_bytes) { return row_bytes >= 32 ? 2 : 3; }
+
 // ---- rows ----------------------------------------------------------------------------------------
 // A "row" is a stretch of tokens whose state starts from its own initial state and ends in its own
 // final state: one batch element, or one sequence of cu_seqlens (reference.py:170-203). Tokens are

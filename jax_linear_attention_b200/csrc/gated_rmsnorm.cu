@@ -66,8 +66,11 @@ __device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
 // Sum over the `lanes` threads of a group. lanes <= 32: an aligned butterfly inside the warp. Wider: the block is one
 // group (blockDim.x == lanes); every thread of the block must call this.
 __device__ __forceinline__ float group_sum(float v, int lanes, float* red) {
-  const int width = lanes < 32 ? lanes : 32;
-  for (int off = width >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {  // five predicated butterflies, no loop
+    const float o = __shfl_xor_sync(0xffffffffu, v, off);
+    if (off < lanes) v += o;
+  }
   if (lanes <= 32) return v;
   const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   __syncthreads();  // the previous use of red is over
@@ -81,7 +84,7 @@ __device__ __forceinline__ float group_sum(float v, int lanes, float* red) {
 template <typename T, bool BWD, int MAXT>
 __global__ void __launch_bounds__(MAXT) gated_rmsnorm_kernel(NormParams p) {
   __shared__ float red[32];
-  extern __shared__ float dw_red[];         // backward: [row lanes][cols * 8]
+  extern __shared__ __align__(16) float dw_red[];  // backward: [row lanes][cols * 8]; then the ring of row copies
   const int cv = p.dim / 8;                 // 8-channel vectors per row
   const int lanes = p.group / 8;            // threads per group
   const int cols = p.cols;                  // column threads of this block
@@ -102,24 +105,43 @@ __global__ void __launch_bounds__(MAXT) gated_rmsnorm_kernel(NormParams p) {
   const T* __restrict__ x = static_cast<const T*>(p.x);
   const T* __restrict__ z = static_cast<const T*>(p.z);
   const float inv_group = 1.f / (float)p.group;
+  // The rows arrive through a ring of asynchronous copies in shared memory, private to the thread (behind the
+  // weight-gradient fold buffer): STAGES - 1 rows of x, z (and dy) in flight while one is worked on; a plain loop of
+  // loads left the kernel waiting on memory for most of its time at one or two blocks per SM.
+  constexpr int RB = 8 * (int)sizeof(T), STAGES = ring_stages(RB), NTENS = BWD ? 3 : 2;
+  unsigned char* ring = reinterpret_cast<unsigned char*>(dw_red) + (BWD ? (size_t)blockDim.x * 8 * sizeof(float) : 0);
+  auto slot = [&](int n, int st) { return ring + ((size_t)(n * STAGES + st) * blockDim.x + threadIdx.x) * RB; };
+  const int n_it = (int)((r1 - r0 + lanes_r - 1) / lanes_r);
+  auto request = [&](int it) {
+    const long r = r0 + (long)it * lanes_r + lr;
+    const long idx = ((live && r < r1) ? r : r0) * p.dim + col;  // rows nobody owns read the tile's first row
+    cp_async_row<RB>(slot(0, it % STAGES), x + idx, true);
+    cp_async_row<RB>(slot(1, it % STAGES), z + idx, true);
+    if constexpr (BWD) cp_async_row<RB>(slot(2, it % STAGES), static_cast<const T*>(p.dy) + idx, true);
+    cp_async_commit_group();
+  };
+#pragma unroll
+  for (int it = 0; it < STAGES - 1; ++it) request(it);
   // every thread of the block runs the same number of iterations (group_sum may synchronise the block)
-  for (long rb = r0; rb < r1; rb += lanes_r) {
-    const long r = rb + lr;
+  for (int it = 0; it < n_it; ++it) {
+    const long r = r0 + (long)it * lanes_r + lr;
     const bool on = live && r < r1;
     const long idx = (on ? r : r0) * p.dim + col;
+    request(it + STAGES - 1);
+    cp_async_wait_groups<STAGES - 1>();
     float xv[8], zv[8], gate[8], u[8];
-    load8<T>(x + idx, xv);
-    load8<T>(z + idx, zv);
+    load8<T>(reinterpret_cast<const T*>(slot(0, it % STAGES)), xv);
+    load8<T>(reinterpret_cast<const T*>(slot(1, it % STAGES)), zv);
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float sg = 1.f / (1.f + __expf(-zv[i]));
+      const float sg = fast_rcp(1.f + fast_exp(-zv[i]));
       gate[i] = p.sigmoid_gate ? sg : zv[i] * sg;
       u[i] = p.norm_before_gate ? xv[i] : xv[i] * gate[i];
       ss += u[i] * u[i];
     }
     if (!on) ss = 0.f;
-    const float rstd = rsqrtf(group_sum(ss, lanes, red) * inv_group + p.eps);
+    const float rstd = fast_rsqrt(group_sum(ss, lanes, red) * inv_group + p.eps);
     if (!BWD) {
       float out[8];
 #pragma unroll
@@ -127,7 +149,7 @@ __global__ void __launch_bounds__(MAXT) gated_rmsnorm_kernel(NormParams p) {
       if (on) store8<T>(static_cast<T*>(p.y) + idx, out);
     } else {
       float dyv[8], n[8], dn[8];
-      load8<T>(static_cast<const T*>(p.dy) + idx, dyv);
+      load8<T>(reinterpret_cast<const T*>(slot(2, it % STAGES)), dyv);
       float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -141,7 +163,7 @@ __global__ void __launch_bounds__(MAXT) gated_rmsnorm_kernel(NormParams p) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float du = rstd * (dn[i] - n[i] * mean_dot);
-        const float sg = 1.f / (1.f + __expf(-zv[i]));
+        const float sg = fast_rcp(1.f + fast_exp(-zv[i]));
         const float dact = p.sigmoid_gate ? sg * (1.f - sg) : sg * (1.f + zv[i] * (1.f - sg));  // d gate / d z
         if (p.norm_before_gate) {
           dxv[i] = du;
@@ -159,6 +181,7 @@ __global__ void __launch_bounds__(MAXT) gated_rmsnorm_kernel(NormParams p) {
       }
     }
   }
+  cp_async_wait_groups<0>();  // the trailing groups of the ring
   if (BWD) {
     if (lanes_r > 1) {  // fold the row lanes first: one atomic per channel and block
 #pragma unroll
@@ -215,9 +238,15 @@ int launch(int dtype, NormParams np, cudaStream_t s) {
     set_error("gated rms norm: more than %ld rows per call", 65535 * tile);
     return JLA_ERR_UNSUPPORTED;
   }
-  const size_t smem = BWD && lanes_r > 1 ? sizeof(float) * threads * 8 : 0;
+  const size_t row_bytes = 8 * (dtype == JLA_DTYPE_F32 ? 4 : 2);
+  const size_t smem = (BWD ? sizeof(float) * threads * 8 : 0) +
+                      (size_t)(BWD ? 3 : 2) * ring_stages((int)row_bytes) * threads * row_bytes;
   const dim3 grid((cv + cols - 1) / cols, (unsigned)tiles);
-  auto go = [&](auto kern) { kern<<<grid, threads, smem, s>>>(np); };
+  cudaError_t attr = cudaSuccess;
+  auto go = [&](auto kern) {
+    attr = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (attr == cudaSuccess) kern<<<grid, threads, smem, s>>>(np);
+  };
   const bool wide = threads > 512;
   switch (dtype) {
     case JLA_DTYPE_BF16:
@@ -231,6 +260,7 @@ int launch(int dtype, NormParams np, cudaStream_t s) {
       break;
     default: set_error("gated rms norm: unknown dtype %d", dtype); return JLA_ERR_BAD_ARGUMENT;
   }
+  JLA_CUDA_OK(attr);
   JLA_LAUNCH_OK();
   return JLA_OK;
 }

@@ -184,6 +184,9 @@ def test_gated_rms_norm_matches_the_cpu_restatement(shape, group, act, nbg, dtyp
     (4, None, True, True, True, True, torch.float32),     # plain ShortConv
     (2, 128, False, True, True, False, torch.float32),
     (3, None, True, False, True, False, torch.bfloat16),
+    (4, 256, True, True, True, True, torch.bfloat16),     # a head wider than 32 four-channel lanes: eight per thread
+    (4, 256, True, True, False, False, torch.float32),
+    (1, 128, True, True, False, True, torch.float16),     # no taps behind the token
 ])
 def test_short_conv_matches_the_cpu_restatement(K, head_dim, act, docs, with_state, bias, dtype):
     from jax_linear_attention_b200.layers import short_conv
@@ -216,6 +219,37 @@ def test_short_conv_matches_the_cpu_restatement(K, head_dim, act, docs, with_sta
     assert torch.equal(new_state.detach().double().cpu(), st64.detach())
     for n, a, b in zip(names, got, want):
         assert rel_l2(a.float().cpu().numpy(), b.numpy()) < (tol if n in ("x", "state") else 2e-4), n
+
+
+@pytest.mark.parametrize("T,Cn,head_dim", [(1, 264, None), (3, 264, 8), (33, 136, 136 // 17), (257, 1032, 8), (700, 128, 64)])
+def test_short_conv_ragged_shapes(T, Cn, head_dim):
+    """Sequences shorter than the kernel and than one walk, walks that end inside a group of tokens, and channel
+    counts that fill neither a block nor a warp: forward, every gradient and the carried state against the oracle."""
+    from jax_linear_attention_b200.layers import short_conv
+    from oracle import gates
+
+    torch.manual_seed(5)
+    B, K = 3, 4
+    dev = torch.device("cuda")
+    x = torch.randn(B, T, Cn)
+    w = torch.randn(Cn, K) * 0.5
+    bb = torch.randn(Cn) * 0.3
+    st = torch.randn(B, K - 1, Cn)
+    seg = (torch.arange(T)[None] >= torch.randint(0, T + 1, (B, 1))).to(torch.int32) if T > 1 else None
+    dy = torch.randn(B, T, Cn)
+    vals = {"x": x, "weight": w, "bias": bb, "state": st}
+    leaves = {n: v.to(dev).requires_grad_(True) for n, v in vals.items()}
+    y, new_state = short_conv(leaves["x"], leaves["weight"], leaves["bias"], activation=True, head_dim=head_dim,
+                              segment_ids=None if seg is None else seg.to(dev), state=leaves["state"])
+    got = torch.autograd.grad([y], list(leaves.values()), [dy.to(dev)])
+    ref = {n: v.double().requires_grad_(True) for n, v in vals.items()}
+    y64, st64 = gates.short_conv(ref["x"], ref["weight"], ref["bias"], activation=True, head_dim=head_dim,
+                                 segment_ids=seg, state=ref["state"])
+    want = torch.autograd.grad([y64], list(ref.values()), [dy.double()])
+    assert rel_l2(y.detach().cpu().numpy(), y64.detach().numpy()) < 1e-5
+    assert torch.equal(new_state.detach().double().cpu(), st64.detach())
+    for n, a, b in zip(vals, got, want):
+        assert rel_l2(a.cpu().numpy(), b.numpy()) < 2e-4, n
 
 
 def test_mamba2_ssd_config2_gradient_slice_against_the_oracle():
