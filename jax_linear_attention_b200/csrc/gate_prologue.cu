@@ -115,17 +115,47 @@ __global__ void __launch_bounds__(THREADS) gate_kernel(GateParams p) {
     beta_head[i] = (col + i) / p.C;
     if (b && (col + i) % p.C == 0) beta_cols |= 1u << i;
   }
-  for (long t = t0 + lt; active && t < t1; t += lanes_t) {
+  // VEC = 8: the rows of a (and dg) arrive through a ring of asynchronous copies in shared memory, private to the
+  // thread, STAGES - 1 tokens in flight while one is worked on (a plain loop of loads waits on memory most of the
+  // time at one or two blocks per SM). Tokens past the thread's range are zero-filled and never used.
+  constexpr bool RING = VEC == 8;
+  constexpr int RA = VEC * (int)sizeof(T), RG = VEC * (int)sizeof(float), STAGES = 3;
+  extern __shared__ __align__(16) unsigned char ring[];
+  auto slot_a = [&](int st) { return ring + ((size_t)st * blockDim.x + threadIdx.x) * RA; };
+  auto slot_g = [&](int st) {
+    return ring + (size_t)STAGES * blockDim.x * RA + ((size_t)st * blockDim.x + threadIdx.x) * RG;
+  };
+  auto request = [&](int it) {
+    if constexpr (RING) {
+      const long t = t0 + lt + (long)it * lanes_t;
+      const bool valid = active && t < t1;
+      const long idx = valid ? t * HC + col : 0;
+      cp_async_row<RA>(slot_a(it % STAGES), a + idx, valid);
+      if constexpr (BWD) cp_async_row<RG>(slot_g(it % STAGES), p.dg + idx, valid);
+      cp_async_commit_group();
+    }
+  };
+#pragma unroll
+  for (int it = 0; it < STAGES - 1; ++it) request(it);
+  int it = 0;
+  for (long t = t0 + lt; active && t < t1; t += lanes_t, ++it) {
     const long idx = t * HC + col;
     float x[VEC], out[VEC];
-    load_vec<T, VEC>(a + idx, x);
+    if constexpr (RING) {
+      request(it + STAGES - 1);
+      cp_async_wait_groups<STAGES - 1>();
+      load_vec<T, VEC>(reinterpret_cast<const T*>(slot_a(it % STAGES)), x);
+    } else {
+      load_vec<T, VEC>(a + idx, x);
+    }
     if (!BWD) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) out[i] = neg_a[i] * softplus(x[i] + bias[i]);
       store_vec<float, VEC>(p.g + idx, out);
     } else {
       float dg[VEC];
-      load_vec<float, VEC>(p.dg + idx, dg);
+      if constexpr (RING) load_vec<float, VEC>(reinterpret_cast<const float*>(slot_g(it % STAGES)), dg);
+      else load_vec<float, VEC>(p.dg + idx, dg);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         // one exponential serves the sigmoid and the softplus; the softplus only enters the sum dA_log, where the
@@ -151,6 +181,7 @@ __global__ void __launch_bounds__(THREADS) gate_kernel(GateParams p) {
       else static_cast<T*>(p.db)[bi] = from_f32<T>(p.dbeta[bi] * beta * (1.f - beta / p.mult));
     }
   }
+  if constexpr (RING) cp_async_wait_groups<0>();  // the trailing (empty) groups of the ring
   if (BWD) {
     // parameter gradients: first over the block's token lanes in shared memory, then one atomic per column and block
     __shared__ float red_bias[THREADS * VEC], red_alog[THREADS * VEC];
@@ -197,6 +228,8 @@ int launch_vec(int dtype, const GateParams& gp, cudaStream_t s) {
   }
   const long lanes_t = THREADS / cols;
   long per_lane = gp.tokens / (lanes_t * 64);
+  // up to 16 tokens per thread (4 measured slower: the fixed cost of a block, its ring's first copies and its atomics,
+  // outweighs the better fill of the last round of blocks)
   per_lane = per_lane < 1 ? 1 : (per_lane > 16 ? 16 : per_lane);
   const long tile = per_lane * lanes_t;
   const long tiles = (gp.tokens + tile - 1) / tile;
@@ -208,12 +241,21 @@ int launch_vec(int dtype, const GateParams& gp, cudaStream_t s) {
   q.tokens_per_lane = (int)per_lane;
   q.cols = cols;
   const dim3 grid(groups / cols, (unsigned)tiles);
+  // the ring of row copies (VEC = 8): three stages of a, and of dg in the backward, per thread
+  const size_t es = dtype == JLA_DTYPE_F32 ? 4 : 2;
+  const size_t smem = VEC == 8 ? (size_t)3 * THREADS * (VEC * es + (BWD ? VEC * sizeof(float) : 0)) : 0;
+  cudaError_t attr = cudaSuccess;
+  auto go = [&](auto kern) {
+    attr = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (attr == cudaSuccess) kern<<<grid, THREADS, smem, s>>>(q);
+  };
   switch (dtype) {
-    case JLA_DTYPE_BF16: gate_kernel<__nv_bfloat16, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
-    case JLA_DTYPE_F16: gate_kernel<__half, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
-    case JLA_DTYPE_F32: gate_kernel<float, BWD, VEC><<<grid, THREADS, 0, s>>>(q); break;
+    case JLA_DTYPE_BF16: go(gate_kernel<__nv_bfloat16, BWD, VEC>); break;
+    case JLA_DTYPE_F16: go(gate_kernel<__half, BWD, VEC>); break;
+    case JLA_DTYPE_F32: go(gate_kernel<float, BWD, VEC>); break;
     default: set_error("gate prologue: unknown dtype %d", dtype); return JLA_ERR_BAD_ARGUMENT;
   }
+  JLA_CUDA_OK(attr);
   JLA_LAUNCH_OK();
   return JLA_OK;
 }

@@ -108,7 +108,7 @@ __device__ __forceinline__ float head_sum(float v, int lanes) {
   return v;
 }
 
-// A thread owns VEC adjacent channels and walks TT consecutive tokens of one batch row in time order, with the K - 1
+// A thread owns VEC adjacent channels and walks TT (TT_FWD or TT_BWD) consecutive tokens of one batch row in time order, with the K - 1
 // rows in front of the current token (and, backward, the K - 1 pre-activation gradients behind it) in registers: no
 // shared-memory staging, every row is loaded once per thread (plus K - 1 rows of overlap per walk) and the loads of
 // UNROLL tokens are in flight together. The 32 lanes of a warp hold adjacent channel vectors of the same tokens, so a
@@ -116,7 +116,9 @@ __device__ __forceinline__ float head_sum(float v, int lanes) {
 // ranges; backward, the SUB walks' parameter gradients are summed in shared memory before one atomic per entry.
 constexpr int COLS = 32;
 constexpr int SUB = THREADS / COLS;
-constexpr int TT = 32;
+// Tokens per walk (16-token walks in the forward, to fill the last round of blocks better, measured slower: the
+// fixed cost of a walk, its first rows and its weights, weighs more).
+constexpr int TT_FWD = 32, TT_BWD = 32;
 constexpr int UNROLL_FWD = 4, UNROLL_BWD = 4;  // tokens per group (the backward holds twice the rows per token)
 static_assert(UNROLL_BWD >= KMAX - 1 && UNROLL_FWD >= KMAX - 1, "the window slides by whole groups");
 
@@ -177,6 +179,7 @@ __device__ __forceinline__ void conv_token(const ConvParams& p, const float (&w)
 template <typename T, bool BWD, int K, int VEC>
 __global__ void __launch_bounds__(THREADS, BWD ? (VEC == 4 ? 2 : 1) : (VEC == 4 ? 3 : 1)) short_conv_kernel(ConvParams p) {
   constexpr int UNROLL = BWD ? UNROLL_BWD : UNROLL_FWD;
+  constexpr int TT = BWD ? TT_BWD : TT_FWD;
   constexpr int RB = VEC * (int)sizeof(T);       // bytes of one row of this thread
   constexpr int STAGES = ring_stages(RB);        // groups in the ring: one worked on, the others in flight
   extern __shared__ __align__(16) unsigned char ring_raw[];
@@ -222,14 +225,15 @@ __global__ void __launch_bounds__(THREADS, BWD ? (VEC == 4 ? 2 : 1) : (VEC == 4 
 #pragma unroll
     for (int j = 0; j < KMAX; ++j) w[j][c] = j < K ? p.w[(long)(col + c) * K + j] : 0.f;
   }
-  // document ids: lane i of the warp holds that of token ta + i (and of ta + 32 + i for the backward's overhang);
+  // document ids: lane i of the warp holds that of token ta + i (and of ta + 32 + i for the overhang of a 32-token walk);
   // a token's id is one shuffle
-  static_assert(TT == 32 && COLS == 32, "one document id per lane of the walk's warp");
+  static_assert(TT + KMAX - 1 <= 32 || TT == 32, "one document id per lane of the walk's warp, two for the overhang");
+  static_assert(COLS == 32, "a walk is one warp");
   const int32_t* srow = p.seg ? p.seg + (long)b * p.T : nullptr;
   auto seg_of = [&](int t) { return srow ? srow[t < p.T ? t : p.T - 1] : 0; };
   const int seg_walk = seg_of(ta + lane);
-  const int seg_over = BWD && lane < K - 1 ? seg_of(ta + TT + lane) : 0;
-  auto seg_tok = [&](int i) { return __shfl_sync(0xffffffffu, i < TT ? seg_walk : seg_over, i & (TT - 1)); };
+  const int seg_over = BWD && lane < K - 1 ? seg_of(ta + 32 + lane) : 0;
+  auto seg_tok = [&](int i) { return __shfl_sync(0xffffffffu, i < 32 ? seg_walk : seg_over, i & 31); };
   // rows[0 .. K - 2]: the K - 1 rows in front of the group; rows[K - 1 + u]: token t + u of the group (float32: a
   // row is converted once and used by K tokens)
   float rows[K - 1 + UNROLL][VEC];
@@ -407,6 +411,7 @@ int launch(int dtype, ConvParams cp, cudaStream_t s) {
     // always: the backward adds a static array, and the sum of the two is what the 48 KB default limits
     JLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // the token-tile index lives in gridDim.y (<= 65535): larger problems go in slices of batch rows
+    constexpr int TT = BWD ? TT_BWD : TT_FWD;
     const int tiles_per_row = (cp.T + SUB * TT - 1) / (SUB * TT);
     const int rows_per_launch = tiles_per_row > 65535 ? 0 : 65535 / tiles_per_row;
     if (rows_per_launch == 0) {
