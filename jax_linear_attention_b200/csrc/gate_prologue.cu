@@ -86,7 +86,7 @@ __device__ __forceinline__ void store_vec(T* p, const float (&f)[VEC]) {
 // A thread owns VEC adjacent (h, c) columns (one 16-byte load of 16-bit activations) and walks every `lanes_t`-th token
 // of its block's tile. Block layout: min(H * C / VEC, THREADS) column threads x the remaining threads as token lanes.
 template <typename T, bool BWD, int VEC>
-__global__ void __launch_bounds__(THREADS) gate_kernel(GateParams p) {
+__global__ void __launch_bounds__(THREADS, 2) gate_kernel(GateParams p) {
   const int HC = p.H * p.C;
   const int groups = HC / VEC;
   const int cols = p.cols;
