@@ -35,8 +35,11 @@ struct FwdSmem {
   static constexpr int kStageElems = 2 * 64 * LDK + 64 * LDV + (DELTA ? 64 * LDC : 0);
   static constexpr int kStageBytes = kStageElems * 2 + 512 + 64;  // + gates (128 f32) + runs (64 u8)
   // Without the delta rule only the 16-bit state copy lives outside the stages: the output is staged in the chunk's
-  // dead q tile and the Gamma_r factor of the state update is applied to the key fragments in registers.
-  static constexpr int kBytes = 2 * kStageBytes + (K * LDV + (DELTA ? 3 * 64 * LDV + 64 * LDC : 0)) * 2;
+  // dead q tile and the Gamma_r factor of the state update is applied to the key fragments in registers. Where the
+  // output is wider than the q tile (K = 64, V = 128) it gets a tile of its own behind the state copy.
+  static constexpr bool kOwnOutTile = !DELTA && V > K;
+  static constexpr int kBytes =
+      2 * kStageBytes + (K * LDV + (DELTA ? 3 * 64 * LDV + 64 * LDC : 0) + (kOwnOutTile ? 64 * LDV : 0)) * 2;
 };
 
 // (Without the delta rule and with V = 64 -- the Mamba-2 shape, 4 x 128 chains at B = 8, H = 64 -- two CTAs share an SM:
@@ -204,8 +207,8 @@ __global__ void __launch_bounds__(256, (!DELTA && V == 64) ? 2 : 1) sg_fwd_kerne
     const T* vn = DELTA ? Vnb : vS;
     warp_gemm_ra<T, ONT, 4, B_KN>(accO, pfrag, vn + c0, LDV, lane);
     // O staged in Wb; without the delta rule in the q tile, which every warp finished reading before S3
-    T* oS = DELTA ? Wb : stage_q(s);
-    constexpr int LDO = DELTA ? LDV : LDK;
+    T* oS = (DELTA || L::kOwnOutTile) ? Wb : stage_q(s);  // (Wb: the first tile behind the state copy)
+    constexpr int LDO = (DELTA || L::kOwnOutTile) ? LDV : LDK;
     store_acc<T, ONT>(oS, LDO, r0, c0, accO, lane, p.scale, p.scale);
     __syncthreads();  // S4: every warp is done with Sb and the staging tile holds O
     store_tile<T, V>(static_cast<T*>(p.o) + ((long)m.tok0 * p.H + h) * V, (long)p.H * V, oS, LDO, m.len, tid, 256);

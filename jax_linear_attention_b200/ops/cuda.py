@@ -54,6 +54,25 @@ def _problem(kind: str, dtype, B, T, H, Hk, K, V, num_seqs, scale, flags, precis
     return p
 
 
+VALUE_BLOCK = 128  # value channels per head of the chunk kernels
+
+
+def _value_blocks(kind, dtype, key_dim, value_dim, path, read_key) -> int:
+    """How many 128-channel blocks a wide value head is cut into for the chunk kernels, 1 if the call runs as it is.
+
+    The columns of the state are independent recurrences (``S[:, j]`` only ever meets ``v[j]``), so a head with
+    ``V = n * 128`` value channels is exactly ``n`` value heads of 128 that share the head's key and gates: grouped
+    heads, which the kernels have anyway. Without this a 16-bit call with ``V`` in (256, 384, 512) -- the reference's
+    wide heads, ``src/jla/ops/mosaic_gpu/scalar_gate_kb.py`` -- would run the fp32 token scan (256) or not at all."""
+    if dtype == torch.float32 or read_key or path == "recurrent":
+        return 1
+    if value_dim <= VALUE_BLOCK or value_dim % VALUE_BLOCK:
+        return 1
+    if key_dim != 128 and (kind == "kda" or key_dim != 64):
+        return 1
+    return value_dim // VALUE_BLOCK
+
+
 def unsupported_reason(kind: str, q, k, v, gates: tuple, options: dict, *, read_key: bool = False) -> str | None:
     """Why the CUDA kernels cannot run this call (``None`` if they can); ``read_key``: the call passes a separate
     read key (Gated DeltaNet-2), which only the KDA chunk kernels and the token scan take.
@@ -106,7 +125,8 @@ def unsupported_reason(kind: str, q, k, v, gates: tuple, options: dict, *, read_
         precision = _path(options.get("precision"))
     except ValueError as err:
         return str(err)
-    p = _problem(kind, q.dtype, batch, seq_len, heads, kv_heads, key_dim, value_dim,
+    blocks = _value_blocks(kind, q.dtype, key_dim, value_dim, precision, read_key)  # wide value heads run in blocks
+    p = _problem(kind, q.dtype, batch, seq_len, heads * blocks, kv_heads, key_dim, value_dim // blocks,
                  0 if cu is None else max(rows, 0), 1.0, 0, precision)
     if read_key:
         p.k_read = 1  # only looked at for being non-NULL
@@ -314,6 +334,28 @@ def _split_applies(kind, q, v, cu_seqlens, initial_state, precision) -> int:
     return pieces(1, v.shape[2], q.shape[1], delta=kind != "simple_gla", sm_count=sms)
 
 
+def _run_value_blocks(n, kind, q, k, v, g, beta, *, initial_state, output_final_state, **options):
+    """The call with every value head cut into ``n`` heads of 128 channels (see ``_value_blocks``): ``v`` and ``o``
+    are views, the gates are repeated per block (autograd sums their gradients back), the states are permuted."""
+    batch, seq_len, heads, width = v.shape
+
+    def per_block(x):  # [B, T, H(, K)] -> [B, T, H * n(, K)]
+        return None if x is None else x.repeat_interleave(n, dim=2)
+
+    def split_state(s):  # [R, H, K, V] -> [R, H * n, K, 128]
+        if s is None:
+            return None
+        r, _, kd, _ = s.shape
+        return s.reshape(r, heads, kd, n, VALUE_BLOCK).permute(0, 1, 3, 2, 4).reshape(r, heads * n, kd, VALUE_BLOCK)
+
+    o, final = _run(kind, q, k, v.reshape(batch, seq_len, heads * n, VALUE_BLOCK), per_block(g), per_block(beta),
+                    initial_state=split_state(initial_state), output_final_state=output_final_state, **options)
+    if final is not None:
+        r, _, kd, _ = final.shape
+        final = final.reshape(r, heads, n, kd, VALUE_BLOCK).permute(0, 1, 3, 2, 4).reshape(r, heads, kd, width)
+    return o.reshape(batch, seq_len, heads, width), final
+
+
 def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_state, cu_seqlens, segment_ids,
          use_qk_l2norm=False, chunk_size=CHUNK, precision=None, sub_chunk=None, k_read=None):
     del sub_chunk  # the kernels choose their own sub-blocking
@@ -330,6 +372,11 @@ def _run(kind: str, q, k, v, g, beta, *, scale, initial_state, output_final_stat
     dev = q.device
     if scale is None:
         scale = q.shape[-1] ** -0.5
+    blocks = _value_blocks(kind, q.dtype, q.shape[-1], v.shape[-1], _path(precision), k_read is not None)
+    if blocks > 1:
+        return _run_value_blocks(blocks, kind, q, k, v, g, beta, scale=scale, initial_state=initial_state,
+                                 output_final_state=output_final_state, cu_seqlens=cu_seqlens, segment_ids=segment_ids,
+                                 use_qk_l2norm=use_qk_l2norm, chunk_size=chunk_size, precision=precision)
     cp = 1 if k_read is not None else _split_applies(kind, q, v, cu_seqlens, initial_state, precision)
     if cp > 1:
         from ..distributed.context_parallel import context_parallel_linear_attention, plan_pieces

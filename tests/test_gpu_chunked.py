@@ -63,6 +63,7 @@ CASES = [
     ("simple_gla", dict(B=1, T=1100, H=8, Hk=2, K=128, V=64, docs="mixed", h0=True)),
     ("simple_gla", dict(B=2, T=1000, H=8, Hk=1, K=128, V=64, docs="mixed", h0=True)),      # Mamba-2 shared B/C
     ("simple_gla", dict(B=1, T=1024, H=4, K=128, V=128, docs="mixed", h0=True, gates="extreme")),
+    ("simple_gla", dict(B=1, T=300, H=4, Hk=2, K=64, V=128, docs="mixed", h0=True)),  # output wider than the q tile
 ]
 
 
@@ -74,6 +75,30 @@ def test_outputs_and_gradients_bf16(kind, spec):
     got = run_cuda(kind, case, scale=scale, dtype="bfloat16", l2norm=l2)
     table = compare(got, want, TOL, f"{kind} {spec}")
     assert all(np.isfinite(v).all() for v in got.values()), table
+
+
+WIDE = [
+    ("gated_deltanet", dict(B=2, T=300, H=2, K=128, V=256, docs="mixed", h0=True)),            # the usual expand_v = 2
+    ("gated_deltanet", dict(B=1, T=200, H=4, Hk=2, K=128, V=512, docs="uniform", h0=True, l2norm=True)),
+    ("simple_gla", dict(B=1, T=260, H=2, K=64, V=384, docs="mixed", h0=True)),
+    ("kda", dict(B=1, T=200, H=2, K=128, V=256, docs="mixed", h0=True, gates="kda_baseline")),
+]
+
+
+@pytest.mark.parametrize("kind,spec", WIDE, ids=[f"{k}-V{s['V']}" for k, s in WIDE])
+def test_wide_value_heads_run_as_blocks_of_128_channels(kind, spec):
+    """V = 256, 384, 512: the chunk kernels run the head as V / 128 value heads that share its key and gates (the
+    columns of the state are independent recurrences). Outputs, final state and every gradient -- the gates' are
+    summed over the blocks, the states permuted back -- against the float64 oracle; and where the token scan can run
+    the shape (V = 256) the two paths give different bits, i.e. the chunk kernels did run."""
+    case = make_case(kind, seed=7 + spec["V"], **spec)
+    scale, l2 = case["meta"]["scale"], bool(spec.get("l2norm"))
+    want = run_oracle(kind, case, scale=scale, l2norm=l2)
+    got = run_cuda(kind, case, scale=scale, dtype="bfloat16", l2norm=l2)
+    compare(got, want, TOL, f"wide {kind} {spec}")
+    if spec["V"] == 256:
+        scan = run_cuda(kind, case, scale=scale, dtype="bfloat16", l2norm=l2, precision="highest")
+        assert any(not np.array_equal(got[n], scan[n]) for n in got), "the chunk kernels did not run"
 
 
 def test_float16():
