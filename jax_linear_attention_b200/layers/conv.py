@@ -44,6 +44,7 @@ class _ShortConv(torch.autograd.Function):
         return y
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dy):
         x, weight, bias, state, seg = ctx.saved_tensors
         head_dim, activation = ctx.cfg

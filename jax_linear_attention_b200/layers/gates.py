@@ -44,6 +44,7 @@ class _GatePrologue(torch.autograd.Function):
         return g, beta
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dg, dbeta):
         a, a_log, dt_bias, b = ctx.saved_tensors
         heads = a.shape[2]

@@ -42,6 +42,7 @@ class _GatedRMSNorm(torch.autograd.Function):
         return y
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dy):
         x, z, weight = ctx.saved_tensors
         eps, sigmoid_gate, norm_before_gate, group = ctx.cfg

@@ -85,6 +85,7 @@ class _SsdInputs(torch.autograd.Function):
         return v, g
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dv, dg):
         x, dt, a, d = ctx.saved_tensors
         dv = torch.zeros_like(x) if dv is None else dv.contiguous()
@@ -111,6 +112,7 @@ class _SsdOutput(torch.autograd.Function):
         return y
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, dy):
         x, d = ctx.saved_tensors
         dy = dy.contiguous()
