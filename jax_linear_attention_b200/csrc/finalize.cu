@@ -21,16 +21,56 @@ __global__ void finalize_key_grad_kernel(const float* __restrict__ acc, const T*
   const int group = H / Hk;
   float dy[8], x[8];  // K <= 256
   float sumsq = 0.f;
+  const bool vec4 = (K & 3) == 0;  // a lane owns channels 4 * lane .. + 3 (and 128 + those): 16-byte loads
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int c = lane + 32 * i;
-    dy[i] = 0.f;
-    x[i] = 0.f;
-    if (c < K) {
-      for (int hh = 0; hh < group; ++hh) dy[i] += acc[(tok * H + hk * group + hh) * K + c];
-      if (l2norm) {
-        x[i] = to_f32(raw[row * K + c]);
-        sumsq += x[i] * x[i];
+  for (int i = 0; i < 8; ++i) dy[i] = x[i] = 0.f;
+  if (vec4) {
+    // the heads of the group are walked four at a time with all their loads in flight before the first add (the
+    // per-head accumulators of a large call do not fit L2: the sum is bound by how many bytes a warp keeps in flight)
+    const float* base = acc + (tok * H + (long)hk * group) * K;
+    for (int h0 = 0; h0 < group; h0 += 4) {
+      float4 v[4][2];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int c = 4 * lane + 128 * half;
+          v[j][half] = (h0 + j < group && c < K) ? *reinterpret_cast<const float4*>(base + (long)(h0 + j) * K + c)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          dy[4 * half] += v[j][half].x, dy[4 * half + 1] += v[j][half].y;
+          dy[4 * half + 2] += v[j][half].z, dy[4 * half + 3] += v[j][half].w;
+        }
+      }
+    }
+    if (l2norm) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int c = 4 * lane + 128 * half;
+        if (c < K) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            x[4 * half + j] = to_f32(raw[row * K + c + j]);
+            sumsq += x[4 * half + j] * x[4 * half + j];
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      if (c < K) {
+        for (int hh = 0; hh < group; ++hh) dy[i] += acc[(tok * H + hk * group + hh) * K + c];
+        if (l2norm) {
+          x[i] = to_f32(raw[row * K + c]);
+          sumsq += x[i] * x[i];
+        }
       }
     }
   }
@@ -46,7 +86,7 @@ __global__ void finalize_key_grad_kernel(const float* __restrict__ acc, const T*
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int c = lane + 32 * i;
+    const int c = vec4 ? 4 * lane + 128 * (i >> 2) + (i & 3) : lane + 32 * i;
     if (c < K) out[row * K + c] = from_f32<T>(dy[i]);
   }
 }
