@@ -101,6 +101,18 @@ def test_dispatcher_mirrors_reference_errors():
     assert ops.cuda.SUPPORTS["gdn2"](q4, q4, vs, q4, q4, vs)
     assert "b must be" in ops.cuda.unsupported_reason("gdn2", q4, q4, vs, (q4, gs, vs), {})
     assert "b must be" in ops.cuda.unsupported_reason("gdn2", qs, qs, vs, (qs, qs, vs), {})
+    # wide value heads: 16-bit calls with V = 256, 384, 512 are answered for their blocks of 128 channels (K = 128, or
+    # 64 for the scalar-gate kinds); other widths, the token scan asked for by name, and read keys are not
+    bf = torch.bfloat16
+    qb, gb = Spec((1, 300, 2, 128), bf), Spec((1, 300, 2), torch.float32)
+    for width, ok in ((256, True), (384, True), (512, True), (320, False), (640, True)):
+        assert ops.cuda.SUPPORTS["gated_deltanet"](qb, qb, Spec((1, 300, 2, width), bf), gb, gb) is ok, width
+    v512 = Spec((1, 300, 2, 512), bf)
+    assert not ops.cuda.SUPPORTS["gated_deltanet"](qb, qb, v512, gb, gb, precision="highest")
+    assert ops.cuda.SUPPORTS["simple_gla"](Spec((1, 300, 2, 64), bf), Spec((1, 300, 2, 64), bf), v512, gb)
+    assert not ops.cuda.SUPPORTS["kda"](Spec((1, 300, 2, 64), bf), Spec((1, 300, 2, 64), bf), v512,
+                                        Spec((1, 300, 2, 64), torch.float32), gb)
+    assert ops.cuda._value_blocks("kda", bf, 128, 256, "auto", True) == 1
 
 
 def test_register_adds_an_implementation():
