@@ -325,8 +325,8 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     if args.workload not in ("gdn", "kda"):
-        print(json.dumps(dict(impl="reference", unavailable=f"the timed CPU port covers the gdn and kda workloads, not "
-                                                             f"{args.workload}")))
+        emit_line(dict(impl="reference", unavailable=f"the timed CPU port covers the gdn and kda workloads, not "
+                                                      f"{args.workload}"))
         return
     case = host_case(args.workload, seed=0)
     rows = min(CPU_ROWS, case["q"].shape[0])
@@ -349,7 +349,7 @@ def run_reference(args) -> None:
                             "reference's JAX CPU path is unavailable on this box (JAX not installed)"),
                 cpu_baseline=dict(value=value, unit="tokens/s", cores=torch.get_num_threads(), kind="port", sample=sample),
                 e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
-    print(json.dumps(line))
+    emit_line(line)
 
 
 def bind_to_gpu_numa_node(local: int) -> str:
@@ -413,6 +413,28 @@ class Deadline:
         self.timer.cancel()
 
 
+_LINE_FD = None  # the process's original standard output once main() has claimed it
+
+
+def claim_stdout() -> None:
+    """The contract is ONE JSON line on standard output. Libraries write there too (NCCL prints its version line on
+    file descriptor 1 when the first communicator comes up), so descriptor 1 is pointed at standard error for the
+    whole run and the line goes to a saved copy of the original."""
+    global _LINE_FD
+    sys.stdout.flush()
+    _LINE_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit_line(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    if _LINE_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_LINE_FD, text)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -426,6 +448,7 @@ def main() -> None:
     ap.add_argument("--single-block", action="store_true", help="time one block of --steps steps only (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    claim_stdout()
     if args.impl == "reference":
         run_reference(args)
         return
@@ -649,7 +672,7 @@ def main() -> None:
         def emit():
             if rank == 0 and not printed.is_set():
                 printed.set()
-                print(json.dumps(line), flush=True)
+                emit_line(line)
 
         def expire():
             if rank == 0:
@@ -668,7 +691,7 @@ def main() -> None:
                     line[key] = res
         emit()
     elif rank == 0:
-        print(json.dumps(line), flush=True)
+        emit_line(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
