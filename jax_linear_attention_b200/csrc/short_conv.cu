@@ -108,12 +108,16 @@ __device__ __forceinline__ float head_sum(float v, int lanes) {
   return v;
 }
 
-// A thread owns VEC adjacent channels and walks TT (TT_FWD or TT_BWD) consecutive tokens of one batch row in time order, with the K - 1
-// rows in front of the current token (and, backward, the K - 1 pre-activation gradients behind it) in registers: no
-// shared-memory staging, every row is loaded once per thread (plus K - 1 rows of overlap per walk) and the loads of
-// UNROLL tokens are in flight together. The 32 lanes of a warp hold adjacent channel vectors of the same tokens, so a
-// head's sums (head_dim / VEC lanes) are warp butterflies. A block is 32 lanes x SUB walks over adjacent token
-// ranges; backward, the SUB walks' parameter gradients are summed in shared memory before one atomic per entry.
+// A thread owns VEC adjacent channels and walks TT (TT_FWD or TT_BWD) consecutive tokens of one batch row in time
+// order, with the K - 1 rows in front of the current token (and, backward, the K - 1 pre-activation gradients behind
+// it) in registers as float32. Its rows of x (and of the upstream gradient) come through a ring of asynchronous
+// copies in shared memory that only this thread reads: groups of UNROLL tokens, two groups in flight while one is
+// worked on, no block-wide barrier (plain loads in the loop, even written a group ahead in the source, left the
+// kernel waiting on memory: the compiler is free to move them next to their use). Every row is fetched once per
+// thread, plus K - 1 rows of overlap per walk. The 32 lanes of a warp hold adjacent channel vectors of the same
+// tokens, so a head's sums (head_dim / VEC lanes) are warp butterflies and a token's document id is one shuffle. A
+// block is 32 lanes x SUB walks over adjacent token ranges; backward, the SUB walks' parameter gradients are summed
+// in shared memory before one atomic per entry.
 constexpr int COLS = 32;
 constexpr int SUB = THREADS / COLS;
 // Tokens per walk (16-token walks in the forward, to fill the last round of blocks better, measured slower: the
