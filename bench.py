@@ -1,6 +1,6 @@
 """Benchmark of the hot path: Gated DeltaNet chunk forward + backward at B8 T2048 H16 K = V = 128, bf16, packed documents.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gdn|ssd|kda|gdn2|longctx]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gdn|ssd|kda|gdn2|gdnv256|longctx]
 
 One step = one forward + backward of ``ops.linear_attention("gated_deltanet", ...)`` over one batch
 (B=8, T=2048, H=16, K=V=128, bf16 q/k/v/dO, fp32 gates, packed documents of uniform length 64-2048 as
@@ -55,6 +55,9 @@ WORKLOADS = {
     "kda": dict(name="config3: kda B4 T4096 H16 K128 V128 bf16, packed docs U[128,4096]", index=3),
     "gdn2": dict(name="gdn2 (Gated DeltaNet-2, erase and write gates per channel) at config3's shape: B4 T4096 H16 K128 "
                       "V128 bf16, packed docs U[128,4096]", index=None),
+    "gdnv256": dict(name="gated_deltanet with wide value heads (head 128, expand_v = 2): B8 T2048 H16 K128 V256 bf16, "
+                         "packed docs U[64,2048]; the chunk kernels run each head as two blocks of 128 value channels",
+                    index=None),
     "longctx": dict(name="config4: gated_deltanet B1 T1064960 H16 K128 V128 bf16, packed docs U[4096,131072], "
                          "sequence-parallel over the ranks", index=4),
 }
@@ -63,6 +66,7 @@ METRICS = {
     "ssd": "Mamba-2 SSD chunk fwd+bwd tokens/s (B8·T2048·H64·P64·N128 bf16)",
     "kda": "KDA fwd+bwd tokens/s (B4·T4096·H16·d128 bf16)",
     "gdn2": "Gated DeltaNet-2 fwd+bwd tokens/s (B4·T4096·H16·d128 bf16)",
+    "gdnv256": "GDN fwd+bwd tokens/s with wide value heads (B8·T2048·H16·K128·V256 bf16)",
     "longctx": "GDN fwd+bwd tokens/s on one 1,064,960-token sequence (H16·d128 bf16), sequence-parallel",
 }
 LONG_T = 1_064_960
@@ -163,6 +167,9 @@ def host_case(workload: str, seed: int) -> dict:
     if workload == "gdn2":  # no published configuration: the KDA workload's shape and gates, b and w as sigmoids
         return make_case("gdn2", seed=seed, B=4, T=4096, H=16, K=128, V=128, dtype="bfloat16", gates="kda_baseline",
                          docs="uniform", doc_range=(128, 4096))
+    if workload == "gdnv256":  # config 1's batch, documents and gates with twice the value channels per head
+        return make_case("gated_deltanet", seed=seed, B=8, T=2048, H=16, K=128, V=256, dtype="bfloat16",
+                         gates="baseline", docs="uniform", doc_range=(64, 2048))
     return baseline_config(WORKLOADS[workload]["index"], seed=seed)
 
 
@@ -225,7 +232,7 @@ def to_torch_host(case: dict, workload: str) -> dict:
 
 
 GRAD_NAMES = {"gdn": ("q", "k", "v", "g", "beta"), "kda": ("q", "k", "v", "g", "beta"),
-              "gdn2": ("q", "k", "v", "g", "b", "w"),
+              "gdn2": ("q", "k", "v", "g", "b", "w"), "gdnv256": ("q", "k", "v", "g", "beta"),
               "ssd": ("x", "dt", "A", "B", "C"), "longctx": ("q", "k", "v", "g", "beta")}
 
 
@@ -260,7 +267,7 @@ def run_step(workload: str, dev: dict):
         o, _ = ops.linear_attention("gdn2", dev["q"], dev["k"], dev["v"], g=dev["g"], b=dev["b"], w=dev["w"],
                                     segment_ids=dev.get("seg"))
     else:
-        kind = "gated_deltanet" if workload == "gdn" else "kda"
+        kind = "kda" if workload == "kda" else "gated_deltanet"
         o, _ = ops.linear_attention(kind, dev["q"], dev["k"], dev["v"], g=dev["g"], beta=dev["beta"],
                                     segment_ids=dev.get("seg"))
     grads = torch.autograd.grad(o, leaves, dev["do"])
@@ -592,6 +599,8 @@ def main() -> None:
         launches = sum(v["launches"] for v in prof.values()) // max(len(prof_blocks_ms), 1)  # per timed block
         K, V = (case["q"].shape[3], case["v"].shape[3]) if "q" in case else (case["B"].shape[3], case["x"].shape[3])
         H = case["v"].shape[2] if "v" in case else case["x"].shape[2]
+        if V > 128 and V % 128 == 0:  # wide value heads run as V / 128 heads of 128 channels: count those
+            H, V = H * (V // 128), 128
         units = (tokens // CHUNK) * H  # (chunk, head) pairs per launch
         model = kernel_model(K, V, delta=args.workload != "ssd", save=True)
         roof = None
